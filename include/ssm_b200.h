@@ -1,0 +1,313 @@
+/*
+ * ssm_b200 — C ABI of the B200 (sm_100a) backend for the five state-space operators
+ * of the b-vitamins/ssm package.
+ *
+ * Every entry point takes a plain argument struct (raw device pointers, sizes, element
+ * strides, dtype codes) plus a CUDA stream handle, enqueues its kernels on that stream and
+ * returns without synchronising.  The library never allocates: outputs and scratch are
+ * passed in by the caller.  Return value: 0 on success; a negative SSM_ERR_* code when an
+ * argument is rejected (nothing was launched); a positive value is a cudaError_t from the
+ * launch.  ssm_b200_last_error() returns a thread-local description of the last failure.
+ *
+ * The functions replace, one for one, the compiled operators that the upstream package
+ * binds in src/ssm/ops/cuda/bindings.cpp:96-152 (the citation beside each declaration
+ * names the host function there whose device work it takes over).  Layouts follow the
+ * upstream Python specification src/ssm/ops/python/reference.py.
+ */
+#ifndef SSM_B200_H_
+#define SSM_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SSM_B200_ABI_VERSION 1
+
+/* element types of activation tensors */
+enum { SSM_F32 = 0, SSM_BF16 = 1, SSM_F16 = 2 };
+
+enum {
+  SSM_OK = 0,
+  SSM_ERR_NULL = -1,        /* a required pointer is NULL */
+  SSM_ERR_SHAPE = -2,       /* a size is negative/zero where it may not be, or sizes disagree */
+  SSM_ERR_DTYPE = -3,       /* unknown dtype code */
+  SSM_ERR_ALIGN = -4,       /* a pointer misses its natural alignment */
+  SSM_ERR_UNSUPPORTED = -5, /* valid in the operator's contract but outside what is built */
+  SSM_ERR_TOO_LARGE = -6,   /* exceeds a documented capacity */
+  SSM_ERR_DEVICE = -7       /* device-side status word reported a bounded wait that ran out */
+};
+
+/* The stream is a cudaStream_t passed as an opaque pointer so that this header needs no CUDA include. */
+typedef void* ssm_stream_t;
+
+int ssm_b200_abi_version(void);
+const char* ssm_b200_last_error(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Selective scan (Mamba-1), forward.   Replaces selective_scan_cuda
+ * (src/ssm/ops/cuda/selective_scan.cu:1034-1161; spec reference.py:87-194).
+ *
+ *   dl_t = softplus?(delta_t + dt_bias);  h_t = exp(dl_t*A) .* h_{t-1} + dl_t*B_t*u_t
+ *   y_t  = <C_t, h_t> + D*u_t;            out_t = y_t * silu(z_t)
+ *
+ * u, delta, z, out: (batch, dim, len) contiguous, element type io_dtype.  A: (dim, nstate)
+ * fp32.  Bm / Cm are addressed as  base[b*sb + g*sg + n*sn + t*st]  (element strides, type
+ * bc_dtype) with g = d / (dim / bc_groups); this one form covers the (D,N), (B,D,N) and
+ * grouped time-varying (B,G,N,L) layouts of reference.py:22-56.  D, dt_bias: (dim) fp32
+ * or NULL.  initial_state: (batch, dim, nstate) fp32 or NULL (zeros).  last_state: optional
+ * output (batch, dim, nstate) of type last_dtype.  checkpoints: optional output
+ * (batch, dim, ceil(len / ssm_scan_checkpoint_interval()), nstate) fp32 holding the state
+ * before every interval; the backward pass needs it.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t batch, dim, len, nstate;
+  int32_t io_dtype, bc_dtype, last_dtype, delta_softplus;
+  const void* u;
+  const void* delta;
+  const void* z; /* nullable */
+  const float* A;
+  const void* Bm;
+  const void* Cm;
+  int32_t bc_groups, reserved0;
+  int64_t b_sb, b_sg, b_sn, b_st;
+  int64_t c_sb, c_sg, c_sn, c_st;
+  const float* D;             /* nullable */
+  const float* dt_bias;       /* nullable */
+  const float* initial_state; /* nullable */
+  void* out;
+  void* last_state;   /* nullable */
+  float* checkpoints; /* nullable */
+} ssm_scan_fwd_args;
+
+int ssm_scan_checkpoint_interval(void);
+int ssm_selective_scan_fwd(const ssm_scan_fwd_args* args, ssm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Selective scan, backward.   Replaces selective_scan_backward_cuda
+ * (src/ssm/ops/cuda/selective_scan.cu:1696-1875) and, because grad_last_state is
+ * handled on the device, the Python fall-back in src/ssm/ops/__init__.py:365-436.
+ *
+ * fwd holds the forward call's arguments (out/last_state unused; checkpoints required).
+ * dout: (batch, dim, len) io_dtype.  dlast_state: (batch, dim, nstate) fp32 or NULL.
+ * du, ddelta, dz: io_dtype (dz NULL iff fwd.z is NULL).  dA (dim, nstate), dD, ddt_bias
+ * (dim): fp32, ACCUMULATED into (caller zero-fills); dD / ddt_bias may be NULL.
+ * dB / dC: fp32 buffers addressed with db_* / dc_* strides exactly like Bm / Cm,
+ * accumulated into (caller zero-fills).
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  ssm_scan_fwd_args fwd;
+  const void* dout;
+  const float* dlast_state; /* nullable */
+  void* du;
+  void* ddelta;
+  void* dz; /* nullable */
+  float* dA;
+  float* dB;
+  float* dC;
+  int64_t db_sb, db_sg, db_sn, db_st;
+  int64_t dc_sb, dc_sg, dc_sn, dc_st;
+  float* dD;       /* nullable */
+  float* ddt_bias; /* nullable */
+} ssm_scan_bwd_args;
+
+int ssm_selective_scan_bwd(const ssm_scan_bwd_args* args, ssm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Single-token state step (decode).   Replaces selective_state_step_cuda
+ * (src/ssm/ops/cuda/state_step.cu:310-434; spec reference.py:197-309).
+ *
+ * state: (batch, dim, nstate) fp32, updated in place.  x, z, out: (batch, dim) io_dtype.
+ * Parameters are per channel when param_heads == 0: dt (batch, dim), A (dim, nstate),
+ * D / dt_bias (dim).  With param_heads = H > 0 (Mamba-2 layout, channel d belongs to head
+ * d / (dim / H)) they are per head: dt (batch, H), A (H), D / dt_bias (H).  Bm / Cm:
+ * base[b*sb + g*sg + n*sn], type bc_dtype, g = d / (dim / bc_groups), which covers (D,N),
+ * (B,D,N) and grouped (B,G,N).
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t batch, dim, nstate, io_dtype;
+  int32_t bc_dtype, bc_groups, dt_softplus, param_heads;
+  float* state;
+  const void* x;
+  const void* dt;
+  const void* z; /* nullable */
+  const float* A;
+  const void* Bm;
+  const void* Cm;
+  int64_t b_sb, b_sg, b_sn;
+  int64_t c_sb, c_sg, c_sn;
+  const float* D;       /* nullable */
+  const float* dt_bias; /* nullable */
+  void* out;
+} ssm_step_args;
+
+int ssm_selective_state_step(const ssm_step_args* args, ssm_stream_t stream);
+
+/* Backward of the step (per-channel parameters only).  Replaces
+ * selective_state_step_backward_cuda (src/ssm/ops/cuda/state_step.cu:436-693).
+ * state is the state BEFORE the step.  dout (batch, dim) io_dtype; dnew_state
+ * (batch, dim, nstate) fp32 or NULL.  dstate (batch, dim, nstate) fp32; dx, ddt, dz
+ * io_dtype; dA, dD, ddt_bias, dB, dC fp32 accumulated into (caller zero-fills);
+ * dB / dC use the Bm / Cm strides of fwd. */
+typedef struct {
+  ssm_step_args fwd;
+  const void* dout;
+  const float* dnew_state; /* nullable */
+  float* dstate;
+  void* dx;
+  void* ddt;
+  void* dz; /* nullable */
+  float* dA;
+  float* dB;
+  float* dC;
+  float* dD;       /* nullable */
+  float* ddt_bias; /* nullable */
+} ssm_step_bwd_args;
+
+int ssm_selective_state_step_bwd(const ssm_step_bwd_args* args, ssm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Element-wise chunked recurrence ("ssd_chunk_scan" upstream).   Replaces
+ * ssd_chunk_scan_cuda (src/ssm/ops/cuda/ssd_chunk_scan.cu:637-860; spec reference.py:312-463).
+ *
+ * X, Y: (batch, len, heads, proj) io_dtype.  dt: (batch, len, heads) io_dtype.  Every
+ * parameter p in {A, Bm, Cm, D, z, initial} is addressed  base[b*sb + t*st + h*sh + q*sq]
+ * with zero strides for broadcast axes (A/D/initial fp32; Bm/Cm/z of type par_dtype).
+ * seq_lens: (batch) int64 on the device or NULL; outputs beyond a row's length are zero.
+ * final_state: optional output (batch, heads, proj) fp32 (additive; upstream returns none).
+ * chunk_size splits the sequence into independently processed chunks (it has no numerical
+ * effect beyond rounding).  scratch: fp32 workspace of ssm_chunk_scan_scratch_floats()
+ * elements; when NULL the sequence is walked serially by one thread per (batch, head, proj).
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* ptr;
+  int64_t sb, st, sh, sq;
+} ssm_bcast4;
+
+typedef struct {
+  int32_t batch, len, heads, proj;
+  int32_t io_dtype, par_dtype, reserved0, reserved1;
+  const void* X;
+  const void* dt;
+  ssm_bcast4 A, Bm, Cm, D, z, initial; /* D, z, initial: ptr may be NULL */
+  const int64_t* seq_lens;             /* nullable */
+  void* Y;
+  float* final_state; /* nullable */
+  float* scratch;     /* nullable */
+  int32_t chunk_size, reserved2;
+} ssm_chunk_args;
+
+int64_t ssm_chunk_scan_scratch_floats(int32_t batch, int32_t len, int32_t heads, int32_t proj, int32_t chunk_size);
+int ssm_chunk_scan_fwd(const ssm_chunk_args* args, ssm_stream_t stream);
+
+/* Backward.  Replaces ssd_chunk_scan_backward_cuda (src/ssm/ops/cuda/ssd_chunk_scan.cu:341-635).
+ * dY io_dtype.  dX (io_dtype), ddt fp32 (batch, len, heads), and fp32 gradient buffers
+ * dA/dB/dC/dD/dz/dinitial addressed with the strides given here (broadcast axes = stride 0),
+ * accumulated into (caller zero-fills).  history: scratch (batch, len, heads, proj) fp32. */
+typedef struct {
+  ssm_chunk_args fwd;
+  const void* dY;
+  void* dX;
+  float* ddt;
+  ssm_bcast4 dA, dB, dC, dD, dz, dinitial; /* ptr as float*; NULL to skip where fwd's is NULL */
+  float* history;
+} ssm_chunk_bwd_args;
+
+int ssm_chunk_scan_bwd(const ssm_chunk_bwd_args* args, ssm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Depthwise causal conv1d.   Replaces dw_causal_conv_cuda / dw_causal_conv_backward_cuda
+ * (src/ssm/ops/cuda/dw_causal_conv.cu:771-857, 859-965; spec reference.py:466-537).
+ *
+ * x, y: channels_first ? (batch, channels, len) : (batch, len, channels), io_dtype.
+ * weight: (channels, width) fp32, tap j multiplies x[t - (width-1) + j].  bias fp32/NULL.
+ * 1 <= width <= 8.  Optional halo: (batch, channels, width-1) fp32 inputs that precede
+ * t = 0 (sequence-sharded prefill; NULL means zeros, the upstream behaviour).
+ * Backward: dx io_dtype; dweight (channels, width), dbias (channels) fp32 accumulated into.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t batch, channels, len, width;
+  int32_t io_dtype, channels_first, silu, reserved0;
+  const void* x;
+  const float* weight;
+  const float* bias; /* nullable */
+  const float* halo; /* nullable */
+  void* y;
+} ssm_conv_args;
+
+int ssm_dw_causal_conv_fwd(const ssm_conv_args* args, ssm_stream_t stream);
+
+typedef struct {
+  ssm_conv_args fwd;
+  const void* dy;
+  void* dx;
+  float* dweight;
+  float* dbias; /* nullable */
+} ssm_conv_bwd_args;
+
+int ssm_dw_causal_conv_bwd(const ssm_conv_bwd_args* args, ssm_stream_t stream);
+
+/* Decode-time form of the same convolution: push one token into the rolling window and take
+ * the dot product.  Upstream does this with torch.roll in Python
+ * (src/ssm/modules/mamba1.py:345-353).  conv_state: (batch, channels, width) fp32, shifted
+ * left by one and x appended, in place.  x, out: (batch, channels) io_dtype;
+ * out = silu?(bias + <conv_state, weight>). */
+typedef struct {
+  int32_t batch, channels, width, io_dtype;
+  int32_t silu, reserved0;
+  float* conv_state;
+  const void* x;
+  const float* weight;
+  const float* bias; /* nullable */
+  void* out;
+} ssm_conv_update_args;
+
+int ssm_dw_causal_conv_update(const ssm_conv_update_args* args, ssm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Residual add fused with LayerNorm / RMSNorm.   Replaces fused_layer_norm_cuda /
+ * fused_layer_norm_backward_cuda (src/ssm/ops/cuda/layer_norm.cu:372-496, 498-676; spec
+ * reference.py:540-609).
+ *
+ * x, y: (rows, hidden) io_dtype.  residual: res_dtype or NULL.  weight, bias fp32.
+ * prenorm: y = norm(x + residual)*w + b, else y = norm(x)*w + b + residual.
+ * All arithmetic is fp32 (upstream's residual_in_fp32 only matters for fp64 inputs, which
+ * are not built).  hidden <= 16384 (16-bit) / 8192 (fp32).  residual_out: optional
+ * (rows, hidden) of resout_dtype receiving x + residual (additive extension).
+ * Backward: dx io_dtype, dresidual res_dtype (NULL iff residual NULL); dweight, dbias fp32
+ * (hidden) written (not accumulated); partial: scratch fp32 of
+ * ssm_norm_bwd_scratch_floats(rows, hidden) floats.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t rows;
+  int32_t hidden, io_dtype, res_dtype, resout_dtype;
+  int32_t is_rms, prenorm, reserved0, reserved2;
+  float eps, reserved1;
+  const void* x;
+  const void* residual; /* nullable */
+  const float* weight;
+  const float* bias; /* nullable */
+  void* y;
+  void* residual_out; /* nullable */
+} ssm_norm_args;
+
+int ssm_fused_add_norm_fwd(const ssm_norm_args* args, ssm_stream_t stream);
+
+typedef struct {
+  ssm_norm_args fwd;
+  const void* dy;
+  void* dx;
+  void* dresidual; /* nullable */
+  float* dweight;
+  float* dbias; /* nullable */
+  float* partial;
+} ssm_norm_bwd_args;
+
+int64_t ssm_norm_bwd_scratch_floats(int64_t rows, int32_t hidden);
+int ssm_fused_add_norm_bwd(const ssm_norm_bwd_args* args, ssm_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SSM_B200_H_ */

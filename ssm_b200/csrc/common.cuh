@@ -1,0 +1,160 @@
+// Shared device/host helpers for the sm_100a operator kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdio>
+
+#include "../../include/ssm_b200.h"
+
+namespace ssmb {
+
+// ---------------------------------------------------------------------------------------
+// host: error reporting
+// ---------------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+inline int fail(int code, const char* what) {
+  set_error("%s", what);
+  return code;
+}
+#define SSM_REQUIRE(cond, code, what) \
+  do {                                \
+    if (!(cond)) return ::ssmb::fail((code), (what)); \
+  } while (0)
+
+inline int launch_status(const char* kernel) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: %s", kernel, cudaGetErrorString(e));
+    return (int)e;
+  }
+  return SSM_OK;
+}
+
+inline bool valid_dtype(int d) { return d == SSM_F32 || d == SSM_BF16 || d == SSM_F16; }
+inline int dtype_size(int d) { return d == SSM_F32 ? 4 : 2; }
+inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// ---------------------------------------------------------------------------------------
+// device: scalar conversion
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+
+// Load element i of an array whose element type is given at run time.
+__device__ __forceinline__ float load_dyn(const void* base, int64_t i, int dtype) {
+  if (dtype == SSM_F32) return __ldg(reinterpret_cast<const float*>(base) + i);
+  if (dtype == SSM_BF16) return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(base) + i));
+  return __half2float(__ldg(reinterpret_cast<const __half*>(base) + i));
+}
+__device__ __forceinline__ void store_dyn(void* base, int64_t i, int dtype, float v) {
+  if (dtype == SSM_F32) reinterpret_cast<float*>(base)[i] = v;
+  else if (dtype == SSM_BF16) reinterpret_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<__half*>(base)[i] = __float2half_rn(v);
+}
+
+// ---------------------------------------------------------------------------------------
+// device: 16-byte vectors of T  (4 x fp32 or 8 x 16-bit)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+struct Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  uint4 raw;
+  __device__ __forceinline__ void load(const T* p) { raw = __ldg(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void load_stream(const T* p) { raw = __ldcs(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void store(T* p) const { *reinterpret_cast<uint4*>(p) = raw; }
+  __device__ __forceinline__ void store_stream(T* p) const { __stcs(reinterpret_cast<uint4*>(p), raw); }
+  __device__ __forceinline__ void unpack(float (&f)[N]) const {
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] = to_f<T>(e[i]);
+  }
+  __device__ __forceinline__ void pack(const float (&f)[N]) {
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < N; ++i) e[i] = from_f<T>(f[i]);
+  }
+};
+
+// ---------------------------------------------------------------------------------------
+// device: math
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float exp_fast(float x) { return ex2_approx(x * kLog2e); }
+// torch.nn.functional.softplus with its defaults: identity above 20, log1p(exp(x)) below.
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+// SiLU through the special-function unit: x * rcp(1 + 2^(-x*log2e)); relative error ~1e-6.
+__device__ __forceinline__ float silu_fast(float x) { return x * rcp_approx(1.f + ex2_approx(-x * kLog2e)); }
+__device__ __forceinline__ float sigmoid_fast(float x) { return rcp_approx(1.f + ex2_approx(-x * kLog2e)); }
+__device__ __forceinline__ float silu_grad_fast(float x) {
+  const float s = sigmoid_fast(x);
+  return s * (1.f + x * (1.f - s));
+}
+// d/dx softplus(x) with the same switch point.
+__device__ __forceinline__ float softplus_grad_f(float x) { return x > 20.f ? 1.f : sigmoid_f(x); }
+
+// ---------------------------------------------------------------------------------------
+// device: reduce-scatter over a group of LANES lanes whose lane ids differ in the bits
+// [log2(STRIDE), log2(STRIDE*LANES)).  On entry every lane holds COUNT partial sums
+// (COUNT a multiple of LANES).  On exit lane with group index g (= (lane / STRIDE) % LANES)
+// holds, in p[0 .. COUNT/LANES), the group-wide totals of entries
+// g*(COUNT/LANES) + i.  Costs COUNT*(1-1/LANES) shuffles instead of COUNT*log2(LANES).
+// ---------------------------------------------------------------------------------------
+template <int LANES, int STRIDE, int COUNT>
+__device__ __forceinline__ void reduce_scatter(float (&p)[COUNT], int lane) {
+  static_assert(COUNT % LANES == 0, "COUNT must be a multiple of LANES");
+#pragma unroll
+  for (int off = LANES / 2, len = COUNT / 2; off >= 1; off >>= 1, len >>= 1) {
+    const bool upper = (lane & (off * STRIDE)) != 0;
+#pragma unroll
+    for (int i = 0; i < len; ++i) {
+      const float send = upper ? p[i] : p[i + len];
+      const float keep = upper ? p[i + len] : p[i];
+      p[i] = keep + __shfl_xor_sync(0xffffffffu, send, off * STRIDE);
+    }
+  }
+}
+
+// all-reduce (sum) over the same kind of lane group
+template <int LANES, int STRIDE>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int off = LANES / 2; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off * STRIDE);
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) { return group_sum<32, 1>(v); }
+
+}  // namespace ssmb

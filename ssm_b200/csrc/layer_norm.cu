@@ -1,0 +1,528 @@
+// Residual add fused with LayerNorm / RMSNorm, forward and backward, sm_100a.
+//
+// HBM-bound: each row is read once into registers (x and residual as 16-byte vectors),
+// the mean and the centred variance are both computed from those registers (the two-pass
+// form of the specification, no E[x^2]-mean^2 cancellation), and y / residual_out are
+// written once.  A row is owned by a group of G threads (a warp, or 128 / 512 threads for
+// wide rows).  The backward kernel is persistent: every thread keeps the weight / bias
+// gradient of its own columns in registers across all rows its CTA visits, the CTA writes
+// one partial row, and a second small kernel folds the partials -- no atomics, bitwise
+// reproducible.
+#include "common.cuh"
+
+namespace ssmb {
+
+constexpr int kNormFwdChunks = 4;  // 16-byte chunks of x per thread, forward
+constexpr int kNormBwdChunks = 2;  // backward keeps three more row-sized arrays in registers
+constexpr int kNormBwdMaxCtas = 592;  // 4 per SM on a 148-SM part
+
+// V consecutive elements of run-time type -> fp32
+template <int V>
+__device__ __forceinline__ void load_dyn_vec(const void* base, int64_t i, int dtype, float (&f)[V]) {
+  if (dtype == SSM_F32) {
+    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + i);
+#pragma unroll
+    for (int k = 0; k < V / 4; ++k) {
+      const float4 v = __ldcs(p + k);
+      f[4 * k] = v.x, f[4 * k + 1] = v.y, f[4 * k + 2] = v.z, f[4 * k + 3] = v.w;
+    }
+  } else if constexpr (V == 8) {
+    const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + i));
+    if (dtype == SSM_BF16) {
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] = __bfloat162float(e[k]);
+    } else {
+      const __half* e = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] = __half2float(e[k]);
+    }
+  } else {
+    const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + i));
+    if (dtype == SSM_BF16) {
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) f[k] = __bfloat162float(e[k]);
+    } else {
+      const __half* e = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) f[k] = __half2float(e[k]);
+    }
+  }
+}
+template <int V>
+__device__ __forceinline__ void store_dyn_vec(void* base, int64_t i, int dtype, const float (&f)[V]) {
+  if (dtype == SSM_F32) {
+    float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + i);
+#pragma unroll
+    for (int k = 0; k < V / 4; ++k) __stcs(p + k, make_float4(f[4 * k], f[4 * k + 1], f[4 * k + 2], f[4 * k + 3]));
+  } else if constexpr (V == 8) {
+    uint4 raw;
+    if (dtype == SSM_BF16) {
+      __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) e[k] = __float2bfloat16_rn(f[k]);
+    } else {
+      __half* e = reinterpret_cast<__half*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) e[k] = __float2half_rn(f[k]);
+    }
+    __stcs(reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(base) + i), raw);
+  } else {
+    uint2 raw;
+    if (dtype == SSM_BF16) {
+      __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) e[k] = __float2bfloat16_rn(f[k]);
+    } else {
+      __half* e = reinterpret_cast<__half*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) e[k] = __float2half_rn(f[k]);
+    }
+    __stcs(reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(base) + i), raw);
+  }
+}
+
+// Sum over the G threads of a row group.  G == 32: shuffles only.  G > 32: one row per CTA.
+template <int G>
+__device__ __forceinline__ float group_allsum(float v, float* scratch) {
+  v = warp_sum(v);
+  if constexpr (G > 32) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();  // scratch reuse
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < G / 32; ++w) t += scratch[w];
+    v = t;
+  }
+  return v;
+}
+
+template <typename T, int G>
+struct NormCfg {
+  static constexpr int V = 16 / sizeof(T);
+  static constexpr int BLOCK = G < 128 ? 128 : G;
+  static constexpr int RPC = BLOCK / G;  // rows per CTA pass
+};
+
+// Loads the row into registers as s = x (+ residual when prenorm); returns through refs.
+template <typename T, int G, int MC>
+__device__ __forceinline__ void norm_load_row(const ssm_norm_args& a, int64_t row, int gt, int nchunk, float (&s)[MC][16 / sizeof(T)],
+                                              float (&r)[MC][16 / sizeof(T)]) {
+  constexpr int V = 16 / sizeof(T);
+#pragma unroll
+  for (int c = 0; c < MC; ++c) {
+    const int ch = c * G + gt;
+    if (ch < nchunk) {
+      const int64_t off = row * a.hidden + (int64_t)ch * V;
+      Vec16<T> v;
+      v.load_stream(reinterpret_cast<const T*>(a.x) + off);
+      v.unpack(s[c]);
+      if (a.residual) {
+        load_dyn_vec<V>(a.residual, off, a.res_dtype, r[c]);
+        if (a.prenorm) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) s[c][i] += r[c][i];
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < V; ++i) s[c][i] = 0.f, r[c][i] = 0.f;
+    }
+  }
+}
+
+template <typename T, int G, int MC>
+__device__ __forceinline__ void norm_stats(const ssm_norm_args& a, int gt, int nchunk, const float (&s)[MC][16 / sizeof(T)], float* scratch,
+                                           float& mean, float& rstd) {
+  constexpr int V = 16 / sizeof(T);
+  const float inv = 1.f / (float)a.hidden;
+  mean = 0.f;
+  if (!a.is_rms) {
+    float t = 0.f;
+#pragma unroll
+    for (int c = 0; c < MC; ++c)
+#pragma unroll
+      for (int i = 0; i < V; ++i) t += s[c][i];
+    mean = group_allsum<G>(t, scratch) * inv;
+  }
+  float q = 0.f;
+#pragma unroll
+  for (int c = 0; c < MC; ++c) {
+    if (c * G + gt < nchunk) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float d = s[c][i] - mean;
+        q = fmaf(d, d, q);
+      }
+    }
+  }
+  rstd = rsqrtf(group_allsum<G>(q, scratch) * inv + a.eps);
+}
+
+template <typename T, int G>
+__global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_fwd_kernel(const ssm_norm_args a) {
+  using Cfg = NormCfg<T, G>;
+  constexpr int V = Cfg::V;
+  __shared__ float scratch[32];
+  const int gt = threadIdx.x % G;
+  const int64_t row = (int64_t)blockIdx.x * Cfg::RPC + threadIdx.x / G;
+  if (row >= a.rows) return;  // whole groups leave together (G >= 32; G > 32 has one row per CTA)
+  const int nchunk = a.hidden / V;
+  float s[kNormFwdChunks][V], r[kNormFwdChunks][V];
+  norm_load_row<T, G, kNormFwdChunks>(a, row, gt, nchunk, s, r);
+  if (a.residual_out) {
+#pragma unroll
+    for (int c = 0; c < kNormFwdChunks; ++c) {
+      const int ch = c * G + gt;
+      if (ch < nchunk) {
+        float o[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) o[i] = (a.residual && !a.prenorm) ? s[c][i] + r[c][i] : s[c][i];
+        store_dyn_vec<V>(a.residual_out, row * a.hidden + (int64_t)ch * V, a.resout_dtype, o);
+      }
+    }
+  }
+  float mean, rstd;
+  norm_stats<T, G, kNormFwdChunks>(a, gt, nchunk, s, scratch, mean, rstd);
+#pragma unroll
+  for (int c = 0; c < kNormFwdChunks; ++c) {
+    const int ch = c * G + gt;
+    if (ch < nchunk) {
+      float o[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const int col = ch * V + i;
+        float y = (s[c][i] - mean) * rstd * __ldg(a.weight + col);
+        if (a.bias) y += __ldg(a.bias + col);
+        if (a.residual && !a.prenorm) y += r[c][i];
+        o[i] = y;
+      }
+      Vec16<T> v;
+      v.pack(o);
+      v.store_stream(reinterpret_cast<T*>(a.y) + row * a.hidden + (int64_t)ch * V);
+    }
+  }
+}
+
+template <typename T, int G>
+__global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_bwd_kernel(const ssm_norm_bwd_args g) {
+  using Cfg = NormCfg<T, G>;
+  constexpr int V = Cfg::V;
+  const ssm_norm_args& a = g.fwd;
+  __shared__ float scratch[32];
+  const int gt = threadIdx.x % G, slot = threadIdx.x / G;
+  const int nchunk = a.hidden / V;
+  const float inv = 1.f / (float)a.hidden;
+  float dw[kNormBwdChunks][V], db[kNormBwdChunks][V], w[kNormBwdChunks][V];
+#pragma unroll
+  for (int c = 0; c < kNormBwdChunks; ++c)
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int col = (c * G + gt) * V + i;
+      dw[c][i] = 0.f, db[c][i] = 0.f;
+      w[c][i] = col < a.hidden ? __ldg(a.weight + col) : 0.f;
+    }
+  const int64_t npass = (a.rows + Cfg::RPC - 1) / Cfg::RPC;
+  for (int64_t pass = blockIdx.x; pass < npass; pass += gridDim.x) {
+    const int64_t row = pass * Cfg::RPC + slot;
+    const bool live = row < a.rows;  // G == 32: a dead warp still joins nothing but its own shuffles
+    float s[kNormBwdChunks][V], r[kNormBwdChunks][V], dy[kNormBwdChunks][V];
+    if (live) norm_load_row<T, G, kNormBwdChunks>(a, row, gt, nchunk, s, r);
+    else {
+#pragma unroll
+      for (int c = 0; c < kNormBwdChunks; ++c)
+#pragma unroll
+        for (int i = 0; i < V; ++i) s[c][i] = 0.f, r[c][i] = 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < kNormBwdChunks; ++c) {
+      const int ch = c * G + gt;
+      if (live && ch < nchunk) {
+        Vec16<T> v;
+        v.load_stream(reinterpret_cast<const T*>(g.dy) + row * a.hidden + (int64_t)ch * V);
+        v.unpack(dy[c]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) dy[c][i] = 0.f;
+      }
+    }
+    float mean, rstd;
+    norm_stats<T, G, kNormBwdChunks>(a, gt, nchunk, s, scratch, mean, rstd);
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < kNormBwdChunks; ++c)
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float xh = (s[c][i] - mean) * rstd;
+        const float wdy = dy[c][i] * w[c][i];
+        s[c][i] = xh;  // keep xhat
+        c1 = fmaf(wdy, xh, c1);
+        c2 += wdy;
+        if (live && (c * G + gt) < nchunk) {
+          dw[c][i] = fmaf(dy[c][i], xh, dw[c][i]);
+          db[c][i] += dy[c][i];
+        }
+      }
+    c1 = group_allsum<G>(c1, scratch) * inv;
+    c2 = a.is_rms ? 0.f : group_allsum<G>(c2, scratch) * inv;
+    if (live) {
+#pragma unroll
+      for (int c = 0; c < kNormBwdChunks; ++c) {
+        const int ch = c * G + gt;
+        if (ch < nchunk) {
+          float dsv[V];
+#pragma unroll
+          for (int i = 0; i < V; ++i) dsv[i] = (dy[c][i] * w[c][i] - s[c][i] * c1 - c2) * rstd;
+          const int64_t off = row * a.hidden + (int64_t)ch * V;
+          Vec16<T> v;
+          v.pack(dsv);
+          v.store_stream(reinterpret_cast<T*>(g.dx) + off);
+          if (g.dresidual) {
+            if (a.prenorm) store_dyn_vec<V>(g.dresidual, off, a.res_dtype, dsv);
+            else store_dyn_vec<V>(g.dresidual, off, a.res_dtype, dy[c]);
+          }
+        }
+      }
+    }
+  }
+  // fold the RPC row slots of this CTA, then write the CTA's partial rows
+  if constexpr (Cfg::RPC > 1) {
+    __shared__ float fold[Cfg::RPC][2][kNormBwdChunks * V * G + 1];
+#pragma unroll
+    for (int c = 0; c < kNormBwdChunks; ++c)
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        fold[slot][0][(c * V + i) * G + gt] = dw[c][i];
+        fold[slot][1][(c * V + i) * G + gt] = db[c][i];
+      }
+    __syncthreads();
+    if (slot == 0) {
+#pragma unroll
+      for (int c = 0; c < kNormBwdChunks; ++c)
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          float tw = 0.f, tb = 0.f;
+#pragma unroll
+          for (int q = 0; q < Cfg::RPC; ++q) tw += fold[q][0][(c * V + i) * G + gt], tb += fold[q][1][(c * V + i) * G + gt];
+          dw[c][i] = tw, db[c][i] = tb;
+        }
+    }
+  }
+  if (slot == 0) {
+    float* pw = g.partial + (int64_t)blockIdx.x * 2 * a.hidden;
+    float* pb = pw + a.hidden;
+#pragma unroll
+    for (int c = 0; c < kNormBwdChunks; ++c) {
+      const int ch = c * G + gt;
+      if (ch < nchunk) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) pw[ch * V + i] = dw[c][i], pb[ch * V + i] = db[c][i];
+      }
+    }
+  }
+}
+
+__global__ void norm_fold_kernel(const float* __restrict__ partial, int nctas, int hidden, float* __restrict__ dweight, float* __restrict__ dbias) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= hidden) return;
+  float tw = 0.f, tb = 0.f;
+  for (int k = 0; k < nctas; ++k) {
+    tw += partial[(int64_t)k * 2 * hidden + col];
+    tb += partial[(int64_t)k * 2 * hidden + hidden + col];
+  }
+  dweight[col] = tw;
+  if (dbias) dbias[col] = tb;
+}
+
+// ---- fallback for rows that cannot be vectorised (hidden not a multiple of the vector, or
+// ---- misaligned pointers): one CTA per row, strided scalar accesses, atomics for dw / db.
+template <typename T>
+__device__ __forceinline__ float norm_s_at(const ssm_norm_args& a, int64_t off) {
+  float v = to_f<T>(reinterpret_cast<const T*>(a.x)[off]);
+  if (a.residual && a.prenorm) v += load_dyn(a.residual, off, a.res_dtype);
+  return v;
+}
+__device__ __forceinline__ float block_allsum128(float v, float* scratch) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return scratch[0] + scratch[1] + scratch[2] + scratch[3];
+}
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(128) norm_scalar_kernel(const ssm_norm_bwd_args g) {
+  const ssm_norm_args& a = g.fwd;
+  __shared__ float scratch[4];
+  const int64_t row = blockIdx.x;
+  const int64_t base = row * a.hidden;
+  const float inv = 1.f / (float)a.hidden;
+  float mean = 0.f;
+  if (!a.is_rms) {
+    float t = 0.f;
+    for (int c = threadIdx.x; c < a.hidden; c += 128) t += norm_s_at<T>(a, base + c);
+    mean = block_allsum128(t, scratch) * inv;
+  }
+  float q = 0.f;
+  for (int c = threadIdx.x; c < a.hidden; c += 128) {
+    const float d = norm_s_at<T>(a, base + c) - mean;
+    q = fmaf(d, d, q);
+  }
+  const float rstd = rsqrtf(block_allsum128(q, scratch) * inv + a.eps);
+  if (!BWD) {
+    for (int c = threadIdx.x; c < a.hidden; c += 128) {
+      const float sv = norm_s_at<T>(a, base + c);
+      float y = (sv - mean) * rstd * __ldg(a.weight + c);
+      if (a.bias) y += __ldg(a.bias + c);
+      if (a.residual && !a.prenorm) y += load_dyn(a.residual, base + c, a.res_dtype);
+      reinterpret_cast<T*>(a.y)[base + c] = from_f<T>(y);
+      if (a.residual_out) {
+        float ro = to_f<T>(reinterpret_cast<const T*>(a.x)[base + c]);
+        if (a.residual) ro += load_dyn(a.residual, base + c, a.res_dtype);
+        store_dyn(a.residual_out, base + c, a.resout_dtype, ro);
+      }
+    }
+  } else {
+    float c1 = 0.f, c2 = 0.f;
+    for (int c = threadIdx.x; c < a.hidden; c += 128) {
+      const float xh = (norm_s_at<T>(a, base + c) - mean) * rstd;
+      const float dyv = to_f<T>(reinterpret_cast<const T*>(g.dy)[base + c]);
+      const float wdy = dyv * __ldg(a.weight + c);
+      c1 = fmaf(wdy, xh, c1);
+      c2 += wdy;
+      atomicAdd(g.dweight + c, dyv * xh);
+      if (g.dbias) atomicAdd(g.dbias + c, dyv);
+    }
+    c1 = block_allsum128(c1, scratch) * inv;
+    c2 = a.is_rms ? 0.f : block_allsum128(c2, scratch) * inv;
+    for (int c = threadIdx.x; c < a.hidden; c += 128) {
+      const float xh = (norm_s_at<T>(a, base + c) - mean) * rstd;
+      const float dyv = to_f<T>(reinterpret_cast<const T*>(g.dy)[base + c]);
+      const float ds = (dyv * __ldg(a.weight + c) - xh * c1 - c2) * rstd;
+      reinterpret_cast<T*>(g.dx)[base + c] = from_f<T>(ds);
+      if (g.dresidual) store_dyn(g.dresidual, base + c, a.res_dtype, a.prenorm ? ds : dyv);
+    }
+  }
+}
+
+static int norm_validate(const ssm_norm_args* a) {
+  SSM_REQUIRE(a != nullptr, SSM_ERR_NULL, "fused_layer_norm: args is NULL");
+  SSM_REQUIRE(a->rows >= 0 && a->hidden >= 1, SSM_ERR_SHAPE, "fused_layer_norm: bad shape");
+  SSM_REQUIRE(valid_dtype(a->io_dtype), SSM_ERR_DTYPE, "fused_layer_norm: unknown dtype");
+  SSM_REQUIRE(!a->residual || valid_dtype(a->res_dtype), SSM_ERR_DTYPE, "fused_layer_norm: unknown residual dtype");
+  SSM_REQUIRE(!a->residual_out || valid_dtype(a->resout_dtype), SSM_ERR_DTYPE, "fused_layer_norm: unknown residual_out dtype");
+  SSM_REQUIRE(a->rows < (1ll << 31), SSM_ERR_TOO_LARGE, "fused_layer_norm: too many rows");
+  return SSM_OK;
+}
+
+static bool norm_vec_ok(const ssm_norm_args& a, int maxchunks, const void* p1, const void* p2, const void* p3) {
+  const int V = 16 / dtype_size(a.io_dtype);
+  if (a.hidden % V != 0) return false;
+  if (a.hidden > 512 * maxchunks * V) return false;
+  auto ok = [](const void* p) { return p == nullptr || aligned_to(p, 16); };
+  // residual / residual_out / dresidual rows of fp32 with hidden % V == 0 are 16-byte aligned too
+  return ok(a.x) && ok(a.y) && ok(a.residual) && ok(a.residual_out) && ok(p1) && ok(p2) && ok(p3);
+}
+
+static int norm_group(const ssm_norm_args& a, int maxchunks) {
+  const int V = 16 / dtype_size(a.io_dtype);
+  const int nchunk = a.hidden / V;
+  if (nchunk <= 32 * maxchunks) return 32;
+  if (nchunk <= 128 * maxchunks) return 128;
+  return 512;
+}
+
+static int norm_bwd_ctas(const ssm_norm_args& a, int rpc) {
+  const int64_t npass = (a.rows + rpc - 1) / rpc;
+  return (int)(npass < kNormBwdMaxCtas ? npass : kNormBwdMaxCtas);
+}
+
+template <typename T, int G>
+static int norm_fwd_launch(const ssm_norm_args& a, cudaStream_t st) {
+  using Cfg = NormCfg<T, G>;
+  const unsigned grid = (unsigned)((a.rows + Cfg::RPC - 1) / Cfg::RPC);
+  norm_fwd_kernel<T, G><<<grid, Cfg::BLOCK, 0, st>>>(a);
+  return launch_status("norm_fwd_kernel");
+}
+template <typename T, int G>
+static int norm_bwd_launch(const ssm_norm_bwd_args& g, cudaStream_t st) {
+  using Cfg = NormCfg<T, G>;
+  const int nctas = norm_bwd_ctas(g.fwd, Cfg::RPC);
+  norm_bwd_kernel<T, G><<<nctas, Cfg::BLOCK, 0, st>>>(g);
+  if (int rc = launch_status("norm_bwd_kernel")) return rc;
+  norm_fold_kernel<<<(g.fwd.hidden + 127) / 128, 128, 0, st>>>(g.partial, nctas, g.fwd.hidden, g.dweight, g.dbias);
+  return launch_status("norm_fold_kernel");
+}
+
+template <typename T>
+static int norm_fwd_t(const ssm_norm_args& a, cudaStream_t st) {
+  if (!norm_vec_ok(a, kNormFwdChunks, nullptr, nullptr, nullptr)) {
+    ssm_norm_bwd_args g{};
+    g.fwd = a;
+    norm_scalar_kernel<T, false><<<(unsigned)a.rows, 128, 0, st>>>(g);
+    return launch_status("norm_scalar_kernel");
+  }
+  switch (norm_group(a, kNormFwdChunks)) {
+    case 32: return norm_fwd_launch<T, 32>(a, st);
+    case 128: return norm_fwd_launch<T, 128>(a, st);
+    default: return norm_fwd_launch<T, 512>(a, st);
+  }
+}
+template <typename T>
+static int norm_bwd_t(const ssm_norm_bwd_args& g, cudaStream_t st) {
+  const ssm_norm_args& a = g.fwd;
+  if (!norm_vec_ok(a, kNormBwdChunks, g.dy, g.dx, g.dresidual)) {
+    cudaMemsetAsync(g.dweight, 0, sizeof(float) * a.hidden, st);
+    if (g.dbias) cudaMemsetAsync(g.dbias, 0, sizeof(float) * a.hidden, st);
+    norm_scalar_kernel<T, true><<<(unsigned)a.rows, 128, 0, st>>>(g);
+    return launch_status("norm_scalar_kernel");
+  }
+  switch (norm_group(a, kNormBwdChunks)) {
+    case 32: return norm_bwd_launch<T, 32>(g, st);
+    case 128: return norm_bwd_launch<T, 128>(g, st);
+    default: return norm_bwd_launch<T, 512>(g, st);
+  }
+}
+
+}  // namespace ssmb
+
+using namespace ssmb;
+
+extern "C" int ssm_fused_add_norm_fwd(const ssm_norm_args* a, ssm_stream_t stream) {
+  if (int rc = norm_validate(a)) return rc;
+  if (a->rows == 0) return SSM_OK;
+  SSM_REQUIRE(a->x && a->y && a->weight, SSM_ERR_NULL, "fused_layer_norm: x, weight and y are required");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (a->io_dtype) {
+    case SSM_F32: return norm_fwd_t<float>(*a, st);
+    case SSM_BF16: return norm_fwd_t<__nv_bfloat16>(*a, st);
+    default: return norm_fwd_t<__half>(*a, st);
+  }
+}
+
+extern "C" int64_t ssm_norm_bwd_scratch_floats(int64_t rows, int32_t hidden) {
+  (void)rows;
+  return (int64_t)2 * hidden * kNormBwdMaxCtas;
+}
+
+extern "C" int ssm_fused_add_norm_bwd(const ssm_norm_bwd_args* g, ssm_stream_t stream) {
+  SSM_REQUIRE(g != nullptr, SSM_ERR_NULL, "fused_layer_norm_backward: args is NULL");
+  const ssm_norm_args* a = &g->fwd;
+  if (int rc = norm_validate(a)) return rc;
+  SSM_REQUIRE(g->dweight, SSM_ERR_NULL, "fused_layer_norm_backward: dweight is required");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (a->rows == 0) {
+    cudaMemsetAsync(g->dweight, 0, sizeof(float) * a->hidden, st);
+    if (g->dbias) cudaMemsetAsync(g->dbias, 0, sizeof(float) * a->hidden, st);
+    return SSM_OK;
+  }
+  SSM_REQUIRE(a->x && a->weight && g->dy && g->dx && g->partial, SSM_ERR_NULL, "fused_layer_norm_backward: missing pointer");
+  SSM_REQUIRE(!a->residual == !g->dresidual || !g->dresidual, SSM_ERR_NULL, "fused_layer_norm_backward: dresidual without residual");
+  switch (a->io_dtype) {
+    case SSM_F32: return norm_bwd_t<float>(*g, st);
+    case SSM_BF16: return norm_bwd_t<__nv_bfloat16>(*g, st);
+    default: return norm_bwd_t<__half>(*g, st);
+  }
+}

@@ -1,0 +1,901 @@
+"""The five state-space operators on the B200 CUDA library, with the upstream signatures.
+
+``selective_scan``, ``selective_state_step``, ``ssd_chunk_scan``, ``dw_causal_conv`` and
+``fused_layer_norm`` take the arguments of ``ssm.ops`` in b-vitamins/ssm
+(src/ssm/ops/__init__.py:1255-1690; semantics src/ssm/ops/python/reference.py), accept CUDA
+tensors only, and are differentiable through ``torch.autograd.Function`` wrappers whose
+forward and backward both run hand-written sm_100a kernels behind the C ABI of
+``include/ssm_b200.h``.  Contract violations raise ``ValueError`` as upstream does.  There is
+no CPU path and no PyTorch fallback: a missing library or a CPU tensor is an error.
+
+Additive keyword arguments that upstream does not have are marked "extension" below; their
+defaults reproduce upstream behaviour.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Any, Optional
+
+import torch
+
+from . import _lib as L
+
+Tensor = torch.Tensor
+
+_CODES = {torch.float32: L.F32, torch.bfloat16: L.BF16, torch.float16: L.F16}
+
+
+def _code(t: Tensor, what: str) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise ValueError(f"{what}: dtype {t.dtype} is not built (float32, bfloat16 and float16 are)") from None
+
+
+def _need_cuda(*ts: Optional[Tensor]) -> torch.device:
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("ssm_b200 operators run on CUDA tensors only; there is no CPU fallback")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError("all tensors must be on the same CUDA device")
+    assert dev is not None
+    return dev
+
+
+def _p(t: Optional[Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _f32(t: Optional[Tensor]) -> Optional[Tensor]:
+    if t is None:
+        return None
+    return t.detach().to(torch.float32).contiguous()
+
+
+def _c(t: Optional[Tensor]) -> Optional[Tensor]:
+    if t is None:
+        return None
+    t = t.detach()
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _call(fn, args) -> None:
+    try:
+        L.check(fn(C.byref(args), _stream()))
+    except L.BackendError as exc:
+        if exc.code < 0:
+            raise ValueError(str(exc)) from None
+        raise
+
+
+# =========================================================================================
+# selective_scan
+# =========================================================================================
+
+
+def _scan_coeff(name: str, p: Tensor, nb: int, nd: int, nn: int, nl: int):
+    """Return (tensor, groups, (sb, sg, sn, st)) for the B / C layouts of reference.py:22-56."""
+    if p.dim() == 2:
+        if tuple(p.shape) != (nd, nn):
+            raise ValueError(f"{name} must have shape (D, N).")
+        return _f32(p), nd, (0, nn, 1, 0)
+    if p.dim() == 3:
+        if tuple(p.shape) != (nb, nd, nn):
+            raise ValueError(f"{name} must have shape (B, D, N) when 3-D.")
+        return _f32(p), nd, (nd * nn, nn, 1, 0)
+    if p.dim() == 4:
+        if p.shape[0] != nb or p.shape[-1] != nl:
+            raise ValueError(f"{name} must have shape (B, G, N, L) when 4-D.")
+        g = p.shape[1]
+        if g == 0 or nd % g != 0:
+            raise ValueError("Group dimension must divide D.")
+        if p.shape[2] != nn:
+            raise ValueError(f"{name} has mismatched state dimension.")
+        return _c(p), g, (g * nn * nl, nn * nl, nl, 1)
+    raise ValueError(f"Unsupported rank for {name}.")
+
+
+class _ScanCtx:
+    """Validated, contiguous inputs of one selective-scan call."""
+
+    def __init__(self, u, delta, A, B, C_, D, z, dt_bias, softplus, initial_state):
+        if u.ndim != 3 or delta.ndim != 3:
+            raise ValueError("u and delta must have shape (B, D, L).")
+        nb, nd, nl = u.shape
+        if tuple(delta.shape) != (nb, nd, nl):
+            raise ValueError("delta must match the shape of u.")
+        if A.ndim != 2 or tuple(A.shape) != (nd, A.shape[-1]):
+            raise ValueError("A must have shape (D, N).")
+        nn = A.shape[-1]
+        if nn < 1 or nn > 256:
+            raise ValueError("selective_scan: the state dimension must be in [1, 256].")
+        if A.is_complex():
+            raise ValueError("selective_scan: complex A is not built")
+        _need_cuda(u, delta, A, B, C_, D, z, dt_bias, initial_state)
+        self.io = _code(u, "selective_scan")
+        self.shape = (nb, nd, nl, nn)
+        self.u = _c(u)
+        self.delta = _c(delta.to(u.dtype))
+        self.A = _f32(A)
+        Bt, gb, sB = _scan_coeff("B", B, nb, nd, nn, nl)
+        Ct, gc, sC = _scan_coeff("C", C_, nb, nd, nn, nl)
+        if gb != gc:
+            # differing group counts: expand the coarser one so that one group map serves both
+            g = max(gb, gc)
+            if g % min(gb, gc) != 0:
+                raise ValueError("B and C group dimensions must nest.")
+            if gb < g:
+                Bt, sB = _regroup(Bt, sB, gb, g, nb, nn, nl)
+            else:
+                Ct, sC = _regroup(Ct, sC, gc, g, nb, nn, nl)
+            gb = g
+        if Bt.dtype != Ct.dtype:
+            Bt, Ct = Bt.float(), Ct.float()
+        _code(Bt, "selective_scan B/C")
+        self.B, self.C, self.groups, self.sB, self.sC = Bt, Ct, gb, sB, sC
+        if D is not None and tuple(D.shape) != (nd,):
+            raise ValueError("D must have shape (D,).")
+        if z is not None and tuple(z.shape) != (nb, nd, nl):
+            raise ValueError("z must have shape (B, D, L).")
+        if dt_bias is not None and tuple(dt_bias.shape) != (nd,):
+            raise ValueError("dt_bias must have shape (D,).")
+        if initial_state is not None and tuple(initial_state.shape) != (nb, nd, nn):
+            raise ValueError("initial_state must have shape (B, D, N).")
+        self.D = _f32(D)
+        self.z = None if z is None else _c(z.to(u.dtype))
+        self.dt_bias = _f32(dt_bias)
+        self.init = _f32(initial_state)
+        self.softplus = bool(softplus)
+
+    def fill(self, a: L.ScanFwdArgs) -> None:
+        nb, nd, nl, nn = self.shape
+        a.batch, a.dim, a.len, a.nstate = nb, nd, nl, nn
+        a.io_dtype, a.bc_dtype = self.io, _CODES[self.B.dtype]
+        a.delta_softplus = int(self.softplus)
+        a.u, a.delta, a.z, a.A = _p(self.u), _p(self.delta), _p(self.z), _p(self.A)
+        a.Bm, a.Cm, a.bc_groups = _p(self.B), _p(self.C), self.groups
+        a.b_sb, a.b_sg, a.b_sn, a.b_st = self.sB
+        a.c_sb, a.c_sg, a.c_sn, a.c_st = self.sC
+        a.D, a.dt_bias, a.initial_state = _p(self.D), _p(self.dt_bias), _p(self.init)
+
+
+def _regroup(t: Tensor, strides, g_old: int, g_new: int, nb: int, nn: int, nl: int):
+    """Repeat a coarser-grouped (B, G, N, L) coefficient so that it has ``g_new`` groups."""
+    if strides[3] == 0:  # (D, N) / (B, D, N) are always per channel; cannot be coarser
+        raise ValueError("B and C group dimensions must nest.")
+    t = t.repeat_interleave(g_new // g_old, dim=1).contiguous()
+    return t, (g_new * nn * nl, nn * nl, nl, 1)
+
+
+def _scan_forward(ctx: _ScanCtx, want_last: bool, want_ckpt: bool, last_dtype: torch.dtype):
+    nb, nd, nl, nn = ctx.shape
+    lib = L.load()
+    out = torch.empty_like(ctx.u)
+    last = torch.empty(nb, nd, nn, dtype=last_dtype, device=ctx.u.device) if want_last else None
+    ck = None
+    if want_ckpt:
+        iv = lib.ssm_scan_checkpoint_interval()
+        ck = torch.empty(nb, nd, max(1, (nl + iv - 1) // iv), nn, dtype=torch.float32, device=ctx.u.device)
+    a = L.ScanFwdArgs()
+    ctx.fill(a)
+    a.out, a.last_state, a.checkpoints = _p(out), _p(last), _p(ck)
+    a.last_dtype = _CODES[last_dtype] if want_last else 0
+    _call(lib.ssm_selective_scan_fwd, a)
+    return out, last, ck
+
+
+def _scan_backward(ctx: _ScanCtx, ck: Tensor, grad_out: Tensor, grad_last: Optional[Tensor], B_like: Tensor, C_like: Tensor):
+    nb, nd, nl, nn = ctx.shape
+    lib = L.load()
+    dev = ctx.u.device
+    du = torch.empty_like(ctx.u)
+    ddelta = torch.empty_like(ctx.u)
+    dz = torch.empty_like(ctx.u) if ctx.z is not None else None
+    dA = torch.zeros(nd, nn, dtype=torch.float32, device=dev)
+    # gradient buffers in the layout of the (contiguous) coefficients the kernel read
+    dB = torch.zeros(ctx.B.shape, dtype=torch.float32, device=dev)
+    dC = torch.zeros(ctx.C.shape, dtype=torch.float32, device=dev)
+    dD = torch.zeros(nd, dtype=torch.float32, device=dev) if ctx.D is not None else None
+    dbias = torch.zeros(nd, dtype=torch.float32, device=dev) if ctx.dt_bias is not None else None
+    g = L.ScanBwdArgs()
+    ctx.fill(g.fwd)
+    g.fwd.checkpoints = _p(ck)
+    go = _c(grad_out.to(ctx.u.dtype))
+    gl = _f32(grad_last)
+    g.dout, g.dlast_state = _p(go), _p(gl)
+    g.du, g.ddelta, g.dz = _p(du), _p(ddelta), _p(dz)
+    g.dA, g.dB, g.dC, g.dD, g.ddt_bias = _p(dA), _p(dB), _p(dC), _p(dD), _p(dbias)
+    g.db_sb, g.db_sg, g.db_sn, g.db_st = ctx.sB
+    g.dc_sb, g.dc_sg, g.dc_sn, g.dc_st = ctx.sC
+    _call(lib.ssm_selective_scan_bwd, g)
+
+    def fold(grad: Tensor, like: Tensor) -> Tensor:
+        if grad.shape != like.shape:  # the coefficient had been regrouped: sum the repeats back
+            rep = grad.shape[1] // like.shape[1]
+            grad = grad.view(like.shape[0], like.shape[1], rep, *like.shape[2:]).sum(2)
+        return grad.to(like.dtype)
+
+    return du, ddelta, dA, fold(dB, B_like), fold(dC, C_like), dD, dz, dbias
+
+
+class _SelectiveScanFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, u, delta, A, B, C_, D, z, dt_bias, softplus, return_last_state, initial_state, keep_state_fp32):
+        sc = _ScanCtx(u, delta, A, B, C_, D, z, dt_bias, softplus, initial_state)
+        needs = any(t is not None and t.requires_grad for t in (u, delta, A, B, C_, D, z, dt_bias))
+        last_dtype = torch.float32 if keep_state_fp32 else u.dtype
+        out, last, ck = _scan_forward(sc, return_last_state, needs, last_dtype)
+        ctx.sc, ctx.ck = sc, ck
+        ctx.like = (B, C_, A, D, z, dt_bias, delta)
+        if return_last_state:
+            return out, last
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_last=None):
+        sc: _ScanCtx = ctx.sc
+        B, C_, A, D, z, dt_bias, delta = ctx.like
+        if grad_out is None:
+            grad_out = torch.zeros_like(sc.u)
+        du, ddelta, dA, dB, dC, dD, dz, dbias = _scan_backward(sc, ctx.ck, grad_out, grad_last, B, C_)
+        return (
+            du,
+            ddelta.to(delta.dtype),
+            dA.to(A.dtype),
+            dB,
+            dC,
+            None if D is None else dD.to(D.dtype),
+            None if z is None else dz.to(z.dtype),
+            None if dt_bias is None else dbias.to(dt_bias.dtype),
+            None, None, None, None,
+        )
+
+
+def selective_scan(
+    u: Tensor,
+    delta: Tensor,
+    A: Tensor,
+    B: Tensor,
+    C: Tensor,
+    D: Optional[Tensor] = None,
+    z: Optional[Tensor] = None,
+    dt_bias: Optional[Tensor] = None,
+    softplus: bool = False,
+    return_last_state: bool = False,
+    initial_state: Optional[Tensor] = None,
+    keep_state_fp32: bool = False,
+):
+    """Mamba-1 selective scan (upstream ``ssm.ops.selective_scan``, reference.py:87-194).
+
+    Extensions: ``initial_state`` ``(B, D, N)`` starts the recurrence from a given state (no
+    gradient flows into it); ``keep_state_fp32`` returns the last state in fp32 instead of
+    ``u.dtype``.
+    """
+    res = _SelectiveScanFn.apply(u, delta, A, B, C, D, z, dt_bias, softplus, return_last_state, initial_state, keep_state_fp32)
+    return res
+
+
+# =========================================================================================
+# selective_state_step
+# =========================================================================================
+
+
+def _step_coeff(name: str, p: Tensor, nb: int, nd: int, nn: int):
+    if p.dim() == 2:
+        if tuple(p.shape) != (nd, nn):
+            raise ValueError(f"{name} must have shape (D, N).")
+        return nd, (0, nn, 1)
+    if p.dim() == 3 and p.shape[0] == nb:
+        g = p.shape[1]
+        if p.shape[2] != nn:
+            raise ValueError(f"{name} must have matching state dimension.")
+        if g == 0 or nd % g != 0:
+            raise ValueError(f"{name} group dimension must divide D.")
+        return g, (g * nn, nn, 1)
+    raise ValueError(f"{name} must have shape (D, N), (B, D, N) or (B, G, N).")
+
+
+class _StepCtx:
+    def __init__(self, state, x, dt, A, B, C_, D, z, dt_bias, softplus):
+        if state.ndim != 3:
+            raise ValueError("state must have shape (B, D, N).")
+        if x.ndim != 2 or dt.ndim != 2:
+            raise ValueError("x and dt must have shape (B, D).")
+        nb, nd, nn = state.shape
+        if tuple(x.shape) != (nb, nd) or tuple(dt.shape) != (nb, nd):
+            raise ValueError("x and dt must match the first two dimensions of state.")
+        if tuple(A.shape) != (nd, nn):
+            raise ValueError("A must have shape (D, N).")
+        _need_cuda(state, x, dt, A, B, C_, D, z, dt_bias)
+        self.shape = (nb, nd, nn)
+        self.io = _code(x, "selective_state_step")
+        gb, self.sB = _step_coeff("B", B, nb, nd, nn)
+        gc, self.sC = _step_coeff("C", C_, nb, nd, nn)
+        Bt, Ct = _c(B), _c(C_)
+        if gb != gc or Bt.dtype != Ct.dtype or Bt.dtype not in _CODES:
+            # bring both to per-channel fp32 (B, D, N) / (D, N) form
+            Bt, gb, self.sB = _expand_step(Bt, gb, nb, nd, nn)
+            Ct, gc, self.sC = _expand_step(Ct, gc, nb, nd, nn)
+        self.B, self.C, self.groups = Bt, Ct, gb
+        if D is not None and tuple(D.shape) != (nd,):
+            raise ValueError("D must have shape (D,).")
+        if z is not None and tuple(z.shape) != (nb, nd):
+            raise ValueError("z must have shape (B, D).")
+        if dt_bias is not None and tuple(dt_bias.shape) != (nd,):
+            raise ValueError("dt_bias must have shape (D,).")
+        self.x, self.dt = _c(x), _c(dt.to(x.dtype))
+        self.z = None if z is None else _c(z.to(x.dtype))
+        self.A, self.D, self.dt_bias = _f32(A), _f32(D), _f32(dt_bias)
+        self.softplus = bool(softplus)
+
+    def fill(self, a: L.StepArgs, state32: Tensor) -> None:
+        nb, nd, nn = self.shape
+        a.batch, a.dim, a.nstate, a.io_dtype = nb, nd, nn, self.io
+        a.bc_dtype, a.bc_groups, a.dt_softplus, a.param_heads = _CODES[self.B.dtype], self.groups, int(self.softplus), 0
+        a.state, a.x, a.dt, a.z, a.A = _p(state32), _p(self.x), _p(self.dt), _p(self.z), _p(self.A)
+        a.Bm, a.Cm = _p(self.B), _p(self.C)
+        a.b_sb, a.b_sg, a.b_sn = self.sB
+        a.c_sb, a.c_sg, a.c_sn = self.sC
+        a.D, a.dt_bias = _p(self.D), _p(self.dt_bias)
+
+
+def _expand_step(t: Tensor, g: int, nb: int, nd: int, nn: int):
+    t = t.float()
+    if t.dim() == 3 and g != nd:
+        t = t.repeat_interleave(nd // g, dim=1)
+    t = t.contiguous()
+    return t, nd, ((0, nn, 1) if t.dim() == 2 else (nd * nn, nn, 1))
+
+
+def _step_forward(sc: _StepCtx, state: Tensor) -> Tensor:
+    """Runs the step; ``state`` is updated in place (through an fp32 copy if it is not fp32)."""
+    lib = L.load()
+    direct = state.dtype == torch.float32 and state.is_contiguous()
+    work = state.detach() if direct else state.detach().float().contiguous()
+    out = torch.empty_like(sc.x)
+    a = L.StepArgs()
+    sc.fill(a, work)
+    a.out = _p(out)
+    _call(lib.ssm_selective_state_step, a)
+    if not direct:
+        state.detach().copy_(work)
+    return out
+
+
+class _StateStepFn(torch.autograd.Function):
+    """Out-of-place form used when gradients are needed: returns (y, new_state)."""
+
+    @staticmethod
+    def forward(ctx, state, x, dt, A, B, C_, D, z, dt_bias, softplus):
+        sc = _StepCtx(state, x, dt, A, B, C_, D, z, dt_bias, softplus)
+        old = state.detach().float().contiguous()
+        new = old.clone()
+        y = _step_forward(sc, new)
+        ctx.sc, ctx.old = sc, old
+        ctx.like = (state, dt, A, B, C_, D, z, dt_bias)
+        return y, new.to(state.dtype)
+
+    @staticmethod
+    def backward(ctx, gy, gstate):
+        sc: _StepCtx = ctx.sc
+        state, dt, A, B, C_, D, z, dt_bias = ctx.like
+        nb, nd, nn = sc.shape
+        lib = L.load()
+        dev = sc.x.device
+        g = L.StepBwdArgs()
+        sc.fill(g.fwd, ctx.old)
+        gy = torch.zeros_like(sc.x) if gy is None else _c(gy.to(sc.x.dtype))
+        gs = _f32(gstate)
+        dstate = torch.empty(nb, nd, nn, dtype=torch.float32, device=dev)
+        dx, ddt = torch.empty_like(sc.x), torch.empty_like(sc.x)
+        dz = torch.empty_like(sc.x) if sc.z is not None else None
+        dA = torch.zeros(nd, nn, dtype=torch.float32, device=dev)
+        dB = torch.zeros(sc.B.shape, dtype=torch.float32, device=dev)
+        dC = torch.zeros(sc.C.shape, dtype=torch.float32, device=dev)
+        dD = torch.zeros(nd, dtype=torch.float32, device=dev) if sc.D is not None else None
+        db = torch.zeros(nd, dtype=torch.float32, device=dev) if sc.dt_bias is not None else None
+        g.dout, g.dnew_state, g.dstate = _p(gy), _p(gs), _p(dstate)
+        g.dx, g.ddt, g.dz = _p(dx), _p(ddt), _p(dz)
+        g.dA, g.dB, g.dC, g.dD, g.ddt_bias = _p(dA), _p(dB), _p(dC), _p(dD), _p(db)
+        _call(lib.ssm_selective_state_step_bwd, g)
+
+        def fold(grad: Tensor, like: Tensor) -> Tensor:
+            if grad.shape != like.shape:  # grouped (B, G, N) had been expanded to (B, D, N)
+                rep = grad.shape[1] // like.shape[1]
+                grad = grad.view(like.shape[0], like.shape[1], rep, like.shape[2]).sum(2)
+            return grad.to(like.dtype)
+
+        return (
+            dstate.to(state.dtype), dx, ddt.to(dt.dtype), dA.to(A.dtype), fold(dB, B), fold(dC, C_),
+            None if D is None else dD.to(D.dtype),
+            None if z is None else dz.to(z.dtype),
+            None if dt_bias is None else db.to(dt_bias.dtype),
+            None,
+        )
+
+
+def selective_state_step(
+    state: Tensor,
+    x: Tensor,
+    dt: Tensor,
+    A: Tensor,
+    B: Tensor,
+    C: Tensor,
+    D: Optional[Tensor] = None,
+    z: Optional[Tensor] = None,
+    dt_bias: Optional[Tensor] = None,
+    softplus: bool = True,
+) -> Tensor:
+    """One decode token; ``state`` ``(B, D, N)`` is overwritten in place (upstream
+    ``ssm.ops.selective_state_step``, reference.py:197-309)."""
+    if any(t is not None and t.requires_grad for t in (state, x, dt, A, B, C, D, z, dt_bias)) and torch.is_grad_enabled():
+        y, new = _StateStepFn.apply(state, x, dt, A, B, C, D, z, dt_bias, softplus)
+        with torch.no_grad():
+            state.copy_(new)
+        return y
+    sc = _StepCtx(state, x, dt, A, B, C, D, z, dt_bias, softplus)
+    return _step_forward(sc, state)
+
+
+def selective_state_step_heads(
+    state: Tensor, x: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor,
+    D: Optional[Tensor] = None, z: Optional[Tensor] = None, dt_bias: Optional[Tensor] = None, softplus: bool = True,
+) -> Tensor:
+    """Extension: Mamba-2 decode step.  ``state (B, H, P, N)`` fp32 in place, ``x, z (B, H, P)``,
+    ``dt (B, H)``, ``A, D, dt_bias (H,)``, ``B, C (B, G, N)``; returns ``(B, H, P)``.  Equivalent to
+    the upstream step on ``H*P`` flattened channels with per-head parameters broadcast."""
+    if state.ndim != 4 or x.ndim != 3:
+        raise ValueError("state must be (B, H, P, N) and x (B, H, P).")
+    nb, nh, npj, nn = state.shape
+    if tuple(x.shape) != (nb, nh, npj) or tuple(dt.shape) != (nb, nh) or tuple(A.shape) != (nh,):
+        raise ValueError("x must be (B, H, P), dt (B, H) and A (H,).")
+    if B.ndim != 3 or B.shape != C.shape or B.shape[0] != nb or B.shape[2] != nn or nh % B.shape[1] != 0:
+        raise ValueError("B and C must have shape (B, G, N) with G dividing H.")
+    _need_cuda(state, x, dt, A, B, C, D, z, dt_bias)
+    if state.dtype != torch.float32 or not state.is_contiguous():
+        raise ValueError("state must be a contiguous float32 tensor.")
+    lib = L.load()
+    xs, dts = _c(x), _c(dt.to(x.dtype))
+    zs = None if z is None else _c(z.to(x.dtype))
+    Bt, Ct = _c(B), _c(C)
+    if Bt.dtype != Ct.dtype or Bt.dtype not in _CODES:
+        Bt, Ct = Bt.float(), Ct.float()
+    A32, D32, b32 = _f32(A), _f32(D), _f32(dt_bias)
+    out = torch.empty_like(xs)
+    g = Bt.shape[1]
+    a = L.StepArgs()
+    a.batch, a.dim, a.nstate, a.io_dtype = nb, nh * npj, nn, _code(x, "selective_state_step_heads")
+    a.bc_dtype, a.bc_groups, a.dt_softplus, a.param_heads = _CODES[Bt.dtype], g, int(softplus), nh
+    a.state, a.x, a.dt, a.z, a.A = _p(state), _p(xs), _p(dts), _p(zs), _p(A32)
+    a.Bm, a.Cm = _p(Bt), _p(Ct)
+    a.b_sb, a.b_sg, a.b_sn = g * nn, nn, 1
+    a.c_sb, a.c_sg, a.c_sn = g * nn, nn, 1
+    a.D, a.dt_bias, a.out = _p(D32), _p(b32), _p(out)
+    _call(lib.ssm_selective_state_step, a)
+    return out
+
+
+# =========================================================================================
+# ssd_chunk_scan (element-wise chunked recurrence)
+# =========================================================================================
+
+
+def _seq_lens(seq_meta: Optional[dict[str, Any]], nb: int, nl: int, device) -> Optional[Tensor]:
+    """Per-row valid lengths as an int64 device tensor (reference.py:413-428)."""
+    if not seq_meta:
+        return None
+    if seq_meta.get("cu_seqlens") is not None:
+        cu = torch.as_tensor(seq_meta["cu_seqlens"]).to(device=device, dtype=torch.long)
+        if cu.numel() != nb + 1:
+            raise ValueError("cu_seqlens must have length B + 1.")
+        return (cu[1:] - cu[:-1]).contiguous()
+    if seq_meta.get("seq_lens") is not None:
+        sl = torch.as_tensor(seq_meta["seq_lens"]).to(device=device, dtype=torch.long)
+        if sl.numel() != nb:
+            raise ValueError("seq_lens must have length B.")
+        return sl.contiguous()
+    raise ValueError("seq_meta must provide cu_seqlens or seq_lens.")
+
+
+def _bc4(t: Optional[Tensor], kind: str) -> tuple[Optional[int], tuple[int, int, int, int]]:
+    """Pointer and (sb, st, sh, sq) strides of a contiguous parameter of layout ``kind``."""
+    if t is None:
+        return None, (0, 0, 0, 0)
+    if kind == "h":
+        return t.data_ptr(), (0, 0, 1, 0)
+    if kind == "hp":
+        return t.data_ptr(), (0, 0, t.shape[1], 1)
+    if kind == "bhp":
+        return t.data_ptr(), (t.shape[1] * t.shape[2], 0, t.shape[2], 1)
+    if kind == "blh":
+        return t.data_ptr(), (t.shape[1] * t.shape[2], t.shape[2], 1, 0)
+    if kind == "blhp":
+        return t.data_ptr(), (t.shape[1] * t.shape[2] * t.shape[3], t.shape[2] * t.shape[3], t.shape[3], 1)
+    raise AssertionError(kind)
+
+
+def _set_bc4(dst: L.Bcast4, ptr: Optional[int], strides) -> None:
+    dst.ptr = ptr
+    dst.sb, dst.st, dst.sh, dst.sq = strides
+
+
+class _ChunkCtx:
+    def __init__(self, X, dt, A, B, C_, chunk_size, D, z, seq_meta, initial_states):
+        if X.ndim != 4:
+            raise ValueError("X must have shape (B, L, H, P).")
+        if dt.ndim != 3:
+            raise ValueError("dt must have shape (B, L, H).")
+        nb, nl, nh, npj = X.shape
+        if tuple(dt.shape) != (nb, nl, nh):
+            raise ValueError("dt must align with (B, L, H).")
+        if int(chunk_size) <= 0:
+            raise ValueError("chunk_size must be positive.")
+        _need_cuda(X, dt, A, B, C_, D, z, initial_states)
+        self.shape = (nb, nl, nh, npj)
+        self.chunk = int(chunk_size)
+        self.io = _code(X, "ssd_chunk_scan")
+        self.X, self.dt = _c(X), _c(dt.to(X.dtype))
+        if A.ndim == 1:
+            if A.shape[0] != nh:
+                raise ValueError("A must have shape (H,) when 1-D.")
+            self.A, self.kA = _f32(A), "h"
+        elif A.ndim == 2:
+            if tuple(A.shape) != (nh, npj):
+                raise ValueError("A must have shape (H, P) when 2-D.")
+            self.A, self.kA = _f32(A), "hp"
+        else:
+            raise ValueError("A must be 1-D or 2-D.")
+
+        def coeff(name, p):
+            if p.dim() == 2:
+                if tuple(p.shape) != (nh, npj):
+                    raise ValueError(f"{name} must have shape (H, P).")
+                return "hp"
+            if p.dim() == 3:
+                if tuple(p.shape) != (nb, nh, npj):
+                    raise ValueError(f"{name} must be (B, H, P) when 3-D.")
+                return "bhp"
+            if p.dim() == 4:
+                if tuple(p.shape) != (nb, nl, nh, npj):
+                    raise ValueError(f"{name} must have shape (B, L, H, P) when 4-D.")
+                return "blhp"
+            raise ValueError(f"Unsupported rank for {name}.")
+
+        self.kB, self.kC = coeff("B", B), coeff("C", C_)
+        self.kD = None
+        if D is not None:
+            if D.ndim == 1 and D.shape[0] == nh:
+                self.kD = "h"
+            elif D.ndim == 2 and tuple(D.shape) == (nh, npj):
+                self.kD = "hp"
+            else:
+                raise ValueError("D must have shape (H,) or (H, P).")
+        self.kz = None
+        if z is not None:
+            if z.ndim == 3 and tuple(z.shape) == (nb, nl, nh):
+                self.kz = "blh"
+            elif z.ndim == 4 and tuple(z.shape) == (nb, nl, nh, npj):
+                self.kz = "blhp"
+            else:
+                raise ValueError("z must have shape (B, L, H) or (B, L, H, P).")
+        if initial_states is not None and tuple(initial_states.shape) != (nb, nh, npj):
+            raise ValueError("initial_states must have shape (B, H, P).")
+        # B, C and z share one run-time dtype in the kernel
+        par = [t for t in (B, C_, z) if t is not None]
+        pd = par[0].dtype if all(t.dtype == par[0].dtype for t in par) and par[0].dtype in _CODES else torch.float32
+        self.par = _CODES[pd]
+        self.B, self.C = _c(B.to(pd)), _c(C_.to(pd))
+        self.z = None if z is None else _c(z.to(pd))
+        self.D = _f32(D)
+        self.init = _f32(initial_states)
+        self.lens = _seq_lens(seq_meta, nb, nl, X.device)
+
+    def fill(self, a: L.ChunkArgs) -> None:
+        nb, nl, nh, npj = self.shape
+        a.batch, a.len, a.heads, a.proj = nb, nl, nh, npj
+        a.io_dtype, a.par_dtype, a.chunk_size = self.io, self.par, self.chunk
+        a.X, a.dt = _p(self.X), _p(self.dt)
+        _set_bc4(a.A, *_bc4(self.A, self.kA))
+        _set_bc4(a.Bm, *_bc4(self.B, self.kB))
+        _set_bc4(a.Cm, *_bc4(self.C, self.kC))
+        _set_bc4(a.D, *_bc4(self.D, self.kD or "h"))
+        _set_bc4(a.z, *_bc4(self.z, self.kz or "blh"))
+        _set_bc4(a.initial, *_bc4(self.init, "bhp"))
+        a.seq_lens = _p(self.lens)
+
+
+def _chunk_forward(cc: _ChunkCtx, want_final: bool = False):
+    nb, nl, nh, npj = cc.shape
+    lib = L.load()
+    Y = torch.empty_like(cc.X)
+    final = torch.empty(nb, nh, npj, dtype=torch.float32, device=cc.X.device) if want_final else None
+    n = lib.ssm_chunk_scan_scratch_floats(nb, nl, nh, npj, cc.chunk)
+    scratch = torch.empty(max(int(n), 1), dtype=torch.float32, device=cc.X.device)
+    a = L.ChunkArgs()
+    cc.fill(a)
+    a.Y, a.final_state, a.scratch = _p(Y), _p(final), _p(scratch)
+    _call(lib.ssm_chunk_scan_fwd, a)
+    return Y, final
+
+
+class _ChunkScanFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, X, dt, A, B, C_, chunk_size, D, z, seq_meta, initial_states):
+        cc = _ChunkCtx(X, dt, A, B, C_, chunk_size, D, z, seq_meta, initial_states)
+        Y, _ = _chunk_forward(cc)
+        ctx.cc = cc
+        ctx.like = (dt, A, B, C_, D, z, initial_states)
+        return Y
+
+    @staticmethod
+    def backward(ctx, gY):
+        cc: _ChunkCtx = ctx.cc
+        dt, A, B, C_, D, z, init = ctx.like
+        nb, nl, nh, npj = cc.shape
+        lib = L.load()
+        dev = cc.X.device
+        zeros = lambda t: None if t is None else torch.zeros(t.shape, dtype=torch.float32, device=dev)  # noqa: E731
+        dX = torch.empty_like(cc.X)
+        ddt = torch.zeros(nb, nl, nh, dtype=torch.float32, device=dev)
+        dA, dB, dC, dD, dz, dI = zeros(cc.A), zeros(cc.B), zeros(cc.C), zeros(cc.D), zeros(cc.z), zeros(cc.init)
+        hist = torch.empty(nb, max(nl, 1), nh, npj, dtype=torch.float32, device=dev)
+        g = L.ChunkBwdArgs()
+        cc.fill(g.fwd)
+        gy = _c(gY.to(cc.X.dtype))
+        g.dY, g.dX, g.ddt, g.history = _p(gy), _p(dX), _p(ddt), _p(hist)
+        _set_bc4(g.dA, *_bc4(dA, cc.kA))
+        _set_bc4(g.dB, *_bc4(dB, cc.kB))
+        _set_bc4(g.dC, *_bc4(dC, cc.kC))
+        _set_bc4(g.dD, *_bc4(dD, cc.kD or "h"))
+        _set_bc4(g.dz, *_bc4(dz, cc.kz or "blh"))
+        _set_bc4(g.dinitial, *_bc4(dI, "bhp"))
+        _call(lib.ssm_chunk_scan_bwd, g)
+        return (
+            dX, ddt.to(dt.dtype), dA.to(A.dtype), dB.to(B.dtype), dC.to(C_.dtype), None,
+            None if D is None else dD.to(D.dtype),
+            None if z is None else dz.to(z.dtype),
+            None,
+            None if init is None else dI.to(init.dtype),
+        )
+
+
+def ssd_chunk_scan(
+    X: Tensor,
+    dt: Tensor,
+    A: Tensor,
+    B: Tensor,
+    C: Tensor,
+    chunk_size: int,
+    D: Optional[Tensor] = None,
+    z: Optional[Tensor] = None,
+    seq_meta: Optional[dict[str, Any]] = None,
+    initial_states: Optional[Tensor] = None,
+) -> Tensor:
+    """Element-wise chunked recurrence over ``(B, L, H, P)`` (upstream ``ssm.ops.ssd_chunk_scan``,
+    reference.py:312-463)."""
+    return _ChunkScanFn.apply(X, dt, A, B, C, chunk_size, D, z, seq_meta, initial_states)
+
+
+# =========================================================================================
+# dw_causal_conv
+# =========================================================================================
+
+
+class _ConvCtx:
+    def __init__(self, x, weight, bias, activation, halo=None):
+        if x.ndim != 3:
+            raise ValueError("x must have shape (B, C, L) or (B, L, C).")
+        nc = weight.shape[0]
+        if x.shape[1] == nc:
+            self.first = True
+        elif x.shape[2] == nc:
+            self.first = False
+        else:
+            raise ValueError("weight channel dimension must match x.")
+        if weight.ndim == 3:
+            if weight.shape[1] != 1:
+                raise ValueError("Expected depthwise weights with shape (C, 1, K).")
+            w2 = weight[:, 0, :]
+        elif weight.ndim == 2:
+            w2 = weight
+        else:
+            raise ValueError("weight must have 2 or 3 dimensions.")
+        if bias is not None and tuple(bias.shape) != (nc,):
+            raise ValueError("bias must have shape (C,).")
+        act = str(activation).lower()
+        if act not in ("silu", "swish", "identity", "none"):
+            raise ValueError(f"Unsupported activation '{activation}'.")
+        k = w2.shape[1]
+        if k < 1 or k > 8:
+            raise ValueError("dw_causal_conv: kernel width must be in [1, 8].")
+        _need_cuda(x, weight, bias, halo)
+        self.silu = act in ("silu", "swish")
+        self.io = _code(x, "dw_causal_conv")
+        self.x, self.w, self.b = _c(x), _f32(w2), _f32(bias)
+        self.nb = x.shape[0]
+        self.nc, self.k = nc, k
+        self.nl = x.shape[2] if self.first else x.shape[1]
+        if halo is not None and tuple(halo.shape) != (self.nb, nc, k - 1):
+            raise ValueError("halo must have shape (B, C, K-1).")
+        self.halo = _f32(halo)
+
+    def fill(self, a: L.ConvArgs) -> None:
+        a.batch, a.channels, a.len, a.width = self.nb, self.nc, self.nl, self.k
+        a.io_dtype, a.channels_first, a.silu = self.io, int(self.first), int(self.silu)
+        a.x, a.weight, a.bias, a.halo = _p(self.x), _p(self.w), _p(self.b), _p(self.halo)
+
+
+class _ConvFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, activation, halo):
+        cc = _ConvCtx(x, weight, bias, activation, halo)
+        y = torch.empty_like(cc.x)
+        a = L.ConvArgs()
+        cc.fill(a)
+        a.y = _p(y)
+        _call(L.load().ssm_dw_causal_conv_fwd, a)
+        ctx.cc, ctx.like = cc, (weight, bias)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        cc: _ConvCtx = ctx.cc
+        weight, bias = ctx.like
+        dev = cc.x.device
+        dx = torch.empty_like(cc.x)
+        dw = torch.zeros(cc.nc, cc.k, dtype=torch.float32, device=dev)
+        db = torch.zeros(cc.nc, dtype=torch.float32, device=dev) if bias is not None else None
+        g = L.ConvBwdArgs()
+        cc.fill(g.fwd)
+        go = _c(gy.to(cc.x.dtype))
+        g.dy, g.dx, g.dweight, g.dbias = _p(go), _p(dx), _p(dw), _p(db)
+        _call(L.load().ssm_dw_causal_conv_bwd, g)
+        return dx, dw.view(weight.shape).to(weight.dtype), None if bias is None else db.to(bias.dtype), None, None
+
+
+def dw_causal_conv(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, activation: str = "silu",
+                   halo: Optional[Tensor] = None) -> Tensor:
+    """Depthwise causal conv1d with optional SiLU (upstream ``ssm.ops.dw_causal_conv``,
+    reference.py:466-537).  Extension: ``halo`` ``(B, C, K-1)`` supplies the inputs that precede
+    ``t = 0`` (sequence-sharded prefill) instead of zeros; no gradient flows into it."""
+    return _ConvFn.apply(x, weight, bias, activation, halo)
+
+
+def dw_causal_conv_update(conv_state: Tensor, x: Tensor, weight: Tensor, bias: Optional[Tensor] = None,
+                          activation: str = "silu") -> Tensor:
+    """Extension: decode-time conv.  Rolls ``conv_state (B, C, K)`` (fp32, in place) left by one,
+    appends ``x (B, C)`` and returns ``act(bias + <conv_state, weight>)`` (what upstream's
+    ``Mamba1.step`` does with ``torch.roll``, modules/mamba1.py:345-353)."""
+    if conv_state.ndim != 3 or x.ndim != 2 or conv_state.shape[:2] != x.shape:
+        raise ValueError("conv_state must be (B, C, K) and x (B, C).")
+    w2 = weight[:, 0, :] if weight.ndim == 3 else weight
+    if tuple(w2.shape) != (x.shape[1], conv_state.shape[2]):
+        raise ValueError("weight must have shape (C, K).")
+    _need_cuda(conv_state, x, weight, bias)
+    if conv_state.dtype != torch.float32 or not conv_state.is_contiguous():
+        raise ValueError("conv_state must be a contiguous float32 tensor.")
+    act = str(activation).lower()
+    if act not in ("silu", "swish", "identity", "none"):
+        raise ValueError(f"Unsupported activation '{activation}'.")
+    xs, w32, b32 = _c(x), _f32(w2), _f32(bias)
+    out = torch.empty_like(xs)
+    a = L.ConvUpdateArgs()
+    a.batch, a.channels, a.width, a.io_dtype = x.shape[0], x.shape[1], conv_state.shape[2], _code(x, "dw_causal_conv_update")
+    a.silu = int(act in ("silu", "swish"))
+    a.conv_state, a.x, a.weight, a.bias, a.out = _p(conv_state), _p(xs), _p(w32), _p(b32), _p(out)
+    _call(L.load().ssm_dw_causal_conv_update, a)
+    return out
+
+
+# =========================================================================================
+# fused_layer_norm
+# =========================================================================================
+
+
+class _NormCtx:
+    def __init__(self, x, weight, bias, residual, is_rms, eps, prenorm):
+        if x.ndim != 3:
+            raise ValueError("x must have shape (B, L, D).")
+        if tuple(weight.shape) != (x.shape[-1],):
+            raise ValueError("weight must match the last dimension of x.")
+        if bias is not None and tuple(bias.shape) != (x.shape[-1],):
+            raise ValueError("bias must match the last dimension of x.")
+        if residual is not None and residual.shape != x.shape:
+            raise ValueError("residual must match the shape of x.")
+        _need_cuda(x, weight, bias, residual)
+        self.io = _code(x, "fused_layer_norm")
+        self.x, self.w, self.b = _c(x), _f32(weight), _f32(bias)
+        self.res = _c(residual)
+        if self.res is not None:
+            _code(self.res, "fused_layer_norm residual")
+        self.is_rms, self.eps, self.prenorm = bool(is_rms), float(eps), bool(prenorm)
+
+    def fill(self, a: L.NormArgs) -> None:
+        a.rows, a.hidden = self.x.shape[0] * self.x.shape[1], self.x.shape[2]
+        a.io_dtype = self.io
+        a.res_dtype = _CODES[self.res.dtype] if self.res is not None else 0
+        a.is_rms, a.prenorm, a.eps = int(self.is_rms), int(self.prenorm), self.eps
+        a.x, a.residual, a.weight, a.bias = _p(self.x), _p(self.res), _p(self.w), _p(self.b)
+
+
+class _NormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual, is_rms, eps, prenorm, return_residual, residual_dtype):
+        nc = _NormCtx(x, weight, bias, residual, is_rms, eps, prenorm)
+        y = torch.empty_like(nc.x)
+        ro = torch.empty(nc.x.shape, dtype=residual_dtype, device=nc.x.device) if return_residual else None
+        a = L.NormArgs()
+        nc.fill(a)
+        a.y, a.residual_out = _p(y), _p(ro)
+        a.resout_dtype = _CODES[residual_dtype] if return_residual else 0
+        _call(L.load().ssm_fused_add_norm_fwd, a)
+        ctx.nc, ctx.like = nc, (weight, bias, residual)
+        if return_residual:
+            ctx.mark_non_differentiable(ro)
+            return y, ro
+        return y
+
+    @staticmethod
+    def backward(ctx, gy, *unused):
+        nc: _NormCtx = ctx.nc
+        weight, bias, residual = ctx.like
+        lib = L.load()
+        dev = nc.x.device
+        hidden = nc.x.shape[2]
+        rows = nc.x.shape[0] * nc.x.shape[1]
+        dx = torch.empty_like(nc.x)
+        dres = torch.empty_like(nc.res) if nc.res is not None else None
+        dw = torch.empty(hidden, dtype=torch.float32, device=dev)
+        db = torch.empty(hidden, dtype=torch.float32, device=dev) if bias is not None else None
+        partial = torch.empty(int(lib.ssm_norm_bwd_scratch_floats(rows, hidden)), dtype=torch.float32, device=dev)
+        g = L.NormBwdArgs()
+        nc.fill(g.fwd)
+        go = _c(gy.to(nc.x.dtype))
+        g.dy, g.dx, g.dresidual, g.dweight, g.dbias, g.partial = _p(go), _p(dx), _p(dres), _p(dw), _p(db), _p(partial)
+        _call(lib.ssm_fused_add_norm_bwd, g)
+        return (
+            dx, dw.to(weight.dtype), None if bias is None else db.to(bias.dtype),
+            None if residual is None else dres.to(residual.dtype),
+            None, None, None, None, None,
+        )
+
+
+def fused_layer_norm(
+    x: Tensor,
+    weight: Tensor,
+    bias: Optional[Tensor],
+    residual: Optional[Tensor] = None,
+    is_rms: bool = False,
+    eps: float = 1e-5,
+    prenorm: bool = True,
+    residual_in_fp32: bool = True,
+    return_residual: bool = False,
+):
+    """Residual add fused with LayerNorm / RMSNorm (upstream ``ssm.ops.fused_layer_norm``,
+    reference.py:540-609).  All arithmetic is fp32, which is what upstream does for fp32, bf16
+    and fp16 inputs whatever ``residual_in_fp32`` says.  Extension: ``return_residual`` also
+    returns ``x + residual`` (fp32 when ``residual_in_fp32``, else ``x.dtype``); that second
+    output is not differentiable."""
+    rd = torch.float32 if residual_in_fp32 else x.dtype
+    return _NormFn.apply(x, weight, bias, residual, is_rms, eps, prenorm, return_residual, rd)
+
+
+__all__ = [
+    "selective_scan",
+    "selective_state_step",
+    "selective_state_step_heads",
+    "ssd_chunk_scan",
+    "dw_causal_conv",
+    "dw_causal_conv_update",
+    "fused_layer_norm",
+]

@@ -1,0 +1,102 @@
+"""GPU parity against the golden fixtures (upstream's own vectors and recorded runs of
+upstream's Python operators): outputs, final states and gradients, through the C ABI."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from tests.fixtures import cases, tol
+from tests.gpu_util import close, leaf
+
+pytestmark = pytest.mark.gpu
+
+PACKS = ("upstream_kats", "reference_runs")
+
+
+def _all(family):
+    return [pytest.param(c, id=f"{p}:{c.name}") for p in PACKS for c in cases(p, family)]
+
+
+def _grads(case, outs, weights, leaves):
+    if not case.grads:
+        return
+    live = {k: v for k, v in leaves.items() if v is not None and k in case.grads and v.requires_grad}
+    total = sum((o.float() * w.float().cuda()).sum() for o, w in zip(outs, weights))
+    got = torch.autograd.grad(total, list(live.values()), allow_unused=True)
+    for (k, _), g in zip(live.items(), got):
+        assert g is not None, f"no gradient for {k}"
+        close(g, case.grads[k], **tol(case, grad=True), what=f"{case.name} d{k}")
+
+
+@pytest.mark.parametrize("case", _all("scan"))
+def test_selective_scan(case):
+    from ssm_b200 import ops
+
+    i = {k: leaf(v) for k, v in case.ins.items()}
+    y, last = ops.selective_scan(i["u"], i["delta"], i["A"], i["B"], i["C"], D=i.get("D"), z=i.get("z"),
+                                 dt_bias=i.get("dt_bias"), softplus=case.opts["softplus"], return_last_state=True)
+    assert y.dtype == i["u"].dtype and last.dtype == i["u"].dtype
+    close(y, case.outs["out"], **tol(case), what=f"{case.name} out")
+    if "last_state" in case.outs:
+        close(last, case.outs["last_state"], **tol(case), what=f"{case.name} last_state")
+    if "grad_out" in case.ins:
+        _grads(case, (y, last), (case.ins["grad_out"], case.ins["grad_last_state"]), i)
+    else:
+        _grads(case, (y,), (torch.ones_like(y),), i)
+
+
+@pytest.mark.parametrize("case", _all("step"))
+def test_selective_state_step(case):
+    from ssm_b200 import ops
+
+    i = {k: leaf(v, grad=False) for k, v in case.ins.items()}
+    y = ops.selective_state_step(i["state"], i["x"], i["dt"], i["A"], i["B"], i["C"], D=i.get("D"), z=i.get("z"),
+                                 dt_bias=i.get("dt_bias"), softplus=case.opts["softplus"])
+    close(y, case.outs["y"], **tol(case), what=f"{case.name} y")
+    close(i["state"], case.outs["state"], **tol(case), what=f"{case.name} state")
+
+
+@pytest.mark.parametrize("case", _all("chunk"))
+def test_ssd_chunk_scan(case):
+    from ssm_b200 import ops
+
+    i = {k: leaf(v) for k, v in case.ins.items()}
+    meta = None
+    if "cu_seqlens" in i:
+        meta = {"cu_seqlens": i["cu_seqlens"]}
+    elif "seq_lens" in i:
+        meta = {"seq_lens": i["seq_lens"]}
+    Y = ops.ssd_chunk_scan(i["X"], i["dt"], i["A"], i["B"], i["C"], case.opts["chunk_size"], D=i.get("D"), z=i.get("z"),
+                           seq_meta=meta, initial_states=i.get("initial_states"))
+    close(Y, case.outs["Y"], **tol(case), what=f"{case.name} Y")
+    if "grad_out" in case.ins:
+        _grads(case, (Y,), (case.ins["grad_out"],), i)
+
+
+@pytest.mark.parametrize("case", _all("conv"))
+def test_dw_causal_conv(case):
+    from ssm_b200 import ops
+
+    i = {k: leaf(v) for k, v in case.ins.items()}
+    y = ops.dw_causal_conv(i["x"], i["weight"], bias=i.get("bias"), activation=case.opts["activation"])
+    assert y.shape == i["x"].shape and y.dtype == i["x"].dtype
+    close(y, case.outs["y"], **tol(case), what=f"{case.name} y")
+    w = case.ins["grad_out"] if "grad_out" in case.ins else torch.ones_like(y)
+    _grads(case, (y,), (w,), i)
+
+
+@pytest.mark.parametrize("case", _all("norm"))
+def test_fused_layer_norm(case):
+    from ssm_b200 import ops
+
+    i = {k: leaf(v) for k, v in case.ins.items()}
+    o = case.opts
+    y, res = ops.fused_layer_norm(i["x"], i["weight"], i.get("bias"), residual=i.get("residual"), is_rms=o["is_rms"],
+                                  eps=o["eps"], prenorm=o["prenorm"], residual_in_fp32=o.get("residual_in_fp32", True),
+                                  return_residual=True)
+    close(y, case.outs["y"], **tol(case), what=f"{case.name} y")
+    if "residual_out" in case.outs:
+        close(res, case.outs["residual_out"], **tol(case), what=f"{case.name} residual_out")
+    w = case.ins["grad_out"] if "grad_out" in case.ins else torch.ones_like(y)
+    _grads(case, (y,), (w,), i)
