@@ -307,6 +307,28 @@ typedef struct {
 int64_t ssm_norm_bwd_scratch_floats(int64_t rows, int32_t hidden);
 int ssm_fused_add_norm_bwd(const ssm_norm_bwd_args* args, ssm_stream_t stream);
 
+/* Backward of the fused add + norm for callers that are not allowed to allocate device memory
+ * (it has no counterpart in the upstream package).  Code that runs inside someone else's memory
+ * plan -- an inference server that hands out one fixed arena at start-up, a plugin that must not
+ * touch the CUDA allocator of its host process, a real-time loop that cannot risk the implicit
+ * synchronisation of cudaMalloc / cudaFree -- cannot provide the `partial` scratch that
+ * ssm_fused_add_norm_bwd needs.  This entry point computes the same result but keeps that
+ * scratch in a fixed array inside the library's own device image: `args->partial` is ignored
+ * and neither this call nor anything it launches allocates or frees memory.
+ *
+ * Limits and rules:
+ *  - hidden <= 8192 (larger rows are rejected with SSM_ERR_TOO_LARGE); the array takes
+ *    9.25 MiB on every GPU that loads the library, for the life of the process;
+ *  - the first call on each device looks up the array's device address (with that device
+ *    current) and remembers it; make that first call outside any stream capture;
+ *  - all calls on a device share the one array.  Nothing in it has to start at zero (every
+ *    launch overwrites the part it later reads), but two calls whose kernels overlap on
+ *    the GPU (different streams, no ordering) race on it: serialise them on one stream or
+ *    with events;
+ *  - weight / bias gradients are summed over at most 148 partial rows instead of up to 592, so
+ *    they can differ from ssm_fused_add_norm_bwd in the last bits; dx / dresidual are identical. */
+int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* args, ssm_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

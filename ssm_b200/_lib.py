@@ -135,6 +135,7 @@ ENTRY_POINTS = {
     "ssm_fused_add_norm_fwd": (C.c_int, [C.POINTER(NormArgs), vp]),
     "ssm_norm_bwd_scratch_floats": (C.c_int64, [i64, i32]),
     "ssm_fused_add_norm_bwd": (C.c_int, [C.POINTER(NormBwdArgs), vp]),
+    "ssm_fused_add_norm_bwd_noalloc": (C.c_int, [C.POINTER(NormBwdArgs), vp]),
 }
 
 _lib = None

@@ -8,6 +8,8 @@
 // gradient of its own columns in registers across all rows its CTA visits, the CTA writes
 // one partial row, and a second small kernel folds the partials -- no atomics, bitwise
 // reproducible.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ssmb {
@@ -486,6 +488,79 @@ static int norm_bwd_t(const ssm_norm_bwd_args& g, cudaStream_t st) {
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Backward variant for callers that must not allocate device memory.
+//
+// The persistent backward kernel needs a scratch area for its per-CTA partial weight / bias
+// gradients.  Here that area is a fixed array that lives in the library's device image, so
+// the call performs no cudaMalloc / cudaFree and asks no allocator for anything.  The price
+// is a fixed capacity (hidden <= kNoAllocMaxHidden, at most kNoAllocCtas partial rows) and
+// 9.25 MiB of device memory held on every GPU that loads the library until the process ends.
+// ---------------------------------------------------------------------------------------
+constexpr int kNoAllocMaxHidden = 8192;
+constexpr int kNoAllocCtas = 148;  // one partial row per SM
+constexpr size_t kNoAllocFloats = (size_t)2 * kNoAllocMaxHidden * kNoAllocCtas;
+static __device__ __align__(256) float g_norm_noalloc_scratch[kNoAllocFloats];
+
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_noalloc_addr[kNoAllocMaxDevices];  // device address of the array, per device; set once
+static std::mutex g_noalloc_mutex;
+
+// In host code the array's name is only a handle: the address a kernel can use has to be
+// asked for, per device, with that device current.
+static int noalloc_scratch_address(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    set_error("fused_layer_norm_backward_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return fail(SSM_ERR_UNSUPPORTED, "fused_layer_norm_backward_noalloc: device index out of range");
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_norm_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("fused_layer_norm_backward_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : SSM_ERR_DEVICE;
+    }
+    g_noalloc_addr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_addr[dev];
+  return SSM_OK;
+}
+
+template <typename T, int G>
+static int norm_bwd_launch_capped(const ssm_norm_bwd_args& g, cudaStream_t st, int max_ctas) {
+  using Cfg = NormCfg<T, G>;
+  int nctas = norm_bwd_ctas(g.fwd, Cfg::RPC);
+  if (nctas > max_ctas) nctas = max_ctas;
+  norm_bwd_kernel<T, G><<<nctas, Cfg::BLOCK, 0, st>>>(g);
+  if (int rc = launch_status("norm_bwd_kernel")) return rc;
+  norm_fold_kernel<<<(g.fwd.hidden + 127) / 128, 128, 0, st>>>(g.partial, nctas, g.fwd.hidden, g.dweight, g.dbias);
+  return launch_status("norm_fold_kernel");
+}
+
+template <typename T>
+static int norm_bwd_noalloc_t(const ssm_norm_bwd_args& g, float* scratch, cudaStream_t st) {
+  const ssm_norm_args& a = g.fwd;
+  if (!norm_vec_ok(a, kNormBwdChunks, g.dy, g.dx, g.dresidual)) {
+    // rows that cannot be vectorised take the scalar kernel, which needs no scratch at all
+    cudaMemsetAsync(g.dweight, 0, sizeof(float) * a.hidden, st);
+    if (g.dbias) cudaMemsetAsync(g.dbias, 0, sizeof(float) * a.hidden, st);
+    norm_scalar_kernel<T, true><<<(unsigned)a.rows, 128, 0, st>>>(g);
+    return launch_status("norm_scalar_kernel");
+  }
+  ssm_norm_bwd_args h = g;
+  h.partial = scratch;
+  switch (norm_group(a, kNormBwdChunks)) {
+    case 32: return norm_bwd_launch_capped<T, 32>(h, st, kNoAllocCtas);
+    case 128: return norm_bwd_launch_capped<T, 128>(h, st, kNoAllocCtas);
+    default: return norm_bwd_launch_capped<T, 512>(h, st, kNoAllocCtas);
+  }
+}
+
 }  // namespace ssmb
 
 using namespace ssmb;
@@ -524,5 +599,29 @@ extern "C" int ssm_fused_add_norm_bwd(const ssm_norm_bwd_args* g, ssm_stream_t s
     case SSM_F32: return norm_bwd_t<float>(*g, st);
     case SSM_BF16: return norm_bwd_t<__nv_bfloat16>(*g, st);
     default: return norm_bwd_t<__half>(*g, st);
+  }
+}
+
+extern "C" int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* g, ssm_stream_t stream) {
+  SSM_REQUIRE(g != nullptr, SSM_ERR_NULL, "fused_layer_norm_backward_noalloc: args is NULL");
+  const ssm_norm_args* a = &g->fwd;
+  if (int rc = norm_validate(a)) return rc;
+  SSM_REQUIRE(a->hidden <= kNoAllocMaxHidden, SSM_ERR_TOO_LARGE,
+              "fused_layer_norm_backward_noalloc: hidden exceeds the built-in scratch capacity (8192); use ssm_fused_add_norm_bwd");
+  SSM_REQUIRE(g->dweight, SSM_ERR_NULL, "fused_layer_norm_backward_noalloc: dweight is required");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (a->rows == 0) {
+    cudaMemsetAsync(g->dweight, 0, sizeof(float) * a->hidden, st);
+    if (g->dbias) cudaMemsetAsync(g->dbias, 0, sizeof(float) * a->hidden, st);
+    return SSM_OK;
+  }
+  SSM_REQUIRE(a->x && a->weight && g->dy && g->dx, SSM_ERR_NULL, "fused_layer_norm_backward_noalloc: missing pointer");
+  SSM_REQUIRE(a->residual || !g->dresidual, SSM_ERR_NULL, "fused_layer_norm_backward_noalloc: dresidual without residual");
+  float* scratch = nullptr;
+  if (int rc = noalloc_scratch_address(&scratch)) return rc;
+  switch (a->io_dtype) {
+    case SSM_F32: return norm_bwd_noalloc_t<float>(*g, scratch, st);
+    case SSM_BF16: return norm_bwd_noalloc_t<__nv_bfloat16>(*g, scratch, st);
+    default: return norm_bwd_noalloc_t<__half>(*g, scratch, st);
   }
 }
