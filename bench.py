@@ -116,7 +116,7 @@ def make_weights(cfg, device, dtype, seed=0):
         return (torch.randn(o, i, generator=g) / i ** 0.5).to(dtype)
 
     w = dict(
-        in_proj=lin(2 * di, dm), conv_w=(torch.rand(di, k, generator=g) - 0.5).to(dtype), conv_b=torch.zeros(di, dtype=dtype),
+        in_x=lin(di, dm), in_z=lin(di, dm), conv_w=(torch.rand(di, k, generator=g) - 0.5).to(dtype), conv_b=torch.zeros(di, dtype=dtype),
         x_proj=lin(r + 2 * n, di), dt_proj=lin(di, r),
         dt_bias=(torch.rand(di, generator=g) * 2 - 4).float(),  # softplus^-1 of a small positive step
         A=(-torch.exp(torch.randn(di, n, generator=g) * 0.5)).float(), D=torch.randn(di, generator=g).float(),
@@ -128,16 +128,16 @@ def make_weights(cfg, device, dtype, seed=0):
 def block_forward(ops, w, cfg, hidden, residual):
     """hidden (B, L, d_model) activations, residual (B, L, d_model) fp32 stream -> (normed, new_residual)."""
     n, r = cfg["d_state"], cfg["dt_rank"]
-    xz = torch.matmul(w["in_proj"], hidden.transpose(1, 2))           # (B, 2*Di, L)
-    x, z = xz.chunk(2, dim=1)
-    u = ops.dw_causal_conv(x.contiguous(), w["conv_w"], w["conv_b"], "silu")
+    ht = hidden.transpose(1, 2)
+    x = torch.matmul(w["in_x"], ht)                                    # (B, Di, L): the two halves of in_proj
+    z = torch.matmul(w["in_z"], ht)
+    u = ops.dw_causal_conv(x, w["conv_w"], w["conv_b"], "silu")
     x_dbl = torch.matmul(w["x_proj"], u)                               # (B, R + 2N, L)
     dt_low, Bm, Cm = torch.split(x_dbl, [r, n, n], dim=1)
     delta = torch.matmul(w["dt_proj"], dt_low)                         # (B, Di, L)
-    y = ops.selective_scan(u, delta, w["A"], Bm.unsqueeze(1), Cm.unsqueeze(1), D=w["D"], z=z.contiguous(), dt_bias=w["dt_bias"],
-                           softplus=True)
-    out = torch.matmul(w["out_proj"], y).transpose(1, 2)              # (B, L, d_model)
-    return ops.fused_layer_norm(out.contiguous(), w["norm_w"], None, residual=residual, is_rms=True, eps=1e-5, prenorm=True,
+    y = ops.selective_scan(u, delta, w["A"], Bm.unsqueeze(1), Cm.unsqueeze(1), D=w["D"], z=z, dt_bias=w["dt_bias"], softplus=True)
+    out = torch.matmul(y.transpose(1, 2), w["out_proj"].t())          # (B, L, d_model)
+    return ops.fused_layer_norm(out, w["norm_w"], None, residual=residual, is_rms=True, eps=1e-5, prenorm=True,
                                 residual_in_fp32=True, return_residual=True)
 
 
@@ -197,6 +197,8 @@ def run_gpu(args):
 
     _lib.load()
     cfg = dict(CFG)
+    if args.batch:
+        cfg["batch"] = args.batch
     B, Lq, dm = cfg["batch"], cfg["seqlen"], cfg["d_model"]
     w = make_weights(cfg, dev, torch.bfloat16, seed=0)
     timer = KernelTimer()
@@ -304,7 +306,7 @@ def run_gpu(args):
         "metric": "tokens_per_s", "value": tokens / (ms_dev * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 I/O, fp32 state", "data": "synthetic (seeded N(0,1) activations, random-init weights)",
-        "config": {"workload": "mamba1_block fwd+bwd: batch 8/GPU, seqlen 4096, d_model 768, d_inner 1536, d_state 16, d_conv 4, "
+        "config": {"workload": f"mamba1_block fwd+bwd: batch {B}/GPU, seqlen 4096, d_model 768, d_inner 1536, d_state 16, d_conv 4, "
                                "dt_rank 48, RMSNorm eps 1e-5", "parallelism": f"dp{world} (batch replicas, no collective)",
                    "l2": "per-step working set (>1 GB) exceeds the 126 MB L2; inputs alternate between two buffers"},
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
@@ -382,6 +384,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling on a smaller case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -115,6 +115,28 @@ __device__ __forceinline__ float exp_fast(float x) { return ex2_approx(x * kLog2
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// softplus(x) = max(x, 0) + log1p(exp(-|x|)) on the special-function unit.  For small
+// t = exp(-|x|) the series t - t^2/2 + t^3/3 - t^4/4 replaces log(1 + t), whose argument would lose
+// t's low bits; relative error stays below 4e-6 over the whole range.  Above the switch point
+// of torch.nn.functional.softplus (20) the correction is below half an ulp of x, so the
+// result equals x there as well.
+__device__ __forceinline__ float softplus_fast(float x) {
+  const float t = ex2_approx(-fabsf(x) * kLog2e);
+  const float series = t * fmaf(t, fmaf(t, fmaf(t, -0.25f, 0.33333334f), -0.5f), 1.f);
+  const float l = t < 0.0625f ? series : lg2_approx(1.f + t) * kLn2;
+  return fmaxf(x, 0.f) + l;
+}
+// 1 - exp(-x) for x >= 0 without cancellation for small x (it is sigmoid(pre) when
+// x = softplus(pre), i.e. the derivative of softplus).
+__device__ __forceinline__ float one_minus_exp_neg(float x) {
+  const float series = x * fmaf(x, fmaf(x, fmaf(x, -0.041666668f, 0.16666667f), -0.5f), 1.f);
+  return x < 0.0625f ? series : 1.f - ex2_approx(-x * kLog2e);
+}
 // SiLU through the special-function unit: x * rcp(1 + 2^(-x*log2e)); relative error ~1e-6.
 __device__ __forceinline__ float silu_fast(float x) { return x * rcp_approx(1.f + ex2_approx(-x * kLog2e)); }
 __device__ __forceinline__ float sigmoid_fast(float x) { return rcp_approx(1.f + ex2_approx(-x * kLog2e)); }

@@ -1,0 +1,7 @@
+// Instantiates the selective-scan backward kernels for __nv_bfloat16 activations (one element type per
+// translation unit so that the variants compile in parallel).
+#include "selective_scan_bwd.cuh"
+
+namespace ssmb {
+template int dispatch_bwd<__nv_bfloat16>(const ssm_scan_bwd_args&, const ScanFlags&, cudaStream_t);
+}  // namespace ssmb
