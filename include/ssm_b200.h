@@ -329,6 +329,50 @@ int ssm_fused_add_norm_bwd(const ssm_norm_bwd_args* args, ssm_stream_t stream);
  *    they can differ from ssm_fused_add_norm_bwd in the last bits; dx / dresidual are identical. */
 int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* args, ssm_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------
+ * State-space-dual scan with a d_state axis (Mamba-2), forward, on the tcgen05 tensor cores.
+ * Upstream has no operator of this shape (its ssd_chunk_scan has no state axis,
+ * src/ssm/ops/python/reference.py:312-463); the semantics are those of its selective_scan
+ * (reference.py:87-194) on channel h*P+p with delta[b,h*P+p,t] = dt[b,t,h], A[h*P+p,:] = A[h]
+ * and B, C shared per group, the final state being selective_scan's last state kept in fp32.
+ *
+ * X, z, Y: (batch, len, heads, headdim) io_dtype.  dt: (batch, len, heads) io_dtype.  A: (heads)
+ * fp32.  Bm, Cm: (batch, len, groups, nstate) io_dtype.  D: (heads) or, with d_has_p,
+ * (heads, headdim) fp32, nullable.  dt_bias: (heads) fp32, nullable.  initial_states /
+ * final_states: (batch, heads, headdim, nstate) fp32, nullable.  Built for headdim 64,
+ * nstate 128, chunk_size 256, bf16 / fp16 (ssm_ssd_supported()).  Scratch, in this order, is
+ * carved by the caller from one buffer of ssm_ssd_scratch_bytes() bytes:
+ *   ws_dt, ws_cum : (batch, heads, nchunks * 256) fp32 each
+ *   ws_state      : (batch, nchunks, heads, headdim, nstate) fp32
+ *   ws_state_in   : the same shape in io_dtype
+ * status: optional device int, set non-zero when a bounded device-side wait ran out.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t batch, len, heads, headdim;
+  int32_t nstate, groups, chunk_size, io_dtype;
+  int32_t dt_softplus, d_has_p, reserved0, reserved1;
+  const void* X;
+  const void* dt;
+  const float* A;
+  const void* Bm;
+  const void* Cm;
+  const float* D;              /* nullable */
+  const void* z;               /* nullable */
+  const float* dt_bias;        /* nullable */
+  const float* initial_states; /* nullable */
+  void* Y;
+  float* final_states; /* nullable */
+  float* ws_dt;
+  float* ws_cum;
+  float* ws_state;
+  void* ws_state_in;
+  int32_t* status; /* nullable */
+} ssm_ssd_args;
+
+int ssm_ssd_supported(int32_t headdim, int32_t nstate, int32_t chunk_size, int32_t io_dtype);
+int64_t ssm_ssd_scratch_bytes(int32_t batch, int32_t len, int32_t heads);
+int ssm_ssd_fwd(const ssm_ssd_args* args, ssm_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -117,6 +117,17 @@ class NormBwdArgs(C.Structure):
     _fields_ = [("fwd", NormArgs), ("dy", vp), ("dx", vp), ("dresidual", vp), ("dweight", fp), ("dbias", fp), ("partial", fp)]
 
 
+class SsdArgs(C.Structure):
+    _fields_ = [
+        ("batch", i32), ("len", i32), ("heads", i32), ("headdim", i32),
+        ("nstate", i32), ("groups", i32), ("chunk_size", i32), ("io_dtype", i32),
+        ("dt_softplus", i32), ("d_has_p", i32), ("reserved0", i32), ("reserved1", i32),
+        ("X", vp), ("dt", vp), ("A", fp), ("Bm", vp), ("Cm", vp), ("D", fp), ("z", vp), ("dt_bias", fp),
+        ("initial_states", fp), ("Y", vp), ("final_states", fp),
+        ("ws_dt", fp), ("ws_cum", fp), ("ws_state", fp), ("ws_state_in", vp), ("status", vp),
+    ]
+
+
 # entry point -> (restype, argtypes); every name here is declared in include/ssm_b200.h
 ENTRY_POINTS = {
     "ssm_b200_abi_version": (C.c_int, []),
@@ -136,6 +147,9 @@ ENTRY_POINTS = {
     "ssm_norm_bwd_scratch_floats": (C.c_int64, [i64, i32]),
     "ssm_fused_add_norm_bwd": (C.c_int, [C.POINTER(NormBwdArgs), vp]),
     "ssm_fused_add_norm_bwd_noalloc": (C.c_int, [C.POINTER(NormBwdArgs), vp]),
+    "ssm_ssd_supported": (C.c_int, [i32, i32, i32, i32]),
+    "ssm_ssd_scratch_bytes": (C.c_int64, [i32, i32, i32]),
+    "ssm_ssd_fwd": (C.c_int, [C.POINTER(SsdArgs), vp]),
 }
 
 _lib = None

@@ -1,0 +1,445 @@
+// State-space-dual (Mamba-2) chunked scan with a d_state axis, forward, for sm_100a.
+//
+//   delta_t = softplus?(dt_t + dt_bias);  S_t = exp(delta_t A) S_{t-1} + delta_t x_t B_t^T;  y_t = S_t C_t + D x_t;  y_t *= silu(z_t)
+//
+// evaluated chunk by chunk (Q = 256 steps) in the dual, matrix form, with every contraction on
+// the tcgen05 tensor cores (bf16 / fp16 operands from shared memory, fp32 accumulators in TMEM):
+//
+//   ssd_cumsum_kernel   delta and its running log-decay  cum_i = sum_{k<=i} delta_k A  per chunk
+//   ssd_state_kernel    per (batch, chunk, head): local state  S_c = sum_j exp(cum_last - cum_j) delta_j x_j B_j^T   [N x P GEMM, K = Q]
+//   ssd_pass_kernel     the short serial pass over chunks: incoming state of every chunk (kept in
+//                       the operand dtype for the GEMM below) and the final state in fp32
+//   ssd_scan_kernel     per (batch, chunk, head, 128-row block):  G = C B^T  (TMEM), the decay mask
+//                       exp(cum_i - cum_j) delta_j [j <= i] applied on the TMEM -> register path and
+//                       re-packed as the A operand of  Y_intra = (G o L) X, plus  Y_inter = C S_in;
+//                       y = Y_intra + exp(cum_i) Y_inter + D x, gated, stored.
+//
+// Exponent differences are always formed before exp (never exp(cum_i) / exp(cum_j)), so long
+// sequences stay finite.  Every wait on an mbarrier is bounded and reports through the status word.
+#include <type_traits>
+
+#include "common.cuh"
+#include "tc05.cuh"
+
+namespace ssmb {
+
+constexpr int kQ = 256;    // chunk length
+constexpr int kP = 64;     // head dimension
+constexpr int kN = 128;    // state dimension
+constexpr int kBlk = 128;  // rows per scan CTA
+
+// ---------------------------------------------------------------------------------------------
+// delta and within-chunk cumulative log-decay; one warp per (batch, head, chunk)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, int nchunks) {
+  const int warp = (blockIdx.x * 128 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int total = a.batch * a.heads * nchunks;
+  if (warp >= total) return;
+  const int c = warp % nchunks, h = (warp / nchunks) % a.heads, b = warp / (nchunks * a.heads);
+  const float Ah = __ldg(a.A + h);
+  const float bias = a.dt_bias ? __ldg(a.dt_bias + h) : 0.f;
+  const T* dt = reinterpret_cast<const T*>(a.dt);
+  float* odt = a.ws_dt + ((int64_t)b * a.heads + h) * nchunks * kQ + (int64_t)c * kQ;
+  float* ocum = a.ws_cum + ((int64_t)b * a.heads + h) * nchunks * kQ + (int64_t)c * kQ;
+  float d[kQ / 32], run = 0.f;
+#pragma unroll
+  for (int k = 0; k < kQ / 32; ++k) {
+    const int i = lane * (kQ / 32) + k;  // each lane owns 8 consecutive steps
+    const int t = c * kQ + i;
+    float v = 0.f;
+    if (t < a.len) {
+      v = to_f<T>(dt[((int64_t)b * a.len + t) * a.heads + h]) + bias;
+      if (a.dt_softplus) v = softplus_f(v);
+    }
+    d[k] = v;
+    run += v * Ah;
+  }
+  // exclusive prefix of the lane sums
+  float pre = run;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const float o = __shfl_up_sync(0xffffffffu, pre, off);
+    if (lane >= off) pre += o;
+  }
+  float acc = pre - run;
+#pragma unroll
+  for (int k = 0; k < kQ / 32; ++k) {
+    const int i = lane * (kQ / 32) + k;
+    acc += d[k] * Ah;
+    odt[i] = d[k];
+    ocum[i] = acc;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// local chunk states on the tensor cores:  S[n][p] = sum_j B[j][n] * (w_j x[j][p])
+//   A operand = B^T, MN-major [n/8][j][8];  B operand = w x, MN-major [p/8][j][8];  M = 128 (n), N = 64 (p), K = 256 (j)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) ssd_state_kernel(const ssm_ssd_args a, int nchunks) {
+  extern __shared__ __align__(128) unsigned char smraw[];
+  T* sA = reinterpret_cast<T*>(smraw);                       // 16 x 256 units of 16 bytes = 64 KB
+  T* sB = reinterpret_cast<T*>(smraw + (kN / 8) * kQ * 16);   //  8 x 256 units           = 32 KB
+  __shared__ __align__(8) uint64_t mbar;
+  __shared__ uint32_t tmem_slot;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (a.heads / a.groups);
+  const int t0 = c * kQ;
+
+  if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), 64);
+  if (tid == 0) tc::mbar_init(tc::smem_u32(&mbar), 1);
+
+  // ---- B^T tile: raw 16-byte units, step index fastest across threads -----------------------
+  const T* Bg = reinterpret_cast<const T*>(a.Bm);
+  for (int id = tid; id < (kN / 8) * kQ; id += 128) {
+    const int nc = id / kQ, j = id % kQ;
+    const int t = t0 + j;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < a.len) v = __ldg(reinterpret_cast<const uint4*>(Bg + (((int64_t)b * a.len + t) * a.groups + g) * kN + nc * 8));
+    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(sA) + ((size_t)nc * kQ + j) * 16) = v;
+  }
+  // ---- x tile scaled by w_j = exp(cum_last - cum_j) * delta_j ---------------------------------
+  const float* wdt = a.ws_dt + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
+  const float* wcum = a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
+  const float cum_last = __ldg(wcum + kQ - 1);
+  const T* Xg = reinterpret_cast<const T*>(a.X);
+  for (int id = tid; id < (kP / 8) * kQ; id += 128) {
+    const int pc = id / kQ, j = id % kQ;
+    const int t = t0 + j;
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = 0.f;
+    if (t < a.len) {
+      Vec16<T> v;
+      v.load(Xg + (((int64_t)b * a.len + t) * a.heads + h) * kP + pc * 8);
+      v.unpack(f);
+      const float w = exp_fast(cum_last - __ldg(wcum + j)) * __ldg(wdt + j);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] *= w;
+    }
+    Vec16<T> o;
+    o.pack(f);
+    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(sB) + ((size_t)pc * kQ + j) * 16) = o.raw;
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+
+  if (tid == 0) {
+    constexpr uint32_t idesc = tc::instr_desc(kN, kP, std::is_same<T, __nv_bfloat16>::value ? 1 : 0, 1, 1);
+    const uint32_t a0 = tc::smem_u32(sA), b0 = tc::smem_u32(sB);
+#pragma unroll 1
+    for (int kk = 0; kk < kQ / 16; ++kk) {
+      const uint64_t da = tc::smem_desc(a0 + kk * 256, 128, kQ * 16);  // two groups of 8 steps = 256 bytes per instruction
+      const uint64_t db = tc::smem_desc(b0 + kk * 256, 128, kQ * 16);
+      tc::mma_ss(tmem, da, db, idesc, kk > 0);
+    }
+    tc::commit(tc::smem_u32(&mbar));
+  }
+  const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar), 0));  // warp-uniform
+  tc::fence_after_sync();
+  if (!ok && a.status) atomicExch(a.status, 1);
+
+  // ---- TMEM -> global: thread = state n, 64 columns = p ---------------------------------------
+  if (ok) {
+    float* out = a.ws_state + ((((int64_t)b * nchunks + c) * a.heads + h) * kP) * kN;
+    const int n = warp * 32 + lane;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float v[32];
+      tc::tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + half * 32, v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) out[(int64_t)(half * 32 + i) * kN + n] = v[i];
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, 64);
+}
+
+// ---------------------------------------------------------------------------------------------
+// serial pass over chunks: one thread per (batch, head, p, n)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) ssd_pass_kernel(const ssm_ssd_args a, int nchunks) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  const int64_t per = (int64_t)kP * kN;
+  const int64_t total = (int64_t)a.batch * a.heads * per;
+  if (i >= total) return;
+  const int64_t bh = i / per, pn = i % per;
+  const int b = (int)(bh / a.heads), h = (int)(bh % a.heads);
+  float s = a.initial_states ? __ldg(a.initial_states + i) : 0.f;
+  T* sin = reinterpret_cast<T*>(a.ws_state_in);
+  for (int c = 0; c < nchunks; ++c) {
+    const int64_t slot = (((int64_t)b * nchunks + c) * a.heads + h) * per + pn;
+    sin[slot] = from_f<T>(s);
+    const float decay = exp_fast(__ldg(a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ + kQ - 1));
+    s = fmaf(decay, s, a.ws_state[slot]);
+  }
+  if (a.final_states) a.final_states[i] = s;
+}
+
+// ---------------------------------------------------------------------------------------------
+// chunk scan: one CTA per (row block, head, batch * chunk)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+struct ScanSmem {
+  static constexpr int C_BYTES = kBlk * kN * 2;   // C rows of the block, K-major [n/8][i][8]        32 KB
+  static constexpr int BJ_BYTES = kQ * kN * 2;    // B rows j, K-major [n/8][j][8]; reused for (G o L) 64 KB
+  static constexpr int X_BYTES = kQ * kP * 2;     // x rows j, MN-major [p/8][j][8]                  32 KB
+  static constexpr int S_BYTES = kP * kN * 2;     // incoming state, K-major [n/8][p][8]             16 KB
+  static constexpr int VEC_BYTES = 2 * kQ * 4;    // cum and delta of the chunk
+  static constexpr int TOTAL = C_BYTES + BJ_BYTES + X_BYTES + S_BYTES + VEC_BYTES;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) ssd_scan_kernel(const ssm_ssd_args a, int nchunks) {
+  using M = ScanSmem<T>;
+  extern __shared__ __align__(128) unsigned char smraw[];
+  unsigned char* sC = smraw;
+  unsigned char* sBJ = sC + M::C_BYTES;  // B tile, later the masked G tile (K-major over j)
+  unsigned char* sX = sBJ + M::BJ_BYTES;
+  unsigned char* sS = sX + M::X_BYTES;
+  float* sCum = reinterpret_cast<float*>(sS + M::S_BYTES);
+  float* sDt = sCum + kQ;
+  __shared__ __align__(8) uint64_t mbar[2];
+  __shared__ uint32_t tmem_slot;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int ib = blockIdx.x;  // row block within the chunk
+  const int h = blockIdx.y;
+  const int c = blockIdx.z % nchunks, b = blockIdx.z / nchunks;
+  const int g = h / (a.heads / a.groups);
+  const int t0 = c * kQ;
+  const int KJ = (ib + 1) * kBlk;  // causal: only steps j < KJ can reach this row block
+  const int i_loc = ib * kBlk + tid;  // this thread's row within the chunk
+  const int t_row = t0 + i_loc;
+  constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+
+  if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), 512);
+  if (tid == 0) {
+    tc::mbar_init(tc::smem_u32(&mbar[0]), 1);
+    tc::mbar_init(tc::smem_u32(&mbar[1]), 1);
+  }
+
+  // ---- stage operands ---------------------------------------------------------------------------
+  const float* wdt = a.ws_dt + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
+  const float* wcum = a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
+  for (int i = tid; i < kQ; i += 128) sCum[i] = __ldg(wcum + i), sDt[i] = __ldg(wdt + i);
+  const T* Cg = reinterpret_cast<const T*>(a.Cm);
+  const T* Bg = reinterpret_cast<const T*>(a.Bm);
+  const T* Xg = reinterpret_cast<const T*>(a.X);
+  for (int id = tid; id < (kN / 8) * kBlk; id += 128) {  // C rows of this block
+    const int nc = id / kBlk, i = id % kBlk;
+    const int t = t0 + ib * kBlk + i;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < a.len) v = __ldg(reinterpret_cast<const uint4*>(Cg + (((int64_t)b * a.len + t) * a.groups + g) * kN + nc * 8));
+    *reinterpret_cast<uint4*>(sC + ((size_t)nc * kBlk + i) * 16) = v;
+  }
+  for (int id = tid; id < (kN / 8) * KJ; id += 128) {  // B rows j < KJ
+    const int nc = id / KJ, j = id % KJ;
+    const int t = t0 + j;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < a.len) v = __ldg(reinterpret_cast<const uint4*>(Bg + (((int64_t)b * a.len + t) * a.groups + g) * kN + nc * 8));
+    *reinterpret_cast<uint4*>(sBJ + ((size_t)nc * KJ + j) * 16) = v;
+  }
+  for (int id = tid; id < (kP / 8) * KJ; id += 128) {  // x rows j < KJ
+    const int pc = id / KJ, j = id % KJ;
+    const int t = t0 + j;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < a.len) v = __ldg(reinterpret_cast<const uint4*>(Xg + (((int64_t)b * a.len + t) * a.heads + h) * kP + pc * 8));
+    *reinterpret_cast<uint4*>(sX + ((size_t)pc * KJ + j) * 16) = v;
+  }
+  {  // incoming state (P x N, n contiguous) as K-major B operand [n/8][p][8]
+    const T* Sg = reinterpret_cast<const T*>(a.ws_state_in) + ((((int64_t)b * nchunks + c) * a.heads + h) * kP) * kN;
+    for (int id = tid; id < (kN / 8) * kP; id += 128) {
+      const int nc = id / kP, p = id % kP;
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(Sg + (int64_t)p * kN + nc * 8));
+      *reinterpret_cast<uint4*>(sS + ((size_t)nc * kP + p) * 16) = v;
+    }
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tG = tmem;         // columns [0, 256): G = C B^T
+  const uint32_t tYi = tmem + 256;  // columns [256, 320): (G o L) X
+  const uint32_t tYs = tmem + 320;  // columns [320, 384): C S_in
+
+  // ---- G = C B^T and Y_inter = C S_in ------------------------------------------------------------
+  if (tid == 0) {
+    const uint32_t c0 = tc::smem_u32(sC), b0 = tc::smem_u32(sBJ), s0 = tc::smem_u32(sS);
+    const uint32_t idG = tc::instr_desc(kBlk, KJ, fmt, 0, 0);
+    const uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 0);
+#pragma unroll 1
+    for (int kk = 0; kk < kN / 16; ++kk) {
+      const uint64_t da = tc::smem_desc(c0 + kk * 2 * (kBlk * 16), kBlk * 16, 128);
+      const uint64_t db = tc::smem_desc(b0 + kk * 2 * (KJ * 16), KJ * 16, 128);
+      tc::mma_ss(tG, da, db, idG, kk > 0);
+    }
+    tc::commit(tc::smem_u32(&mbar[0]));
+#pragma unroll 1
+    for (int kk = 0; kk < kN / 16; ++kk) {
+      const uint64_t da = tc::smem_desc(c0 + kk * 2 * (kBlk * 16), kBlk * 16, 128);
+      const uint64_t ds = tc::smem_desc(s0 + kk * 2 * (kP * 16), kP * 16, 128);
+      tc::mma_ss(tYs, da, ds, idS, kk > 0);
+    }
+  }
+  bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[0]), 0));  // warp-uniform
+  tc::fence_after_sync();
+
+  // ---- decay mask on the TMEM -> register path; masked G becomes the A operand (K-major over j) ----
+  // The B tile is dead once G is complete, so the masked tile is written over it: unit (i, j/8) at
+  // (j/8) * (128 * 16) + i * 16.
+  const float cum_i = sCum[i_loc];
+  if (ok) {
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    for (int jb = 0; jb < KJ; jb += 32) {
+      float v[32];
+      tc::tmem_ld32(tG + lane_base + jb, v);
+#pragma unroll
+      for (int q = 0; q < 32; q += 8) {
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int j = jb + q + e;
+          const float m = (j <= i_loc) ? exp_fast(cum_i - sCum[j]) * sDt[j] : 0.f;
+          f[e] = v[q + e] * m;
+        }
+        Vec16<T> o;
+        o.pack(f);
+        *reinterpret_cast<uint4*>(sBJ + ((size_t)((jb + q) / 8) * kBlk + tid) * 16) = o.raw;
+      }
+    }
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+
+  // ---- Y_intra = (G o L) X ---------------------------------------------------------------------
+  if (tid == 0) {
+    const uint32_t g0 = tc::smem_u32(sBJ), x0 = tc::smem_u32(sX);
+    const uint32_t idY = tc::instr_desc(kBlk, kP, fmt, 0, 1);
+#pragma unroll 1
+    for (int kk = 0; kk < KJ / 16; ++kk) {
+      const uint64_t da = tc::smem_desc(g0 + kk * 2 * (kBlk * 16), kBlk * 16, 128);
+      const uint64_t dx = tc::smem_desc(x0 + kk * 256, 128, KJ * 16);
+      tc::mma_ss(tYi, da, dx, idY, kk > 0);
+    }
+    tc::commit(tc::smem_u32(&mbar[1]));  // also covers the C S_in instructions issued earlier
+  }
+  ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[1]), 0)) && ok;
+  tc::fence_after_sync();
+  if (!ok && a.status) atomicExch(a.status, 2);
+
+  // ---- epilogue: y = Y_intra + exp(cum_i) Y_inter + D x, gate, store ------------------------------
+  if (ok) {
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const bool live = t_row < a.len;  // the TMEM loads below are warp-wide; only the stores are per row
+    const float escale = exp_fast(cum_i);
+    const T* zrow = a.z ? reinterpret_cast<const T*>(a.z) + (((int64_t)b * a.len + t_row) * a.heads + h) * kP : nullptr;
+    T* yrow = reinterpret_cast<T*>(a.Y) + (((int64_t)b * a.len + t_row) * a.heads + h) * kP;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float yi[32], ys[32];
+      tc::tmem_ld32(tYi + lane_base + half * 32, yi);
+      tc::tmem_ld32(tYs + lane_base + half * 32, ys);
+#pragma unroll
+      for (int q = 0; q < 32; q += 8) {
+        const int p0 = half * 32 + q;
+        float f[8], xv[8];
+        Vec16<T> xr;
+        xr.raw = *reinterpret_cast<const uint4*>(sX + ((size_t)(p0 / 8) * KJ + i_loc) * 16);
+        xr.unpack(xv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float Dv = 0.f;
+          if (a.D) Dv = a.d_has_p ? __ldg(a.D + h * kP + p0 + e) : __ldg(a.D + h);
+          f[e] = fmaf(escale, ys[q + e], yi[q + e]) + Dv * xv[e];
+        }
+        if (zrow && live) {
+          Vec16<T> zr;
+          zr.load(zrow + p0);
+          float zv[8];
+          zr.unpack(zv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] *= silu_fast(zv[e]);
+        }
+        Vec16<T> o;
+        o.pack(f);
+        if (live) o.store(yrow + p0);
+      }
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, 512);
+}
+
+template <typename T>
+static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
+  const int nchunks = (a.len + kQ - 1) / kQ;
+  {
+    const int warps = a.batch * a.heads * nchunks;
+    ssd_cumsum_kernel<T><<<(warps * 32 + 127) / 128, 128, 0, st>>>(a, nchunks);
+    if (int rc = launch_status("ssd_cumsum_kernel")) return rc;
+  }
+  {
+    const size_t smem = (kN / 8 + kP / 8) * kQ * 16;
+    cudaFuncSetAttribute(ssd_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ssd_state_kernel<T><<<dim3(nchunks, a.heads, a.batch), 128, smem, st>>>(a, nchunks);
+    if (int rc = launch_status("ssd_state_kernel")) return rc;
+  }
+  {
+    const int64_t total = (int64_t)a.batch * a.heads * kP * kN;
+    ssd_pass_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a, nchunks);
+    if (int rc = launch_status("ssd_pass_kernel")) return rc;
+  }
+  {
+    const size_t smem = ScanSmem<T>::TOTAL;
+    cudaFuncSetAttribute(ssd_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ssd_scan_kernel<T><<<dim3(kQ / kBlk, a.heads, a.batch * nchunks), 128, smem, st>>>(a, nchunks);
+    if (int rc = launch_status("ssd_scan_kernel")) return rc;
+  }
+  return SSM_OK;
+}
+
+}  // namespace ssmb
+
+using namespace ssmb;
+
+extern "C" int ssm_ssd_supported(int32_t headdim, int32_t nstate, int32_t chunk_size, int32_t io_dtype) {
+  return headdim == kP && nstate == kN && chunk_size == kQ && (io_dtype == SSM_BF16 || io_dtype == SSM_F16);
+}
+
+extern "C" int64_t ssm_ssd_scratch_bytes(int32_t batch, int32_t len, int32_t heads) {
+  const int64_t nchunks = (len + kQ - 1) / kQ;
+  const int64_t vec = (int64_t)batch * heads * nchunks * kQ * 4;      // delta, cum (each)
+  const int64_t st = (int64_t)batch * nchunks * heads * kP * kN;      // states per chunk
+  return 2 * vec + st * 4 + st * 2;
+}
+
+extern "C" int ssm_ssd_fwd(const ssm_ssd_args* a, ssm_stream_t stream) {
+  SSM_REQUIRE(a != nullptr, SSM_ERR_NULL, "ssd_scan: args is NULL");
+  SSM_REQUIRE(a->batch >= 0 && a->len >= 0 && a->heads >= 1 && a->groups >= 1, SSM_ERR_SHAPE, "ssd_scan: bad shape");
+  SSM_REQUIRE(a->heads % a->groups == 0, SSM_ERR_SHAPE, "Group dimension must divide H.");
+  SSM_REQUIRE(ssm_ssd_supported(a->headdim, a->nstate, a->chunk_size, a->io_dtype), SSM_ERR_UNSUPPORTED,
+              "ssd_scan: the tensor-core path is built for headdim 64, d_state 128, chunk 256, bf16 / fp16");
+  if (a->batch == 0 || a->len == 0) return SSM_OK;
+  SSM_REQUIRE(a->X && a->dt && a->A && a->Bm && a->Cm && a->Y, SSM_ERR_NULL, "ssd_scan: missing tensor");
+  SSM_REQUIRE(a->ws_dt && a->ws_cum && a->ws_state && a->ws_state_in, SSM_ERR_NULL, "ssd_scan: missing scratch");
+  SSM_REQUIRE(aligned_to(a->X, 16) && aligned_to(a->Bm, 16) && aligned_to(a->Cm, 16) && aligned_to(a->Y, 16) && aligned_to(a->ws_state_in, 16) &&
+                  (!a->z || aligned_to(a->z, 16)),
+              SSM_ERR_ALIGN, "ssd_scan: tensors must be 16-byte aligned");
+  const int64_t nchunks = (a->len + kQ - 1) / kQ;
+  SSM_REQUIRE((int64_t)a->batch * nchunks <= 65535 && a->heads <= 65535, SSM_ERR_TOO_LARGE, "ssd_scan: grid too large");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (a->io_dtype == SSM_BF16) return ssd_launch<__nv_bfloat16>(*a, st);
+  return ssd_launch<__half>(*a, st);
+}

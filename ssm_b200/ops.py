@@ -890,6 +890,147 @@ def fused_layer_norm(
     return _NormFn.apply(x, weight, bias, residual, is_rms, eps, prenorm, return_residual, rd)
 
 
+# =========================================================================================
+# ssd_scan: state-space-dual scan with a d_state axis (Mamba-2 layout)
+# =========================================================================================
+
+
+def _ssd_check(X, dt, A, B, C_, D, z, dt_bias, initial_states):
+    if X.ndim != 4 or dt.ndim != 3:
+        raise ValueError("X must be (B, L, H, P) and dt (B, L, H).")
+    nb, nl, nh, npj = X.shape
+    if tuple(dt.shape) != (nb, nl, nh):
+        raise ValueError("dt must align with (B, L, H).")
+    if tuple(A.shape) != (nh,):
+        raise ValueError("A must have shape (H,).")
+    if B.ndim != 4 or B.shape[0] != nb or B.shape[1] != nl or B.shape != C_.shape:
+        raise ValueError("B and C must have shape (B, L, G, N).")
+    ng, nn = B.shape[2], B.shape[3]
+    if ng == 0 or nh % ng != 0:
+        raise ValueError("Group dimension must divide H.")
+    if D is not None and tuple(D.shape) not in ((nh,), (nh, npj)):
+        raise ValueError("D must have shape (H,) or (H, P).")
+    if z is not None and z.shape != X.shape:
+        raise ValueError("z must have shape (B, L, H, P).")
+    if dt_bias is not None and tuple(dt_bias.shape) != (nh,):
+        raise ValueError("dt_bias must have shape (H,).")
+    if initial_states is not None and tuple(initial_states.shape) != (nb, nh, npj, nn):
+        raise ValueError("initial_states must have shape (B, H, P, N).")
+    _need_cuda(X, dt, A, B, C_, D, z, dt_bias, initial_states)
+    return nb, nl, nh, npj, ng, nn
+
+
+def _ssd_via_scan(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states):
+    """The same recurrence through the selective-scan kernels on the ``H*P`` flattened channels
+    (any shape and dtype the scan supports; differentiable).  Returns ``(Y, final_states fp32)``."""
+    nb, nl, nh, npj = X.shape
+    nn = B.shape[3]
+    u = X.permute(0, 2, 3, 1).reshape(nb, nh * npj, nl)
+    delta = dt.permute(0, 2, 1).repeat_interleave(npj, dim=1)
+    A_full = A.float()[:, None, None].expand(nh, npj, nn).reshape(nh * npj, nn)
+    Bs, Cs = B.permute(0, 2, 3, 1), C_.permute(0, 2, 3, 1)
+    D_flat = None if D is None else (D.reshape(-1) if D.ndim == 2 else D[:, None].expand(nh, npj).reshape(-1))
+    z_flat = None if z is None else z.permute(0, 2, 3, 1).reshape(nb, nh * npj, nl)
+    b_flat = None if dt_bias is None else dt_bias[:, None].expand(nh, npj).reshape(-1)
+    init = None if initial_states is None else initial_states.reshape(nb, nh * npj, nn)
+    y, last = selective_scan(u, delta, A_full, Bs, Cs, D=D_flat, z=z_flat, dt_bias=b_flat, softplus=dt_softplus,
+                             return_last_state=True, initial_state=init, keep_state_fp32=True)
+    return y.reshape(nb, nh, npj, nl).permute(0, 3, 1, 2).contiguous(), last.reshape(nb, nh, npj, nn)
+
+
+def _ssd_tensor_core(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states, chunk_size):
+    nb, nl, nh, npj = X.shape
+    ng, nn = B.shape[2], B.shape[3]
+    lib = L.load()
+    dev = X.device
+    io = X.dtype
+    Xc, dtc, Bc, Cc = _c(X), _c(dt.to(io)), _c(B.to(io)), _c(C_.to(io))
+    zc = None if z is None else _c(z.to(io))
+    A32, D32, b32, init32 = _f32(A), _f32(D), _f32(dt_bias), _f32(initial_states)
+    Y = torch.empty_like(Xc)
+    final = torch.empty(nb, nh, npj, nn, dtype=torch.float32, device=dev)
+    nchunks = (nl + chunk_size - 1) // chunk_size
+    ws = torch.empty(int(lib.ssm_ssd_scratch_bytes(nb, nl, nh)), dtype=torch.uint8, device=dev)
+    vec = nb * nh * nchunks * chunk_size * 4
+    st = nb * nchunks * nh * npj * nn
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    a = L.SsdArgs()
+    a.batch, a.len, a.heads, a.headdim = nb, nl, nh, npj
+    a.nstate, a.groups, a.chunk_size, a.io_dtype = nn, ng, chunk_size, _CODES[io]
+    a.dt_softplus, a.d_has_p = int(bool(dt_softplus)), int(D is not None and D.ndim == 2)
+    a.X, a.dt, a.A, a.Bm, a.Cm = _p(Xc), _p(dtc), _p(A32), _p(Bc), _p(Cc)
+    a.D, a.z, a.dt_bias, a.initial_states = _p(D32), _p(zc), _p(b32), _p(init32)
+    a.Y, a.final_states = _p(Y), _p(final)
+    base = ws.data_ptr()
+    a.ws_dt, a.ws_cum, a.ws_state, a.ws_state_in = base, base + vec, base + 2 * vec, base + 2 * vec + st * 4
+    a.status = _p(status)
+    _call(lib.ssm_ssd_fwd, a)
+    return Y, final, status
+
+
+def ssd_tensor_core_supported(X: Tensor, B: Tensor, chunk_size: int) -> bool:
+    """True when :func:`ssd_scan` runs on the tcgen05 kernels for these operands."""
+    return bool(X.is_cuda and X.dtype in (torch.bfloat16, torch.float16)
+                and L.load().ssm_ssd_supported(X.shape[3], B.shape[3], int(chunk_size), _CODES[X.dtype]))
+
+
+class _SsdFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states, chunk_size, check_status):
+        _ssd_check(X, dt, A, B, C_, D, z, dt_bias, initial_states)
+        ctx.args = (X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states)
+        if ssd_tensor_core_supported(X, B, chunk_size):
+            Y, final, status = _ssd_tensor_core(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states, int(chunk_size))
+            if check_status and int(status.item()) != 0:
+                raise RuntimeError(f"ssd_scan: a bounded device-side wait ran out (status {int(status.item())})")
+            return Y, final
+        with torch.no_grad():
+            return _ssd_via_scan(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states)
+
+    @staticmethod
+    def backward(ctx, gY, gfinal):
+        X, dt, A, B, C_, D, z, dt_bias, dt_softplus, init = ctx.args
+        leaves = [None if t is None else t.detach().requires_grad_(t.requires_grad) for t in (X, dt, A, B, C_, D, z, dt_bias)]
+        with torch.enable_grad():
+            Y, final = _ssd_via_scan(*leaves, dt_softplus, init)
+        live = [t for t in leaves if t is not None and t.requires_grad]
+        outs, gouts = [Y], [gY if gY is not None else torch.zeros_like(Y)]
+        if gfinal is not None:
+            outs.append(final)
+            gouts.append(gfinal)
+        grads = iter(torch.autograd.grad(outs, live, gouts, allow_unused=True))
+        res = [next(grads) if (t is not None and t.requires_grad) else None for t in leaves]
+        return (*res, None, None, None, None)
+
+
+def ssd_scan(
+    X: Tensor,
+    dt: Tensor,
+    A: Tensor,
+    B: Tensor,
+    C: Tensor,
+    chunk_size: int = 256,
+    D: Optional[Tensor] = None,
+    z: Optional[Tensor] = None,
+    dt_bias: Optional[Tensor] = None,
+    dt_softplus: bool = False,
+    initial_states: Optional[Tensor] = None,
+    return_final_states: bool = False,
+    check_status: bool = False,
+):
+    """Extension: state-space-dual scan with a ``d_state`` axis (Mamba-2 layout).
+
+    ``X (B,L,H,P)``, ``dt (B,L,H)``, ``A (H,)``, ``B/C (B,L,G,N)``, ``D (H,)|(H,P)``, ``z (B,L,H,P)``,
+    state ``(B,H,P,N)`` fp32.  It is upstream's ``selective_scan`` recurrence (reference.py:173-188)
+    on channel ``h*P+p`` with per-head ``dt`` and ``A``.  For headdim 64, d_state 128, chunk 256 and
+    bf16 / fp16 operands the forward runs as chunked GEMMs on the tcgen05 tensor cores; any other
+    shape or dtype, and every backward pass, goes through the selective-scan kernels on the
+    flattened channels.  ``check_status`` synchronises and raises if a device-side wait timed out.
+    """
+    Y, final = _SsdFn.apply(X, dt, A, B, C, D, z, dt_bias, dt_softplus, initial_states, chunk_size, check_status)
+    return (Y, final) if return_final_states else Y
+
+
 __all__ = [
     "selective_scan",
     "selective_state_step",
@@ -898,4 +1039,6 @@ __all__ = [
     "dw_causal_conv",
     "dw_causal_conv_update",
     "fused_layer_norm",
+    "ssd_scan",
+    "ssd_tensor_core_supported",
 ]

@@ -41,7 +41,7 @@ def test_ctypes_structs_match_c_layout(tmp_path):
         "ssm_step_args": _lib.StepArgs, "ssm_step_bwd_args": _lib.StepBwdArgs,
         "ssm_bcast4": _lib.Bcast4, "ssm_chunk_args": _lib.ChunkArgs, "ssm_chunk_bwd_args": _lib.ChunkBwdArgs,
         "ssm_conv_args": _lib.ConvArgs, "ssm_conv_bwd_args": _lib.ConvBwdArgs, "ssm_conv_update_args": _lib.ConvUpdateArgs,
-        "ssm_norm_args": _lib.NormArgs, "ssm_norm_bwd_args": _lib.NormBwdArgs,
+        "ssm_norm_args": _lib.NormArgs, "ssm_norm_bwd_args": _lib.NormBwdArgs, "ssm_ssd_args": _lib.SsdArgs,
     }
     src = tmp_path / "sizes.c"
     body = "".join(f'  printf("{n} %zu\\n", sizeof({n}));\n' for n in pairs)

@@ -100,3 +100,22 @@ def test_fused_layer_norm(case):
         close(res, case.outs["residual_out"], **tol(case), what=f"{case.name} residual_out")
     w = case.ins["grad_out"] if "grad_out" in case.ins else torch.ones_like(y)
     _grads(case, (y,), (w,), i)
+
+
+@pytest.mark.parametrize("case", _all("ssd"))
+def test_ssd_scan(case):
+    from ssm_b200 import ops
+
+    i = {k: leaf(v) for k, v in case.ins.items()}
+    o = case.opts
+    Y, fin = ops.ssd_scan(i["X"], i["dt"], i["A"], i["B"], i["C"], o["chunk_size"], D=i.get("D"), z=i.get("z"),
+                          dt_bias=i.get("dt_bias"), dt_softplus=o["dt_softplus"], initial_states=i.get("initial_states"),
+                          return_final_states=True)
+    heads = o.get("heads")
+    if heads is not None:  # mamba-ssm vector: only the listed heads follow the exact recurrence
+        close(Y[:, :, heads], case.outs["y"][:, :, heads], **tol(case), what=f"{case.name} y")
+        close(fin[:, heads], case.outs["final_states"][:, heads], **tol(case), what=f"{case.name} final")
+        return
+    close(Y, case.outs["y"], **tol(case), what=f"{case.name} y")
+    close(fin, case.outs["final_states"], **tol(case), what=f"{case.name} final")
+    _grads(case, (Y, fin), (case.ins["grad_out"], case.ins["grad_final_states"]), i)

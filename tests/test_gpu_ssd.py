@@ -1,0 +1,93 @@
+"""The tcgen05 state-space-dual kernels against the CPU oracle (and against the scan-kernel
+path of the same operator) at shapes the tensor-core path is built for."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import ssm_oracle as orc
+from tests.gpu_util import FP32_TOL, HALF_TOL, close
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(nb, nl, nh, ng, dtype, seed, with_init=True):
+    gen = torch.Generator().manual_seed(seed)
+    npj, nn = 64, 128
+    X = torch.randn(nb, nl, nh, npj, generator=gen).to(dtype)
+    dt = (torch.randn(nb, nl, nh, generator=gen) - 3.0).to(dtype)
+    A = -torch.exp(torch.rand(nh, generator=gen) * 2.77)
+    Bm = (torch.randn(nb, nl, ng, nn, generator=gen) / nn ** 0.5).to(dtype)
+    Cm = (torch.randn(nb, nl, ng, nn, generator=gen) / nn ** 0.5).to(dtype)
+    D = torch.randn(nh, generator=gen)
+    z = torch.randn(nb, nl, nh, npj, generator=gen).to(dtype)
+    bias = torch.randn(nh, generator=gen) * 0.3
+    init = torch.randn(nb, nh, npj, nn, generator=gen) * 0.5 if with_init else None
+    return dict(X=X, dt=dt, A=A, B=Bm, C=Cm, D=D, z=z, dt_bias=bias, initial_states=init)
+
+
+CASES = [
+    # batch, len, heads, groups, dtype
+    (1, 256, 1, 1, torch.bfloat16),
+    (2, 512, 3, 1, torch.bfloat16),
+    (1, 700, 4, 2, torch.bfloat16),   # ragged last chunk, two groups
+    (1, 512, 2, 1, torch.float16),
+    (1, 100, 2, 2, torch.bfloat16),   # shorter than one row block
+]
+
+
+@pytest.mark.parametrize("nb,nl,nh,ng,dtype", CASES)
+def test_tensor_core_ssd_matches_oracle(nb, nl, nh, ng, dtype):
+    from ssm_b200 import ops
+
+    t = _inputs(nb, nl, nh, ng, dtype, seed=nl + nh)
+    assert ops.ssd_tensor_core_supported(t["X"].cuda(), t["B"].cuda(), 256)
+    Yo, So = orc.ssd_scan(t["X"], t["dt"], t["A"], t["B"], t["C"], 256, D=t["D"], z=t["z"], dt_bias=t["dt_bias"], dt_softplus=True,
+                          initial_states=t["initial_states"], return_final_states=True)
+    g = {k: (None if v is None else v.cuda()) for k, v in t.items()}
+    Yg, Sg = ops.ssd_scan(g["X"], g["dt"], g["A"], g["B"], g["C"], 256, D=g["D"], z=g["z"], dt_bias=g["dt_bias"], dt_softplus=True,
+                          initial_states=g["initial_states"], return_final_states=True, check_status=True)
+    assert Yg.dtype == dtype and Sg.dtype == torch.float32
+    close(Yg, Yo, **HALF_TOL, what="Y")
+    close(Sg, So, **HALF_TOL, what="final state")
+
+
+def test_tensor_core_ssd_without_optionals_and_matrix_D():
+    from ssm_b200 import ops
+
+    t = _inputs(1, 512, 2, 1, torch.bfloat16, seed=9, with_init=False)
+    Dm = torch.randn(2, 64)
+    dtp = (t["dt"].float().abs() * 0.05 + 0.01).to(torch.bfloat16)
+    Yo, So = orc.ssd_scan(t["X"], dtp, t["A"], t["B"], t["C"], 256, D=Dm, return_final_states=True)
+    Yg, Sg = ops.ssd_scan(t["X"].cuda(), dtp.cuda(), t["A"].cuda(), t["B"].cuda(), t["C"].cuda(), 256, D=Dm.cuda(),
+                          return_final_states=True, check_status=True)
+    close(Yg, Yo, **HALF_TOL, what="Y")
+    close(Sg, So, **HALF_TOL, what="final state")
+
+
+def test_tensor_core_ssd_agrees_with_scan_kernel_path_and_has_gradients():
+    """Same operator, two CUDA paths: chunked tensor-core GEMMs vs the sequential scan kernels."""
+    from ssm_b200 import ops
+
+    t = {k: (None if v is None else v.cuda()) for k, v in _inputs(2, 768, 4, 1, torch.bfloat16, seed=4).items()}
+    Y1, S1 = ops.ssd_scan(t["X"], t["dt"], t["A"], t["B"], t["C"], 256, D=t["D"], z=t["z"], dt_bias=t["dt_bias"], dt_softplus=True,
+                          initial_states=t["initial_states"], return_final_states=True, check_status=True)
+    Y2, S2 = ops._ssd_via_scan(t["X"], t["dt"], t["A"], t["B"], t["C"], t["D"], t["z"], t["dt_bias"], True, t["initial_states"])
+    close(Y1, Y2, **HALF_TOL, what="Y")
+    close(S1, S2, **HALF_TOL, what="final state")
+    # chaining: second half started from the first half's final state
+    h = 512
+    Ya, Sa = ops.ssd_scan(t["X"][:, :h], t["dt"][:, :h], t["A"], t["B"][:, :h], t["C"][:, :h], 256, D=t["D"], z=t["z"][:, :h],
+                          dt_bias=t["dt_bias"], dt_softplus=True, initial_states=t["initial_states"], return_final_states=True)
+    Yb, Sb = ops.ssd_scan(t["X"][:, h:], t["dt"][:, h:], t["A"], t["B"][:, h:], t["C"][:, h:], 256, D=t["D"], z=t["z"][:, h:],
+                          dt_bias=t["dt_bias"], dt_softplus=True, initial_states=Sa, return_final_states=True)
+    close(torch.cat([Ya, Yb], 1), Y1, **HALF_TOL, what="chained Y")
+    close(Sb, S1, **HALF_TOL, what="chained state")
+    # gradients flow (through the scan-kernel backward)
+    X = t["X"].clone().requires_grad_(True)
+    A = t["A"].clone().requires_grad_(True)
+    Y = ops.ssd_scan(X, t["dt"], A, t["B"], t["C"], 256, dt_softplus=True)
+    Y.float().square().mean().backward()
+    assert X.grad is not None and torch.isfinite(X.grad.float()).all() and float(X.grad.float().abs().max()) > 0
+    assert A.grad is not None and torch.isfinite(A.grad).all()
