@@ -376,6 +376,273 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+# --------------------------------------------------------------------------------------
+# other workloads of the same hot path (selected with --workload; one JSON line each)
+# --------------------------------------------------------------------------------------
+def _time_cuda(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_ssd(args):
+    """BASELINE config 3: Mamba-2 SSD chunk scan, batch 8, L 8192, 48 heads x 64, d_state 128, chunk 256, bf16."""
+    from ssm_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B, Lq, H, P, N = args.batch or 8, 8192, 48, 64, 128
+    g = torch.Generator().manual_seed(0)
+    host = dict(
+        X=torch.randn(B, Lq, H, P, generator=g).to(torch.bfloat16), dt=(torch.randn(B, Lq, H, generator=g) - 3).to(torch.bfloat16),
+        Bm=(torch.randn(B, Lq, 1, N, generator=g) / N ** 0.5).to(torch.bfloat16),
+        Cm=(torch.randn(B, Lq, 1, N, generator=g) / N ** 0.5).to(torch.bfloat16), z=torch.randn(B, Lq, H, P, generator=g).to(torch.bfloat16))
+    host = {k: v.pin_memory() for k, v in host.items()}
+    A = (-torch.exp(torch.rand(H, generator=g) * 2.7726)).to(dev)
+    D = torch.randn(H, generator=g).to(dev)
+    d = {k: v.to(dev) for k, v in host.items()}
+
+    def step(t):
+        return ops.ssd_scan(t["X"], t["dt"], A, t["Bm"], t["Cm"], 256, D=D, z=t["z"], dt_softplus=True, return_final_states=True)
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = _time_cuda(lambda: step(d), args.steps, args.warmup)
+    fin_host = torch.empty(B, H, P, N).pin_memory()
+    stage = {k: torch.empty_like(v) for k, v in d.items()}
+
+    def e2e():
+        for k in stage:
+            stage[k].copy_(host[k], non_blocking=True)
+        _, fin = step(stage)
+        fin_host.copy_(fin, non_blocking=True)
+
+    ms_e2e = _time_cuda(e2e, max(2, args.steps // 4), 2)
+    clocks = sampler.stop()
+    peak, kind = measured_peaks()
+    io = 2
+    bytes_alg = 3 * B * Lq * H * P * io + B * Lq * H * io + 2 * B * Lq * N * io + B * H * P * N * 4 + 2 * H * 4
+    flops = B * (Lq // 256) * H * (2 * 256 * 256 * P + 4 * 256 * N * P) + B * (Lq // 256) * 2 * 256 * 256 * N
+    tok = B * Lq
+    print(json.dumps({
+        "metric": "tokens_per_s", "value": tok / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 operands, fp32 accumulate/state",
+        "data": "synthetic (seeded)", "config": {"workload": f"ssd chunk scan fwd: batch {B}, seqlen {Lq}, 48 heads x 64, d_state 128, ngroups 1, chunk 256",
+                                                 "l2": "inputs (>800 MB) exceed the 126 MB L2"},
+        "e2e": {"value": tok / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in host.values()), "d2h_bytes_per_step": fin_host.numel() * 4},
+        "gpu_launches": 4 * args.steps,
+        "roofline": {"kernel": "ssm_ssd_fwd (cumsum + state + pass + scan kernels)", "bound": "hbm", "achieved": bytes_alg / (ms * 1e-3) / 1e9,
+                     "peak": peak, "unit": "GB/s", "frac": bytes_alg / (ms * 1e-3) / 1e9 / peak, "peak_kind": kind, "traffic": None,
+                     "bytes_per_launch": bytes_alg, "tensor_tflops": flops / (ms * 1e-3) / 1e12},
+        "clocks": clocks}))
+
+
+def run_decode(args):
+    """BASELINE config 4: single-token state steps, batch 256 (a) Mamba-1 layer D 5120, N 16; (b) Mamba-2 state 80 x 64 x 128."""
+    from ssm_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator().manual_seed(0)
+    B, dm, di, n, k, r = 256, 2560, 5120, 16, 4, 160
+    bf = torch.bfloat16
+    W = {name: (torch.randn(o, i, generator=g) / i ** 0.5).to(bf).to(dev) for name, (o, i) in
+         dict(in_proj=(2 * di, dm), x_proj=(r + 2 * n, di), dt_proj=(di, r), out_proj=(dm, di)).items()}
+    conv_w = (torch.rand(di, k, generator=g) - 0.5).to(dev)
+    A = (-torch.exp(torch.randn(di, n, generator=g) * 0.5)).to(dev)
+    Dk, bias = torch.randn(di, generator=g).to(dev), (torch.rand(di, generator=g) * 2 - 4).to(dev)
+    ssm_state = (torch.randn(B, di, n, generator=g) * 0.1).to(dev)
+    conv_state = (torch.randn(B, di, k, generator=g) * 0.1).to(dev)
+    tok = torch.randn(B, dm, generator=g).to(bf).to(dev)
+
+    def layer_step():
+        xz = tok @ W["in_proj"].t()
+        x, z = xz[:, :di], xz[:, di:]
+        u = ops.dw_causal_conv_update(conv_state, x, conv_w, None, "silu")
+        xd = u @ W["x_proj"].t()
+        delta = xd[:, :r] @ W["dt_proj"].t()
+        y = ops.selective_state_step(ssm_state, u, delta, A, xd[:, r:r + n].unsqueeze(1), xd[:, r + n:].unsqueeze(1), D=Dk, z=z,
+                                     dt_bias=bias, softplus=True)
+        return y @ W["out_proj"].t()
+
+    # (b) Mamba-2 state update alone
+    H2, P2, N2 = 80, 64, 128
+    st2 = (torch.randn(B, H2, P2, N2, generator=g) * 0.1).to(dev)
+    x2, z2 = torch.randn(B, H2, P2, generator=g).to(bf).to(dev), torch.randn(B, H2, P2, generator=g).to(bf).to(dev)
+    dt2, A2 = torch.randn(B, H2, generator=g).to(bf).to(dev), (-torch.exp(torch.rand(H2, generator=g))).to(dev)
+    B2, C2 = torch.randn(B, 1, N2, generator=g).to(bf).to(dev), torch.randn(B, 1, N2, generator=g).to(bf).to(dev)
+    D2 = torch.randn(H2, generator=g).to(dev)
+
+    def m2_step():
+        return ops.selective_state_step_heads(st2, x2, dt2, A2, B2, C2, D=D2, z=z2, softplus=True)
+
+    def m1_step_only():
+        return ops.selective_state_step(ssm_state, tok[:, :1].expand(B, di).contiguous() if False else x_fixed, d_fixed, A, Bf, Cf, D=Dk, z=z_fixed,
+                                        dt_bias=bias, softplus=True)
+
+    x_fixed, d_fixed, z_fixed = (torch.randn(B, di, generator=g).to(bf).to(dev) for _ in range(3))
+    Bf, Cf = torch.randn(B, 1, n, generator=g).to(bf).to(dev), torch.randn(B, 1, n, generator=g).to(bf).to(dev)
+    steps = max(args.steps, 1000) if args.steps == 20 else args.steps
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms_layer = _time_cuda(layer_step, steps, 20)
+    ms_m1 = _time_cuda(m1_step_only, steps, 20)
+    ms_m2 = _time_cuda(m2_step, min(steps, 200), 5)
+    # CUDA-graph replay of the whole layer step
+    graph_ms = None
+    try:
+        gph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                layer_step()
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(gph):
+            out = layer_step()
+        graph_ms = _time_cuda(gph.replay, steps, 20)
+    except Exception as exc:  # noqa: BLE001
+        graph_ms = f"capture failed: {exc}"
+    clocks = sampler.stop()
+    peak, kind = measured_peaks()
+    m1_bytes = 2 * B * di * n * 4 + 4 * B * di * 2 + 2 * B * n * 2 + di * n * 4
+    m2_bytes = 2 * B * H2 * P2 * N2 * 4 + 3 * B * H2 * P2 * 2
+    val = graph_ms if isinstance(graph_ms, float) else ms_layer
+    print(json.dumps({
+        "metric": "decode_step_us", "value": val * 1e3, "unit": "us/step", "n_gpus": 1, "steps": steps, "warmup": 20,
+        "ms_per_step": val, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations, fp32 state",
+        "data": "synthetic (seeded)", "config": {"workload": "decode: Mamba-1 layer step, batch 256, d_model 2560, d_inner 5120, d_state 16, conv 4, dt_rank 160; "
+                                                 "1000 consecutive steps", "l2": "state (84 MB) + weights exceed nothing; consecutive dependent steps"},
+        "layer_step_us": {"eager": ms_layer * 1e3, "cuda_graph": graph_ms * 1e3 if isinstance(graph_ms, float) else graph_ms},
+        "gpu_launches": 2 * steps,
+        "roofline": {"kernel": "step_fwd_kernel (Mamba-1 state 256x5120x16)", "bound": "hbm", "achieved": m1_bytes / (ms_m1 * 1e-3) / 1e9, "peak": peak,
+                     "unit": "GB/s", "frac": m1_bytes / (ms_m1 * 1e-3) / 1e9 / peak, "peak_kind": kind, "traffic": None, "us_per_launch": ms_m1 * 1e3,
+                     "note": "eager launch through ctypes; the 84 MB state stays L2-resident between steps, so this can exceed the HBM peak"},
+        "mamba2_state_step": {"us_per_launch": ms_m2 * 1e3, "bytes_per_launch": m2_bytes, "achieved_gbs": m2_bytes / (ms_m2 * 1e-3) / 1e9,
+                              "frac": m2_bytes / (ms_m2 * 1e-3) / 1e9 / peak},
+        "clocks": clocks}))
+
+
+def run_scan_c1(args):
+    """BASELINE config 1: selective_scan forward, batch 1, D 512, L 2048, N 16, fp32, gated, skip, softplus, last state."""
+    from ssm_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.manual_seed(0)
+    nb, nd, nl, nn = 1, 512, 2048, 16
+    # rotate over enough distinct input sets to exceed the L2
+    nsets = 10
+    sets = []
+    for _ in range(nsets):
+        sets.append(dict(u=torch.randn(nb, nd, nl), delta=torch.nn.functional.softplus(torch.randn(nb, nd, nl) - 2),
+                         B=torch.randn(nb, 1, nn, nl), C=torch.randn(nb, 1, nn, nl), z=torch.randn(nb, nd, nl)))
+    A, D = -torch.exp(torch.randn(nd, nn) * 0.5), torch.randn(nd)
+    dsets = [{k: v.to(dev) for k, v in s.items()} for s in sets]
+    Ad, Dd = A.to(dev), D.to(dev)
+    it = [0]
+
+    def step():
+        s = dsets[it[0] % nsets]
+        it[0] += 1
+        return ops.selective_scan(s["u"], s["delta"], Ad, s["B"], s["C"], D=Dd, z=s["z"], softplus=True, return_last_state=True)
+
+    ms = _time_cuda(step, max(args.steps, 50), 10)
+    peak, kind = measured_peaks()
+    by = 3 * nb * nd * nl * 4 + 2 * nb * nn * nl * 4 + nd * nn * 4 + nd * 4 + nb * nd * nl * 4 + nb * nd * nn * 4
+    from oracle import ssm_oracle as orc
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    s0 = sets[0]
+    t0 = time.perf_counter()
+    orc.selective_scan(s0["u"], s0["delta"], A, s0["B"], s0["C"], D=D, z=s0["z"], softplus=True, return_last_state=True)
+    cpu_s = time.perf_counter() - t0
+    print(json.dumps({
+        "metric": "tokens_per_s", "value": nb * nl / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": max(args.steps, 50), "warmup": 10,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic (seeded)",
+        "config": {"workload": "selective_scan fwd: batch 1, d_inner 512, seqlen 2048, d_state 16, fp32 (README prefill_2k_d512)",
+                   "l2": "10 rotating input sets (171 MB) exceed the 126 MB L2"},
+        "gpu_launches": max(args.steps, 50),
+        "roofline": {"kernel": "scan_fwd_kernel", "bound": "hbm", "achieved": by / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": by / (ms * 1e-3) / 1e9 / peak, "peak_kind": kind, "traffic": None, "bytes_per_launch": by},
+        "cpu_baseline": {"value": nb * nl / cpu_s, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port", "seconds": cpu_s,
+                         "sample": "the full config once (upstream README reports 1012.9 ms for its Python backend)"}}))
+
+
+def run_ssd_sp(args):
+    """Long-sequence Mamba-2 SSD core, sequence-sharded (BASELINE config 5's per-layer scan): batch 2, seqlen 131072
+    split into contiguous shards over the ranks, 80 heads x 64, d_state 128, chunk 256; strong scaling."""
+    import torch.distributed as dist
+
+    from ssm_b200 import seqpar
+
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev) if world > 1 else dist.init_process_group(
+        "gloo", init_method="tcp://127.0.0.1:29577", rank=0, world_size=1)
+    B, Ltot, H, P, N = 2, args.seqlen or 131072, 80, 64, 128
+    Lq = Ltot // world
+    g = torch.Generator().manual_seed(100 + rank)
+    bf = torch.bfloat16
+    X = torch.randn(B, Lq, H, P, generator=g).to(bf).to(dev)
+    z = torch.randn(B, Lq, H, P, generator=g).to(bf).to(dev)
+    dt = (torch.randn(B, Lq, H, generator=g) - 3).to(bf).to(dev)
+    Bm = (torch.randn(B, Lq, 1, N, generator=g) / N ** 0.5).to(bf).to(dev)
+    Cm = (torch.randn(B, Lq, 1, N, generator=g) / N ** 0.5).to(bf).to(dev)
+    g0 = torch.Generator().manual_seed(7)
+    A = (-torch.exp(torch.rand(H, generator=g0) * 2.7726)).to(dev)
+    D = torch.randn(H, generator=g0).to(dev)
+
+    def step():
+        return seqpar.ssd_scan_sharded(X, dt, A, Bm, Cm, 256, D=D, z=z, dt_softplus=True)
+
+    for _ in range(args.warmup):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        ms = float(t[0])
+        peak, kind = measured_peaks()
+        bytes_alg = (3 * B * Ltot * H * P * 2 + B * Ltot * H * 2 + 2 * B * Ltot * N * 2) / world  # per GPU
+        print(json.dumps({
+            "metric": "tokens_per_s", "value": B * Ltot / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 operands, fp32 accumulate/state", "data": "synthetic (seeded)",
+            "config": {"workload": f"sequence-sharded ssd scan: batch {B}, seqlen {Ltot} in {world} contiguous shards, 80 heads x 64, d_state 128, chunk 256",
+                       "parallelism": f"sp{world}: all-gather of (final state 5.2 MB, log-decay) per rank over NCCL, associative fold",
+                       "l2": "per-GPU inputs exceed the 126 MB L2"},
+            "gpu_launches": 5 * args.steps,
+            "roofline": {"kernel": "ssm_ssd_fwd phases 1+2 per shard", "bound": "hbm", "achieved": bytes_alg / (ms * 1e-3) / 1e9, "peak": peak,
+                         "unit": "GB/s", "frac": bytes_alg / (ms * 1e-3) / 1e9 / peak, "peak_kind": kind, "traffic": None},
+            "clocks": clocks}))
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -385,10 +652,20 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling on a smaller case)")
+    ap.add_argument("--workload", default="mamba1_block", choices=["mamba1_block", "ssd", "decode", "scan_c1", "ssd_sp"])
+    ap.add_argument("--seqlen", type=int, default=0, help="override the total sequence length of the ssd_sp workload")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "ssd":
+        run_ssd(args)
+    elif args.workload == "decode":
+        run_decode(args)
+    elif args.workload == "scan_c1":
+        run_scan_c1(args)
+    elif args.workload == "ssd_sp":
+        run_ssd_sp(args)
     else:
         run_gpu(args)
 

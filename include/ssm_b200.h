@@ -346,11 +346,15 @@ int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* args, ssm_stream_t s
  *   ws_state      : (batch, nchunks, heads, headdim, nstate) fp32
  *   ws_state_in   : the same shape in io_dtype
  * status: optional device int, set non-zero when a bounded device-side wait ran out.
+ * phase: 0 runs everything.  1 stops after the per-chunk states and the pass over chunks (it
+ * fills the scratch and final_states, writes no Y); 2 redoes only the pass over chunks with
+ * the given initial_states and then produces Y from scratch left by phase 1.  A sequence
+ * shard uses 1, exchanges final states with its neighbours, then 2.
  * ------------------------------------------------------------------------------------- */
 typedef struct {
   int32_t batch, len, heads, headdim;
   int32_t nstate, groups, chunk_size, io_dtype;
-  int32_t dt_softplus, d_has_p, reserved0, reserved1;
+  int32_t dt_softplus, d_has_p, phase, reserved1;
   const void* X;
   const void* dt;
   const float* A;

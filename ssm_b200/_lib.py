@@ -121,7 +121,7 @@ class SsdArgs(C.Structure):
     _fields_ = [
         ("batch", i32), ("len", i32), ("heads", i32), ("headdim", i32),
         ("nstate", i32), ("groups", i32), ("chunk_size", i32), ("io_dtype", i32),
-        ("dt_softplus", i32), ("d_has_p", i32), ("reserved0", i32), ("reserved1", i32),
+        ("dt_softplus", i32), ("d_has_p", i32), ("phase", i32), ("reserved1", i32),
         ("X", vp), ("dt", vp), ("A", fp), ("Bm", vp), ("Cm", vp), ("D", fp), ("z", vp), ("dt_bias", fp),
         ("initial_states", fp), ("Y", vp), ("final_states", fp),
         ("ws_dt", fp), ("ws_cum", fp), ("ws_state", fp), ("ws_state_in", vp), ("status", vp),

@@ -19,6 +19,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "scan_common.cuh"
 #include "tc05.cuh"
 
 namespace ssmb {
@@ -96,33 +97,46 @@ __global__ void __launch_bounds__(128) ssd_state_kernel(const ssm_ssd_args a, in
   for (int id = tid; id < (kN / 8) * kQ; id += 128) {
     const int nc = id / kQ, j = id % kQ;
     const int t = t0 + j;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (t < a.len) v = __ldg(reinterpret_cast<const uint4*>(Bg + (((int64_t)b * a.len + t) * a.groups + g) * kN + nc * 8));
-    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(sA) + ((size_t)nc * kQ + j) * 16) = v;
+    const bool okt = t < a.len;
+    cp_async16(reinterpret_cast<unsigned char*>(sA) + ((size_t)nc * kQ + j) * 16,
+               Bg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
   }
+  cp_async_commit();
   // ---- x tile scaled by w_j = exp(cum_last - cum_j) * delta_j ---------------------------------
   const float* wdt = a.ws_dt + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
   const float* wcum = a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
   const float cum_last = __ldg(wcum + kQ - 1);
   const T* Xg = reinterpret_cast<const T*>(a.X);
-  for (int id = tid; id < (kP / 8) * kQ; id += 128) {
-    const int pc = id / kQ, j = id % kQ;
-    const int t = t0 + j;
-    float f[8];
+  constexpr int XU = 8;  // units per thread kept in flight together
+  for (int id0 = tid; id0 < (kP / 8) * kQ; id0 += 128 * XU) {
+    Vec16<T> v[XU];
+    float w[XU];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = 0.f;
-    if (t < a.len) {
-      Vec16<T> v;
-      v.load(Xg + (((int64_t)b * a.len + t) * a.heads + h) * kP + pc * 8);
-      v.unpack(f);
-      const float w = exp_fast(cum_last - __ldg(wcum + j)) * __ldg(wdt + j);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] *= w;
+    for (int q = 0; q < XU; ++q) {
+      const int id = id0 + q * 128;
+      const int pc = id / kQ, j = id % kQ;
+      const int t = t0 + j;
+      v[q].raw = make_uint4(0, 0, 0, 0);
+      w[q] = 0.f;
+      if (t < a.len) {
+        v[q].load(Xg + (((int64_t)b * a.len + t) * a.heads + h) * kP + pc * 8);
+        w[q] = exp_fast(cum_last - __ldg(wcum + j)) * __ldg(wdt + j);
+      }
     }
-    Vec16<T> o;
-    o.pack(f);
-    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(sB) + ((size_t)pc * kQ + j) * 16) = o.raw;
+#pragma unroll
+    for (int q = 0; q < XU; ++q) {
+      const int id = id0 + q * 128;
+      const int pc = id / kQ, j = id % kQ;
+      float f[8];
+      v[q].unpack(f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] *= w[q];
+      Vec16<T> o;
+      o.pack(f);
+      *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(sB) + ((size_t)pc * kQ + j) * 16) = o.raw;
+    }
   }
+  cp_async_wait_all();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -236,32 +250,30 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const ssm_ssd_args a, int
   for (int id = tid; id < (kN / 8) * kBlk; id += 128) {  // C rows of this block
     const int nc = id / kBlk, i = id % kBlk;
     const int t = t0 + ib * kBlk + i;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (t < a.len) v = __ldg(reinterpret_cast<const uint4*>(Cg + (((int64_t)b * a.len + t) * a.groups + g) * kN + nc * 8));
-    *reinterpret_cast<uint4*>(sC + ((size_t)nc * kBlk + i) * 16) = v;
+    const bool okt = t < a.len;
+    cp_async16(sC + ((size_t)nc * kBlk + i) * 16, Cg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
   }
   for (int id = tid; id < (kN / 8) * KJ; id += 128) {  // B rows j < KJ
     const int nc = id / KJ, j = id % KJ;
     const int t = t0 + j;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (t < a.len) v = __ldg(reinterpret_cast<const uint4*>(Bg + (((int64_t)b * a.len + t) * a.groups + g) * kN + nc * 8));
-    *reinterpret_cast<uint4*>(sBJ + ((size_t)nc * KJ + j) * 16) = v;
+    const bool okt = t < a.len;
+    cp_async16(sBJ + ((size_t)nc * KJ + j) * 16, Bg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
   }
   for (int id = tid; id < (kP / 8) * KJ; id += 128) {  // x rows j < KJ
     const int pc = id / KJ, j = id % KJ;
     const int t = t0 + j;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (t < a.len) v = __ldg(reinterpret_cast<const uint4*>(Xg + (((int64_t)b * a.len + t) * a.heads + h) * kP + pc * 8));
-    *reinterpret_cast<uint4*>(sX + ((size_t)pc * KJ + j) * 16) = v;
+    const bool okt = t < a.len;
+    cp_async16(sX + ((size_t)pc * KJ + j) * 16, Xg + (((int64_t)b * a.len + (okt ? t : 0)) * a.heads + h) * kP + pc * 8, okt);
   }
   {  // incoming state (P x N, n contiguous) as K-major B operand [n/8][p][8]
     const T* Sg = reinterpret_cast<const T*>(a.ws_state_in) + ((((int64_t)b * nchunks + c) * a.heads + h) * kP) * kN;
     for (int id = tid; id < (kN / 8) * kP; id += 128) {
       const int nc = id / kP, p = id % kP;
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(Sg + (int64_t)p * kN + nc * 8));
-      *reinterpret_cast<uint4*>(sS + ((size_t)nc * kP + p) * 16) = v;
+      cp_async16(sS + ((size_t)nc * kP + p) * 16, Sg + (int64_t)p * kN + nc * 8, true);
     }
   }
+  cp_async_commit();
+  cp_async_wait_all();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -385,12 +397,12 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const ssm_ssd_args a, int
 template <typename T>
 static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
   const int nchunks = (a.len + kQ - 1) / kQ;
-  {
+  if (a.phase != 2) {
     const int warps = a.batch * a.heads * nchunks;
     ssd_cumsum_kernel<T><<<(warps * 32 + 127) / 128, 128, 0, st>>>(a, nchunks);
     if (int rc = launch_status("ssd_cumsum_kernel")) return rc;
   }
-  {
+  if (a.phase != 2) {
     const size_t smem = (kN / 8 + kP / 8) * kQ * 16;
     cudaFuncSetAttribute(ssd_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ssd_state_kernel<T><<<dim3(nchunks, a.heads, a.batch), 128, smem, st>>>(a, nchunks);
@@ -401,7 +413,7 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
     ssd_pass_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a, nchunks);
     if (int rc = launch_status("ssd_pass_kernel")) return rc;
   }
-  {
+  if (a.phase != 1) {
     const size_t smem = ScanSmem<T>::TOTAL;
     cudaFuncSetAttribute(ssd_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ssd_scan_kernel<T><<<dim3(kQ / kBlk, a.heads, a.batch * nchunks), 128, smem, st>>>(a, nchunks);
@@ -432,9 +444,10 @@ extern "C" int ssm_ssd_fwd(const ssm_ssd_args* a, ssm_stream_t stream) {
   SSM_REQUIRE(ssm_ssd_supported(a->headdim, a->nstate, a->chunk_size, a->io_dtype), SSM_ERR_UNSUPPORTED,
               "ssd_scan: the tensor-core path is built for headdim 64, d_state 128, chunk 256, bf16 / fp16");
   if (a->batch == 0 || a->len == 0) return SSM_OK;
-  SSM_REQUIRE(a->X && a->dt && a->A && a->Bm && a->Cm && a->Y, SSM_ERR_NULL, "ssd_scan: missing tensor");
+  SSM_REQUIRE(a->phase >= 0 && a->phase <= 2, SSM_ERR_SHAPE, "ssd_scan: phase must be 0, 1 or 2");
+  SSM_REQUIRE(a->X && a->dt && a->A && a->Bm && a->Cm && (a->Y || a->phase == 1), SSM_ERR_NULL, "ssd_scan: missing tensor");
   SSM_REQUIRE(a->ws_dt && a->ws_cum && a->ws_state && a->ws_state_in, SSM_ERR_NULL, "ssd_scan: missing scratch");
-  SSM_REQUIRE(aligned_to(a->X, 16) && aligned_to(a->Bm, 16) && aligned_to(a->Cm, 16) && aligned_to(a->Y, 16) && aligned_to(a->ws_state_in, 16) &&
+  SSM_REQUIRE(aligned_to(a->X, 16) && aligned_to(a->Bm, 16) && aligned_to(a->Cm, 16) && (!a->Y || aligned_to(a->Y, 16)) && aligned_to(a->ws_state_in, 16) &&
                   (!a->z || aligned_to(a->z, 16)),
               SSM_ERR_ALIGN, "ssd_scan: tensors must be 16-byte aligned");
   const int64_t nchunks = (a->len + kQ - 1) / kQ;

@@ -66,6 +66,63 @@ __global__ void __launch_bounds__(kStepThreads) step_fwd_kernel(const ssm_step_a
   }
 }
 
+// Fast path: every lane owns NV float4 groups of its row's state, all loaded before any is used so
+// that each thread keeps NV * 16 bytes of the dominant stream in flight; the LPR lanes of a row
+// read adjacent groups.  Needs nstate == 4 * NV * LPR.
+template <typename T, int NV, int LPR>
+__global__ void __launch_bounds__(kStepThreads) step_fwd_vec_kernel(const ssm_step_args a) {
+  const int64_t gid = (int64_t)blockIdx.x * kStepThreads + threadIdx.x;
+  const int64_t rows = (int64_t)a.batch * a.dim;
+  const int64_t row_raw = gid / LPR;
+  const bool live = row_raw < rows;
+  const int64_t row = live ? row_raw : rows - 1;
+  const int sg = (int)(gid % LPR);
+  const int b = (int)(row / a.dim), d = (int)(row % a.dim);
+  constexpr int N = 4 * NV * LPR;
+  const int head = a.param_heads > 0 ? d / (a.dim / a.param_heads) : d;
+  const int64_t prow = a.param_heads > 0 ? (int64_t)b * a.param_heads + head : row;
+  float* st = a.state + row * N;
+  float4 s[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) s[v] = *reinterpret_cast<const float4*>(st + (sg + v * LPR) * 4);
+  const float x = to_f<T>(reinterpret_cast<const T*>(a.x)[row]);
+  float dt = to_f<T>(reinterpret_cast<const T*>(a.dt)[prow]);
+  if (a.dt_bias) dt += __ldg(a.dt_bias + head);
+  if (a.dt_softplus) dt = softplus_fast(dt);
+  const float dtx = dt * x;
+  const int g = d / (a.dim / a.bc_groups);
+  const int64_t boff = (int64_t)b * a.b_sb + (int64_t)g * a.b_sg;
+  const int64_t coff = (int64_t)b * a.c_sb + (int64_t)g * a.c_sg;
+  const float Ahead = a.param_heads > 0 ? __ldg(a.A + head) * kLog2e : 0.f;
+  float y = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int n0 = (sg + v * LPR) * 4;
+    float An[4];
+    if (a.param_heads > 0) {
+      An[0] = An[1] = An[2] = An[3] = Ahead;
+    } else {
+      const float4 q = __ldg(reinterpret_cast<const float4*>(a.A + (int64_t)d * N + n0));
+      An[0] = q.x * kLog2e, An[1] = q.y * kLog2e, An[2] = q.z * kLog2e, An[3] = q.w * kLog2e;
+    }
+    float sv[4] = {s[v].x, s[v].y, s[v].z, s[v].w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float Bn = load_dyn(a.Bm, boff + (int64_t)(n0 + i) * a.b_sn, a.bc_dtype);
+      const float Cn = load_dyn(a.Cm, coff + (int64_t)(n0 + i) * a.c_sn, a.bc_dtype);
+      sv[i] = fmaf(ex2_approx(dt * An[i]), sv[i], dtx * Bn);
+      y = fmaf(Cn, sv[i], y);
+    }
+    if (live) *reinterpret_cast<float4*>(st + n0) = make_float4(sv[0], sv[1], sv[2], sv[3]);
+  }
+  y = group_sum<LPR, 1>(y);
+  if (sg == 0 && live) {
+    if (a.D) y = fmaf(__ldg(a.D + head), x, y);
+    if (a.z) y *= silu_fast(to_f<T>(reinterpret_cast<const T*>(a.z)[row]));
+    reinterpret_cast<T*>(a.out)[row] = from_f<T>(y);
+  }
+}
+
 // Backward of the plain step.  One group of LPR lanes per row, parameter gradients by atomics.
 template <typename T, int LPR>
 __global__ void __launch_bounds__(kStepThreads) step_bwd_kernel(const ssm_step_bwd_args g) {
@@ -159,8 +216,27 @@ static int step_bwd_launch(const ssm_step_bwd_args& g, cudaStream_t st) {
   return launch_status("step_bwd_kernel");
 }
 
+template <typename T, int NV, int LPR>
+static int step_fwd_vec_launch(const ssm_step_args& a, cudaStream_t st) {
+  const int64_t threads = (int64_t)a.batch * a.dim * LPR;
+  step_fwd_vec_kernel<T, NV, LPR><<<(unsigned)((threads + kStepThreads - 1) / kStepThreads), kStepThreads, 0, st>>>(a);
+  return launch_status("step_fwd_vec_kernel");
+}
+
 template <typename T>
 static int step_fwd_t(const ssm_step_args& a, cudaStream_t st) {
+  if (aligned_to(a.state, 16) && aligned_to(a.A, 16)) {
+    switch (a.nstate) {
+      case 4: return step_fwd_vec_launch<T, 1, 1>(a, st);
+      case 8: return step_fwd_vec_launch<T, 2, 1>(a, st);
+      case 16: return step_fwd_vec_launch<T, 4, 1>(a, st);
+      case 32: return step_fwd_vec_launch<T, 4, 2>(a, st);
+      case 64: return step_fwd_vec_launch<T, 4, 4>(a, st);
+      case 128: return step_fwd_vec_launch<T, 4, 8>(a, st);
+      case 256: return step_fwd_vec_launch<T, 4, 16>(a, st);
+      default: break;
+    }
+  }
   const int vec = (a.nstate % 4 == 0) && aligned_to(a.state, 16);
   switch (step_lpr(a.nstate, vec != 0)) {
     case 1: return step_fwd_launch<T, 1>(a, vec, st);

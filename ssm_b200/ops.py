@@ -938,34 +938,58 @@ def _ssd_via_scan(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states):
     return y.reshape(nb, nh, npj, nl).permute(0, 3, 1, 2).contiguous(), last.reshape(nb, nh, npj, nn)
 
 
+class _SsdWorkspace:
+    """Scratch and bookkeeping of one tensor-core SSD call, kept so that a sequence shard can run
+    the state phase, exchange states, and then finish from the same scratch."""
+
+    def __init__(self, X, dt, A, B, C_, D, z, dt_bias, dt_softplus, chunk_size):
+        nb, nl, nh, npj = X.shape
+        self.shape = (nb, nl, nh, npj, B.shape[2], B.shape[3])
+        lib = L.load()
+        io = X.dtype
+        self.io, self.chunk = io, int(chunk_size)
+        self.X, self.dt, self.B, self.C = _c(X), _c(dt.to(io)), _c(B.to(io)), _c(C_.to(io))
+        self.z = None if z is None else _c(z.to(io))
+        self.A, self.D, self.bias = _f32(A), _f32(D), _f32(dt_bias)
+        self.d_has_p = int(D is not None and D.ndim == 2)
+        self.softplus = int(bool(dt_softplus))
+        self.nchunks = (nl + self.chunk - 1) // self.chunk
+        self.ws = torch.empty(int(lib.ssm_ssd_scratch_bytes(nb, nl, nh)), dtype=torch.uint8, device=X.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=X.device)
+
+    def run(self, phase: int, initial_states: Optional[Tensor], want_y: bool):
+        nb, nl, nh, npj, ng, nn = self.shape
+        dev = self.X.device
+        init32 = _f32(initial_states)
+        Y = torch.empty_like(self.X) if want_y else None
+        final = torch.empty(nb, nh, npj, nn, dtype=torch.float32, device=dev)
+        vec = nb * nh * self.nchunks * self.chunk * 4
+        st = nb * self.nchunks * nh * npj * nn
+        a = L.SsdArgs()
+        a.batch, a.len, a.heads, a.headdim = nb, nl, nh, npj
+        a.nstate, a.groups, a.chunk_size, a.io_dtype = nn, ng, self.chunk, _CODES[self.io]
+        a.dt_softplus, a.d_has_p, a.phase = self.softplus, self.d_has_p, phase
+        a.X, a.dt, a.A, a.Bm, a.Cm = _p(self.X), _p(self.dt), _p(self.A), _p(self.B), _p(self.C)
+        a.D, a.z, a.dt_bias, a.initial_states = _p(self.D), _p(self.z), _p(self.bias), _p(init32)
+        a.Y, a.final_states = _p(Y), _p(final)
+        base = self.ws.data_ptr()
+        a.ws_dt, a.ws_cum, a.ws_state, a.ws_state_in = base, base + vec, base + 2 * vec, base + 2 * vec + st * 4
+        a.status = _p(self.status)
+        _call(L.load().ssm_ssd_fwd, a)
+        return Y, final
+
+    def total_log_decay(self) -> Tensor:
+        """(B, H) sum over the shard of delta * A, read from the cumulative sums left in scratch."""
+        nb, nl, nh, _, _, _ = self.shape
+        vec = nb * nh * self.nchunks * self.chunk
+        cum = self.ws[vec * 4: 2 * vec * 4].view(torch.float32).view(nb, nh, self.nchunks, self.chunk)
+        return cum[..., -1].sum(-1)
+
+
 def _ssd_tensor_core(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states, chunk_size):
-    nb, nl, nh, npj = X.shape
-    ng, nn = B.shape[2], B.shape[3]
-    lib = L.load()
-    dev = X.device
-    io = X.dtype
-    Xc, dtc, Bc, Cc = _c(X), _c(dt.to(io)), _c(B.to(io)), _c(C_.to(io))
-    zc = None if z is None else _c(z.to(io))
-    A32, D32, b32, init32 = _f32(A), _f32(D), _f32(dt_bias), _f32(initial_states)
-    Y = torch.empty_like(Xc)
-    final = torch.empty(nb, nh, npj, nn, dtype=torch.float32, device=dev)
-    nchunks = (nl + chunk_size - 1) // chunk_size
-    ws = torch.empty(int(lib.ssm_ssd_scratch_bytes(nb, nl, nh)), dtype=torch.uint8, device=dev)
-    vec = nb * nh * nchunks * chunk_size * 4
-    st = nb * nchunks * nh * npj * nn
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    a = L.SsdArgs()
-    a.batch, a.len, a.heads, a.headdim = nb, nl, nh, npj
-    a.nstate, a.groups, a.chunk_size, a.io_dtype = nn, ng, chunk_size, _CODES[io]
-    a.dt_softplus, a.d_has_p = int(bool(dt_softplus)), int(D is not None and D.ndim == 2)
-    a.X, a.dt, a.A, a.Bm, a.Cm = _p(Xc), _p(dtc), _p(A32), _p(Bc), _p(Cc)
-    a.D, a.z, a.dt_bias, a.initial_states = _p(D32), _p(zc), _p(b32), _p(init32)
-    a.Y, a.final_states = _p(Y), _p(final)
-    base = ws.data_ptr()
-    a.ws_dt, a.ws_cum, a.ws_state, a.ws_state_in = base, base + vec, base + 2 * vec, base + 2 * vec + st * 4
-    a.status = _p(status)
-    _call(lib.ssm_ssd_fwd, a)
-    return Y, final, status
+    w = _SsdWorkspace(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, chunk_size)
+    Y, final = w.run(0, initial_states, True)
+    return Y, final, w.status
 
 
 def ssd_tensor_core_supported(X: Tensor, B: Tensor, chunk_size: int) -> bool:

@@ -1,0 +1,102 @@
+"""Sequence-sharded state-space-dual scan across GPUs (one process per GPU, ``torch.distributed``).
+
+The reference package has no distributed code at all; this is the multi-GPU form of the SSD hot
+path.  Rank ``r`` of ``R`` holds the contiguous tokens ``[r L/R, (r+1) L/R)`` of every sequence.
+The recurrence is linear in the state, so a shard acts on it as ``S_out = P * S_in + S_loc`` with
+``P = exp(sum_t delta_t A)`` per head and ``S_loc`` its final state from a zero start.  Each rank
+
+1. runs the state phase on its shard (no output yet),
+2. all-gathers ``(S_loc, log P)`` -- ``batch x heads x headdim x d_state`` fp32 per rank over
+   NCCL / NVLink -- and folds the shards before it into its true incoming state (the fold is
+   associative, so there is no serial hand-off chain),
+3. finishes from the scratch of step 1 with that incoming state and produces its slice of ``Y``.
+
+Received data always lands in this GPU's own memory through NCCL before any kernel reads it.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+Tensor = torch.Tensor
+
+
+def fold_incoming_state(states: Tensor, log_decay: Tensor, rank: int, initial: Optional[Tensor] = None) -> Tensor:
+    """Incoming state of shard ``rank``.
+
+    ``states``: ``R`` tensors ``(B, H, P, N)``, every shard's final state from a zero start; ``log_decay``: ``R`` tensors ``(B, H)``,
+    every shard's total ``sum delta A``.  ``initial`` is the state before shard 0.
+    ``S_in[r] = sum_{q<r} exp(sum_{q<m<r} logP_m) S_q  (+ exp(sum_{m<r} logP_m) initial)``.
+    """
+    s = torch.zeros_like(states[0]) if initial is None else initial.to(states[0].dtype).clone()
+    for q in range(rank):
+        s = torch.exp(log_decay[q])[..., None, None] * s + states[q]
+    return s
+
+
+def outgoing_state(incoming: Tensor, local: Tensor, log_decay: Tensor) -> Tensor:
+    """Final state of a shard given its incoming state."""
+    return torch.exp(log_decay)[..., None, None] * incoming + local
+
+
+def ssd_scan_sequence_parallel(
+    state_phase: Callable[[], tuple[Tensor, Tensor]],
+    finish_phase: Callable[[Tensor], tuple[Tensor, Tensor]],
+    group: Optional[dist.ProcessGroup] = None,
+    initial_states: Optional[Tensor] = None,
+):
+    """Generic driver: ``state_phase() -> (S_loc, logP)``; ``finish_phase(S_in) -> (Y, S_out)``.
+    Returns ``(Y_shard, S_out)`` where ``S_out`` on the last rank is the sequence's final state."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    s_loc, logp = state_phase()
+    if world == 1:
+        s_in = torch.zeros_like(s_loc) if initial_states is None else initial_states.to(s_loc.dtype)
+        return finish_phase(s_in)
+    all_s = [torch.empty_like(s_loc) for _ in range(world)]
+    all_p = [torch.empty_like(logp) for _ in range(world)]
+    dist.all_gather(all_s, s_loc.contiguous(), group=group)
+    dist.all_gather(all_p, logp.contiguous(), group=group)
+    s_in = fold_incoming_state(all_s, all_p, rank, initial_states)
+    return finish_phase(s_in)
+
+
+def ssd_scan_sharded(X, dt, A, B, C, chunk_size=256, D=None, z=None, dt_bias=None, dt_softplus=False,
+                     initial_states=None, group=None):
+    """Sequence-parallel :func:`ssm_b200.ops.ssd_scan` on this rank's shard (tensor-core path)."""
+    from . import ops
+
+    if not ops.ssd_tensor_core_supported(X, B, chunk_size):
+        raise ValueError("ssd_scan_sharded needs the tensor-core shape (headdim 64, d_state 128, chunk 256, bf16/fp16)")
+    ops._ssd_check(X, dt, A, B, C, D, z, dt_bias, None)
+    w = ops._SsdWorkspace(X, dt, A, B, C, D, z, dt_bias, dt_softplus, chunk_size)
+
+    def state_phase():
+        _, s_loc = w.run(1, None, False)
+        return s_loc, w.total_log_decay()
+
+    def finish_phase(s_in):
+        return w.run(2, s_in, True)
+
+    return ssd_scan_sequence_parallel(state_phase, finish_phase, group, initial_states)
+
+
+def exchange_conv_halo(x_shard: Tensor, width: int, group=None, channels_first: bool = True) -> Optional[Tensor]:
+    """Send this shard's last ``width-1`` inputs to the next rank; returns the halo ``(B, C, width-1)``
+    fp32 received from the previous rank (``None`` on rank 0), for ``dw_causal_conv(..., halo=)``."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    k = width - 1
+    if k == 0 or world == 1:
+        return None
+    tail = (x_shard[:, :, -k:] if channels_first else x_shard[:, -k:, :].transpose(1, 2)).float().contiguous()
+    recv = torch.empty_like(tail)
+    ops_ = []
+    if rank + 1 < world:
+        ops_.append(dist.P2POp(dist.isend, tail, dist.get_global_rank(group, rank + 1) if group else rank + 1, group))
+    if rank > 0:
+        ops_.append(dist.P2POp(dist.irecv, recv, dist.get_global_rank(group, rank - 1) if group else rank - 1, group))
+    for req in dist.batch_isend_irecv(ops_):
+        req.wait()
+    return recv if rank > 0 else None

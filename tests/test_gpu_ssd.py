@@ -91,3 +91,29 @@ def test_tensor_core_ssd_agrees_with_scan_kernel_path_and_has_gradients():
     Y.float().square().mean().backward()
     assert X.grad is not None and torch.isfinite(X.grad.float()).all() and float(X.grad.float().abs().max()) > 0
     assert A.grad is not None and torch.isfinite(A.grad).all()
+
+
+def test_two_phase_shards_reproduce_the_unsharded_scan():
+    """The state phase / finish phase split that sequence sharding uses, with two shards emulated on
+    one GPU: shard states folded on the host side must give the unsharded result."""
+    from ssm_b200 import ops, seqpar
+
+    t = {k: (None if v is None else v.cuda()) for k, v in _inputs(2, 1024, 3, 1, torch.bfloat16, seed=21).items()}
+    Yf, Sf = ops.ssd_scan(t["X"], t["dt"], t["A"], t["B"], t["C"], 256, D=t["D"], z=t["z"], dt_bias=t["dt_bias"], dt_softplus=True,
+                          initial_states=t["initial_states"], return_final_states=True)
+    h = 512
+    shards = []
+    for sl in (slice(0, h), slice(h, 1024)):
+        w = ops._SsdWorkspace(t["X"][:, sl], t["dt"][:, sl], t["A"], t["B"][:, sl], t["C"][:, sl], t["D"], t["z"][:, sl], t["dt_bias"], True, 256)
+        _, s_loc = w.run(1, None, False)
+        shards.append((w, s_loc, w.total_log_decay()))
+    states, logp = [s[1] for s in shards], [s[2] for s in shards]
+    ref_logp = (torch.nn.functional.softplus(t["dt"][:, :h].float() + t["dt_bias"]) * t["A"]).sum(1)
+    close(logp[0], ref_logp, rtol=1e-3, atol=1e-3, what="shard log-decay")
+    outs = []
+    for r, (w, _, _) in enumerate(shards):
+        s_in = seqpar.fold_incoming_state(states, logp, r, t["initial_states"])
+        outs.append(w.run(2, s_in, True))
+    close(torch.cat([outs[0][0], outs[1][0]], 1), Yf, **HALF_TOL, what="Y")
+    close(outs[1][1], Sf, **HALF_TOL, what="final state")
+    assert int(shards[0][0].status.item()) == 0 and int(shards[1][0].status.item()) == 0
