@@ -587,17 +587,20 @@ def run_ssd_sp(args):
     rank, world, local = dist_env()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev) if world > 1 else dist.init_process_group(
-        "gloo", init_method="tcp://127.0.0.1:29577", rank=0, world_size=1)
+    under_launcher = "RANK" in os.environ
+    if under_launcher:
+        dist.init_process_group("nccl", device_id=dev)
     B, Ltot, H, P, N = 2, args.seqlen or 131072, 80, 64, 128
     Lq = Ltot // world
-    g = torch.Generator().manual_seed(100 + rank)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)  # generated on the device: the shard is several GB
     bf = torch.bfloat16
-    X = torch.randn(B, Lq, H, P, generator=g).to(bf).to(dev)
-    z = torch.randn(B, Lq, H, P, generator=g).to(bf).to(dev)
-    dt = (torch.randn(B, Lq, H, generator=g) - 3).to(bf).to(dev)
-    Bm = (torch.randn(B, Lq, 1, N, generator=g) / N ** 0.5).to(bf).to(dev)
-    Cm = (torch.randn(B, Lq, 1, N, generator=g) / N ** 0.5).to(bf).to(dev)
+    X = torch.randn(B, Lq, H, P, generator=g, device=dev, dtype=bf)
+    z = torch.randn(B, Lq, H, P, generator=g, device=dev, dtype=bf)
+    dt = (torch.randn(B, Lq, H, generator=g, device=dev) - 3).to(bf)
+    Bm = (torch.randn(B, Lq, 1, N, generator=g, device=dev) / N ** 0.5).to(bf)
+    Cm = (torch.randn(B, Lq, 1, N, generator=g, device=dev) / N ** 0.5).to(bf)
+    if rank == 0:
+        print(f"[ssd_sp] inputs ready: shard length {Lq}", file=sys.stderr, flush=True)
     g0 = torch.Generator().manual_seed(7)
     A = (-torch.exp(torch.rand(H, generator=g0) * 2.7726)).to(dev)
     D = torch.randn(H, generator=g0).to(dev)
@@ -605,8 +608,12 @@ def run_ssd_sp(args):
     def step():
         return seqpar.ssd_scan_sharded(X, dt, A, Bm, Cm, 256, D=D, z=z, dt_softplus=True)
 
-    for _ in range(args.warmup):
+    tw = time.perf_counter()
+    for i in range(args.warmup):
         step()
+        torch.cuda.synchronize()
+        if rank == 0:
+            print(f"[ssd_sp] warm-up {i}: {time.perf_counter() - tw:.3f} s since start", file=sys.stderr, flush=True)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -640,7 +647,8 @@ def run_ssd_sp(args):
             "roofline": {"kernel": "ssm_ssd_fwd phases 1+2 per shard", "bound": "hbm", "achieved": bytes_alg / (ms * 1e-3) / 1e9, "peak": peak,
                          "unit": "GB/s", "frac": bytes_alg / (ms * 1e-3) / 1e9 / peak, "peak_kind": kind, "traffic": None},
             "clocks": clocks}))
-    dist.destroy_process_group()
+    if under_launcher:
+        dist.destroy_process_group()
 
 
 def main():

@@ -9,7 +9,7 @@
 //   ssd_state_kernel    per (batch, chunk, head): local state  S_c = sum_j exp(cum_last - cum_j) delta_j x_j B_j^T   [N x P GEMM, K = Q]
 //   ssd_pass_kernel     the short serial pass over chunks: incoming state of every chunk (kept in
 //                       the operand dtype for the GEMM below) and the final state in fp32
-//   ssd_scan_kernel     per (batch, chunk, head, 128-row block):  G = C B^T  (TMEM), the decay mask
+//   ssd_scan_kernel     per (batch, chunk, head), one warpgroup per 128-row block:  G = C B^T  (TMEM), the decay mask
 //                       exp(cum_i - cum_j) delta_j [j <= i] applied on the TMEM -> register path and
 //                       re-packed as the A operand of  Y_intra = (G o L) X, plus  Y_inter = C S_in;
 //                       y = Y_intra + exp(cum_i) Y_inter + D x, gated, stored.
@@ -198,39 +198,47 @@ __global__ void __launch_bounds__(256) ssd_pass_kernel(const ssm_ssd_args a, int
 }
 
 // ---------------------------------------------------------------------------------------------
-// chunk scan: one CTA per (row block, head, batch * chunk)
+// chunk scan: one CTA of two warpgroups per (head, batch * chunk); warpgroup w owns rows
+// [128 w, 128 w + 128) of the chunk.  Both share the staged C, B, x and incoming-state tiles.
+//   TMEM columns: G0 [0,128) (rows 0..127 x steps 0..127), G1 [128,384) (rows 128..255 x steps
+//   0..255), C S_in of block 0 [384,448) and of block 1 [448,512); (G o L) X of block w is
+//   accumulated over the first 64 columns of G_w once the warpgroup has consumed G_w.
+//   Shared memory: the masked tile of block 0 overwrites the C tile, that of block 1 the B tile
+//   (both dead once the first group of MMAs has completed).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 struct ScanSmem {
-  static constexpr int C_BYTES = kBlk * kN * 2;   // C rows of the block, K-major [n/8][i][8]        32 KB
-  static constexpr int BJ_BYTES = kQ * kN * 2;    // B rows j, K-major [n/8][j][8]; reused for (G o L) 64 KB
-  static constexpr int X_BYTES = kQ * kP * 2;     // x rows j, MN-major [p/8][j][8]                  32 KB
-  static constexpr int S_BYTES = kP * kN * 2;     // incoming state, K-major [n/8][p][8]             16 KB
-  static constexpr int VEC_BYTES = 2 * kQ * 4;    // cum and delta of the chunk
-  static constexpr int TOTAL = C_BYTES + BJ_BYTES + X_BYTES + S_BYTES + VEC_BYTES;
+  static constexpr int C_BYTES = kQ * kN * 2;   // C rows of the chunk, K-major [n/8][i][8]   64 KB
+  static constexpr int B_BYTES = kQ * kN * 2;   // B rows of the chunk, K-major [n/8][j][8]   64 KB
+  static constexpr int X_BYTES = kQ * kP * 2;   // x rows, MN-major [p/8][j][8]               32 KB
+  static constexpr int S_BYTES = kP * kN * 2;   // incoming state, K-major [n/8][p][8]        16 KB
+  static constexpr int VEC_BYTES = 2 * kQ * 4;  // cum and delta of the chunk
+  static constexpr int TOTAL = C_BYTES + B_BYTES + X_BYTES + S_BYTES + VEC_BYTES;
 };
 
+__device__ __forceinline__ void named_barrier(int id, int nthreads) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory"); }
+
 template <typename T>
-__global__ void __launch_bounds__(128) ssd_scan_kernel(const ssm_ssd_args a, int nchunks) {
+__global__ void __launch_bounds__(256) ssd_scan_kernel(const ssm_ssd_args a, int nchunks) {
   using M = ScanSmem<T>;
   extern __shared__ __align__(128) unsigned char smraw[];
   unsigned char* sC = smraw;
-  unsigned char* sBJ = sC + M::C_BYTES;  // B tile, later the masked G tile (K-major over j)
-  unsigned char* sX = sBJ + M::BJ_BYTES;
+  unsigned char* sB = sC + M::C_BYTES;
+  unsigned char* sX = sB + M::B_BYTES;
   unsigned char* sS = sX + M::X_BYTES;
   float* sCum = reinterpret_cast<float*>(sS + M::S_BYTES);
   float* sDt = sCum + kQ;
-  __shared__ __align__(8) uint64_t mbar[2];
+  __shared__ __align__(8) uint64_t mbar[3];
   __shared__ uint32_t tmem_slot;
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int ib = blockIdx.x;  // row block within the chunk
-  const int h = blockIdx.y;
-  const int c = blockIdx.z % nchunks, b = blockIdx.z / nchunks;
+  const int wg = tid >> 7, wtid = tid & 127;  // warpgroup = row block
+  const int h = blockIdx.x;
+  const int c = blockIdx.y % nchunks, b = blockIdx.y / nchunks;
   const int g = h / (a.heads / a.groups);
   const int t0 = c * kQ;
-  const int KJ = (ib + 1) * kBlk;  // causal: only steps j < KJ can reach this row block
-  const int i_loc = ib * kBlk + tid;  // this thread's row within the chunk
+  const int KJ = (wg + 1) * kBlk;      // causal: steps j < KJ can reach this warpgroup's rows
+  const int i_loc = wg * kBlk + wtid;  // this thread's row within the chunk
   const int t_row = t0 + i_loc;
   constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
 
@@ -238,36 +246,33 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const ssm_ssd_args a, int
   if (tid == 0) {
     tc::mbar_init(tc::smem_u32(&mbar[0]), 1);
     tc::mbar_init(tc::smem_u32(&mbar[1]), 1);
+    tc::mbar_init(tc::smem_u32(&mbar[2]), 1);
   }
 
-  // ---- stage operands ---------------------------------------------------------------------------
+  // ---- stage operands (asynchronous 16-byte copies, step index fastest across threads) ----------
   const float* wdt = a.ws_dt + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
   const float* wcum = a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
-  for (int i = tid; i < kQ; i += 128) sCum[i] = __ldg(wcum + i), sDt[i] = __ldg(wdt + i);
+  sCum[tid] = __ldg(wcum + tid), sDt[tid] = __ldg(wdt + tid);
   const T* Cg = reinterpret_cast<const T*>(a.Cm);
   const T* Bg = reinterpret_cast<const T*>(a.Bm);
   const T* Xg = reinterpret_cast<const T*>(a.X);
-  for (int id = tid; id < (kN / 8) * kBlk; id += 128) {  // C rows of this block
-    const int nc = id / kBlk, i = id % kBlk;
-    const int t = t0 + ib * kBlk + i;
-    const bool okt = t < a.len;
-    cp_async16(sC + ((size_t)nc * kBlk + i) * 16, Cg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
-  }
-  for (int id = tid; id < (kN / 8) * KJ; id += 128) {  // B rows j < KJ
-    const int nc = id / KJ, j = id % KJ;
+  for (int id = tid; id < (kN / 8) * kQ; id += 256) {
+    const int nc = id / kQ, j = id % kQ;
     const int t = t0 + j;
     const bool okt = t < a.len;
-    cp_async16(sBJ + ((size_t)nc * KJ + j) * 16, Bg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
+    const int64_t off = (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8;
+    cp_async16(sC + ((size_t)nc * kQ + j) * 16, Cg + off, okt);
+    cp_async16(sB + ((size_t)nc * kQ + j) * 16, Bg + off, okt);
   }
-  for (int id = tid; id < (kP / 8) * KJ; id += 128) {  // x rows j < KJ
-    const int pc = id / KJ, j = id % KJ;
+  for (int id = tid; id < (kP / 8) * kQ; id += 256) {
+    const int pc = id / kQ, j = id % kQ;
     const int t = t0 + j;
     const bool okt = t < a.len;
-    cp_async16(sX + ((size_t)pc * KJ + j) * 16, Xg + (((int64_t)b * a.len + (okt ? t : 0)) * a.heads + h) * kP + pc * 8, okt);
+    cp_async16(sX + ((size_t)pc * kQ + j) * 16, Xg + (((int64_t)b * a.len + (okt ? t : 0)) * a.heads + h) * kP + pc * 8, okt);
   }
-  {  // incoming state (P x N, n contiguous) as K-major B operand [n/8][p][8]
+  {
     const T* Sg = reinterpret_cast<const T*>(a.ws_state_in) + ((((int64_t)b * nchunks + c) * a.heads + h) * kP) * kN;
-    for (int id = tid; id < (kN / 8) * kP; id += 128) {
+    for (int id = tid; id < (kN / 8) * kP; id += 256) {
       const int nc = id / kP, p = id % kP;
       cp_async16(sS + ((size_t)nc * kP + p) * 16, Sg + (int64_t)p * kN + nc * 8, true);
     }
@@ -279,38 +284,37 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const ssm_ssd_args a, int
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tG = tmem;         // columns [0, 256): G = C B^T
-  const uint32_t tYi = tmem + 256;  // columns [256, 320): (G o L) X
-  const uint32_t tYs = tmem + 320;  // columns [320, 384): C S_in
+  const uint32_t tG = tmem + (wg == 0 ? 0 : 128);    // this warpgroup's G, later its (G o L) X
+  const uint32_t tYs = tmem + 384 + wg * 64;         // this warpgroup's C S_in
 
-  // ---- G = C B^T and Y_inter = C S_in ------------------------------------------------------------
+  // ---- G = C B^T and Y_inter = C S_in for both row blocks ------------------------------------------
   if (tid == 0) {
-    const uint32_t c0 = tc::smem_u32(sC), b0 = tc::smem_u32(sBJ), s0 = tc::smem_u32(sS);
-    const uint32_t idG = tc::instr_desc(kBlk, KJ, fmt, 0, 0);
+    const uint32_t c0 = tc::smem_u32(sC), b0 = tc::smem_u32(sB), s0 = tc::smem_u32(sS);
     const uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 0);
 #pragma unroll 1
-    for (int kk = 0; kk < kN / 16; ++kk) {
-      const uint64_t da = tc::smem_desc(c0 + kk * 2 * (kBlk * 16), kBlk * 16, 128);
-      const uint64_t db = tc::smem_desc(b0 + kk * 2 * (KJ * 16), KJ * 16, 128);
-      tc::mma_ss(tG, da, db, idG, kk > 0);
+    for (int blk = 0; blk < 2; ++blk) {
+      const uint32_t idG = tc::instr_desc(kBlk, (blk + 1) * kBlk, fmt, 0, 0);
+      const uint32_t dG = tmem + (blk == 0 ? 0 : 128), dS = tmem + 384 + blk * 64;
+#pragma unroll 1
+      for (int kk = 0; kk < kN / 16; ++kk) {
+        const uint64_t da = tc::smem_desc(c0 + blk * (kBlk * 16) + kk * 2 * (kQ * 16), kQ * 16, 128);
+        const uint64_t db = tc::smem_desc(b0 + kk * 2 * (kQ * 16), kQ * 16, 128);
+        const uint64_t ds = tc::smem_desc(s0 + kk * 2 * (kP * 16), kP * 16, 128);
+        tc::mma_ss(dG, da, db, idG, kk > 0);
+        tc::mma_ss(dS, da, ds, idS, kk > 0);
+      }
     }
     tc::commit(tc::smem_u32(&mbar[0]));
-#pragma unroll 1
-    for (int kk = 0; kk < kN / 16; ++kk) {
-      const uint64_t da = tc::smem_desc(c0 + kk * 2 * (kBlk * 16), kBlk * 16, 128);
-      const uint64_t ds = tc::smem_desc(s0 + kk * 2 * (kP * 16), kP * 16, 128);
-      tc::mma_ss(tYs, da, ds, idS, kk > 0);
-    }
   }
   bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[0]), 0));  // warp-uniform
   tc::fence_after_sync();
 
-  // ---- decay mask on the TMEM -> register path; masked G becomes the A operand (K-major over j) ----
-  // The B tile is dead once G is complete, so the masked tile is written over it: unit (i, j/8) at
-  // (j/8) * (128 * 16) + i * 16.
+  // ---- decay mask on the TMEM -> register path; the masked tile (K-major over j, 128 rows) replaces
+  // ---- a dead operand tile: unit (i, j/8) at (j/8) * (128 * 16) + i * 16 -----------------------------
+  unsigned char* sA = wg == 0 ? sC : sB;
   const float cum_i = sCum[i_loc];
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
   if (ok) {
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     for (int jb = 0; jb < KJ; jb += 32) {
       float v[32];
       tc::tmem_ld32(tG + lane_base + jb, v);
@@ -325,61 +329,66 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const ssm_ssd_args a, int
         }
         Vec16<T> o;
         o.pack(f);
-        *reinterpret_cast<uint4*>(sBJ + ((size_t)((jb + q) / 8) * kBlk + tid) * 16) = o.raw;
+        *reinterpret_cast<uint4*>(sA + ((size_t)((jb + q) / 8) * kBlk + wtid) * 16) = o.raw;
       }
     }
   }
   tc::fence_async_smem();
   tc::fence_before_sync();
-  __syncthreads();
+  // Both warpgroups must have left the first MMA group's operands before either overwrites them
+  // (block 0's masked tile lands on the C tile that block 1's G also read): that is guaranteed by
+  // the wait on mbar[0] above, which covers all of those MMAs.  From here the warpgroups run apart.
+  named_barrier(1 + wg, 128);
   tc::fence_after_sync();
 
-  // ---- Y_intra = (G o L) X ---------------------------------------------------------------------
-  if (tid == 0) {
-    const uint32_t g0 = tc::smem_u32(sBJ), x0 = tc::smem_u32(sX);
+  // ---- Y_intra = (G o L) X over this warpgroup's own columns ----------------------------------------
+  if (wtid == 0) {
+    const uint32_t g0 = tc::smem_u32(sA), x0 = tc::smem_u32(sX);
     const uint32_t idY = tc::instr_desc(kBlk, kP, fmt, 0, 1);
 #pragma unroll 1
     for (int kk = 0; kk < KJ / 16; ++kk) {
       const uint64_t da = tc::smem_desc(g0 + kk * 2 * (kBlk * 16), kBlk * 16, 128);
-      const uint64_t dx = tc::smem_desc(x0 + kk * 256, 128, KJ * 16);
-      tc::mma_ss(tYi, da, dx, idY, kk > 0);
+      const uint64_t dx = tc::smem_desc(x0 + kk * 256, 128, kQ * 16);
+      tc::mma_ss(tG, da, dx, idY, kk > 0);
     }
-    tc::commit(tc::smem_u32(&mbar[1]));  // also covers the C S_in instructions issued earlier
+    tc::commit(tc::smem_u32(&mbar[1 + wg]));
   }
-  ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[1]), 0)) && ok;
+  ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[1 + wg]), 0)) && ok;
   tc::fence_after_sync();
   if (!ok && a.status) atomicExch(a.status, 2);
 
-  // ---- epilogue: y = Y_intra + exp(cum_i) Y_inter + D x, gate, store ------------------------------
+  // ---- epilogue: y = Y_intra + exp(cum_i) Y_inter + D x, gate, store ----------------------------------
   if (ok) {
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     const bool live = t_row < a.len;  // the TMEM loads below are warp-wide; only the stores are per row
     const float escale = exp_fast(cum_i);
     const T* zrow = a.z ? reinterpret_cast<const T*>(a.z) + (((int64_t)b * a.len + t_row) * a.heads + h) * kP : nullptr;
     T* yrow = reinterpret_cast<T*>(a.Y) + (((int64_t)b * a.len + t_row) * a.heads + h) * kP;
+    const float Dh = (a.D && !a.d_has_p) ? __ldg(a.D + h) : 0.f;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       float yi[32], ys[32];
-      tc::tmem_ld32(tYi + lane_base + half * 32, yi);
+      tc::tmem_ld32(tG + lane_base + half * 32, yi);
       tc::tmem_ld32(tYs + lane_base + half * 32, ys);
+      Vec16<T> zr[4];
+      if (zrow && live) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) zr[q].load(zrow + half * 32 + q * 8);
+      }
 #pragma unroll
       for (int q = 0; q < 32; q += 8) {
         const int p0 = half * 32 + q;
         float f[8], xv[8];
         Vec16<T> xr;
-        xr.raw = *reinterpret_cast<const uint4*>(sX + ((size_t)(p0 / 8) * KJ + i_loc) * 16);
+        xr.raw = *reinterpret_cast<const uint4*>(sX + ((size_t)(p0 / 8) * kQ + i_loc) * 16);
         xr.unpack(xv);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          float Dv = 0.f;
-          if (a.D) Dv = a.d_has_p ? __ldg(a.D + h * kP + p0 + e) : __ldg(a.D + h);
+          const float Dv = (a.D && a.d_has_p) ? __ldg(a.D + h * kP + p0 + e) : Dh;
           f[e] = fmaf(escale, ys[q + e], yi[q + e]) + Dv * xv[e];
         }
         if (zrow && live) {
-          Vec16<T> zr;
-          zr.load(zrow + p0);
           float zv[8];
-          zr.unpack(zv);
+          zr[q / 8].unpack(zv);
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] *= silu_fast(zv[e]);
         }
@@ -416,7 +425,7 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
   if (a.phase != 1) {
     const size_t smem = ScanSmem<T>::TOTAL;
     cudaFuncSetAttribute(ssd_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ssd_scan_kernel<T><<<dim3(kQ / kBlk, a.heads, a.batch * nchunks), 128, smem, st>>>(a, nchunks);
+    ssd_scan_kernel<T><<<dim3(a.heads, a.batch * nchunks), 256, smem, st>>>(a, nchunks);
     if (int rc = launch_status("ssd_scan_kernel")) return rc;
   }
   return SSM_OK;

@@ -50,7 +50,8 @@ def ssd_scan_sequence_parallel(
 ):
     """Generic driver: ``state_phase() -> (S_loc, logP)``; ``finish_phase(S_in) -> (Y, S_out)``.
     Returns ``(Y_shard, S_out)`` where ``S_out`` on the last rank is the sequence's final state."""
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    alone = not (dist.is_available() and dist.is_initialized())
+    rank, world = (0, 1) if alone else (dist.get_rank(group), dist.get_world_size(group))
     s_loc, logp = state_phase()
     if world == 1:
         s_in = torch.zeros_like(s_loc) if initial_states is None else initial_states.to(s_loc.dtype)
@@ -86,7 +87,8 @@ def ssd_scan_sharded(X, dt, A, B, C, chunk_size=256, D=None, z=None, dt_bias=Non
 def exchange_conv_halo(x_shard: Tensor, width: int, group=None, channels_first: bool = True) -> Optional[Tensor]:
     """Send this shard's last ``width-1`` inputs to the next rank; returns the halo ``(B, C, width-1)``
     fp32 received from the previous rank (``None`` on rank 0), for ``dw_causal_conv(..., halo=)``."""
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    alone = not (dist.is_available() and dist.is_initialized())
+    rank, world = (0, 1) if alone else (dist.get_rank(group), dist.get_world_size(group))
     k = width - 1
     if k == 0 or world == 1:
         return None
