@@ -52,7 +52,8 @@ const char* ssm_b200_last_error(void);
  *   dl_t = softplus?(delta_t + dt_bias);  h_t = exp(dl_t*A) .* h_{t-1} + dl_t*B_t*u_t
  *   y_t  = <C_t, h_t> + D*u_t;            out_t = y_t * silu(z_t)
  *
- * u, delta, z, out: (batch, dim, len) contiguous, element type io_dtype.  A: (dim, nstate)
+ * u, delta, z, out: (batch, dim, len) with contiguous time axis and the batch / channel strides
+ * row_sb / row_sd, element type io_dtype.  A: (dim, nstate)
  * fp32.  Bm / Cm are addressed as  base[b*sb + g*sg + n*sn + t*st]  (element strides, type
  * bc_dtype) with g = d / (dim / bc_groups); this one form covers the (D,N), (B,D,N) and
  * grouped time-varying (B,G,N,L) layouts of reference.py:22-56.  D, dt_bias: (dim) fp32
@@ -79,6 +80,11 @@ typedef struct {
   void* out;
   void* last_state;   /* nullable */
   float* checkpoints; /* nullable */
+  /* Element strides of the batch and channel axes of u, delta, z, out (and of dout, du, ddelta,
+   * dz in the backward call); the time axis is contiguous.  Dense (B, D, L) is {dim*len, len};
+   * a (D, B, L) buffer viewed as (B, D, L) is {len, batch*len}, which lets the projections
+   * around the scan be plain 2-D GEMMs with no transposing copies. */
+  int64_t row_sb, row_sd;
 } ssm_scan_fwd_args;
 
 int ssm_scan_checkpoint_interval(void);
@@ -234,6 +240,9 @@ typedef struct {
   const float* bias; /* nullable */
   const float* halo; /* nullable */
   void* y;
+  /* channels_first only: element strides of the batch and channel axes of x, y (and dy, dx);
+   * dense is {channels*len, len}.  Ignored for the channels-last layout. */
+  int64_t row_sb, row_sc;
 } ssm_conv_args;
 
 int ssm_dw_causal_conv_fwd(const ssm_conv_args* args, ssm_stream_t stream);

@@ -26,6 +26,7 @@ class ScanFwdArgs(C.Structure):
         ("c_sb", i64), ("c_sg", i64), ("c_sn", i64), ("c_st", i64),
         ("D", fp), ("dt_bias", fp), ("initial_state", fp),
         ("out", vp), ("last_state", vp), ("checkpoints", fp),
+        ("row_sb", i64), ("row_sd", i64),
     ]
 
 
@@ -88,6 +89,7 @@ class ConvArgs(C.Structure):
         ("batch", i32), ("channels", i32), ("len", i32), ("width", i32),
         ("io_dtype", i32), ("channels_first", i32), ("silu", i32), ("reserved0", i32),
         ("x", vp), ("weight", fp), ("bias", fp), ("halo", fp), ("y", vp),
+        ("row_sb", i64), ("row_sc", i64),
     ]
 
 

@@ -34,9 +34,10 @@ __global__ void __launch_bounds__(kConvThreads) conv_cf_fwd_kernel(const ssm_con
   constexpr int V = 16 / sizeof(T);
   const int64_t rowi = blockIdx.x;  // b * C + c
   const int c = (int)(rowi % a.channels);
+  const int64_t roff = (rowi / a.channels) * a.row_sb + (int64_t)c * a.row_sc;
   const int L = a.len, K = a.width;
-  const T* __restrict__ x = reinterpret_cast<const T*>(a.x) + rowi * L;
-  T* __restrict__ y = reinterpret_cast<T*>(a.y) + rowi * L;
+  const T* __restrict__ x = reinterpret_cast<const T*>(a.x) + roff;
+  T* __restrict__ y = reinterpret_cast<T*>(a.y) + roff;
   const float* halo = a.halo ? a.halo + rowi * (K - 1) : nullptr;
   float wr[KM];
 #pragma unroll
@@ -87,10 +88,11 @@ __global__ void __launch_bounds__(kConvThreads) conv_cf_bwd_kernel(const ssm_con
   const ssm_conv_args& a = g.fwd;
   const int64_t rowi = blockIdx.x;
   const int c = (int)(rowi % a.channels);
+  const int64_t roff = (rowi / a.channels) * a.row_sb + (int64_t)c * a.row_sc;
   const int L = a.len, K = a.width;
-  const T* __restrict__ x = reinterpret_cast<const T*>(a.x) + rowi * L;
-  const T* __restrict__ dy = reinterpret_cast<const T*>(g.dy) + rowi * L;
-  T* __restrict__ dx = reinterpret_cast<T*>(g.dx) + rowi * L;
+  const T* __restrict__ x = reinterpret_cast<const T*>(a.x) + roff;
+  const T* __restrict__ dy = reinterpret_cast<const T*>(g.dy) + roff;
+  T* __restrict__ dx = reinterpret_cast<T*>(g.dx) + roff;
   const float* halo = a.halo ? a.halo + rowi * (K - 1) : nullptr;
   float wr[KM], dwr[KM];
 #pragma unroll
@@ -412,6 +414,7 @@ static int conv_validate(const ssm_conv_args* a) {
   SSM_REQUIRE(a->width >= 1 && a->width <= kConvMaxK, SSM_ERR_UNSUPPORTED, "dw_causal_conv: kernel width must be in [1, 8]");
   SSM_REQUIRE(valid_dtype(a->io_dtype), SSM_ERR_DTYPE, "dw_causal_conv: unknown dtype");
   SSM_REQUIRE(a->batch <= 65535, SSM_ERR_TOO_LARGE, "dw_causal_conv: batch exceeds 65535");
+  SSM_REQUIRE(!a->channels_first || (a->row_sb >= 0 && a->row_sc >= a->len), SSM_ERR_SHAPE, "dw_causal_conv: bad row strides");
   SSM_REQUIRE((int64_t)a->batch * a->channels < (1ll << 31), SSM_ERR_TOO_LARGE, "dw_causal_conv: batch*channels too large");
   return SSM_OK;
 }
@@ -424,7 +427,7 @@ template <typename T, int KM>
 static int conv_fwd_launch(const ssm_conv_args& a, cudaStream_t st) {
   constexpr int V = 16 / sizeof(T);
   if (a.channels_first) {
-    const int vec = (a.len % V == 0) && aligned_to(a.x, 16) && aligned_to(a.y, 16);
+    const int vec = (a.len % V == 0) && (a.row_sb % V == 0) && (a.row_sc % V == 0) && aligned_to(a.x, 16) && aligned_to(a.y, 16);
     conv_cf_fwd_kernel<T, KM><<<(unsigned)((int64_t)a.batch * a.channels), kConvThreads, 0, st>>>(a, vec);
   } else {
     const int vec = (a.channels % V == 0) && aligned_to(a.x, 16) && aligned_to(a.y, 16);

@@ -52,7 +52,7 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // Rows of a (B, D, L) activation tensor for one warp: raw[rr][TL] elements of T.
 template <typename T, int RPW, int TL>
 __device__ __forceinline__ void fill_rows_raw(T* __restrict__ raw, const T* __restrict__ g, int b, int D, int L, int drow0, int t0, bool vec,
-                                              int lane) {
+                                              int lane, int64_t sb, int64_t sd) {
   constexpr int V = 16 / sizeof(T);
   if (vec) {
     constexpr int CH = TL / V;
@@ -61,14 +61,14 @@ __device__ __forceinline__ void fill_rows_raw(T* __restrict__ raw, const T* __re
       const int dd = min(drow0 + rr, D - 1);
       const int t = t0 + ch * V;
       const bool ok = t < L;
-      cp_async16(raw + rr * TL + ch * V, g + ((int64_t)b * D + dd) * L + (ok ? t : 0), ok);
+      cp_async16(raw + rr * TL + ch * V, g + (int64_t)b * sb + (int64_t)dd * sd + (ok ? t : 0), ok);
     }
   } else {
     for (int i = lane; i < RPW * TL; i += 32) {
       const int rr = i / TL, tt = i % TL;
       const int dd = min(drow0 + rr, D - 1);
       const int t = t0 + tt;
-      raw[i] = t < L ? g[((int64_t)b * D + dd) * L + t] : from_f<T>(0.f);
+      raw[i] = t < L ? g[(int64_t)b * sb + (int64_t)dd * sd + t] : from_f<T>(0.f);
     }
   }
 }

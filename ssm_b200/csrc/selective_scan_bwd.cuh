@@ -110,10 +110,10 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
   const int ntiles = (L + TL - 1) / TL;
 
   auto fill_raw = [&](int t0) {
-    fill_rows_raw<T, RPW, TL>(rawU, gu, b, D, L, drow0, t0, io_vec, lane);
-    fill_rows_raw<T, RPW, TL>(rawD, gdl, b, D, L, drow0, t0, io_vec, lane);
-    fill_rows_raw<T, RPW, TL>(rawO, gdo, b, D, L, drow0, t0, io_vec, lane);
-    if (gz) fill_rows_raw<T, RPW, TL>(rawZ, gz, b, D, L, drow0, t0, io_vec, lane);
+    fill_rows_raw<T, RPW, TL>(rawU, gu, b, D, L, drow0, t0, io_vec, lane, a.row_sb, a.row_sd);
+    fill_rows_raw<T, RPW, TL>(rawD, gdl, b, D, L, drow0, t0, io_vec, lane, a.row_sb, a.row_sd);
+    fill_rows_raw<T, RPW, TL>(rawO, gdo, b, D, L, drow0, t0, io_vec, lane, a.row_sb, a.row_sd);
+    if (gz) fill_rows_raw<T, RPW, TL>(rawZ, gz, b, D, L, drow0, t0, io_vec, lane, a.row_sb, a.row_sd);
     if (SHARED) {
       fill_bc_raw<TL>(rawB, Bbase, a.bc_dtype, a.b_sn, a.b_st, N, t0, L, bc_vec, tid, NT);
       fill_bc_raw<TL>(rawC, Cbase, a.bc_dtype, a.c_sn, a.c_st, N, t0, L, bc_vec, tid, NT);
@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
         const int t = t0 + ch * V;
         if (dd < D && t < L) {
           const int o = rr * TLP + ch * V;
-          const int64_t base = ((int64_t)b * D + dd) * L + t;
+          const int64_t base = (int64_t)b * a.row_sb + (int64_t)dd * a.row_sd + t;
           float f[V];
           Vec16<T> v;
 #pragma unroll
@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
         const int t = t0 + tt;
         if (dd < D && t < L) {
           const int o = rr * TLP + tt;
-          const int64_t base = ((int64_t)b * D + dd) * L + t;
+          const int64_t base = (int64_t)b * a.row_sb + (int64_t)dd * a.row_sd + t;
           gdu[base] = from_f<T>(sDy[o]);
           gdd[base] = from_f<T>(sU[o]);
           if (gdz) gdz[base] = from_f<T>(sZf[o]);

@@ -26,7 +26,8 @@ int ssmb::scan_validate(const ssm_scan_fwd_args* a, ScanFlags* fl, int rows_per_
   SSM_REQUIRE(a->bc_groups >= 1 && a->dim % a->bc_groups == 0, SSM_ERR_SHAPE, "Group dimension must divide D.");
   const int esz = dtype_size(a->io_dtype);
   const int v = 16 / esz;
-  fl->io_vec = (a->len % v == 0) && aligned_to(a->u, 16) && aligned_to(a->delta, 16) && (!a->z || aligned_to(a->z, 16)) &&
+  SSM_REQUIRE(a->row_sb >= 0 && a->row_sd >= a->len, SSM_ERR_SHAPE, "selective_scan: bad row strides");
+  fl->io_vec = (a->len % v == 0) && (a->row_sb % v == 0) && (a->row_sd % v == 0) && aligned_to(a->u, 16) && aligned_to(a->delta, 16) && (!a->z || aligned_to(a->z, 16)) &&
                (!a->out || aligned_to(a->out, 16));
   const int bv = 16 / dtype_size(a->bc_dtype);
   auto ok = [&](const void* p, int64_t sb, int64_t sg, int64_t sn, int64_t st) {

@@ -95,9 +95,9 @@ __global__ void __launch_bounds__(kScanWarps * 32) scan_fwd_kernel(const ssm_sca
   const int nck = (L + kScanCkpt - 1) / kScanCkpt;
 
   auto fill_raw = [&](int t0) {
-    fill_rows_raw<T, RPW, TL>(rawU, gu, b, D, L, drow0, t0, io_vec, lane);
-    fill_rows_raw<T, RPW, TL>(rawD, gdl, b, D, L, drow0, t0, io_vec, lane);
-    if (gz) fill_rows_raw<T, RPW, TL>(rawZ, gz, b, D, L, drow0, t0, io_vec, lane);
+    fill_rows_raw<T, RPW, TL>(rawU, gu, b, D, L, drow0, t0, io_vec, lane, a.row_sb, a.row_sd);
+    fill_rows_raw<T, RPW, TL>(rawD, gdl, b, D, L, drow0, t0, io_vec, lane, a.row_sb, a.row_sd);
+    if (gz) fill_rows_raw<T, RPW, TL>(rawZ, gz, b, D, L, drow0, t0, io_vec, lane, a.row_sb, a.row_sd);
     if (SHARED) {
       fill_bc_raw<TL>(rawB, Bbase, a.bc_dtype, a.b_sn, a.b_st, N, t0, L, bc_vec, tid, NT);
       fill_bc_raw<TL>(rawC, Cbase, a.bc_dtype, a.c_sn, a.c_st, N, t0, L, bc_vec, tid, NT);
@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(kScanWarps * 32) scan_fwd_kernel(const ssm_sca
           }
           Vec16<T> v;
           v.pack(f);
-          v.store_stream(gout + ((int64_t)b * D + dd) * L + t);
+          v.store_stream(gout + (int64_t)b * a.row_sb + (int64_t)dd * a.row_sd + t);
         }
       }
     } else {
@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(kScanWarps * 32) scan_fwd_kernel(const ssm_sca
         const int rr = i / TL, tt = i % TL;
         const int dd = drow0 + rr;
         const int t = t0 + tt;
-        if (dd < D && t < L) gout[((int64_t)b * D + dd) * L + t] = from_f<T>(sY[rr * TLP + tt] * sG[rr * TLP + tt]);
+        if (dd < D && t < L) gout[(int64_t)b * a.row_sb + (int64_t)dd * a.row_sd + t] = from_f<T>(sY[rr * TLP + tt] * sG[rr * TLP + tt]);
       }
     }
   }

@@ -69,6 +69,27 @@ def _c(t: Optional[Tensor]) -> Optional[Tensor]:
     return t if t.is_contiguous() else t.contiguous()
 
 
+def _rows(t: Tensor) -> Tensor:
+    """A (B, D, L) activation in one of the two row layouts the kernels address directly: dense
+    (B, D, L), or a dense (D, B, L) buffer viewed as (B, D, L).  Anything else is copied to dense."""
+    t = t.detach()
+    if t.is_contiguous() or (t.dim() == 3 and t.stride(2) == 1 and t.permute(1, 0, 2).is_contiguous()):
+        return t
+    return t.contiguous()
+
+
+def _rows_like(t: Optional[Tensor], ref: Tensor) -> Optional[Tensor]:
+    """``t`` with the dtype and exactly the strides of ``ref`` (copied only when it differs)."""
+    if t is None:
+        return None
+    t = t.detach()
+    if t.dtype == ref.dtype and t.stride() == ref.stride():
+        return t
+    out = torch.empty_like(ref)
+    out.copy_(t)
+    return out
+
+
 def _call(fn, args) -> None:
     try:
         L.check(fn(C.byref(args), _stream()))
@@ -124,8 +145,8 @@ class _ScanCtx:
         _need_cuda(u, delta, A, B, C_, D, z, dt_bias, initial_state)
         self.io = _code(u, "selective_scan")
         self.shape = (nb, nd, nl, nn)
-        self.u = _c(u)
-        self.delta = _c(delta.to(u.dtype))
+        self.u = _rows(u)
+        self.delta = _rows_like(delta, self.u)
         self.A = _f32(A)
         Bt, gb, sB = _scan_coeff("B", B, nb, nd, nn, nl)
         Ct, gc, sC = _scan_coeff("C", C_, nb, nd, nn, nl)
@@ -152,7 +173,7 @@ class _ScanCtx:
         if initial_state is not None and tuple(initial_state.shape) != (nb, nd, nn):
             raise ValueError("initial_state must have shape (B, D, N).")
         self.D = _f32(D)
-        self.z = None if z is None else _c(z.to(u.dtype))
+        self.z = _rows_like(z, self.u)
         self.dt_bias = _f32(dt_bias)
         self.init = _f32(initial_state)
         self.softplus = bool(softplus)
@@ -167,6 +188,7 @@ class _ScanCtx:
         a.b_sb, a.b_sg, a.b_sn, a.b_st = self.sB
         a.c_sb, a.c_sg, a.c_sn, a.c_st = self.sC
         a.D, a.dt_bias, a.initial_state = _p(self.D), _p(self.dt_bias), _p(self.init)
+        a.row_sb, a.row_sd = (self.u.stride(0), self.u.stride(1)) if self.u.numel() else (nd * nl, nl)
 
 
 def _regroup(t: Tensor, strides, g_old: int, g_new: int, nb: int, nn: int, nl: int):
@@ -210,7 +232,7 @@ def _scan_backward(ctx: _ScanCtx, ck: Tensor, grad_out: Tensor, grad_last: Optio
     g = L.ScanBwdArgs()
     ctx.fill(g.fwd)
     g.fwd.checkpoints = _p(ck)
-    go = _c(grad_out.to(ctx.u.dtype))
+    go = _rows_like(grad_out, ctx.u)
     gl = _f32(grad_last)
     g.dout, g.dlast_state = _p(go), _p(gl)
     g.du, g.ddelta, g.dz = _p(du), _p(ddelta), _p(dz)
@@ -721,7 +743,7 @@ class _ConvCtx:
         _need_cuda(x, weight, bias, halo)
         self.silu = act in ("silu", "swish")
         self.io = _code(x, "dw_causal_conv")
-        self.x, self.w, self.b = _c(x), _f32(w2), _f32(bias)
+        self.x, self.w, self.b = (_rows(x) if self.first else _c(x)), _f32(w2), _f32(bias)
         self.nb = x.shape[0]
         self.nc, self.k = nc, k
         self.nl = x.shape[2] if self.first else x.shape[1]
@@ -733,6 +755,10 @@ class _ConvCtx:
         a.batch, a.channels, a.len, a.width = self.nb, self.nc, self.nl, self.k
         a.io_dtype, a.channels_first, a.silu = self.io, int(self.first), int(self.silu)
         a.x, a.weight, a.bias, a.halo = _p(self.x), _p(self.w), _p(self.b), _p(self.halo)
+        if self.first and self.x.numel():
+            a.row_sb, a.row_sc = self.x.stride(0), self.x.stride(1)
+        else:
+            a.row_sb, a.row_sc = self.nc * self.nl, self.nl
 
 
 class _ConvFn(torch.autograd.Function):
@@ -757,7 +783,7 @@ class _ConvFn(torch.autograd.Function):
         db = torch.zeros(cc.nc, dtype=torch.float32, device=dev) if bias is not None else None
         g = L.ConvBwdArgs()
         cc.fill(g.fwd)
-        go = _c(gy.to(cc.x.dtype))
+        go = _rows_like(gy, cc.x)
         g.dy, g.dx, g.dweight, g.dbias = _p(go), _p(dx), _p(dw), _p(db)
         _call(L.load().ssm_dw_causal_conv_bwd, g)
         return dx, dw.view(weight.shape).to(weight.dtype), None if bias is None else db.to(bias.dtype), None, None

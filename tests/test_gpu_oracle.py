@@ -334,3 +334,36 @@ def test_backend_object_serves_upstream_calling_convention():
     close(yn, orc.fused_layer_norm(xn, wn, None, is_rms=True), **FP32_TOL, what="rms")
     g4 = be.fused_layer_norm_backward(torch.ones_like(yn), c(xn), c(wn), None, None, True, 1e-5, True, True)
     assert len(g4) == 4 and g4[2].numel() == 0 and g4[3].numel() == 0
+
+
+def test_channel_major_row_layout_matches_dense():
+    """(D, B, L) buffers viewed as (B, D, L) are addressed in place by the scan and the conv (forward
+    and backward) and give the dense-layout results."""
+    from ssm_b200 import ops
+
+    torch.manual_seed(5)
+    nb, nd, nl, nn = 3, 40, 200, 16
+    dev = "cuda"
+
+    def cm(*shape, dtype=torch.bfloat16):  # channel-major buffer, (B, D, L) view
+        return torch.randn(shape[1], shape[0], shape[2], device=dev, dtype=dtype).permute(1, 0, 2)
+
+    u, delta, z, go = cm(nb, nd, nl), cm(nb, nd, nl), cm(nb, nd, nl), cm(nb, nd, nl)
+    assert not u.is_contiguous()
+    A = -torch.exp(torch.randn(nd, nn, device=dev) * 0.5)
+    Bm, Cm = torch.randn(nb, 1, nn, nl, device=dev, dtype=torch.bfloat16), torch.randn(nb, 1, nn, nl, device=dev, dtype=torch.bfloat16)
+    D, bias = torch.randn(nd, device=dev), torch.randn(nd, device=dev) * 0.5
+    w = torch.rand(nd, 4, device=dev) - 0.5
+
+    def run(tensors):
+        uu, dd, zz, gg = (t.clone().requires_grad_(True) if i < 3 else t for i, t in enumerate(tensors))
+        x = ops.dw_causal_conv(uu, w, None, "silu")
+        y, s = ops.selective_scan(x, dd, A, Bm, Cm, D=D, z=zz, dt_bias=bias, softplus=True, return_last_state=True)
+        y.backward(gg)
+        return y, s, uu.grad, dd.grad, zz.grad
+
+    got = run((u, delta, z, go))
+    want = run(tuple(t.contiguous() for t in (u, delta, z, go)))
+    assert got[0].stride() == u.stride()  # the output keeps the layout of its input
+    for g_, w_, name in zip(got, want, ("y", "state", "du", "ddelta", "dz")):
+        assert torch.equal(g_.contiguous(), w_.contiguous()), name
