@@ -26,7 +26,7 @@ struct BwdShape : ScanShape<NS, LPR> {
   // floats
   static constexpr int BC_WORK = SHARED ? 4 * TL * S::NP : 0;  // B, C, dB, dC as [TL][NP]
   static constexpr int WARP_ROWS = 4 * S::RPW * TLP;
-  static constexpr int WARP_HIST = (TL + 1) * 32 * NS;
+  static constexpr int WARP_HIST = (TL / 2 + 1) * 32 * NS;  // states after every second step (+ the checkpoint)
   static constexpr int WARP_WORK = WARP_ROWS + WARP_HIST;
   // bytes
   static constexpr int BC_RAW_BYTES = SHARED ? 2 * S::NP * TL * 4 : 0;
@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
   float* sU = sDl + RPW * TLP;      // u; overwritten step by step with ddelta once u is dead
   float* sDy = sU + RPW * TLP;      // dout * silu(z); overwritten step by step with du
   float* sZf = sDy + RPW * TLP;     // dout * silu'(z), finished into dz once y is rebuilt
-  float* hist = sZf + RPW * TLP;    // [(TL+1)][32][NS]
+  float* hist = sZf + RPW * TLP;    // [(TL/2+1)][32][NS]: slot m = state after step 2m-1 (slot 0: the checkpoint)
   char* rawbase = reinterpret_cast<char*>(smem + S::BC_WORK + NW * S::WARP_WORK);
   char* rawB = rawbase;
   char* rawC = rawbase + S::BC_RAW_BYTES / 2;
@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
     float* rDy = sDy + r * TLP;
     float* rZf = sZf + r * TLP;
     const float Dv = a.D ? __ldg(a.D + d) : 0.f;
-    float* hl = hist + lane * NS;  // this lane's states of step t live at hl[(t + 1) * 32 * NS]
+    float* hl = hist + lane * NS;  // this lane's states of slot m live at hl[m * 32 * NS]
 
     auto load_bc = [&](const float* tile, const char* base, int64_t sn, int64_t st, int tt, float (&v)[NS]) {
       if (SHARED) {
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
               h[j / 2] = __ffma2_rn(da, h[j / 2], __fmul2_rn(du2, make_float2(bv[j], bv[j + 1])));
               if (gz) acc = __ffma2_rn(make_float2(cv[j], cv[j + 1]), h[j / 2], acc);
             }
-            hist_store(tt + i + 1, h);
+            if (i & 1) hist_store((tt + i + 1) / 2, h);  // the even steps are rebuilt from their predecessor
             p[q + i] = acc.x + acc.y;
           }
         }
@@ -282,35 +282,51 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
 #pragma unroll
         for (int e = NS * 4; e < CNT4; ++e) vB[e] = 0.f, vC[e] = 0.f;
         float2 hc[NS / 2];
-        hist_load(tt + 4, hc);
-#pragma unroll
-        for (int i = 3; i >= 0; --i) {
-          float bv[NS], cv[NS];
-          float2 hp[NS / 2];
-          load_bc(sB, Bbase, a.b_sn, a.b_st, tt + i, bv);
-          load_bc(sC, Cbase, a.c_sn, a.c_st, tt + i, cv);
-          hist_load(tt + i, hp);
+        hist_load((tt + 4) / 2, hc);  // state after step tt + 3
+        // one adjoint step: hcur / hprev are the states after / before step tt + i, da its decay
+        auto adjoint_step = [&](int i, const float (&bv)[NS], const float (&cv)[NS], const float2 (&da)[NS / 2], const float2 (&hcur)[NS / 2],
+                                const float2 (&hprev)[NS / 2]) {
           const float2 dl2 = make_float2(dl[i], dl[i]);
           const float2 du2 = make_float2(du[i], du[i]);
           const float2 dy2 = make_float2(dy[i], dy[i]);
           float2 a1 = make_float2(0.f, 0.f), a2 = make_float2(0.f, 0.f);
 #pragma unroll
           for (int j = 0; j < NS; j += 2) {
-            const float2 e = __fmul2_rn(dl2, A2[j / 2]);
-            const float2 da = make_float2(ex2_approx(e.x), ex2_approx(e.y));
             const float2 G = __ffma2_rn(make_float2(cv[j], cv[j + 1]), dy2, carry[j / 2]);
-            const float2 vc = __fmul2_rn(dy2, hc[j / 2]);
+            const float2 vc = __fmul2_rn(dy2, hcur[j / 2]);
             const float2 vb = __fmul2_rn(G, du2);
             vC[i * NS + j] = vc.x, vC[i * NS + j + 1] = vc.y;
             vB[i * NS + j] = vb.x, vB[i * NS + j + 1] = vb.y;
             a1 = __ffma2_rn(G, make_float2(bv[j], bv[j + 1]), a1);
-            const float2 gha = __fmul2_rn(__fmul2_rn(G, hp[j / 2]), da);
+            const float2 gha = __fmul2_rn(__fmul2_rn(G, hprev[j / 2]), da[j / 2]);
             a2 = __ffma2_rn(gha, A2[j / 2], a2);
             dAacc[j / 2] = __ffma2_rn(gha, dl2, dAacc[j / 2]);
-            carry[j / 2] = __fmul2_rn(da, G);
-            hc[j / 2] = hp[j / 2];
+            carry[j / 2] = __fmul2_rn(da[j / 2], G);
           }
           s1[q + i] = a1.x + a1.y, s2[q + i] = a2.x + a2.y;
+        };
+#pragma unroll
+        for (int pr = 1; pr >= 0; --pr) {
+          const int ihi = 2 * pr + 1, ilo = 2 * pr;
+          float bh[NS], ch[NS], bl[NS], cl[NS];
+          float2 hm[NS / 2], hmid[NS / 2], dahi[NS / 2], dalo[NS / 2];
+          load_bc(sB, Bbase, a.b_sn, a.b_st, tt + ihi, bh);
+          load_bc(sC, Cbase, a.c_sn, a.c_st, tt + ihi, ch);
+          load_bc(sB, Bbase, a.b_sn, a.b_st, tt + ilo, bl);
+          load_bc(sC, Cbase, a.c_sn, a.c_st, tt + ilo, cl);
+          hist_load((tt + ilo) / 2, hm);  // state after step tt + ilo - 1
+          const float2 dlh = make_float2(dl[ihi], dl[ihi]), dll = make_float2(dl[ilo], dl[ilo]), dul = make_float2(du[ilo], du[ilo]);
+#pragma unroll
+          for (int j = 0; j < NS; j += 2) {
+            const float2 eh = __fmul2_rn(dlh, A2[j / 2]), el = __fmul2_rn(dll, A2[j / 2]);
+            dahi[j / 2] = make_float2(ex2_approx(eh.x), ex2_approx(eh.y));
+            dalo[j / 2] = make_float2(ex2_approx(el.x), ex2_approx(el.y));
+            hmid[j / 2] = __ffma2_rn(dalo[j / 2], hm[j / 2], __fmul2_rn(dul, make_float2(bl[j], bl[j + 1])));  // state after step tt + ilo
+          }
+          adjoint_step(ihi, bh, ch, dahi, hc, hmid);
+          adjoint_step(ilo, bl, cl, dalo, hmid, hm);
+#pragma unroll
+          for (int j = 0; j < NS / 2; ++j) hc[j] = hm[j];
         }
         if (SHARED) {
           reduce_scatter<RPW, LPR, CNT4>(vB, lane);
