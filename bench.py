@@ -62,7 +62,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20", "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -326,8 +326,11 @@ def run_gpu(args):
                 "d2h_bytes_per_step": 4},
         "gpu_launches": int(round(per_step_launches * args.steps)),
         "roofline": {"kernel": "scan_bwd_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None, "bytes_per_launch": bwd_bytes,
-                     "ms_per_launch": bwd_ms},
+                     "frac": achieved / peak, "peak_kind": peak_kind,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch captured with ncu at batch 2
+                     # (profiles/scan_kernels_ncu_batch2.md: 173.64 MB), scaled by the batch ratio
+                     "traffic": 173.64e6 * B / 2, "bytes_per_launch": bwd_bytes, "ms_per_launch": bwd_ms,
+                     "note": "instruction/latency-bound kernel (one ex2 and ~35 warp instructions per 32 (row,state,step)); see DESIGN.md"},
         "kernels": {"scan_fwd_kernel": {"ms_per_launch": fwd_ms, "bytes_per_launch": fwd_bytes,
                                         "achieved_gbs": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak}},
         "clocks": clocks,
