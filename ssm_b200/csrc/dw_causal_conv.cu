@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(kConvThreads) conv_cf_fwd_kernel(const ssm_con
 //   dx[t] = sum_m wr[m] dpre[t+m];  dwr[m] += sum_t dpre[t] x[t-m];  dbias += sum_t dpre[t]
 // ---------------------------------------------------------------------------------------
 template <typename T, int KM>
-__global__ void __launch_bounds__(kConvThreads) conv_cf_bwd_kernel(const ssm_conv_bwd_args g) {
+__global__ void __launch_bounds__(kConvThreads) conv_cf_bwd_kernel(const ssm_conv_bwd_args g, int vec) {
   constexpr int KH = KM - 1;
   const ssm_conv_args& a = g.fwd;
   const int64_t rowi = blockIdx.x;
@@ -100,8 +100,75 @@ __global__ void __launch_bounds__(kConvThreads) conv_cf_bwd_kernel(const ssm_con
   const float bias = a.bias ? __ldg(a.bias + c) : 0.f;
   float db = 0.f;
 
-  constexpr int S = 4;  // outputs per thread per pass; x / dy re-reads hit L1
-  for (int t0 = threadIdx.x * S; t0 < L; t0 += kConvThreads * S) {
+  if (vec) {
+    // 16-byte accesses: a thread owns one vector of outputs and reads the neighbouring
+    // vectors of x (both sides) and dy (later side) through L1.
+    constexpr int V = 16 / sizeof(T);
+    constexpr int NB = (KH + V - 1) / V;  // neighbour vectors per side
+    for (int t0 = threadIdx.x * V; t0 < L; t0 += kConvThreads * V) {
+      float xa[(2 * NB + 1) * V];  // xa[q] = x[t0 - NB * V + q]
+#pragma unroll
+      for (int j = 0; j <= 2 * NB; ++j) {
+        const int tv = t0 + (j - NB) * V;
+        if (tv >= 0 && tv < L) {
+          Vec16<T> v;
+          v.load(x + tv);
+          float f[V];
+          v.unpack(f);
+#pragma unroll
+          for (int i = 0; i < V; ++i) xa[j * V + i] = f[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) xa[j * V + i] = tv < 0 ? conv_x_at<T>(x, halo, K, tv + i, L) : 0.f;
+        }
+      }
+      float dya[(NB + 1) * V];  // dy[t0 + q], zero beyond the row
+#pragma unroll
+      for (int j = 0; j <= NB; ++j) {
+        const int tv = t0 + j * V;
+        float f[V];
+        if (tv < L) {
+          Vec16<T> v;
+          v.load(dy + tv);
+          v.unpack(f);
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) f[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) dya[j * V + i] = f[i];
+      }
+      float dp[V + KH];  // dpre[t0 + i]
+#pragma unroll
+      for (int i = 0; i < V + KH; ++i) {
+        float pre = bias;
+#pragma unroll
+        for (int m = 0; m < KM; ++m)
+          if (m < K) pre = fmaf(wr[m], xa[NB * V + i - m], pre);
+        float v = dya[i];
+        if (a.silu) v *= silu_grad_fast(pre);
+        dp[i] = (i < V + K - 1) ? v : 0.f;
+      }
+      float out[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        float acc = 0.f;
+#pragma unroll
+        for (int m = 0; m < KM; ++m)
+          if (m < K) {
+            acc = fmaf(wr[m], dp[i + m], acc);
+            dwr[m] = fmaf(dp[i], xa[NB * V + i - m], dwr[m]);
+          }
+        out[i] = acc;
+        db += dp[i];
+      }
+      Vec16<T> v;
+      v.pack(out);
+      v.store_stream(dx + t0);
+    }
+  }
+  constexpr int S = 4;  // scalar path: outputs per thread per pass; x / dy re-reads hit L1
+  for (int t0 = vec ? L : threadIdx.x * S; t0 < L; t0 += kConvThreads * S) {
     float xw[S + 2 * KH];  // xw[q] = x[t0 - KH + q]
 #pragma unroll
     for (int q = 0; q < S + 2 * KH; ++q) {
@@ -440,7 +507,10 @@ template <typename T, int KM>
 static int conv_bwd_launch(const ssm_conv_bwd_args& g, cudaStream_t st) {
   const ssm_conv_args& a = g.fwd;
   if (a.channels_first) {
-    conv_cf_bwd_kernel<T, KM><<<(unsigned)((int64_t)a.batch * a.channels), kConvThreads, 0, st>>>(g);
+    constexpr int VT = 16 / sizeof(T);
+    const int vec = (a.len % VT == 0) && (a.row_sb % VT == 0) && (a.row_sc % VT == 0) && aligned_to(a.x, 16) && aligned_to(g.dy, 16) &&
+                    aligned_to(g.dx, 16);
+    conv_cf_bwd_kernel<T, KM><<<(unsigned)((int64_t)a.batch * a.channels), kConvThreads, 0, st>>>(g, vec);
   } else {
     constexpr int V = 4;
     const size_t gb = V * sizeof(T);

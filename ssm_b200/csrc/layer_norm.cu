@@ -327,16 +327,30 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_bwd_kernel(const ss
   }
 }
 
-__global__ void norm_fold_kernel(const float* __restrict__ partial, int nctas, int hidden, float* __restrict__ dweight, float* __restrict__ dbias) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= hidden) return;
+// Column sums of the per-CTA partial rows: 32 columns x kFoldLanes partial-row lanes per CTA,
+// so the loads of a column are spread over many threads instead of one serial chain.
+constexpr int kFoldLanes = 16;
+__global__ void __launch_bounds__(32 * kFoldLanes) norm_fold_kernel(const float* __restrict__ partial, int nctas, int hidden,
+                                                                   float* __restrict__ dweight, float* __restrict__ dbias) {
+  __shared__ float sw[kFoldLanes][33], sb[kFoldLanes][33];
+  const int cx = threadIdx.x & 31, ky = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;
   float tw = 0.f, tb = 0.f;
-  for (int k = 0; k < nctas; ++k) {
-    tw += partial[(int64_t)k * 2 * hidden + col];
-    tb += partial[(int64_t)k * 2 * hidden + hidden + col];
+  if (col < hidden) {
+#pragma unroll 4
+    for (int k = ky; k < nctas; k += kFoldLanes) {
+      tw += __ldg(partial + (int64_t)k * 2 * hidden + col);
+      tb += __ldg(partial + (int64_t)k * 2 * hidden + hidden + col);
+    }
   }
-  dweight[col] = tw;
-  if (dbias) dbias[col] = tb;
+  sw[ky][cx] = tw, sb[ky][cx] = tb;
+  __syncthreads();
+  if (ky == 0 && col < hidden) {
+#pragma unroll
+    for (int k = 1; k < kFoldLanes; ++k) tw += sw[k][cx], tb += sb[k][cx];
+    dweight[col] = tw;
+    if (dbias) dbias[col] = tb;
+  }
 }
 
 // ---- fallback for rows that cannot be vectorised (hidden not a multiple of the vector, or
@@ -454,7 +468,7 @@ static int norm_bwd_launch(const ssm_norm_bwd_args& g, cudaStream_t st) {
   const int nctas = norm_bwd_ctas(g.fwd, Cfg::RPC);
   norm_bwd_kernel<T, G><<<nctas, Cfg::BLOCK, 0, st>>>(g);
   if (int rc = launch_status("norm_bwd_kernel")) return rc;
-  norm_fold_kernel<<<(g.fwd.hidden + 127) / 128, 128, 0, st>>>(g.partial, nctas, g.fwd.hidden, g.dweight, g.dbias);
+  norm_fold_kernel<<<(g.fwd.hidden + 31) / 32, 32 * kFoldLanes, 0, st>>>(g.partial, nctas, g.fwd.hidden, g.dweight, g.dbias);
   return launch_status("norm_fold_kernel");
 }
 
@@ -538,7 +552,7 @@ static int norm_bwd_launch_capped(const ssm_norm_bwd_args& g, cudaStream_t st, i
   if (nctas > max_ctas) nctas = max_ctas;
   norm_bwd_kernel<T, G><<<nctas, Cfg::BLOCK, 0, st>>>(g);
   if (int rc = launch_status("norm_bwd_kernel")) return rc;
-  norm_fold_kernel<<<(g.fwd.hidden + 127) / 128, 128, 0, st>>>(g.partial, nctas, g.fwd.hidden, g.dweight, g.dbias);
+  norm_fold_kernel<<<(g.fwd.hidden + 31) / 32, 32 * kFoldLanes, 0, st>>>(g.partial, nctas, g.fwd.hidden, g.dweight, g.dbias);
   return launch_status("norm_fold_kernel");
 }
 

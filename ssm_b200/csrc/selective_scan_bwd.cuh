@@ -7,8 +7,9 @@
 // carried in registers across tiles; grad_last_state seeds it.  Contractions over states
 // (du, ddelta, y for dz) are register reduce-scatters across the lanes of a row;
 // contractions over the rows that share a B / C group (dB, dC) are reduce-scatters across
-// the rows of a warp, then shared-memory accumulation across the CTA's warps and one global
-// atomic per CTA, state and step.
+// the rows of a warp, done through a per-warp shared-memory staging area: every lane writes
+// its (state, 4 steps) products as 16-byte groups, then each lane sums one (state, 4 steps)
+// group over the warp's rows and adds it to global memory with one vector reduction.
 #pragma once
 
 #include "scan_common.cuh"
@@ -22,12 +23,12 @@ struct BwdShape : ScanShape<NS, LPR> {
   static constexpr int ROWS = NW * S::RPW;
   static constexpr int TL = kScanCkpt;
   static constexpr int TLP = TL + 4;
-  static constexpr int CNT4 = NS * 4 > S::RPW ? NS * 4 : S::RPW;  // entries per 4-step row reduction
   // floats
-  static constexpr int BC_WORK = SHARED ? 4 * TL * S::NP : 0;  // B, C, dB, dC as [TL][NP]
+  static constexpr int BC_WORK = SHARED ? 2 * TL * S::NP : 0;  // B, C as [TL][NP]
   static constexpr int WARP_ROWS = 4 * S::RPW * TLP;
-  static constexpr int WARP_HIST = (TL / 2 + 1) * 32 * NS;  // states after every second step (+ the checkpoint)
-  static constexpr int WARP_WORK = WARP_ROWS + WARP_HIST;
+  static constexpr int WARP_HIST = (TL / 4 + 1) * 32 * NS;  // states after every fourth step (+ the checkpoint)
+  static constexpr int WARP_STAGE = SHARED ? 2 * S::NP * S::RPW * 4 : 0;  // dB / dC products of 4 steps: [2 * NP][RPW][4]
+  static constexpr int WARP_WORK = WARP_ROWS + WARP_HIST + WARP_STAGE;
   // bytes
   static constexpr int BC_RAW_BYTES = SHARED ? 2 * S::NP * TL * 4 : 0;
   static constexpr int WARP_RAW_BYTES = 4 * S::RPW * TL * (int)sizeof(T);
@@ -37,9 +38,9 @@ struct BwdShape : ScanShape<NS, LPR> {
 };
 
 template <typename T, int NS, int LPR, bool SHARED>
-__global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bwd_kernel(const ssm_scan_bwd_args g, const ScanFlags fl) {
+__global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32, BwdShape<T, NS, LPR, SHARED>::NW == 4 ? 3 : 1) scan_bwd_kernel(const ssm_scan_bwd_args g, const ScanFlags fl) {
   using S = BwdShape<T, NS, LPR, SHARED>;
-  constexpr int NP = S::NP, RPW = S::RPW, ROWS = S::ROWS, TB = S::TB, TL = S::TL, TLP = S::TLP, NW = S::NW, CNT4 = S::CNT4;
+  constexpr int NP = S::NP, RPW = S::RPW, ROWS = S::ROWS, TB = S::TB, TL = S::TL, TLP = S::TLP, NW = S::NW;
   constexpr int V = 16 / sizeof(T);
   constexpr int NT = NW * 32;
   const ssm_scan_fwd_args& a = g.fwd;
@@ -47,15 +48,14 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
   extern __shared__ __align__(16) float smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float* sB = smem;  // [TL][NP] each
-  float* sC = sB + S::BC_WORK / 4;
-  float* sdB = sC + S::BC_WORK / 4;
-  float* sdC = sdB + S::BC_WORK / 4;
+  float* sC = sB + S::BC_WORK / 2;
   float* wbase = smem + S::BC_WORK + warp * S::WARP_WORK;
   float* sDl = wbase;               // delta after bias / softplus (0 beyond the sequence)
   float* sU = sDl + RPW * TLP;      // u; overwritten step by step with ddelta once u is dead
   float* sDy = sU + RPW * TLP;      // dout * silu(z); overwritten step by step with du
   float* sZf = sDy + RPW * TLP;     // dout * silu'(z), finished into dz once y is rebuilt
-  float* hist = sZf + RPW * TLP;    // [(TL/2+1)][32][NS]: slot m = state after step 2m-1 (slot 0: the checkpoint)
+  float* hist = sZf + RPW * TLP;    // [(TL/4+1)][32][NS]: slot m = state after step 4m-1 (slot 0: the checkpoint)
+  float* stage = hist + S::WARP_HIST;
   char* rawbase = reinterpret_cast<char*>(smem + S::BC_WORK + NW * S::WARP_WORK);
   char* rawB = rawbase;
   char* rawC = rawbase + S::BC_RAW_BYTES / 2;
@@ -176,7 +176,6 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
     if (SHARED) {
       convert_bc<TL, NP>(sB, rawB, raw_bc_dtype, N, tid, NT);
       convert_bc<TL, NP>(sC, rawC, raw_bc_dtype, N, tid, NT);
-      for (int i = tid; i < 2 * TL * NP; i += NT) sdB[i] = 0.f;  // dB and dC accumulators
     }
     __syncthreads();
     if (k > 0) fill_raw(t0 - TL);  // next (earlier) tile; overlaps the work below
@@ -248,7 +247,7 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
               h[j / 2] = __ffma2_rn(da, h[j / 2], __fmul2_rn(du2, make_float2(bv[j], bv[j + 1])));
               if (gz) acc = __ffma2_rn(make_float2(cv[j], cv[j + 1]), h[j / 2], acc);
             }
-            if (i & 1) hist_store((tt + i + 1) / 2, h);  // the even steps are rebuilt from their predecessor
+            if (i == 3) hist_store((tt + 4) / 4, h);  // the steps in between are rebuilt from their predecessors
             p[q + i] = acc.x + acc.y;
           }
         }
@@ -266,6 +265,8 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
     __syncwarp();
 
     // ---- adjoint recurrence, last step of the tile first ------------------------------------------
+    float2 hc[NS / 2];
+    hist_load(TL / 4, hc);  // state after the tile's last step
 #pragma unroll 1
     for (int tb0 = TL - TB; tb0 >= 0; tb0 -= TB) {
       float s1[TB], s2[TB];
@@ -278,69 +279,104 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
         const float dl[4] = {dl4.x, dl4.y, dl4.z, dl4.w};
         const float du[4] = {dl4.x * u4.x, dl4.y * u4.y, dl4.z * u4.z, dl4.w * u4.w};
         const float dy[4] = {dy4.x, dy4.y, dy4.z, dy4.w};
-        float vB[CNT4], vC[CNT4];  // entry i * NS + j: step tt + i, state j
+        float vB[4 * NS], vC[4 * NS];  // entry i * NS + j: step tt + i, state j
+        // states after steps tt - 1 .. tt + 2 (hs[0] from the history, the rest rebuilt) and the four decays
+        float2 hs[4][NS / 2], da[4][NS / 2];
+        hist_load(tt / 4, hs[0]);
 #pragma unroll
-        for (int e = NS * 4; e < CNT4; ++e) vB[e] = 0.f, vC[e] = 0.f;
-        float2 hc[NS / 2];
-        hist_load((tt + 4) / 2, hc);  // state after step tt + 3
-        // one adjoint step: hcur / hprev are the states after / before step tt + i, da its decay
-        auto adjoint_step = [&](int i, const float (&bv)[NS], const float (&cv)[NS], const float2 (&da)[NS / 2], const float2 (&hcur)[NS / 2],
-                                const float2 (&hprev)[NS / 2]) {
+        for (int i = 0; i < 4; ++i) {
+          const float2 dl2 = make_float2(dl[i], dl[i]);
+#pragma unroll
+          for (int j = 0; j < NS; j += 2) {
+            const float2 e = __fmul2_rn(dl2, A2[j / 2]);
+            da[i][j / 2] = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+          }
+          if (i < 3) {
+            float bv[NS];
+            load_bc(sB, Bbase, a.b_sn, a.b_st, tt + i, bv);
+            const float2 du2 = make_float2(du[i], du[i]);
+#pragma unroll
+            for (int j = 0; j < NS; j += 2)
+              hs[i + 1][j / 2] = __ffma2_rn(da[i][j / 2], hs[i][j / 2], __fmul2_rn(du2, make_float2(bv[j], bv[j + 1])));
+          }
+        }
+#pragma unroll
+        for (int i = 3; i >= 0; --i) {
+          // one adjoint step: hcur / hprev are the states after / before step tt + i
+          float bv[NS], cv[NS];
+          load_bc(sB, Bbase, a.b_sn, a.b_st, tt + i, bv);
+          load_bc(sC, Cbase, a.c_sn, a.c_st, tt + i, cv);
           const float2 dl2 = make_float2(dl[i], dl[i]);
           const float2 du2 = make_float2(du[i], du[i]);
           const float2 dy2 = make_float2(dy[i], dy[i]);
           float2 a1 = make_float2(0.f, 0.f), a2 = make_float2(0.f, 0.f);
 #pragma unroll
           for (int j = 0; j < NS; j += 2) {
+            const float2 hcur = i == 3 ? hc[j / 2] : hs[i == 3 ? 0 : i + 1][j / 2];
             const float2 G = __ffma2_rn(make_float2(cv[j], cv[j + 1]), dy2, carry[j / 2]);
-            const float2 vc = __fmul2_rn(dy2, hcur[j / 2]);
+            const float2 vc = __fmul2_rn(dy2, hcur);
             const float2 vb = __fmul2_rn(G, du2);
             vC[i * NS + j] = vc.x, vC[i * NS + j + 1] = vc.y;
             vB[i * NS + j] = vb.x, vB[i * NS + j + 1] = vb.y;
             a1 = __ffma2_rn(G, make_float2(bv[j], bv[j + 1]), a1);
-            const float2 gha = __fmul2_rn(__fmul2_rn(G, hprev[j / 2]), da[j / 2]);
+            const float2 gha = __fmul2_rn(__fmul2_rn(G, hs[i][j / 2]), da[i][j / 2]);
             a2 = __ffma2_rn(gha, A2[j / 2], a2);
             dAacc[j / 2] = __ffma2_rn(gha, dl2, dAacc[j / 2]);
-            carry[j / 2] = __fmul2_rn(da[j / 2], G);
+            carry[j / 2] = __fmul2_rn(da[i][j / 2], G);
           }
           s1[q + i] = a1.x + a1.y, s2[q + i] = a2.x + a2.y;
-        };
-#pragma unroll
-        for (int pr = 1; pr >= 0; --pr) {
-          const int ihi = 2 * pr + 1, ilo = 2 * pr;
-          float bh[NS], ch[NS], bl[NS], cl[NS];
-          float2 hm[NS / 2], hmid[NS / 2], dahi[NS / 2], dalo[NS / 2];
-          load_bc(sB, Bbase, a.b_sn, a.b_st, tt + ihi, bh);
-          load_bc(sC, Cbase, a.c_sn, a.c_st, tt + ihi, ch);
-          load_bc(sB, Bbase, a.b_sn, a.b_st, tt + ilo, bl);
-          load_bc(sC, Cbase, a.c_sn, a.c_st, tt + ilo, cl);
-          hist_load((tt + ilo) / 2, hm);  // state after step tt + ilo - 1
-          const float2 dlh = make_float2(dl[ihi], dl[ihi]), dll = make_float2(dl[ilo], dl[ilo]), dul = make_float2(du[ilo], du[ilo]);
-#pragma unroll
-          for (int j = 0; j < NS; j += 2) {
-            const float2 eh = __fmul2_rn(dlh, A2[j / 2]), el = __fmul2_rn(dll, A2[j / 2]);
-            dahi[j / 2] = make_float2(ex2_approx(eh.x), ex2_approx(eh.y));
-            dalo[j / 2] = make_float2(ex2_approx(el.x), ex2_approx(el.y));
-            hmid[j / 2] = __ffma2_rn(dalo[j / 2], hm[j / 2], __fmul2_rn(dul, make_float2(bl[j], bl[j + 1])));  // state after step tt + ilo
-          }
-          adjoint_step(ihi, bh, ch, dahi, hc, hmid);
-          adjoint_step(ilo, bl, cl, dalo, hmid, hm);
-#pragma unroll
-          for (int j = 0; j < NS / 2; ++j) hc[j] = hm[j];
         }
-        if (SHARED) {
-          reduce_scatter<RPW, LPR, CNT4>(vB, lane);
-          reduce_scatter<RPW, LPR, CNT4>(vC, lane);
-          constexpr int PERR = CNT4 / RPW;
 #pragma unroll
-          for (int i = 0; i < PERR; ++i) {
-            const int e = r * PERR + i;
-            if (e < NS * 4) {
-              const int o = (tt + e / NS) * NP + sg * NS + (e % NS);
-              atomicAdd(sdB + o, vB[i]);
-              atomicAdd(sdC + o, vC[i]);
+        for (int j = 0; j < NS / 2; ++j) hc[j] = hs[0][j];
+        if (SHARED) {
+          // lanes -> staging area: group (output o, row slot) holds the four steps' products
+          constexpr int ROT = LPR <= 8 ? 8 / LPR : 0;
+          const int slot = (r + ROT * sg) & (RPW - 1);
+#pragma unroll
+          for (int j = 0; j < NS; ++j) {
+            const int o = sg * NS + j;
+            *reinterpret_cast<float4*>(stage + ((o * RPW + slot) << 2)) = make_float4(vB[j], vB[NS + j], vB[2 * NS + j], vB[3 * NS + j]);
+            *reinterpret_cast<float4*>(stage + (((NP + o) * RPW + slot) << 2)) = make_float4(vC[j], vC[NS + j], vC[2 * NS + j], vC[3 * NS + j]);
+          }
+          __syncwarp();
+          constexpr int O = 2 * NP;                  // outputs: (dB | dC) x state
+          constexpr int PARTS = O >= 32 ? 1 : 32 / O;  // lanes sharing one output, each summing RPW / PARTS rows
+          constexpr int RP = RPW / PARTS;
+#pragma unroll
+          for (int m = 0; m < (O >= 32 ? O / 32 : 1); ++m) {
+            const int o = O >= 32 ? lane + 32 * m : lane % O;
+            const int part = O >= 32 ? 0 : lane / O;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int kk = 0; kk < RP; ++kk) {
+              const int sl = part * RP + ((kk + o) & (RP - 1));
+              const float4 v = *reinterpret_cast<const float4*>(stage + ((o * RPW + sl) << 2));
+              acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+            }
+#pragma unroll
+            for (int off = O; off < 32; off <<= 1) {
+              acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
+              acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+              acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
+              acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+            }
+            const int n = o % NP;
+            const int t = t0 + tt;
+            if (part == 0 && n < N && t < L) {
+              float* dst = o < NP ? g.dB + dboff + (int64_t)n * g.db_sn + (int64_t)t * g.db_st
+                                  : g.dC + dcoff + (int64_t)n * g.dc_sn + (int64_t)t * g.dc_st;
+              const int64_t st = o < NP ? g.db_st : g.dc_st;
+              if (st == 1 && t + 3 < L && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
+              } else {
+                const float av[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  if (t + i < L) atomicAdd(dst + i * st, av[i]);
+              }
             }
           }
+          __syncwarp();  // staging area is free for the next four steps
         } else if (row_ok) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -374,20 +410,9 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32) scan_bw
         rU[tt] = dd;                           // ddelta
       }
     }
-    if (SHARED) __syncthreads();
-    else __syncwarp();
+    __syncwarp();
 
-    // ---- flush the tile's dB / dC, write du / ddelta / dz ---------------------------------------
-    if (SHARED) {
-      for (int i = tid; i < N * TL; i += NT) {
-        const int n = i / TL, tt = i % TL;
-        const int t = t0 + tt;
-        if (t < L) {
-          atomicAdd(g.dB + dboff + (int64_t)n * g.db_sn + (int64_t)t * g.db_st, sdB[tt * NP + n]);
-          atomicAdd(g.dC + dcoff + (int64_t)n * g.dc_sn + (int64_t)t * g.dc_st, sdC[tt * NP + n]);
-        }
-      }
-    }
+    // ---- write du / ddelta / dz -----------------------------------------------------------------
     if (io_vec) {
       constexpr int CH = TL / V;
       for (int c = lane; c < RPW * CH; c += 32) {
