@@ -351,7 +351,8 @@ int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* args, ssm_stream_t s
  * final_states: (batch, heads, headdim, nstate) fp32, nullable.  Built for headdim 64,
  * nstate 128, chunk_size 256, bf16 / fp16 (ssm_ssd_supported()).  Scratch, in this order, is
  * carved by the caller from one buffer of ssm_ssd_scratch_bytes() bytes:
- *   ws_dt, ws_cum : (batch, heads, nchunks * 256) fp32 each
+ *   ws_dt, ws_cum : (batch, heads, nchunks * 256) fp32 each; per chunk ws_cum[i] = log2(e) * sum_{k<=i} delta_k A
+ *                   (running decay exponent, base 2) and ws_dt[i] = ws_cum[i] - log2(delta_i)
  *   ws_state      : (batch, nchunks, heads, headdim, nstate) fp32
  *   ws_state_in   : the same shape in io_dtype
  * status: optional device int, set non-zero when a bounded device-side wait ran out.

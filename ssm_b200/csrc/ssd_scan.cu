@@ -5,7 +5,7 @@
 // evaluated chunk by chunk (Q = 256 steps) in the dual, matrix form, with every contraction on
 // the tcgen05 tensor cores (bf16 / fp16 operands from shared memory, fp32 accumulators in TMEM):
 //
-//   ssd_cumsum_kernel   delta and its running log-decay  cum_i = sum_{k<=i} delta_k A  per chunk
+//   ssd_cumsum_kernel   per chunk the running decay exponent  c_i = log2(e) sum_{k<=i} delta_k A  and  c_i - log2(delta_i)
 //   ssd_state_kernel    per (batch, chunk, head): local state  S_c = sum_j exp(cum_last - cum_j) delta_j x_j B_j^T   [N x P GEMM, K = Q]
 //   ssd_pass_kernel     the short serial pass over chunks: incoming state of every chunk (kept in
 //                       the operand dtype for the GEMM below) and the final state in fp32
@@ -68,8 +68,9 @@ __global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, i
   for (int k = 0; k < kQ / 32; ++k) {
     const int i = lane * (kQ / 32) + k;
     acc += d[k] * Ah;
-    odt[i] = d[k];
-    ocum[i] = acc;
+    const float c2 = acc * kLog2e;
+    ocum[i] = c2;                      // running decay exponent, base 2
+    odt[i] = c2 - lg2_approx(d[k]);    // the same with delta folded in: exp2(x - odt[j]) = exp2(x - c2_j) * delta_j  (delta 0 -> +inf -> weight 0)
   }
 }
 
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(128) ssd_state_kernel(const ssm_ssd_args a, in
       w[q] = 0.f;
       if (t < a.len) {
         v[q].load(Xg + (((int64_t)b * a.len + t) * a.heads + h) * kP + pc * 8);
-        w[q] = exp_fast(cum_last - __ldg(wcum + j)) * __ldg(wdt + j);
+        w[q] = ex2_approx(cum_last - __ldg(wdt + j));
       }
     }
 #pragma unroll
@@ -180,227 +181,356 @@ __global__ void __launch_bounds__(128) ssd_state_kernel(const ssm_ssd_args a, in
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) ssd_pass_kernel(const ssm_ssd_args a, int nchunks) {
+  // thread = one element of the (p, n) state of one (batch, head), in the order of the operand
+  // tile the scan kernel copies:  q = ((n / 8) * P + p) * 8 + n % 8  (K-major units of 16 bytes)
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   const int64_t per = (int64_t)kP * kN;
   const int64_t total = (int64_t)a.batch * a.heads * per;
   if (i >= total) return;
-  const int64_t bh = i / per, pn = i % per;
+  const int64_t bh = i / per;
+  const int q = (int)(i % per);
+  const int e = q & 7, p = (q >> 3) % kP, nc = q / (8 * kP);
+  const int pn = p * kN + nc * 8 + e;
   const int b = (int)(bh / a.heads), h = (int)(bh % a.heads);
-  float s = a.initial_states ? __ldg(a.initial_states + i) : 0.f;
+  float s = a.initial_states ? __ldg(a.initial_states + bh * per + pn) : 0.f;
   T* sin = reinterpret_cast<T*>(a.ws_state_in);
   for (int c = 0; c < nchunks; ++c) {
-    const int64_t slot = (((int64_t)b * nchunks + c) * a.heads + h) * per + pn;
-    sin[slot] = from_f<T>(s);
-    const float decay = exp_fast(__ldg(a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ + kQ - 1));
-    s = fmaf(decay, s, a.ws_state[slot]);
+    const int64_t blk = (((int64_t)b * nchunks + c) * a.heads + h) * per;
+    sin[blk + q] = from_f<T>(s);
+    const float decay = ex2_approx(__ldg(a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ + kQ - 1));
+    s = fmaf(decay, s, a.ws_state[blk + pn]);
   }
-  if (a.final_states) a.final_states[i] = s;
+  if (a.final_states) a.final_states[bh * per + pn] = s;
 }
 
 // ---------------------------------------------------------------------------------------------
-// chunk scan: one CTA of two warpgroups per (head, batch * chunk); warpgroup w owns rows
-// [128 w, 128 w + 128) of the chunk.  Both share the staged C, B, x and incoming-state tiles.
-//   TMEM columns: G0 [0,128) (rows 0..127 x steps 0..127), G1 [128,384) (rows 128..255 x steps
-//   0..255), C S_in of block 0 [384,448) and of block 1 [448,512); (G o L) X of block w is
-//   accumulated over the first 64 columns of G_w once the warpgroup has consumed G_w.
-//   Shared memory: the masked tile of block 0 overwrites the C tile, that of block 1 the B tile
-//   (both dead once the first group of MMAs has completed).
+// chunk scan: one CTA (256 threads) per (batch, chunk, 128-row block m, part of the heads of one
+// B / C group).  Heads of a group share B and C, so  G = C_m B^T  (128 x 128 (m+1), causal: only
+// steps before the block's last row) is formed ONCE per CTA; every thread then keeps its part of
+// G (one row, half of the steps) in registers while the CTA walks its heads:
+//   per head:  G times the head's decay mask exp2(c_i - c_j) delta_j [j <= i], packed as the A
+//              operand (overwrites the dead B tile);  Y_intra = (G o L) X  and  Y_inter = C_m S_in
+//              accumulate in TMEM while the previous head's result is read back, gated and staged.
+//   Copies (cp.async, whole 128 / 256-byte rows per group of lanes) run one head ahead into the
+//   other half of a double buffer: x, the incoming state, the exponent vectors; z goes through
+//   the same 16 KB staging tile that carries y back out, so that every global access of the
+//   head loop touches whole 128-byte lines.
+//   TMEM columns: G [0,256); per buffer b: Y_intra [256+128b, +64), Y_inter [320+128b, +64).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 struct ScanSmem {
-  static constexpr int C_BYTES = kQ * kN * 2;   // C rows of the chunk, K-major [n/8][i][8]   64 KB
-  static constexpr int B_BYTES = kQ * kN * 2;   // B rows of the chunk, K-major [n/8][j][8]   64 KB
-  static constexpr int X_BYTES = kQ * kP * 2;   // x rows, MN-major [p/8][j][8]               32 KB
-  static constexpr int S_BYTES = kP * kN * 2;   // incoming state, K-major [n/8][p][8]        16 KB
-  static constexpr int VEC_BYTES = 2 * kQ * 4;  // cum and delta of the chunk
-  static constexpr int TOTAL = C_BYTES + B_BYTES + X_BYTES + S_BYTES + VEC_BYTES;
+  static constexpr int C_BYTES = kBlk * kN * 2;     // C rows of the block, K-major [n/8][i][8]            32 KB
+  static constexpr int B_BYTES = kQ * kN * 2;       // B rows, K-major [n/8][j][8]; later the masked tile  64 KB
+  static constexpr int X_BYTES = kQ * kP * 2;       // x rows, MN-major [p/8][j][8]                         32 KB (x2)
+  static constexpr int S_BYTES = kP * kN * 2;       // incoming state, K-major [n/8][p][8]                  16 KB (x2)
+  static constexpr int VEC_BYTES = 2 * kQ * 4;      // c and c - log2(delta) of the chunk                     2 KB (x2)
+  static constexpr int Z_BYTES = kBlk * kP * 2;     // z in / y out of one head: [row][8 chunks of 16 B], chunk ^= row & 7   16 KB
+  static constexpr int TOTAL = C_BYTES + B_BYTES + 2 * (X_BYTES + S_BYTES + VEC_BYTES) + Z_BYTES;
 };
 
-__device__ __forceinline__ void named_barrier(int id, int nthreads) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory"); }
+constexpr int kScanThreads = 256;
 
-template <typename T>
-__global__ void __launch_bounds__(256) ssd_scan_kernel(const ssm_ssd_args a, int nchunks) {
+// Body for row block MB (0: rows 0..127, steps 0..127; 1: rows 128..255, steps 0..255).
+template <typename T, int MB>
+__device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks, int hpc, int nparts, unsigned char* smraw, uint64_t* mbar,
+                                              uint32_t* tmem_slot) {
   using M = ScanSmem<T>;
-  extern __shared__ __align__(128) unsigned char smraw[];
+  constexpr int KJ = (MB + 1) * kBlk;  // steps that can reach this block's rows
+  constexpr int NCH = KJ / 64;         // 32-step column chunks per thread (the two warpgroups interleave chunks)
   unsigned char* sC = smraw;
-  unsigned char* sB = sC + M::C_BYTES;
-  unsigned char* sX = sB + M::B_BYTES;
-  unsigned char* sS = sX + M::X_BYTES;
-  float* sCum = reinterpret_cast<float*>(sS + M::S_BYTES);
-  float* sDt = sCum + kQ;
-  __shared__ __align__(8) uint64_t mbar[3];
-  __shared__ uint32_t tmem_slot;
+  unsigned char* sBA = sC + M::C_BYTES;
+  unsigned char* sX = sBA + M::B_BYTES;        // two buffers
+  unsigned char* sS = sX + 2 * M::X_BYTES;     // two buffers
+  float* sVec = reinterpret_cast<float*>(sS + 2 * M::S_BYTES);  // two buffers of [c | c - log2 delta]
+  unsigned char* sZ = reinterpret_cast<unsigned char*>(sVec) + 2 * M::VEC_BYTES;
 
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int wg = tid >> 7, wtid = tid & 127;  // warpgroup = row block
-  const int h = blockIdx.x;
-  const int c = blockIdx.y % nchunks, b = blockIdx.y / nchunks;
-  const int g = h / (a.heads / a.groups);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wg = tid >> 7;                     // column chunks wg, wg + 2, ... in the mask stage; column half in the epilogue
+  const int half_grid = gridDim.x >> 1;
+  const int rem = (int)blockIdx.x % half_grid;
+  const int part = rem % nparts, bc = rem / nparts;
+  const int c = bc % nchunks, b = bc / nchunks;
+  const int h0 = part * hpc;
+  const int nh = min(hpc, a.heads - h0);
+  const int g = h0 / (a.heads / a.groups);
   const int t0 = c * kQ;
-  const int KJ = (wg + 1) * kBlk;      // causal: steps j < KJ can reach this warpgroup's rows
-  const int i_loc = wg * kBlk + wtid;  // this thread's row within the chunk
-  const int t_row = t0 + i_loc;
+  const int i_loc = (warp & 3) * 32 + lane;    // row within the block = TMEM lane
+  const int i_chunk = MB * kBlk + i_loc;       // row within the chunk
+  const int rc = MB * 4 + (warp & 3);          // this warp's rows as a 32-step chunk index
   constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
 
-  if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), 512);
-  if (tid == 0) {
-    tc::mbar_init(tc::smem_u32(&mbar[0]), 1);
-    tc::mbar_init(tc::smem_u32(&mbar[1]), 1);
-    tc::mbar_init(tc::smem_u32(&mbar[2]), 1);
-  }
-
-  // ---- stage operands (asynchronous 16-byte copies, step index fastest across threads) ----------
-  const float* wdt = a.ws_dt + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
-  const float* wcum = a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
-  sCum[tid] = __ldg(wcum + tid), sDt[tid] = __ldg(wdt + tid);
   const T* Cg = reinterpret_cast<const T*>(a.Cm);
   const T* Bg = reinterpret_cast<const T*>(a.Bm);
   const T* Xg = reinterpret_cast<const T*>(a.X);
-  for (int id = tid; id < (kN / 8) * kQ; id += 256) {
-    const int nc = id / kQ, j = id % kQ;
-    const int t = t0 + j;
-    const bool okt = t < a.len;
-    const int64_t off = (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8;
-    cp_async16(sC + ((size_t)nc * kQ + j) * 16, Cg + off, okt);
-    cp_async16(sB + ((size_t)nc * kQ + j) * 16, Bg + off, okt);
-  }
-  for (int id = tid; id < (kP / 8) * kQ; id += 256) {
-    const int pc = id / kQ, j = id % kQ;
-    const int t = t0 + j;
-    const bool okt = t < a.len;
-    cp_async16(sX + ((size_t)pc * kQ + j) * 16, Xg + (((int64_t)b * a.len + (okt ? t : 0)) * a.heads + h) * kP + pc * 8, okt);
-  }
+  const T* Zg = reinterpret_cast<const T*>(a.z);
+  T* Yg = reinterpret_cast<T*>(a.Y);
+
+  // ---- C rows of the block, B rows of the reachable steps: 16 lanes copy one 256-byte row -----------
   {
-    const T* Sg = reinterpret_cast<const T*>(a.ws_state_in) + ((((int64_t)b * nchunks + c) * a.heads + h) * kP) * kN;
-    for (int id = tid; id < (kN / 8) * kP; id += 256) {
-      const int nc = id / kP, p = id % kP;
-      cp_async16(sS + ((size_t)nc * kP + p) * 16, Sg + (int64_t)p * kN + nc * 8, true);
+    const int nc = tid & 15, r0 = tid >> 4;
+    for (int i = r0; i < kBlk; i += 16) {
+      const int t = t0 + MB * kBlk + i;
+      const bool okt = t < a.len;
+      cp_async16(sC + ((size_t)nc * kBlk + i) * 16, Cg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
+    }
+    for (int j = r0; j < KJ; j += 16) {
+      const int t = t0 + j;
+      const bool okt = t < a.len;
+      cp_async16(sBA + ((size_t)nc * KJ + j) * 16, Bg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
     }
   }
   cp_async_commit();
-  cp_async_wait_all();
+
+  // Per-thread copy plan for one head.  x: 8 lanes copy one 128-byte row; incoming state: a
+  // straight copy (it is stored in operand order); exponent vectors: 16-byte pieces.
+  const int xpc = tid & 7, xr0 = tid >> 3;
+  const int64_t xrow_stride = (int64_t)a.heads * kP;
+  const T* xsrc0 = Xg + ((int64_t)b * a.len + t0) * xrow_stride + xpc * 8;
+  const int64_t sbase = (((int64_t)b * nchunks + c) * a.heads) * (int64_t)(kP * kN) + tid * 8;
+  const int64_t vbase = ((int64_t)b * a.heads * nchunks + c) * kQ;
+  auto prefetch = [&](int h, int buf) {
+    unsigned char* dX = sX + buf * M::X_BYTES + (size_t)xpc * KJ * 16;
+    const T* xs = xsrc0 + (int64_t)h * kP;
+#pragma unroll
+    for (int k = 0; k < KJ / 32; ++k) {
+      const int j = xr0 + 32 * k;
+      const bool okt = t0 + j < a.len;
+      cp_async16(dX + (size_t)j * 16, xs + (okt ? (int64_t)j * xrow_stride : 0), okt);
+    }
+    unsigned char* dS = sS + buf * M::S_BYTES + (size_t)tid * 16;
+    const T* ss = reinterpret_cast<const T*>(a.ws_state_in) + sbase + (int64_t)h * (kP * kN);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) cp_async16(dS + (size_t)k * kScanThreads * 16, ss + k * kScanThreads * 8, true);
+    float* dV = sVec + buf * (2 * kQ);
+    const int64_t voff = vbase + (int64_t)h * nchunks * kQ;
+    if (tid < KJ / 4) cp_async16(dV + tid * 4, a.ws_cum + voff + tid * 4, true);
+    else if (tid >= 128 && tid < 128 + KJ / 4) cp_async16(dV + kQ + (tid - 128) * 4, a.ws_dt + voff + (tid - 128) * 4, true);
+  };
+  // z / y staging: 8 lanes handle one 128-byte row of the block; slot of (row, 16-byte chunk) is swizzled
+  // so that both these row-wise accesses and the epilogue's one-row-per-thread accesses avoid bank conflicts
+  const int64_t zrow0 = (int64_t)b * a.len + t0 + MB * kBlk;  // token of the block's first row
+  auto z_slot = [&](int row, int chunk) { return sZ + ((size_t)row * 8 + (chunk ^ (row & 7))) * 16; };
+  auto copy_z = [&](int h) {
+    if (!Zg) return;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int row = xr0 + 32 * k;
+      const bool okt = t0 + MB * kBlk + row < a.len;
+      cp_async16(z_slot(row, xpc), Zg + ((zrow0 + (okt ? row : 0)) * a.heads + h) * kP + xpc * 8, okt);
+    }
+  };
+  auto store_y = [&](int h) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int row = xr0 + 32 * k;
+      if (t0 + MB * kBlk + row < a.len) {
+        const uint4 v = *reinterpret_cast<const uint4*>(z_slot(row, xpc));
+        *reinterpret_cast<uint4*>(Yg + ((zrow0 + row) * a.heads + h) * kP + xpc * 8) = v;
+      }
+    }
+  };
+  prefetch(h0, 0);
+  cp_async_commit();
+
+  asm volatile("cp.async.wait_group 1;\n" ::: "memory");  // C and B have landed (the head's group may still be in flight)
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-  const uint32_t tmem = tmem_slot;
-  const uint32_t tG = tmem + (wg == 0 ? 0 : 128);    // this warpgroup's G, later its (G o L) X
-  const uint32_t tYs = tmem + 384 + wg * 64;         // this warpgroup's C S_in
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
-  // ---- G = C B^T and Y_inter = C S_in for both row blocks ------------------------------------------
+  // ---- G = C_m B^T ------------------------------------------------------------------------------------
   if (tid == 0) {
-    const uint32_t c0 = tc::smem_u32(sC), b0 = tc::smem_u32(sB), s0 = tc::smem_u32(sS);
-    const uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 0);
-#pragma unroll 1
-    for (int blk = 0; blk < 2; ++blk) {
-      const uint32_t idG = tc::instr_desc(kBlk, (blk + 1) * kBlk, fmt, 0, 0);
-      const uint32_t dG = tmem + (blk == 0 ? 0 : 128), dS = tmem + 384 + blk * 64;
-#pragma unroll 1
-      for (int kk = 0; kk < kN / 16; ++kk) {
-        const uint64_t da = tc::smem_desc(c0 + blk * (kBlk * 16) + kk * 2 * (kQ * 16), kQ * 16, 128);
-        const uint64_t db = tc::smem_desc(b0 + kk * 2 * (kQ * 16), kQ * 16, 128);
-        const uint64_t ds = tc::smem_desc(s0 + kk * 2 * (kP * 16), kP * 16, 128);
-        tc::mma_ss(dG, da, db, idG, kk > 0);
-        tc::mma_ss(dS, da, ds, idS, kk > 0);
-      }
-    }
+    const uint64_t dc0 = tc::smem_desc(tc::smem_u32(sC), kBlk * 16, 128);
+    const uint64_t db0 = tc::smem_desc(tc::smem_u32(sBA), KJ * 16, 128);
+    constexpr uint32_t idG = tc::instr_desc(kBlk, KJ, fmt, 0, 0);
+#pragma unroll
+    for (int kk = 0; kk < kN / 16; ++kk)
+      tc::mma_ss(tmem, dc0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), db0 + (uint64_t)(kk * ((2 * KJ * 16) >> 4)), idG, kk > 0);
     tc::commit(tc::smem_u32(&mbar[0]));
   }
   bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[0]), 0));  // warp-uniform
   tc::fence_after_sync();
 
-  // ---- decay mask on the TMEM -> register path; the masked tile (K-major over j, 128 rows) replaces
-  // ---- a dead operand tile: unit (i, j/8) at (j/8) * (128 * 16) + i * 16 -----------------------------
-  unsigned char* sA = wg == 0 ? sC : sB;
-  const float cum_i = sCum[i_loc];
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  if (ok) {
-    for (int jb = 0; jb < KJ; jb += 32) {
-      float v[32];
-      tc::tmem_ld32(tG + lane_base + jb, v);
+  // This thread's part of G stays in registers for all heads: row i_loc, chunks wg, wg + 2, ...
+  float vG[NCH][32];
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int cc = wg + 2 * k;
+    if (ok && cc <= rc) {
+      tc::tmem_ld32(tmem + lane_base + cc * 32, vG[k]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) vG[k][e] = 0.f;
+    }
+  }
+
+  // epilogue of head h from buffer `buf`: y = Y_intra + exp2(c_i) Y_inter + D x, gated by the z row in
+  // the staging tile, written back to the same slots.  Thread = row i_loc, this warpgroup's 32 columns.
+  auto epilogue = [&](int h, int buf, float ct, const uint4 (&xr)[4]) {
+    const float escale = ex2_approx(ct);
+    float yi[32], ys[32];
+    tc::tmem_ld32(tmem + lane_base + 256 + buf * 128 + wg * 32, yi);
+    tc::tmem_ld32(tmem + lane_base + 320 + buf * 128 + wg * 32, ys);
+    const float Dh = (a.D && !a.d_has_p) ? __ldg(a.D + h) : 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float f[8], xv[8];
+      Vec16<T> xx;
+      xx.raw = xr[q];
+      xx.unpack(xv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float Dv = (a.D && a.d_has_p) ? __ldg(a.D + h * kP + wg * 32 + q * 8 + e) : Dh;
+        f[e] = fmaf(escale, ys[q * 8 + e], yi[q * 8 + e]) + Dv * xv[e];
+      }
+      unsigned char* slot = z_slot(i_loc, wg * 4 + q);
+      if (Zg) {
+        float zv[8];
+        Vec16<T> zz;
+        zz.raw = *reinterpret_cast<const uint4*>(slot);
+        zz.unpack(zv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] *= silu_fast(zv[e]);
+      }
+      Vec16<T> o;
+      o.pack(f);
+      *reinterpret_cast<uint4*>(slot) = o.raw;
+    }
+  };
+
+  float ct_prev = 0.f;   // the previous head's row exponent and x row, carried into its (deferred) epilogue
+  uint4 xr_prev[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) xr_prev[q] = make_uint4(0, 0, 0, 0);
+  int fail = 0;
+#pragma unroll 1
+  for (int hi = 0; hi < nh; ++hi) {
+    const int h = h0 + hi, buf = hi & 1;
+    cp_async_wait_all();  // this thread's copies for head hi
+    // MMAs of the previous head: the masked tile, the other buffer and its accumulators are free / ready
+    if (hi > 0) ok = tc::mbar_wait(tc::smem_u32(&mbar[1 + (buf ^ 1)]), ((hi - 1) >> 1) & 1) && ok;
+    tc::fence_after_sync();
+    ok = __syncthreads_and(ok);  // every thread's copies and staged y are visible; the verdict on the waits is CTA-wide
+    if (!ok) {
+      fail = 1;
+      break;
+    }
+    if (hi >= 2) store_y(h - 2);     // staged by the epilogue of the previous iteration
+    if (hi >= 1) copy_z(h - 1);      // same lanes, same slots: ordered after the reads above
+    cp_async_commit();
+    if (hi + 1 < nh) prefetch(h + 1, buf ^ 1);
+    cp_async_commit();
+
+    // ---- decay mask: G (registers) -> masked tile, K-major over j: unit (i, j/8) at (j/8) * 2048 + i * 16
+    const float* vc = sVec + buf * (2 * kQ);
+    const float* vcp = vc + kQ;
+    const float ct = vc[i_chunk];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int cc = wg + 2 * k;  // chunk of 32 steps: fully causal (cc < rc), diagonal (cc == rc) or empty (cc > rc) for this warp's rows
+      const int jb = cc * 32;
+      unsigned char* dst = sBA + ((size_t)(jb / 8) * kBlk + i_loc) * 16;
+      if (cc > rc) {
+        const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + (size_t)q * kBlk * 16) = zero;
+        continue;
+      }
+      const bool diag = cc == rc;
 #pragma unroll
       for (int q = 0; q < 32; q += 8) {
+        const float4 c0 = *reinterpret_cast<const float4*>(vcp + jb + q);
+        const float4 c1 = *reinterpret_cast<const float4*>(vcp + jb + q + 4);
+        const float cj[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
         float f[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int j = jb + q + e;
-          const float m = (j <= i_loc) ? exp_fast(cum_i - sCum[j]) * sDt[j] : 0.f;
-          f[e] = v[q + e] * m;
+          float w = ex2_approx(ct - cj[e]);
+          if (diag && q + e > lane) w = 0.f;
+          f[e] = vG[k][q + e] * w;
         }
         Vec16<T> o;
         o.pack(f);
-        *reinterpret_cast<uint4*>(sA + ((size_t)((jb + q) / 8) * kBlk + wtid) * 16) = o.raw;
+        *reinterpret_cast<uint4*>(dst + (size_t)(q / 8) * kBlk * 16) = o.raw;
       }
     }
-  }
-  tc::fence_async_smem();
-  tc::fence_before_sync();
-  // Both warpgroups must have left the first MMA group's operands before either overwrites them
-  // (block 0's masked tile lands on the C tile that block 1's G also read): that is guaranteed by
-  // the wait on mbar[0] above, which covers all of those MMAs.  From here the warpgroups run apart.
-  named_barrier(1 + wg, 128);
-  tc::fence_after_sync();
+    // this row of x (for D x in the epilogue one iteration later)
+    uint4 xr[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) xr[q] = *reinterpret_cast<const uint4*>(sX + buf * M::X_BYTES + ((size_t)(wg * 4 + q) * KJ + i_chunk) * 16);
 
-  // ---- Y_intra = (G o L) X over this warpgroup's own columns ----------------------------------------
-  if (wtid == 0) {
-    const uint32_t g0 = tc::smem_u32(sA), x0 = tc::smem_u32(sX);
-    const uint32_t idY = tc::instr_desc(kBlk, kP, fmt, 0, 1);
-#pragma unroll 1
-    for (int kk = 0; kk < KJ / 16; ++kk) {
-      const uint64_t da = tc::smem_desc(g0 + kk * 2 * (kBlk * 16), kBlk * 16, 128);
-      const uint64_t dx = tc::smem_desc(x0 + kk * 256, 128, kQ * 16);
-      tc::mma_ss(tG, da, dx, idY, kk > 0);
-    }
-    tc::commit(tc::smem_u32(&mbar[1 + wg]));
-  }
-  ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[1 + wg]), 0)) && ok;
-  tc::fence_after_sync();
-  if (!ok && a.status) atomicExch(a.status, 2);
+    asm volatile("cp.async.wait_group 1;\n" ::: "memory");  // z of the previous head (the next head's operands may still be in flight)
+    tc::fence_async_smem();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
 
-  // ---- epilogue: y = Y_intra + exp(cum_i) Y_inter + D x, gate, store ----------------------------------
-  if (ok) {
-    const bool live = t_row < a.len;  // the TMEM loads below are warp-wide; only the stores are per row
-    const float escale = exp_fast(cum_i);
-    const T* zrow = a.z ? reinterpret_cast<const T*>(a.z) + (((int64_t)b * a.len + t_row) * a.heads + h) * kP : nullptr;
-    T* yrow = reinterpret_cast<T*>(a.Y) + (((int64_t)b * a.len + t_row) * a.heads + h) * kP;
-    const float Dh = (a.D && !a.d_has_p) ? __ldg(a.D + h) : 0.f;
+    // ---- Y_intra = (G o L) X,  Y_inter = C_m S_in  for this head ------------------------------------------
+    if (tid == 0) {
+      // descriptors differ from instruction to instruction only in the start address (16-byte units, low bits)
+      const uint64_t da0 = tc::smem_desc(tc::smem_u32(sBA), kBlk * 16, 128);
+      const uint64_t dx0 = tc::smem_desc(tc::smem_u32(sX + buf * M::X_BYTES), 128, KJ * 16);
+      const uint64_t dc0 = tc::smem_desc(tc::smem_u32(sC), kBlk * 16, 128);
+      const uint64_t ds0 = tc::smem_desc(tc::smem_u32(sS + buf * M::S_BYTES), kP * 16, 128);
+      constexpr uint32_t idY = tc::instr_desc(kBlk, kP, fmt, 0, 1);
+      constexpr uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 0);
+      const uint32_t dY = tmem + 256 + buf * 128, dS = dY + 64;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      float yi[32], ys[32];
-      tc::tmem_ld32(tG + lane_base + half * 32, yi);
-      tc::tmem_ld32(tYs + lane_base + half * 32, ys);
-      Vec16<T> zr[4];
-      if (zrow && live) {
+      for (int kk = 0; kk < KJ / 16; ++kk)
+        tc::mma_ss(dY, da0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), dx0 + (uint64_t)(kk * (256 >> 4)), idY, kk > 0);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) zr[q].load(zrow + half * 32 + q * 8);
-      }
+      for (int kk = 0; kk < kN / 16; ++kk)
+        tc::mma_ss(dS, dc0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), ds0 + (uint64_t)(kk * ((2 * kP * 16) >> 4)), idS, kk > 0);
+      tc::commit(tc::smem_u32(&mbar[1 + buf]));
+    }
+    // ---- the previous head's result, while the tensor cores work on this one ---------------------------------
+    if (hi > 0) epilogue(h - 1, buf ^ 1, ct_prev, xr_prev);
+    ct_prev = ct;
 #pragma unroll
-      for (int q = 0; q < 32; q += 8) {
-        const int p0 = half * 32 + q;
-        float f[8], xv[8];
-        Vec16<T> xr;
-        xr.raw = *reinterpret_cast<const uint4*>(sX + ((size_t)(p0 / 8) * kQ + i_loc) * 16);
-        xr.unpack(xv);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float Dv = (a.D && a.d_has_p) ? __ldg(a.D + h * kP + p0 + e) : Dh;
-          f[e] = fmaf(escale, ys[q + e], yi[q + e]) + Dv * xv[e];
-        }
-        if (zrow && live) {
-          float zv[8];
-          zr[q / 8].unpack(zv);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] *= silu_fast(zv[e]);
-        }
-        Vec16<T> o;
-        o.pack(f);
-        if (live) o.store(yrow + p0);
-      }
+    for (int q = 0; q < 4; ++q) xr_prev[q] = xr[q];
+  }
+  if (!fail && nh > 0) {
+    const int last = nh - 1, buf = last & 1;
+    ok = tc::mbar_wait(tc::smem_u32(&mbar[1 + buf]), (last >> 1) & 1);
+    tc::fence_after_sync();
+    ok = __syncthreads_and(ok);
+    if (ok) {
+      if (nh >= 2) store_y(h0 + last - 1);
+      copy_z(h0 + last);
+      cp_async_commit();
+      cp_async_wait_all();
+      __syncthreads();
+      epilogue(h0 + last, buf, ct_prev, xr_prev);
+      __syncthreads();
+      store_y(h0 + last);
+    } else {
+      fail = 1;
     }
   }
+  if (fail && tid == 0 && a.status) atomicExch(a.status, 2);
+  cp_async_wait_all();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads, 1) ssd_scan_kernel(const ssm_ssd_args a, int nchunks, int hpc, int nparts) {
+  extern __shared__ __align__(128) unsigned char smraw[];
+  __shared__ __align__(8) uint64_t mbar[3];    // 0: G, 1 + b: head MMAs into buffer b
+  __shared__ uint32_t tmem_slot;
+  const int warp = threadIdx.x >> 5;
+  if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), 512);
+  if (threadIdx.x == 0) {
+    tc::mbar_init(tc::smem_u32(&mbar[0]), 1);
+    tc::mbar_init(tc::smem_u32(&mbar[1]), 1);
+    tc::mbar_init(tc::smem_u32(&mbar[2]), 1);
+  }
+  // the heavier blocks (rows 128..255) are scheduled first
+  if ((int)blockIdx.x < (int)(gridDim.x >> 1)) ssd_scan_body<T, 1>(a, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
+  else ssd_scan_body<T, 0>(a, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(tmem, 512);
+  if (warp == 0) tc::tmem_dealloc(tmem_slot, 512);
 }
 
 template <typename T>
@@ -425,7 +555,14 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
   if (a.phase != 1) {
     const size_t smem = ScanSmem<T>::TOTAL;
     cudaFuncSetAttribute(ssd_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ssd_scan_kernel<T><<<dim3(a.heads, a.batch * nchunks), 256, smem, st>>>(a, nchunks);
+    // heads per CTA: the largest divisor of the heads of one B / C group that is <= 12, so that a
+    // CTA's heads share one G and the grid still has several CTAs per SM to balance
+    const int hpg = a.heads / a.groups;
+    int hpc = 1;
+    for (int d = 1; d <= 12; ++d)
+      if (hpg % d == 0) hpc = d;
+    const int nparts = a.heads / hpc;
+    ssd_scan_kernel<T><<<2 * nparts * a.batch * nchunks, kScanThreads, smem, st>>>(a, nchunks, hpc, nparts);
     if (int rc = launch_status("ssd_scan_kernel")) return rc;
   }
   return SSM_OK;
@@ -460,7 +597,8 @@ extern "C" int ssm_ssd_fwd(const ssm_ssd_args* a, ssm_stream_t stream) {
                   (!a->z || aligned_to(a->z, 16)),
               SSM_ERR_ALIGN, "ssd_scan: tensors must be 16-byte aligned");
   const int64_t nchunks = (a->len + kQ - 1) / kQ;
-  SSM_REQUIRE((int64_t)a->batch * nchunks <= 65535 && a->heads <= 65535, SSM_ERR_TOO_LARGE, "ssd_scan: grid too large");
+  SSM_REQUIRE((int64_t)a->batch * nchunks <= 65535 && a->heads <= 65535 && (int64_t)a->batch * nchunks * a->heads * 2 < (1ll << 31), SSM_ERR_TOO_LARGE,
+              "ssd_scan: grid too large");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (a->io_dtype == SSM_BF16) return ssd_launch<__nv_bfloat16>(*a, st);
   return ssd_launch<__half>(*a, st);

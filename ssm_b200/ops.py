@@ -15,6 +15,7 @@ defaults reproduce upstream behaviour.
 from __future__ import annotations
 
 import ctypes as C
+import math
 from typing import Any, Optional
 
 import torch
@@ -1009,7 +1010,7 @@ class _SsdWorkspace:
         nb, nl, nh, _, _, _ = self.shape
         vec = nb * nh * self.nchunks * self.chunk
         cum = self.ws[vec * 4: 2 * vec * 4].view(torch.float32).view(nb, nh, self.nchunks, self.chunk)
-        return cum[..., -1].sum(-1)
+        return cum[..., -1].sum(-1) * math.log(2.0)  # the scratch holds base-2 exponents
 
 
 def _ssd_tensor_core(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states, chunk_size):
