@@ -75,105 +75,150 @@ __global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, i
 }
 
 // ---------------------------------------------------------------------------------------------
-// local chunk states on the tensor cores:  S[n][p] = sum_j B[j][n] * (w_j x[j][p])
+// local chunk states on the tensor cores:  S[n][p] = sum_j B[j][n] * (w_j x[j][p]),  w_j = exp2(c_last - (c_j - log2 delta_j))
 //   A operand = B^T, MN-major [n/8][j][8];  B operand = w x, MN-major [p/8][j][8];  M = 128 (n), N = 64 (p), K = 256 (j)
+// One CTA (256 threads) per (batch, chunk, part of the heads of one B / C group): the B^T tile is
+// copied once and shared by the CTA's heads.  Per head: the raw x rows (cp.async, one head ahead)
+// are scaled into the operand tile, thread 0 issues the 16 MMAs into one of two TMEM accumulators,
+// and the previous head's accumulator is stored meanwhile (thread = state n, coalesced over n).
 // ---------------------------------------------------------------------------------------------
+struct StateSmem {
+  static constexpr int A_BYTES = (kN / 8) * kQ * 16;   // 64 KB
+  static constexpr int X_BYTES = (kP / 8) * kQ * 16;   // 32 KB: raw rows, and two operand buffers
+  static constexpr int VEC_BYTES = kQ * 4;             // c - log2(delta) of the chunk (x2)
+  static constexpr int TOTAL = A_BYTES + 3 * X_BYTES + 2 * VEC_BYTES;
+};
+
 template <typename T>
-__global__ void __launch_bounds__(128) ssd_state_kernel(const ssm_ssd_args a, int nchunks) {
+__global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a, int nchunks, int hpc, int nparts) {
   extern __shared__ __align__(128) unsigned char smraw[];
-  T* sA = reinterpret_cast<T*>(smraw);                       // 16 x 256 units of 16 bytes = 64 KB
-  T* sB = reinterpret_cast<T*>(smraw + (kN / 8) * kQ * 16);   //  8 x 256 units           = 32 KB
-  __shared__ __align__(8) uint64_t mbar;
+  unsigned char* sA = smraw;
+  unsigned char* sRaw = sA + StateSmem::A_BYTES;
+  unsigned char* sXo = sRaw + StateSmem::X_BYTES;  // two operand buffers
+  float* sVec = reinterpret_cast<float*>(sXo + 2 * StateSmem::X_BYTES);
+  __shared__ __align__(8) uint64_t mbar[2];
   __shared__ uint32_t tmem_slot;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int g = h / (a.heads / a.groups);
+  const int wg = tid >> 7;
+  const int part = (int)blockIdx.x % nparts, bc = (int)blockIdx.x / nparts;
+  const int c = bc % nchunks, b = bc / nchunks;
+  const int h0 = part * hpc;
+  const int nh = min(hpc, a.heads - h0);
+  const int g = h0 / (a.heads / a.groups);
   const int t0 = c * kQ;
+  constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
 
-  if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), 64);
-  if (tid == 0) tc::mbar_init(tc::smem_u32(&mbar), 1);
-
-  // ---- B^T tile: raw 16-byte units, step index fastest across threads -----------------------
-  const T* Bg = reinterpret_cast<const T*>(a.Bm);
-  for (int id = tid; id < (kN / 8) * kQ; id += 128) {
-    const int nc = id / kQ, j = id % kQ;
-    const int t = t0 + j;
-    const bool okt = t < a.len;
-    cp_async16(reinterpret_cast<unsigned char*>(sA) + ((size_t)nc * kQ + j) * 16,
-               Bg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
-  }
-  cp_async_commit();
-  // ---- x tile scaled by w_j = exp(cum_last - cum_j) * delta_j ---------------------------------
-  const float* wdt = a.ws_dt + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
-  const float* wcum = a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
-  const float cum_last = __ldg(wcum + kQ - 1);
-  const T* Xg = reinterpret_cast<const T*>(a.X);
-  constexpr int XU = 8;  // units per thread kept in flight together
-  for (int id0 = tid; id0 < (kP / 8) * kQ; id0 += 128 * XU) {
-    Vec16<T> v[XU];
-    float w[XU];
-#pragma unroll
-    for (int q = 0; q < XU; ++q) {
-      const int id = id0 + q * 128;
-      const int pc = id / kQ, j = id % kQ;
-      const int t = t0 + j;
-      v[q].raw = make_uint4(0, 0, 0, 0);
-      w[q] = 0.f;
-      if (t < a.len) {
-        v[q].load(Xg + (((int64_t)b * a.len + t) * a.heads + h) * kP + pc * 8);
-        w[q] = ex2_approx(cum_last - __ldg(wdt + j));
-      }
-    }
-#pragma unroll
-    for (int q = 0; q < XU; ++q) {
-      const int id = id0 + q * 128;
-      const int pc = id / kQ, j = id % kQ;
-      float f[8];
-      v[q].unpack(f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] *= w[q];
-      Vec16<T> o;
-      o.pack(f);
-      *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(sB) + ((size_t)pc * kQ + j) * 16) = o.raw;
-    }
-  }
-  cp_async_wait_all();
-  tc::fence_async_smem();
-  tc::fence_before_sync();
-  __syncthreads();
-  tc::fence_after_sync();
-  const uint32_t tmem = tmem_slot;
-
+  if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), 128);
   if (tid == 0) {
-    constexpr uint32_t idesc = tc::instr_desc(kN, kP, std::is_same<T, __nv_bfloat16>::value ? 1 : 0, 1, 1);
-    const uint32_t a0 = tc::smem_u32(sA), b0 = tc::smem_u32(sB);
-#pragma unroll 1
-    for (int kk = 0; kk < kQ / 16; ++kk) {
-      const uint64_t da = tc::smem_desc(a0 + kk * 256, 128, kQ * 16);  // two groups of 8 steps = 256 bytes per instruction
-      const uint64_t db = tc::smem_desc(b0 + kk * 256, 128, kQ * 16);
-      tc::mma_ss(tmem, da, db, idesc, kk > 0);
-    }
-    tc::commit(tc::smem_u32(&mbar));
+    tc::mbar_init(tc::smem_u32(&mbar[0]), 1);
+    tc::mbar_init(tc::smem_u32(&mbar[1]), 1);
   }
-  const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar), 0));  // warp-uniform
-  tc::fence_after_sync();
-  if (!ok && a.status) atomicExch(a.status, 1);
 
-  // ---- TMEM -> global: thread = state n, 64 columns = p ---------------------------------------
-  if (ok) {
-    float* out = a.ws_state + ((((int64_t)b * nchunks + c) * a.heads + h) * kP) * kN;
-    const int n = warp * 32 + lane;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      float v[32];
-      tc::tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + half * 32, v);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) out[(int64_t)(half * 32 + i) * kN + n] = v[i];
+  // ---- B^T tile: 16 lanes copy one 256-byte row of B ---------------------------------------------
+  const T* Bg = reinterpret_cast<const T*>(a.Bm);
+  {
+    const int nc = tid & 15, r0 = tid >> 4;
+    for (int j = r0; j < kQ; j += 16) {
+      const int t = t0 + j;
+      const bool okt = t < a.len;
+      cp_async16(sA + ((size_t)nc * kQ + j) * 16, Bg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
     }
   }
+  // raw x rows and the exponent vector of one head: 8 lanes copy one 128-byte row
+  const T* Xg = reinterpret_cast<const T*>(a.X);
+  const int xpc = tid & 7, xr0 = tid >> 3;
+  const int64_t xrow_stride = (int64_t)a.heads * kP;
+  const T* xsrc0 = Xg + ((int64_t)b * a.len + t0) * xrow_stride + xpc * 8;
+  const int64_t vbase = ((int64_t)b * a.heads * nchunks + c) * kQ;
+  auto prefetch = [&](int h, int vb) {
+    const T* xs = xsrc0 + (int64_t)h * kP;
+#pragma unroll
+    for (int k = 0; k < kQ / 32; ++k) {
+      const int j = xr0 + 32 * k;
+      const bool okt = t0 + j < a.len;
+      cp_async16(sRaw + ((size_t)xpc * kQ + j) * 16, xs + (okt ? (int64_t)j * xrow_stride : 0), okt);
+    }
+    if (tid < kQ / 4) cp_async16(sVec + vb * kQ + tid * 4, a.ws_dt + vbase + (int64_t)h * nchunks * kQ + tid * 4, true);
+  };
+  prefetch(h0, 0);
+  cp_async_commit();
+
+  __syncthreads();  // TMEM address and barriers are set up
+  const uint32_t tmem = tmem_slot;
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+
+  // accumulator `buf` -> global: thread = state n, this warpgroup's 32 of the 64 columns p
+  auto store_state = [&](int h, int buf) {
+    float v[32];
+    tc::tmem_ld32(tmem + lane_base + buf * 64 + wg * 32, v);
+    float* out = a.ws_state + ((((int64_t)b * nchunks + c) * a.heads + h) * kP + wg * 32) * kN + (warp & 3) * 32 + lane;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) out[(int64_t)i * kN] = v[i];
+  };
+
+  bool ok = true;
+  int fail = 0;
+#pragma unroll 1
+  for (int hi = 0; hi < nh; ++hi) {
+    const int h = h0 + hi, buf = hi & 1;
+    cp_async_wait_all();
+    __syncthreads();  // raw rows and vector of head hi (and, the first time, B^T) are visible
+
+    // ---- scale: operand[buf] = w_j * raw, unit (p/8, j) ------------------------------------------------
+    // the MMAs that last read operand[buf] (head hi - 2) were waited for before the previous store
+    const float* vcp = sVec + buf * kQ;
+    const float c_last = __ldg(a.ws_cum + vbase + (int64_t)h * nchunks * kQ + kQ - 1);
+    unsigned char* dX = sXo + buf * StateSmem::X_BYTES;
+#pragma unroll
+    for (int k = 0; k < (kP / 8) * kQ / 256; ++k) {
+      const int u = tid + 256 * k;  // unit index = pc * kQ + j
+      const int j = u % kQ;
+      const float w = ex2_approx(c_last - vcp[j]);
+      Vec16<T> v;
+      v.raw = *reinterpret_cast<const uint4*>(sRaw + (size_t)u * 16);
+      float f[8];
+      v.unpack(f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] *= w;
+      v.pack(f);
+      *reinterpret_cast<uint4*>(dX + (size_t)u * 16) = v.raw;
+    }
+    tc::fence_async_smem();
+    tc::fence_before_sync();
+    __syncthreads();  // operand complete; the raw buffer and the vector slot are free again
+    tc::fence_after_sync();
+    if (hi + 1 < nh) prefetch(h + 1, buf ^ 1);
+    cp_async_commit();
+
+    if (tid == 0) {
+      constexpr uint32_t idesc = tc::instr_desc(kN, kP, fmt, 1, 1);
+      const uint64_t da0 = tc::smem_desc(tc::smem_u32(sA), 128, kQ * 16);
+      const uint64_t db0 = tc::smem_desc(tc::smem_u32(dX), 128, kQ * 16);
+#pragma unroll
+      for (int kk = 0; kk < kQ / 16; ++kk)  // two groups of 8 steps = 256 bytes per instruction
+        tc::mma_ss(tmem + buf * 64, da0 + (uint64_t)(kk * (256 >> 4)), db0 + (uint64_t)(kk * (256 >> 4)), idesc, kk > 0);
+      tc::commit(tc::smem_u32(&mbar[buf]));
+    }
+    // ---- the previous head's state, while the tensor cores work on this one --------------------------------
+    if (hi > 0) {
+      ok = !fail && __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[buf ^ 1]), ((hi - 1) >> 1) & 1));  // no more waiting once one ran out
+      tc::fence_after_sync();
+      if (ok) store_state(h - 1, buf ^ 1);
+      else fail = 1;
+    }
+  }
+  if (nh > 0) {
+    const int last = nh - 1;
+    ok = !fail && __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[last & 1]), (last >> 1) & 1));
+    tc::fence_after_sync();
+    if (ok) store_state(h0 + last, last & 1);
+    else fail = 1;
+  }
+  if (fail && lane == 0 && a.status) atomicExch(a.status, 1);
+  cp_async_wait_all();
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(tmem, 64);
+  if (warp == 0) tc::tmem_dealloc(tmem, 128);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -536,15 +581,22 @@ __global__ void __launch_bounds__(kScanThreads, 1) ssd_scan_kernel(const ssm_ssd
 template <typename T>
 static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
   const int nchunks = (a.len + kQ - 1) / kQ;
+  // heads per CTA: the largest divisor of the heads of one B / C group that is <= 12, so that a
+  // CTA's heads share their B / C tiles and the grid still has several CTAs per SM to balance
+  const int hpg = a.heads / a.groups;
+  int hpc = 1;
+  for (int d = 1; d <= 12; ++d)
+    if (hpg % d == 0) hpc = d;
+  const int nparts = a.heads / hpc;
   if (a.phase != 2) {
     const int warps = a.batch * a.heads * nchunks;
     ssd_cumsum_kernel<T><<<(warps * 32 + 127) / 128, 128, 0, st>>>(a, nchunks);
     if (int rc = launch_status("ssd_cumsum_kernel")) return rc;
   }
   if (a.phase != 2) {
-    const size_t smem = (kN / 8 + kP / 8) * kQ * 16;
+    const size_t smem = StateSmem::TOTAL;
     cudaFuncSetAttribute(ssd_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ssd_state_kernel<T><<<dim3(nchunks, a.heads, a.batch), 128, smem, st>>>(a, nchunks);
+    ssd_state_kernel<T><<<nparts * a.batch * nchunks, 256, smem, st>>>(a, nchunks, hpc, nparts);
     if (int rc = launch_status("ssd_state_kernel")) return rc;
   }
   {
@@ -555,13 +607,6 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
   if (a.phase != 1) {
     const size_t smem = ScanSmem<T>::TOTAL;
     cudaFuncSetAttribute(ssd_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    // heads per CTA: the largest divisor of the heads of one B / C group that is <= 12, so that a
-    // CTA's heads share one G and the grid still has several CTAs per SM to balance
-    const int hpg = a.heads / a.groups;
-    int hpc = 1;
-    for (int d = 1; d <= 12; ++d)
-      if (hpg % d == 0) hpc = d;
-    const int nparts = a.heads / hpc;
     ssd_scan_kernel<T><<<2 * nparts * a.batch * nchunks, kScanThreads, smem, st>>>(a, nchunks, hpc, nparts);
     if (int rc = launch_status("ssd_scan_kernel")) return rc;
   }
