@@ -333,23 +333,35 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
   const T* xsrc0 = Xg + ((int64_t)b * a.len + t0) * xrow_stride + xpc * 8;
   const int64_t sbase = (((int64_t)b * nchunks + c) * a.heads) * (int64_t)(kP * kN) + tid * 8;
   const int64_t vbase = ((int64_t)b * a.heads * nchunks + c) * kQ;
-  auto prefetch = [&](int h, int buf) {
+  // One head's copies are issued in NCH parts, interleaved with the mask stage, so that the
+  // load/store unit's queue drains while the warp computes instead of stalling the issue.
+  auto prefetch_part = [&](int h, int buf, int part) {
+    constexpr int XP = (KJ / 32) / NCH;  // x passes per part
     unsigned char* dX = sX + buf * M::X_BYTES + (size_t)xpc * KJ * 16;
     const T* xs = xsrc0 + (int64_t)h * kP;
 #pragma unroll
-    for (int k = 0; k < KJ / 32; ++k) {
-      const int j = xr0 + 32 * k;
+    for (int k = 0; k < XP; ++k) {
+      const int j = xr0 + 32 * (part * XP + k);
       const bool okt = t0 + j < a.len;
       cp_async16(dX + (size_t)j * 16, xs + (okt ? (int64_t)j * xrow_stride : 0), okt);
     }
     unsigned char* dS = sS + buf * M::S_BYTES + (size_t)tid * 16;
     const T* ss = reinterpret_cast<const T*>(a.ws_state_in) + sbase + (int64_t)h * (kP * kN);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) cp_async16(dS + (size_t)k * kScanThreads * 16, ss + k * kScanThreads * 8, true);
-    float* dV = sVec + buf * (2 * kQ);
-    const int64_t voff = vbase + (int64_t)h * nchunks * kQ;
-    if (tid < KJ / 4) cp_async16(dV + tid * 4, a.ws_cum + voff + tid * 4, true);
-    else if (tid >= 128 && tid < 128 + KJ / 4) cp_async16(dV + kQ + (tid - 128) * 4, a.ws_dt + voff + (tid - 128) * 4, true);
+    for (int k = 0; k < 4 / NCH; ++k) {
+      const int kk = part * (4 / NCH) + k;
+      cp_async16(dS + (size_t)kk * kScanThreads * 16, ss + kk * kScanThreads * 8, true);
+    }
+    if (part == 0) {
+      float* dV = sVec + buf * (2 * kQ);
+      const int64_t voff = vbase + (int64_t)h * nchunks * kQ;
+      if (tid < KJ / 4) cp_async16(dV + tid * 4, a.ws_cum + voff + tid * 4, true);
+      else if (tid >= 128 && tid < 128 + KJ / 4) cp_async16(dV + kQ + (tid - 128) * 4, a.ws_dt + voff + (tid - 128) * 4, true);
+    }
+  };
+  auto prefetch = [&](int h, int buf) {
+#pragma unroll
+    for (int part = 0; part < NCH; ++part) prefetch_part(h, buf, part);
   };
   // z / y staging: 8 lanes handle one 128-byte row of the block; slot of (row, 16-byte chunk) is swizzled
   // so that both these row-wise accesses and the epilogue's one-row-per-thread accesses avoid bank conflicts
@@ -465,8 +477,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
     if (hi >= 2) store_y(h - 2);     // staged by the epilogue of the previous iteration
     if (hi >= 1) copy_z(h - 1);      // same lanes, same slots: ordered after the reads above
     cp_async_commit();
-    if (hi + 1 < nh) prefetch(h + 1, buf ^ 1);
-    cp_async_commit();
+    const bool more = hi + 1 < nh;
 
     // ---- decay mask: G (registers) -> masked tile, K-major over j: unit (i, j/8) at (j/8) * 2048 + i * 16
     const float* vc = sVec + buf * (2 * kQ);
@@ -474,6 +485,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
     const float ct = vc[i_chunk];
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
+      if (more) prefetch_part(h + 1, buf ^ 1, k);
       const int cc = wg + 2 * k;  // chunk of 32 steps: fully causal (cc < rc), diagonal (cc == rc) or empty (cc > rc) for this warp's rows
       const int jb = cc * 32;
       unsigned char* dst = sBA + ((size_t)(jb / 8) * kBlk + i_loc) * 16;
@@ -501,6 +513,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
         *reinterpret_cast<uint4*>(dst + (size_t)(q / 8) * kBlk * 16) = o.raw;
       }
     }
+    cp_async_commit();
     // this row of x (for D x in the epilogue one iteration later)
     uint4 xr[4];
 #pragma unroll
