@@ -270,7 +270,8 @@ struct ScanSmem {
   static constexpr int S_BYTES = kP * kN * 2;       // incoming state, K-major [n/8][p][8]                  16 KB (x2)
   static constexpr int VEC_BYTES = 2 * kQ * 4;      // c and c - log2(delta) of the chunk                     2 KB (x2)
   static constexpr int Z_BYTES = kBlk * kP * 2;     // z in / y out of one head: [row][8 chunks of 16 B], chunk ^= row & 7   16 KB
-  static constexpr int TOTAL = C_BYTES + B_BYTES + 2 * (X_BYTES + S_BYTES + VEC_BYTES) + Z_BYTES;
+  static constexpr int W_BYTES = 8 * 128 * 4;       // per warp: the column factors of its (up to) four mask chunks            4 KB
+  static constexpr int TOTAL = C_BYTES + B_BYTES + 2 * (X_BYTES + S_BYTES + VEC_BYTES) + Z_BYTES + W_BYTES;
 };
 
 constexpr int kScanThreads = 256;
@@ -291,6 +292,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wg = tid >> 7;                     // column chunks wg, wg + 2, ... in the mask stage; column half in the epilogue
+  float* sW = reinterpret_cast<float*>(sZ + M::Z_BYTES) + warp * 128;  // this warp's column factors
   const int half_grid = gridDim.x >> 1;
   const int rem = (int)blockIdx.x % half_grid;
   const int part = rem % nparts, bc = rem / nparts;
@@ -483,6 +485,24 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
     const float* vc = sVec + buf * (2 * kQ);
     const float* vcp = vc + kQ;
     const float ct = vc[i_chunk];
+    // The weight exp2(c_i - c'_j) of a 32-step chunk factors as exp2(c_i - r) * exp2(r - c'_j) with r = c at the
+    // chunk's first step (row factor <= 1 for causal rows, column factor bounded by the decay inside the chunk).
+    // Each lane forms one column factor per chunk, each thread one row factor per chunk: 2 ex2 per 32 elements
+    // instead of 32.  Chunks whose internal decay exceeds 2^60 keep the exact per-element form.
+    float arow[NCH];
+    bool fast[NCH];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int cc = wg + 2 * k;
+      arow[k] = 0.f, fast[k] = false;
+      if (cc <= rc) {
+        const float r = vc[cc * 32];
+        fast[k] = r - vc[cc * 32 + 31] < 60.f;  // same for every lane
+        arow[k] = ex2_approx(ct - r);
+        sW[k * 32 + lane] = ex2_approx(r - vcp[cc * 32 + lane]);
+      }
+    }
+    __syncwarp();
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       if (more) prefetch_part(h + 1, buf ^ 1, k);
@@ -496,21 +516,42 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
         continue;
       }
       const bool diag = cc == rc;
+      if (fast[k]) {
+        const float2 a2 = make_float2(arow[k], arow[k]);
 #pragma unroll
-      for (int q = 0; q < 32; q += 8) {
-        const float4 c0 = *reinterpret_cast<const float4*>(vcp + jb + q);
-        const float4 c1 = *reinterpret_cast<const float4*>(vcp + jb + q + 4);
-        const float cj[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-        float f[8];
+        for (int q = 0; q < 32; q += 8) {
+          const float4 b0 = *reinterpret_cast<const float4*>(sW + k * 32 + q);
+          const float4 b1 = *reinterpret_cast<const float4*>(sW + k * 32 + q + 4);
+          const float2 bp[4] = {make_float2(b0.x, b0.y), make_float2(b0.z, b0.w), make_float2(b1.x, b1.y), make_float2(b1.z, b1.w)};
+          float f[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          float w = ex2_approx(ct - cj[e]);
-          if (diag && q + e > lane) w = 0.f;
-          f[e] = vG[k][q + e] * w;
+          for (int e = 0; e < 8; e += 2) {
+            float2 w = __fmul2_rn(__fmul2_rn(make_float2(vG[k][q + e], vG[k][q + e + 1]), bp[e / 2]), a2);
+            if (diag && q + e > lane) w.x = 0.f;
+            if (diag && q + e + 1 > lane) w.y = 0.f;
+            f[e] = w.x, f[e + 1] = w.y;
+          }
+          Vec16<T> o;
+          o.pack(f);
+          *reinterpret_cast<uint4*>(dst + (size_t)(q / 8) * kBlk * 16) = o.raw;
         }
-        Vec16<T> o;
-        o.pack(f);
-        *reinterpret_cast<uint4*>(dst + (size_t)(q / 8) * kBlk * 16) = o.raw;
+      } else {
+#pragma unroll
+        for (int q = 0; q < 32; q += 8) {
+          const float4 c0 = *reinterpret_cast<const float4*>(vcp + jb + q);
+          const float4 c1 = *reinterpret_cast<const float4*>(vcp + jb + q + 4);
+          const float cj[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            float w = ex2_approx(ct - cj[e]);
+            if (diag && q + e > lane) w = 0.f;
+            f[e] = vG[k][q + e] * w;
+          }
+          Vec16<T> o;
+          o.pack(f);
+          *reinterpret_cast<uint4*>(dst + (size_t)(q / 8) * kBlk * 16) = o.raw;
+        }
       }
     }
     cp_async_commit();

@@ -66,6 +66,22 @@ def test_tensor_core_ssd_without_optionals_and_matrix_D():
     close(Sg, So, **HALF_TOL, what="final state")
 
 
+def test_tensor_core_ssd_strong_decay_takes_the_exact_mask_form():
+    """Steps whose decay inside a 32-step chunk exceeds 2^60 cannot use the factored mask; mixed with mild heads."""
+    from ssm_b200 import ops
+
+    t = _inputs(1, 768, 4, 1, torch.bfloat16, seed=21)
+    A = torch.tensor([-16.0, -0.5, -12.0, -1.0])
+    dtp = torch.rand(1, 768, 4, generator=torch.Generator().manual_seed(5)).mul(0.6).add(0.05).to(torch.bfloat16)
+    dtp[:, 300:340] = 0.0  # steps without any update
+    Yo, So = orc.ssd_scan(t["X"], dtp, A, t["B"], t["C"], 256, D=t["D"], z=t["z"], initial_states=t["initial_states"], return_final_states=True)
+    Yg, Sg = ops.ssd_scan(t["X"].cuda(), dtp.cuda(), A.cuda(), t["B"].cuda(), t["C"].cuda(), 256, D=t["D"].cuda(), z=t["z"].cuda(),
+                          initial_states=t["initial_states"].cuda(), return_final_states=True, check_status=True)
+    assert torch.isfinite(Yg.float()).all() and torch.isfinite(Sg).all()
+    close(Yg, Yo, **HALF_TOL, what="Y")
+    close(Sg, So, **HALF_TOL, what="final state")
+
+
 def test_tensor_core_ssd_agrees_with_scan_kernel_path_and_has_gradients():
     """Same operator, two CUDA paths: chunked tensor-core GEMMs vs the sequential scan kernels."""
     from ssm_b200 import ops
