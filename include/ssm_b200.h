@@ -353,8 +353,10 @@ int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* args, ssm_stream_t s
  * carved by the caller from one buffer of ssm_ssd_scratch_bytes() bytes:
  *   ws_dt, ws_cum : (batch, heads, nchunks * 256) fp32 each; per chunk ws_cum[i] = log2(e) * sum_{k<=i} delta_k A
  *                   (running decay exponent, base 2) and ws_dt[i] = ws_cum[i] - log2(delta_i)
- *   ws_state      : (batch, nchunks, heads, headdim, nstate) fp32
- *   ws_state_in   : the same shape in io_dtype
+ *   ws_state      : (batch, heads, headdim, nstate) fp32 — the final state reached from the given (or zero)
+ *                   initial state, kept for a later phase-2 call on the same scratch
+ *   ws_state_in   : (batch, nchunks, heads, headdim * nstate) in io_dtype — the state before every chunk, in
+ *                   the operand order of the scan kernel
  * status: optional device int, set non-zero when a bounded device-side wait ran out.
  * phase: 0 runs everything.  1 stops after the per-chunk states and the pass over chunks (it
  * fills the scratch and final_states, writes no Y); 2 redoes only the pass over chunks with

@@ -6,9 +6,10 @@
 // the tcgen05 tensor cores (bf16 / fp16 operands from shared memory, fp32 accumulators in TMEM):
 //
 //   ssd_cumsum_kernel   per chunk the running decay exponent  c_i = log2(e) sum_{k<=i} delta_k A  and  c_i - log2(delta_i)
-//   ssd_state_kernel    per (batch, chunk, head): local state  S_c = sum_j exp(cum_last - cum_j) delta_j x_j B_j^T   [N x P GEMM, K = Q]
-//   ssd_pass_kernel     the short serial pass over chunks: incoming state of every chunk (kept in
+//   ssd_state_kernel    per (batch, head), chunks in order: local state  S_c = sum_j exp2(c_last - c_j) delta_j x_j B_j^T   [N x P GEMM, K = Q]
+//                       folded into the running state in registers; the state before every chunk (kept in
 //                       the operand dtype for the GEMM below) and the final state in fp32
+//   ssd_fold_init_kernel  (sequence shards only) adds a late-arriving incoming state to those by linearity
 //   ssd_scan_kernel     per (batch, chunk, head), one warpgroup per 128-row block:  G = C B^T  (TMEM), the decay mask
 //                       exp(cum_i - cum_j) delta_j [j <= i] applied on the TMEM -> register path and
 //                       re-packed as the A operand of  Y_intra = (G o L) X, plus  Y_inter = C S_in;
@@ -75,144 +76,182 @@ __global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, i
 }
 
 // ---------------------------------------------------------------------------------------------
-// local chunk states on the tensor cores:  S[n][p] = sum_j B[j][n] * (w_j x[j][p]),  w_j = exp2(c_last - (c_j - log2 delta_j))
-//   A operand = B^T, MN-major [n/8][j][8];  B operand = w x, MN-major [p/8][j][8];  M = 128 (n), N = 64 (p), K = 256 (j)
-// One CTA (256 threads) per (batch, chunk, part of the heads of one B / C group): the B^T tile is
-// copied once and shared by the CTA's heads.  Per head: the raw x rows (cp.async, one head ahead)
-// are scaled into the operand tile, thread 0 issues the 16 MMAs into one of two TMEM accumulators,
-// and the previous head's accumulator is stored meanwhile (thread = state n, coalesced over n).
+// chunk states, local and carried, in one pass:  one CTA (256 threads) per (batch, head) walks the
+// chunks in order.  Per chunk the tensor cores form  S_c[n][p] = sum_j B[j][n] * (w_j x[j][p]),
+// w_j = exp2(c_last - (c_j - log2 delta_j)), in two half-chunk stages of a four-stage ring
+//   A operand = B^T, MN-major, stored [j/8][n/8][j%8][8];  B operand = w x, MN-major [j/8][p/8][j%8][8];  M = 128 (n), N = 64 (p),
+//   K = 128 per stage.  (Units that are neighbours along M / N are 128 bytes apart, so the tensor core's reads of one
+//   K slice fall on different banks; with the [n/8][j][8] order they were 2 KB apart and the MMAs ran 4-5x slower.)
+// while the threads keep the running state in registers (thread = state n, 32 of the 64 columns p):
+//   state <- exp2(c_last) * state + S_c ;  the state BEFORE each chunk goes out in the operand dtype,
+// in the operand order of the scan kernel (MN-major units [p/8][n][8]).  The per-chunk local states
+// never touch global memory.  Copies (cp.async, whole rows) run two stages ahead; a stage's buffer
+// is refilled once the MMAs that read it have completed (tcgen05.commit -> mbarrier).
 // ---------------------------------------------------------------------------------------------
 struct StateSmem {
-  static constexpr int A_BYTES = (kN / 8) * kQ * 16;   // 64 KB
-  static constexpr int X_BYTES = (kP / 8) * kQ * 16;   // 32 KB: raw rows, and two operand buffers
-  static constexpr int VEC_BYTES = kQ * 4;             // c - log2(delta) of the chunk (x2)
-  static constexpr int TOTAL = A_BYTES + 3 * X_BYTES + 2 * VEC_BYTES;
+  static constexpr int kHalf = kQ / 2;                       // steps per stage
+  static constexpr int A_BYTES = (kN / 8) * kHalf * 16;      // 32 KB
+  static constexpr int X_BYTES = (kP / 8) * kHalf * 16;      // 16 KB
+  static constexpr int STAGE = A_BYTES + X_BYTES;
+  static constexpr int NSTAGE = 4;
+  static constexpr int VEC_BYTES = kQ * 4;                   // c - log2(delta) of a chunk (x2)
+  static constexpr int TOTAL = NSTAGE * STAGE + 2 * VEC_BYTES;
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a, int nchunks, int hpc, int nparts) {
+__global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a, int nchunks) {
+  using M = StateSmem;
+  constexpr int kHalf = M::kHalf;
   extern __shared__ __align__(128) unsigned char smraw[];
-  unsigned char* sA = smraw;
-  unsigned char* sRaw = sA + StateSmem::A_BYTES;
-  unsigned char* sXo = sRaw + StateSmem::X_BYTES;  // two operand buffers
-  float* sVec = reinterpret_cast<float*>(sXo + 2 * StateSmem::X_BYTES);
-  __shared__ __align__(8) uint64_t mbar[2];
+  float* sVec = reinterpret_cast<float*>(smraw + M::NSTAGE * M::STAGE);
+  __shared__ __align__(8) uint64_t mbar_free[M::NSTAGE];  // the MMAs that read a stage's buffer have completed
+  __shared__ __align__(8) uint64_t mbar_acc[2];           // a chunk's accumulator is complete
   __shared__ uint32_t tmem_slot;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wg = tid >> 7;
-  const int part = (int)blockIdx.x % nparts, bc = (int)blockIdx.x / nparts;
-  const int c = bc % nchunks, b = bc / nchunks;
-  const int h0 = part * hpc;
-  const int nh = min(hpc, a.heads - h0);
-  const int g = h0 / (a.heads / a.groups);
-  const int t0 = c * kQ;
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int g = h / (a.heads / a.groups);
+  const int n = (warp & 3) * 32 + lane;  // this thread's state index = TMEM lane
   constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
 
   if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), 128);
   if (tid == 0) {
-    tc::mbar_init(tc::smem_u32(&mbar[0]), 1);
-    tc::mbar_init(tc::smem_u32(&mbar[1]), 1);
+    for (int i = 0; i < M::NSTAGE; ++i) tc::mbar_init(tc::smem_u32(&mbar_free[i]), 1);
+    tc::mbar_init(tc::smem_u32(&mbar_acc[0]), 1);
+    tc::mbar_init(tc::smem_u32(&mbar_acc[1]), 1);
   }
 
-  // ---- B^T tile: 16 lanes copy one 256-byte row of B ---------------------------------------------
   const T* Bg = reinterpret_cast<const T*>(a.Bm);
-  {
-    const int nc = tid & 15, r0 = tid >> 4;
-    for (int j = r0; j < kQ; j += 16) {
-      const int t = t0 + j;
-      const bool okt = t < a.len;
-      cp_async16(sA + ((size_t)nc * kQ + j) * 16, Bg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
-    }
-  }
-  // raw x rows and the exponent vector of one head: 8 lanes copy one 128-byte row
   const T* Xg = reinterpret_cast<const T*>(a.X);
-  const int xpc = tid & 7, xr0 = tid >> 3;
-  const int64_t xrow_stride = (int64_t)a.heads * kP;
-  const T* xsrc0 = Xg + ((int64_t)b * a.len + t0) * xrow_stride + xpc * 8;
-  const int64_t vbase = ((int64_t)b * a.heads * nchunks + c) * kQ;
-  auto prefetch = [&](int h, int vb) {
-    const T* xs = xsrc0 + (int64_t)h * kP;
+  const int64_t vrow = ((int64_t)b * a.heads + h) * nchunks * kQ;  // this (batch, head)'s exponent vectors
+  const int nst = 2 * nchunks;
+  // stage s = (chunk s / 2, half s % 2): 16 lanes copy one 256-byte row of B, 8 lanes one 128-byte row of x
+  auto copy_stage = [&](int s) {
+    unsigned char* base = smraw + (s & 3) * M::STAGE;
+    const int tq = (s >> 1) * kQ + (s & 1) * kHalf;  // first step of the stage
+    {
+      const int nc = tid & 15, r0 = tid >> 4;
 #pragma unroll
-    for (int k = 0; k < kQ / 32; ++k) {
-      const int j = xr0 + 32 * k;
-      const bool okt = t0 + j < a.len;
-      cp_async16(sRaw + ((size_t)xpc * kQ + j) * 16, xs + (okt ? (int64_t)j * xrow_stride : 0), okt);
+      for (int k = 0; k < kHalf / 16; ++k) {
+        const int j = r0 + 16 * k;
+        const bool okt = tq + j < a.len;
+        cp_async16(base + (size_t)(j >> 3) * (kN * 16) + nc * 128 + (j & 7) * 16, Bg + (((int64_t)b * a.len + (okt ? tq + j : 0)) * a.groups + g) * kN + nc * 8, okt);
+      }
     }
-    if (tid < kQ / 4) cp_async16(sVec + vb * kQ + tid * 4, a.ws_dt + vbase + (int64_t)h * nchunks * kQ + tid * 4, true);
+    {
+      const int pc = tid & 7, r0 = tid >> 3;
+#pragma unroll
+      for (int k = 0; k < kHalf / 32; ++k) {
+        const int j = r0 + 32 * k;
+        const bool okt = tq + j < a.len;
+        cp_async16(base + M::A_BYTES + (size_t)(j >> 3) * (kP * 16) + pc * 128 + (j & 7) * 16, Xg + (((int64_t)b * a.len + (okt ? tq + j : 0)) * a.heads + h) * kP + pc * 8, okt);
+      }
+    }
+    if ((s & 1) == 0 && tid < kQ / 4) cp_async16(sVec + ((s >> 1) & 1) * kQ + tid * 4, a.ws_dt + vrow + (int64_t)(s >> 1) * kQ + tid * 4, true);
   };
-  prefetch(h0, 0);
+  copy_stage(0);
+  cp_async_commit();
+  if (nst > 1) copy_stage(1);
   cp_async_commit();
 
   __syncthreads();  // TMEM address and barriers are set up
   const uint32_t tmem = tmem_slot;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
-  // accumulator `buf` -> global: thread = state n, this warpgroup's 32 of the 64 columns p
-  auto store_state = [&](int h, int buf) {
-    float v[32];
-    tc::tmem_ld32(tmem + lane_base + buf * 64 + wg * 32, v);
-    float* out = a.ws_state + ((((int64_t)b * nchunks + c) * a.heads + h) * kP + wg * 32) * kN + (warp & 3) * 32 + lane;
+  // running state: st[i] = S[n][wg * 32 + i]
+  float st[32];
+  {
+    const float* init = a.initial_states ? a.initial_states + (((int64_t)b * a.heads + h) * kP + wg * 32) * kN + n : nullptr;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) out[(int64_t)i * kN] = v[i];
+    for (int i = 0; i < 32; ++i) st[i] = init ? __ldg(init + (int64_t)i * kN) : 0.f;
+  }
+  T* sin = reinterpret_cast<T*>(a.ws_state_in);
+  // the state before chunk c, in the operand dtype: unit (p / 8, n) of the (batch, chunk, head) tile
+  auto emit_state_in = [&](int c) {
+    T* blk = sin + (((int64_t)b * nchunks + c) * a.heads + h) * (int64_t)(kP * kN);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      Vec16<T> o;
+      o.pack(*reinterpret_cast<const float(*)[8]>(&st[q * 8]));
+      *reinterpret_cast<uint4*>(blk + ((size_t)(wg * 4 + q) * kN + n) * 8) = o.raw;
+    }
+  };
+  // fold chunk c's finished accumulator into the running state
+  auto fold_chunk = [&](int c) -> bool {
+    const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_acc[c & 1]), (c >> 1) & 1));
+    tc::fence_after_sync();
+    if (ok) {
+      const float decay = ex2_approx(__ldg(a.ws_cum + vrow + (int64_t)c * kQ + kQ - 1));
+      float v[32];
+      tc::tmem_ld32(tmem + lane_base + (c & 1) * 64 + wg * 32, v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) st[i] = fmaf(decay, st[i], v[i]);
+    }
+    return ok;
   };
 
-  bool ok = true;
   int fail = 0;
 #pragma unroll 1
-  for (int hi = 0; hi < nh; ++hi) {
-    const int h = h0 + hi, buf = hi & 1;
-    cp_async_wait_all();
-    __syncthreads();  // raw rows and vector of head hi (and, the first time, B^T) are visible
+  for (int s = 0; s < nst; ++s) {
+    const int c = s >> 1, hf = s & 1;
+    // ---- refill the buffer two stages ahead; it was last read by the MMAs of stage s - 2 -------------
+    if (s + 2 < nst) {
+      if (s >= 2 && !fail) fail = !__all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_free[(s + 2) & 3]), ((s - 2) >> 2) & 1));
+      copy_stage(s + 2);
+    }
+    cp_async_commit();
+    // ---- a new chunk begins: fold the previous chunk, hand out the state before this one ----------------
+    if (hf == 0) {
+      if (c >= 1 && !fail) fail = !fold_chunk(c - 1);
+      emit_state_in(c);
+    }
+    asm volatile("cp.async.wait_group 2;\n" ::: "memory");  // this stage's copies (two younger groups may be in flight)
+    __syncthreads();
 
-    // ---- scale: operand[buf] = w_j * raw, unit (p/8, j) ------------------------------------------------
-    // the MMAs that last read operand[buf] (head hi - 2) were waited for before the previous store
-    const float* vcp = sVec + buf * kQ;
-    const float c_last = __ldg(a.ws_cum + vbase + (int64_t)h * nchunks * kQ + kQ - 1);
-    unsigned char* dX = sXo + buf * StateSmem::X_BYTES;
+    // ---- scale the x rows in place: w_j x_j -----------------------------------------------------------------
+    unsigned char* base = smraw + (s & 3) * M::STAGE;
+    const float* vcp = sVec + (c & 1) * kQ + hf * kHalf;
+    const float c_last = __ldg(a.ws_cum + vrow + (int64_t)c * kQ + kQ - 1);
 #pragma unroll
-    for (int k = 0; k < (kP / 8) * kQ / 256; ++k) {
-      const int u = tid + 256 * k;  // unit index = pc * kQ + j
-      const int j = u % kQ;
-      const float w = ex2_approx(c_last - vcp[j]);
+    for (int k = 0; k < (kP / 8) * kHalf / 256; ++k) {
+      const int u = tid + 256 * k;  // unit index = (j / 8) * 64 + pc * 8 + j % 8
+      const float w = ex2_approx(c_last - vcp[(u >> 6) * 8 + (u & 7)]);
+      unsigned char* px = base + M::A_BYTES + (size_t)u * 16;
       Vec16<T> v;
-      v.raw = *reinterpret_cast<const uint4*>(sRaw + (size_t)u * 16);
+      v.raw = *reinterpret_cast<const uint4*>(px);
       float f[8];
       v.unpack(f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) f[i] *= w;
       v.pack(f);
-      *reinterpret_cast<uint4*>(dX + (size_t)u * 16) = v.raw;
+      *reinterpret_cast<uint4*>(px) = v.raw;
     }
     tc::fence_async_smem();
     tc::fence_before_sync();
-    __syncthreads();  // operand complete; the raw buffer and the vector slot are free again
+    __syncthreads();
     tc::fence_after_sync();
-    if (hi + 1 < nh) prefetch(h + 1, buf ^ 1);
-    cp_async_commit();
 
     if (tid == 0) {
       constexpr uint32_t idesc = tc::instr_desc(kN, kP, fmt, 1, 1);
-      const uint64_t da0 = tc::smem_desc(tc::smem_u32(sA), 128, kQ * 16);
-      const uint64_t db0 = tc::smem_desc(tc::smem_u32(dX), 128, kQ * 16);
+      const uint64_t da0 = tc::smem_desc(tc::smem_u32(base), kN * 16, 128);
+      const uint64_t db0 = tc::smem_desc(tc::smem_u32(base + M::A_BYTES), kP * 16, 128);
 #pragma unroll
-      for (int kk = 0; kk < kQ / 16; ++kk)  // two groups of 8 steps = 256 bytes per instruction
-        tc::mma_ss(tmem + buf * 64, da0 + (uint64_t)(kk * (256 >> 4)), db0 + (uint64_t)(kk * (256 >> 4)), idesc, kk > 0);
-      tc::commit(tc::smem_u32(&mbar[buf]));
-    }
-    // ---- the previous head's state, while the tensor cores work on this one --------------------------------
-    if (hi > 0) {
-      ok = !fail && __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[buf ^ 1]), ((hi - 1) >> 1) & 1));  // no more waiting once one ran out
-      tc::fence_after_sync();
-      if (ok) store_state(h - 1, buf ^ 1);
-      else fail = 1;
+      for (int kk = 0; kk < kHalf / 16; ++kk)  // two groups of 8 steps per instruction
+        tc::mma_ss(tmem + (c & 1) * 64, da0 + (uint64_t)(kk * ((2 * kN * 16) >> 4)), db0 + (uint64_t)(kk * ((2 * kP * 16) >> 4)), idesc,
+                   hf > 0 || kk > 0);
+      tc::commit(tc::smem_u32(&mbar_free[s & 3]));
+      if (hf == 1) tc::commit(tc::smem_u32(&mbar_acc[c & 1]));
     }
   }
-  if (nh > 0) {
-    const int last = nh - 1;
-    ok = !fail && __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[last & 1]), (last >> 1) & 1));
-    tc::fence_after_sync();
-    if (ok) store_state(h0 + last, last & 1);
-    else fail = 1;
+  if (nchunks > 0 && !fail) fail = !fold_chunk(nchunks - 1);
+  // final state in fp32, (p, n) order: to the caller, and kept in scratch for a later phase 2
+  if (!fail) {
+    const int64_t off = (((int64_t)b * a.heads + h) * kP + wg * 32) * kN + n;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (a.final_states) a.final_states[off + (int64_t)i * kN] = st[i];
+      a.ws_state[off + (int64_t)i * kN] = st[i];
+    }
   }
   if (fail && lane == 0 && a.status) atomicExch(a.status, 1);
   cp_async_wait_all();
@@ -222,30 +261,30 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
 }
 
 // ---------------------------------------------------------------------------------------------
-// serial pass over chunks: one thread per (batch, head, p, n)
+// phase 2 of a sequence shard: the shard's incoming state S0 arrives after the chunk states were
+// formed from a zero state.  By linearity  state_before_chunk_c += exp2(sum_{c' < c} c_last[c']) * S0
+// and  final += exp2(sum_c c_last[c]) * S0.  One thread per element, operand order of the scan kernel.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) ssd_pass_kernel(const ssm_ssd_args a, int nchunks) {
-  // thread = one element of the (p, n) state of one (batch, head), in the order of the operand
-  // tile the scan kernel copies:  q = ((n / 8) * P + p) * 8 + n % 8  (K-major units of 16 bytes)
+__global__ void __launch_bounds__(256) ssd_fold_init_kernel(const ssm_ssd_args a, int nchunks) {
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   const int64_t per = (int64_t)kP * kN;
   const int64_t total = (int64_t)a.batch * a.heads * per;
   if (i >= total) return;
   const int64_t bh = i / per;
-  const int q = (int)(i % per);
-  const int e = q & 7, p = (q >> 3) % kP, nc = q / (8 * kP);
-  const int pn = p * kN + nc * 8 + e;
+  const int q = (int)(i % per);  // ((p / 8) * N + n) * 8 + p % 8
+  const int e = q & 7, n = (q >> 3) % kN, pc = q / (8 * kN);
+  const int pn = (pc * 8 + e) * kN + n;
   const int b = (int)(bh / a.heads), h = (int)(bh % a.heads);
-  float s = a.initial_states ? __ldg(a.initial_states + bh * per + pn) : 0.f;
+  const float s0 = a.initial_states ? __ldg(a.initial_states + bh * per + pn) : 0.f;
   T* sin = reinterpret_cast<T*>(a.ws_state_in);
+  float expo = 0.f;
   for (int c = 0; c < nchunks; ++c) {
-    const int64_t blk = (((int64_t)b * nchunks + c) * a.heads + h) * per;
-    sin[blk + q] = from_f<T>(s);
-    const float decay = ex2_approx(__ldg(a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ + kQ - 1));
-    s = fmaf(decay, s, a.ws_state[blk + pn]);
+    const int64_t idx = (((int64_t)b * nchunks + c) * a.heads + h) * per + q;
+    if (a.initial_states) sin[idx] = from_f<T>(to_f<T>(sin[idx]) + ex2_approx(expo) * s0);
+    expo += __ldg(a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ + kQ - 1);
   }
-  if (a.final_states) a.final_states[bh * per + pn] = s;
+  if (a.final_states) a.final_states[bh * per + pn] = a.ws_state[bh * per + pn] + ex2_approx(expo) * s0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -267,7 +306,7 @@ struct ScanSmem {
   static constexpr int C_BYTES = kBlk * kN * 2;     // C rows of the block, K-major [n/8][i][8]            32 KB
   static constexpr int B_BYTES = kQ * kN * 2;       // B rows, K-major [n/8][j][8]; later the masked tile  64 KB
   static constexpr int X_BYTES = kQ * kP * 2;       // x rows, MN-major [p/8][j][8]                         32 KB (x2)
-  static constexpr int S_BYTES = kP * kN * 2;       // incoming state, K-major [n/8][p][8]                  16 KB (x2)
+  static constexpr int S_BYTES = kP * kN * 2;       // incoming state, MN-major [p/8][n][8]                 16 KB (x2)
   static constexpr int VEC_BYTES = 2 * kQ * 4;      // c and c - log2(delta) of the chunk                     2 KB (x2)
   static constexpr int Z_BYTES = kBlk * kP * 2;     // z in / y out of one head: [row][8 chunks of 16 B], chunk ^= row & 7   16 KB
   static constexpr int W_BYTES = 8 * 128 * 4;       // per warp: the column factors of its (up to) four mask chunks            4 KB
@@ -572,16 +611,16 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
       const uint64_t da0 = tc::smem_desc(tc::smem_u32(sBA), kBlk * 16, 128);
       const uint64_t dx0 = tc::smem_desc(tc::smem_u32(sX + buf * M::X_BYTES), 128, KJ * 16);
       const uint64_t dc0 = tc::smem_desc(tc::smem_u32(sC), kBlk * 16, 128);
-      const uint64_t ds0 = tc::smem_desc(tc::smem_u32(sS + buf * M::S_BYTES), kP * 16, 128);
+      const uint64_t ds0 = tc::smem_desc(tc::smem_u32(sS + buf * M::S_BYTES), 128, kN * 16);
       constexpr uint32_t idY = tc::instr_desc(kBlk, kP, fmt, 0, 1);
-      constexpr uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 0);
+      constexpr uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 1);
       const uint32_t dY = tmem + 256 + buf * 128, dS = dY + 64;
 #pragma unroll
       for (int kk = 0; kk < KJ / 16; ++kk)
         tc::mma_ss(dY, da0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), dx0 + (uint64_t)(kk * (256 >> 4)), idY, kk > 0);
 #pragma unroll
       for (int kk = 0; kk < kN / 16; ++kk)
-        tc::mma_ss(dS, dc0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), ds0 + (uint64_t)(kk * ((2 * kP * 16) >> 4)), idS, kk > 0);
+        tc::mma_ss(dS, dc0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), ds0 + (uint64_t)(kk * (256 >> 4)), idS, kk > 0);
       tc::commit(tc::smem_u32(&mbar[1 + buf]));
     }
     // ---- the previous head's result, while the tensor cores work on this one ---------------------------------
@@ -650,13 +689,12 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
   if (a.phase != 2) {
     const size_t smem = StateSmem::TOTAL;
     cudaFuncSetAttribute(ssd_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ssd_state_kernel<T><<<nparts * a.batch * nchunks, 256, smem, st>>>(a, nchunks, hpc, nparts);
+    ssd_state_kernel<T><<<dim3(a.heads, a.batch), 256, smem, st>>>(a, nchunks);
     if (int rc = launch_status("ssd_state_kernel")) return rc;
-  }
-  {
+  } else {
     const int64_t total = (int64_t)a.batch * a.heads * kP * kN;
-    ssd_pass_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a, nchunks);
-    if (int rc = launch_status("ssd_pass_kernel")) return rc;
+    ssd_fold_init_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a, nchunks);
+    if (int rc = launch_status("ssd_fold_init_kernel")) return rc;
   }
   if (a.phase != 1) {
     const size_t smem = ScanSmem<T>::TOTAL;
@@ -678,8 +716,9 @@ extern "C" int ssm_ssd_supported(int32_t headdim, int32_t nstate, int32_t chunk_
 extern "C" int64_t ssm_ssd_scratch_bytes(int32_t batch, int32_t len, int32_t heads) {
   const int64_t nchunks = (len + kQ - 1) / kQ;
   const int64_t vec = (int64_t)batch * heads * nchunks * kQ * 4;      // delta, cum (each)
-  const int64_t st = (int64_t)batch * nchunks * heads * kP * kN;      // states per chunk
-  return 2 * vec + st * 4 + st * 2;
+  const int64_t fin = (int64_t)batch * heads * kP * kN * 4;           // shard-local final state, fp32
+  const int64_t st = (int64_t)batch * nchunks * heads * kP * kN * 2;  // state before every chunk, operand dtype
+  return 2 * vec + fin + st;
 }
 
 extern "C" int ssm_ssd_fwd(const ssm_ssd_args* a, ssm_stream_t stream) {

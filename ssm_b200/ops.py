@@ -991,7 +991,7 @@ class _SsdWorkspace:
         Y = torch.empty_like(self.X) if want_y else None
         final = torch.empty(nb, nh, npj, nn, dtype=torch.float32, device=dev)
         vec = nb * nh * self.nchunks * self.chunk * 4
-        st = nb * self.nchunks * nh * npj * nn
+        fin = nb * nh * npj * nn * 4
         a = L.SsdArgs()
         a.batch, a.len, a.heads, a.headdim = nb, nl, nh, npj
         a.nstate, a.groups, a.chunk_size, a.io_dtype = nn, ng, self.chunk, _CODES[self.io]
@@ -1000,7 +1000,7 @@ class _SsdWorkspace:
         a.D, a.z, a.dt_bias, a.initial_states = _p(self.D), _p(self.z), _p(self.bias), _p(init32)
         a.Y, a.final_states = _p(Y), _p(final)
         base = self.ws.data_ptr()
-        a.ws_dt, a.ws_cum, a.ws_state, a.ws_state_in = base, base + vec, base + 2 * vec, base + 2 * vec + st * 4
+        a.ws_dt, a.ws_cum, a.ws_state, a.ws_state_in = base, base + vec, base + 2 * vec, base + 2 * vec + fin
         a.status = _p(self.status)
         _call(L.load().ssm_ssd_fwd, a)
         return Y, final

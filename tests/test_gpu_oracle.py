@@ -233,6 +233,8 @@ CONV_CASES = [
     (1, 7, 131, 3, True, "identity", torch.float32), (2, 10, 77, 7, False, "silu", torch.float32),
     (2, 64, 256, 4, True, "silu", torch.bfloat16), (2, 64, 256, 4, False, "silu", torch.bfloat16),
     (1, 16, 40, 8, True, "swish", torch.float16), (3, 9, 5, 2, False, "none", torch.float32),
+    (2, 12, 64, 7, True, "silu", torch.float32),   # channels-first, 16-byte accesses, taps reaching two vectors back
+    (2, 12, 72, 8, True, "silu", torch.bfloat16),  # widest kernel, length a multiple of the vector but not of the block
 ]
 
 
@@ -267,6 +269,28 @@ def test_conv_halo_splits_a_sequence():
     y1 = ops.dw_causal_conv(x[..., :h].contiguous(), w, b, "silu")
     y2 = ops.dw_causal_conv(x[..., h:].contiguous(), w, b, "silu", halo=x[..., h - (k - 1):h].float().contiguous())
     assert torch.equal(torch.cat([y1, y2], dim=-1), y)
+
+
+def test_conv_halo_backward_matches_the_unsplit_sequence():
+    from ssm_b200 import ops
+
+    torch.manual_seed(5)
+    nb, nc, nl, k, h = 2, 24, 384, 4, 128
+    x = torch.randn(nb, nc, nl, device="cuda")
+    w, b = (torch.rand(nc, k, device="cuda") - 0.5), torch.randn(nc, device="cuda") * 0.1
+    gy = torch.randn(nb, nc, nl, device="cuda")
+    xf, wf, bf = (t.clone().requires_grad_(True) for t in (x, w, b))
+    ops.dw_causal_conv(xf, wf, bf, "silu").backward(gy)
+    x1, x2 = x[..., :h].contiguous().requires_grad_(True), x[..., h:].contiguous().requires_grad_(True)
+    w2, b2 = w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    y1 = ops.dw_causal_conv(x1, w2, b2, "silu")
+    y2 = ops.dw_causal_conv(x2, w2, b2, "silu", halo=x[..., h - (k - 1):h].contiguous())
+    (y1 * gy[..., :h]).sum().add((y2 * gy[..., h:]).sum()).backward()
+    close(x2.grad, xf.grad[..., h:], **FP32_TOL, what="dx of the second shard")
+    # the first shard's last K-1 inputs also feed the second shard's outputs; that part flows through the halo
+    close(x1.grad[..., : h - (k - 1)], xf.grad[..., : h - (k - 1)], **FP32_TOL, what="dx of the first shard")
+    close(w2.grad, wf.grad, **FP32_TOL, what="dweight")
+    close(b2.grad, bf.grad, **FP32_TOL, what="dbias")
 
 
 NORM_CASES = [
