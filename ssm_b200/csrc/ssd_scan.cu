@@ -79,8 +79,8 @@ __global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, i
 // chunk states, local and carried, in one pass:  one CTA (256 threads) per (batch, head) walks the
 // chunks in order.  Per chunk the tensor cores form  S_c[n][p] = sum_j B[j][n] * (w_j x[j][p]),
 // w_j = exp2(c_last - (c_j - log2 delta_j)), in two half-chunk stages of a four-stage ring
-//   A operand = B^T, MN-major, stored [j/8][n/8][j%8][8];  B operand = w x, MN-major [j/8][p/8][j%8][8];  M = 128 (n), N = 64 (p),
-//   K = 128 per stage.  (Units that are neighbours along M / N are 128 bytes apart, so the tensor core's reads of one
+//   A operand = B^T, MN-major, stored [j/8][n/8][j%8][8];  B operand = w x of the CTA's heads side by side, MN-major
+//   [j/8][head][p/8][j%8][8];  M = 128 (n), N = 64 per head (p), K = 64 per stage.  (Units that are neighbours along M / N are 128 bytes apart, so the tensor core's reads of one
 //   K slice fall on different banks; with the [n/8][j][8] order they were 2 KB apart and the MMAs ran 4-5x slower.)
 // while the threads keep the running state in registers (thread = state n, 32 of the 64 columns p):
 //   state <- exp2(c_last) * state + S_c ;  the state BEFORE each chunk goes out in the operand dtype,
@@ -88,51 +88,56 @@ __global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, i
 // never touch global memory.  Copies (cp.async, whole rows) run two stages ahead; a stage's buffer
 // is refilled once the MMAs that read it have completed (tcgen05.commit -> mbarrier).
 // ---------------------------------------------------------------------------------------------
+// HPC heads of one B / C group per CTA share the B^T tile of every stage (the grid is sized to about one CTA per SM).
+template <int HPC>
 struct StateSmem {
-  static constexpr int kHalf = kQ / 2;                       // steps per stage
-  static constexpr int A_BYTES = (kN / 8) * kHalf * 16;      // 32 KB
-  static constexpr int X_BYTES = (kP / 8) * kHalf * 16;      // 16 KB
-  static constexpr int STAGE = A_BYTES + X_BYTES;
-  static constexpr int NSTAGE = 4;
-  static constexpr int VEC_BYTES = kQ * 4;                   // c - log2(delta) of a chunk (x2)
+  static constexpr int kStep = 64;                            // steps per stage
+  static constexpr int A_BYTES = (kN / 8) * kStep * 16;       // 16 KB
+  static constexpr int X_BYTES = (kP / 8) * kStep * 16;       //  8 KB per head
+  static constexpr int STAGE = A_BYTES + HPC * X_BYTES;
+  static constexpr int NSTAGE = HPC <= 2 ? 6 : (HPC == 3 ? 5 : 4);
+  static constexpr int AHEAD = NSTAGE - 2;                    // stages copied ahead of the one being multiplied
+  static constexpr int VEC_BYTES = HPC * kQ * 4;              // c - log2(delta) of a chunk, per head (x2)
   static constexpr int TOTAL = NSTAGE * STAGE + 2 * VEC_BYTES;
 };
 
-template <typename T>
+template <typename T, int HPC>
 __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a, int nchunks) {
-  using M = StateSmem;
-  constexpr int kHalf = M::kHalf;
+  using M = StateSmem<HPC>;
+  constexpr int kStep = M::kStep, NS = M::NSTAGE, AHEAD = M::AHEAD;
+  constexpr int SPC = kQ / kStep;  // stages per chunk
   extern __shared__ __align__(128) unsigned char smraw[];
-  float* sVec = reinterpret_cast<float*>(smraw + M::NSTAGE * M::STAGE);
-  __shared__ __align__(8) uint64_t mbar_free[M::NSTAGE];  // the MMAs that read a stage's buffer have completed
-  __shared__ __align__(8) uint64_t mbar_acc[2];           // a chunk's accumulator is complete
+  float* sVec = reinterpret_cast<float*>(smraw + NS * M::STAGE);  // [2][HPC][kQ]
+  __shared__ __align__(8) uint64_t mbar_free[NS];   // the MMAs that read a stage's buffer have completed
+  __shared__ __align__(8) uint64_t mbar_acc[2];     // a chunk's accumulators are complete
   __shared__ uint32_t tmem_slot;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wg = tid >> 7;
-  const int h = blockIdx.x, b = blockIdx.y;
-  const int g = h / (a.heads / a.groups);
+  const int h0 = blockIdx.x * HPC, b = blockIdx.y;
+  const int g = h0 / (a.heads / a.groups);
   const int n = (warp & 3) * 32 + lane;  // this thread's state index = TMEM lane
   constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr uint32_t kCols = HPC <= 1 ? 128 : (HPC == 2 ? 256 : 512);  // 2 accumulators of 64 columns per head, a power of two
 
-  if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), 128);
+  if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), kCols);
   if (tid == 0) {
-    for (int i = 0; i < M::NSTAGE; ++i) tc::mbar_init(tc::smem_u32(&mbar_free[i]), 1);
+    for (int i = 0; i < NS; ++i) tc::mbar_init(tc::smem_u32(&mbar_free[i]), 1);
     tc::mbar_init(tc::smem_u32(&mbar_acc[0]), 1);
     tc::mbar_init(tc::smem_u32(&mbar_acc[1]), 1);
   }
 
   const T* Bg = reinterpret_cast<const T*>(a.Bm);
   const T* Xg = reinterpret_cast<const T*>(a.X);
-  const int64_t vrow = ((int64_t)b * a.heads + h) * nchunks * kQ;  // this (batch, head)'s exponent vectors
-  const int nst = 2 * nchunks;
-  // stage s = (chunk s / 2, half s % 2): 16 lanes copy one 256-byte row of B, 8 lanes one 128-byte row of x
+  const int64_t vrow0 = ((int64_t)b * a.heads + h0) * nchunks * kQ;  // exponent vectors of head h0 (next head: + nchunks * kQ)
+  const int nst = SPC * nchunks;
+  // stage s = steps [s * 64, s * 64 + 64): 16 lanes copy one 256-byte row of B, 8 lanes one 128-byte row of x
   auto copy_stage = [&](int s) {
-    unsigned char* base = smraw + (s & 3) * M::STAGE;
-    const int tq = (s >> 1) * kQ + (s & 1) * kHalf;  // first step of the stage
+    unsigned char* base = smraw + (s % NS) * M::STAGE;
+    const int tq = s * kStep;  // first step of the stage
     {
       const int nc = tid & 15, r0 = tid >> 4;
 #pragma unroll
-      for (int k = 0; k < kHalf / 16; ++k) {
+      for (int k = 0; k < kStep / 16; ++k) {
         const int j = r0 + 16 * k;
         const bool okt = tq + j < a.len;
         cp_async16(base + (size_t)(j >> 3) * (kN * 16) + nc * 128 + (j & 7) * 16, Bg + (((int64_t)b * a.len + (okt ? tq + j : 0)) * a.groups + g) * kN + nc * 8, okt);
@@ -141,51 +146,69 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
     {
       const int pc = tid & 7, r0 = tid >> 3;
 #pragma unroll
-      for (int k = 0; k < kHalf / 32; ++k) {
-        const int j = r0 + 32 * k;
-        const bool okt = tq + j < a.len;
-        cp_async16(base + M::A_BYTES + (size_t)(j >> 3) * (kP * 16) + pc * 128 + (j & 7) * 16, Xg + (((int64_t)b * a.len + (okt ? tq + j : 0)) * a.heads + h) * kP + pc * 8, okt);
+      for (int hh = 0; hh < HPC; ++hh) {
+#pragma unroll
+        for (int k = 0; k < kStep / 32; ++k) {
+          const int j = r0 + 32 * k;
+          const bool okt = tq + j < a.len;
+          cp_async16(base + M::A_BYTES + (size_t)(j >> 3) * (HPC * kP * 16) + (hh * 8 + pc) * 128 + (j & 7) * 16,
+                     Xg + (((int64_t)b * a.len + (okt ? tq + j : 0)) * a.heads + h0 + hh) * kP + pc * 8, okt);
+        }
       }
     }
-    if ((s & 1) == 0 && tid < kQ / 4) cp_async16(sVec + ((s >> 1) & 1) * kQ + tid * 4, a.ws_dt + vrow + (int64_t)(s >> 1) * kQ + tid * 4, true);
+    if (s % SPC == 0) {
+      const int c = s / SPC;
+      for (int i = tid; i < HPC * (kQ / 4); i += 256) {
+        const int hh = i / (kQ / 4), q4 = i % (kQ / 4);
+        cp_async16(sVec + ((c & 1) * HPC + hh) * kQ + q4 * 4, a.ws_dt + vrow0 + ((int64_t)hh * nchunks + c) * kQ + q4 * 4, true);
+      }
+    }
   };
-  copy_stage(0);
-  cp_async_commit();
-  if (nst > 1) copy_stage(1);
-  cp_async_commit();
+#pragma unroll
+  for (int s = 0; s < AHEAD; ++s) {
+    if (s < nst) copy_stage(s);
+    cp_async_commit();
+  }
 
   __syncthreads();  // TMEM address and barriers are set up
   const uint32_t tmem = tmem_slot;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
-  // running state: st[i] = S[n][wg * 32 + i]
-  float st[32];
-  {
-    const float* init = a.initial_states ? a.initial_states + (((int64_t)b * a.heads + h) * kP + wg * 32) * kN + n : nullptr;
+  // running states: st[hh][i] = S_{h0 + hh}[n][wg * 32 + i]
+  float st[HPC][32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) st[i] = init ? __ldg(init + (int64_t)i * kN) : 0.f;
+  for (int hh = 0; hh < HPC; ++hh) {
+    const float* init = a.initial_states ? a.initial_states + (((int64_t)b * a.heads + h0 + hh) * kP + wg * 32) * kN + n : nullptr;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) st[hh][i] = init ? __ldg(init + (int64_t)i * kN) : 0.f;
   }
   T* sin = reinterpret_cast<T*>(a.ws_state_in);
-  // the state before chunk c, in the operand dtype: unit (p / 8, n) of the (batch, chunk, head) tile
+  // the states before chunk c, in the operand dtype: unit (p / 8, n) of the (batch, chunk, head) tile
   auto emit_state_in = [&](int c) {
-    T* blk = sin + (((int64_t)b * nchunks + c) * a.heads + h) * (int64_t)(kP * kN);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      Vec16<T> o;
-      o.pack(*reinterpret_cast<const float(*)[8]>(&st[q * 8]));
-      *reinterpret_cast<uint4*>(blk + ((size_t)(wg * 4 + q) * kN + n) * 8) = o.raw;
+    for (int hh = 0; hh < HPC; ++hh) {
+      T* blk = sin + (((int64_t)b * nchunks + c) * a.heads + h0 + hh) * (int64_t)(kP * kN);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        Vec16<T> o;
+        o.pack(*reinterpret_cast<const float(*)[8]>(&st[hh][q * 8]));
+        *reinterpret_cast<uint4*>(blk + ((size_t)(wg * 4 + q) * kN + n) * 8) = o.raw;
+      }
     }
   };
-  // fold chunk c's finished accumulator into the running state
+  // fold chunk c's finished accumulators into the running states
   auto fold_chunk = [&](int c) -> bool {
     const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_acc[c & 1]), (c >> 1) & 1));
     tc::fence_after_sync();
     if (ok) {
-      const float decay = ex2_approx(__ldg(a.ws_cum + vrow + (int64_t)c * kQ + kQ - 1));
-      float v[32];
-      tc::tmem_ld32(tmem + lane_base + (c & 1) * 64 + wg * 32, v);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) st[i] = fmaf(decay, st[i], v[i]);
+      for (int hh = 0; hh < HPC; ++hh) {
+        const float decay = ex2_approx(__ldg(a.ws_cum + vrow0 + ((int64_t)hh * nchunks + c) * kQ + kQ - 1));
+        float v[32];
+        tc::tmem_ld32(tmem + lane_base + ((c & 1) * HPC + hh) * 64 + wg * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) st[hh][i] = fmaf(decay, st[hh][i], v[i]);
+      }
     }
     return ok;
   };
@@ -193,38 +216,42 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
   int fail = 0;
 #pragma unroll 1
   for (int s = 0; s < nst; ++s) {
-    const int c = s >> 1, hf = s & 1;
-    // ---- refill the buffer two stages ahead; it was last read by the MMAs of stage s - 2 -------------
-    if (s + 2 < nst) {
-      if (s >= 2 && !fail) fail = !__all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_free[(s + 2) & 3]), ((s - 2) >> 2) & 1));
-      copy_stage(s + 2);
+    const int c = s / SPC, part = s % SPC;
+    // ---- refill the buffer AHEAD stages ahead; it was last read by the MMAs of stage s + AHEAD - NS ----------
+    if (s + AHEAD < nst) {
+      const int sp = s + AHEAD - NS;  // previous user of that buffer
+      if (sp >= 0 && !fail) fail = !__all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_free[(s + AHEAD) % NS]), (sp / NS) & 1));
+      copy_stage(s + AHEAD);
     }
     cp_async_commit();
-    // ---- a new chunk begins: fold the previous chunk, hand out the state before this one ----------------
-    if (hf == 0) {
+    // ---- a new chunk begins: fold the previous chunk, hand out the states before this one ----------------
+    if (part == 0) {
       if (c >= 1 && !fail) fail = !fold_chunk(c - 1);
       emit_state_in(c);
     }
-    asm volatile("cp.async.wait_group 2;\n" ::: "memory");  // this stage's copies (two younger groups may be in flight)
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(AHEAD) : "memory");  // this stage's copies (younger groups may be in flight)
     __syncthreads();
 
     // ---- scale the x rows in place: w_j x_j -----------------------------------------------------------------
-    unsigned char* base = smraw + (s & 3) * M::STAGE;
-    const float* vcp = sVec + (c & 1) * kQ + hf * kHalf;
-    const float c_last = __ldg(a.ws_cum + vrow + (int64_t)c * kQ + kQ - 1);
+    unsigned char* base = smraw + (s % NS) * M::STAGE;
 #pragma unroll
-    for (int k = 0; k < (kP / 8) * kHalf / 256; ++k) {
-      const int u = tid + 256 * k;  // unit index = (j / 8) * 64 + pc * 8 + j % 8
-      const float w = ex2_approx(c_last - vcp[(u >> 6) * 8 + (u & 7)]);
-      unsigned char* px = base + M::A_BYTES + (size_t)u * 16;
-      Vec16<T> v;
-      v.raw = *reinterpret_cast<const uint4*>(px);
-      float f[8];
-      v.unpack(f);
+    for (int hh = 0; hh < HPC; ++hh) {
+      const float* vcp = sVec + ((c & 1) * HPC + hh) * kQ + part * kStep;
+      const float c_last = __ldg(a.ws_cum + vrow0 + ((int64_t)hh * nchunks + c) * kQ + kQ - 1);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] *= w;
-      v.pack(f);
-      *reinterpret_cast<uint4*>(px) = v.raw;
+      for (int k = 0; k < (kP / 8) * kStep / 256; ++k) {
+        const int u = tid + 256 * k;  // unit of this head: (j / 8) * 64 + pc * 8 + j % 8; the heads' units interleave per 8 steps
+        const float w = ex2_approx(c_last - vcp[(u >> 6) * 8 + (u & 7)]);
+        unsigned char* px = base + M::A_BYTES + ((size_t)(u >> 6) * (HPC * 64) + hh * 64 + (u & 63)) * 16;
+        Vec16<T> v;
+        v.raw = *reinterpret_cast<const uint4*>(px);
+        float f[8];
+        v.unpack(f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] *= w;
+        v.pack(f);
+        *reinterpret_cast<uint4*>(px) = v.raw;
+      }
     }
     tc::fence_async_smem();
     tc::fence_before_sync();
@@ -232,32 +259,44 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
     tc::fence_after_sync();
 
     if (tid == 0) {
-      constexpr uint32_t idesc = tc::instr_desc(kN, kP, fmt, 1, 1);
+      // the heads' x tiles sit side by side along N: one instruction of N = 64 HPC columns serves all of them
+      constexpr uint32_t idesc = tc::instr_desc(kN, HPC * kP, fmt, 1, 1);
       const uint64_t da0 = tc::smem_desc(tc::smem_u32(base), kN * 16, 128);
-      const uint64_t db0 = tc::smem_desc(tc::smem_u32(base + M::A_BYTES), kP * 16, 128);
+      const uint64_t db0 = tc::smem_desc(tc::smem_u32(base + M::A_BYTES), HPC * kP * 16, 128);
 #pragma unroll
-      for (int kk = 0; kk < kHalf / 16; ++kk)  // two groups of 8 steps per instruction
-        tc::mma_ss(tmem + (c & 1) * 64, da0 + (uint64_t)(kk * ((2 * kN * 16) >> 4)), db0 + (uint64_t)(kk * ((2 * kP * 16) >> 4)), idesc,
-                   hf > 0 || kk > 0);
-      tc::commit(tc::smem_u32(&mbar_free[s & 3]));
-      if (hf == 1) tc::commit(tc::smem_u32(&mbar_acc[c & 1]));
+      for (int kk = 0; kk < kStep / 16; ++kk)  // two groups of 8 steps per instruction
+        tc::mma_ss(tmem + (c & 1) * HPC * 64, da0 + (uint64_t)(kk * ((2 * kN * 16) >> 4)), db0 + (uint64_t)(kk * ((2 * HPC * kP * 16) >> 4)), idesc,
+                   part > 0 || kk > 0);
+      tc::commit(tc::smem_u32(&mbar_free[s % NS]));
+      if (part == SPC - 1) tc::commit(tc::smem_u32(&mbar_acc[c & 1]));
     }
   }
   if (nchunks > 0 && !fail) fail = !fold_chunk(nchunks - 1);
-  // final state in fp32, (p, n) order: to the caller, and kept in scratch for a later phase 2
+  // final states in fp32, (p, n) order: to the caller, and kept in scratch for a later phase 2
   if (!fail) {
-    const int64_t off = (((int64_t)b * a.heads + h) * kP + wg * 32) * kN + n;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      if (a.final_states) a.final_states[off + (int64_t)i * kN] = st[i];
-      a.ws_state[off + (int64_t)i * kN] = st[i];
+    for (int hh = 0; hh < HPC; ++hh) {
+      const int64_t off = (((int64_t)b * a.heads + h0 + hh) * kP + wg * 32) * kN + n;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (a.final_states) a.final_states[off + (int64_t)i * kN] = st[hh][i];
+        a.ws_state[off + (int64_t)i * kN] = st[hh][i];
+      }
     }
   }
   if (fail && lane == 0 && a.status) atomicExch(a.status, 1);
   cp_async_wait_all();
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(tmem, 128);
+  if (warp == 0) tc::tmem_dealloc(tmem, kCols);
+}
+
+template <typename T, int HPC>
+static int ssd_state_launch(const ssm_ssd_args& a, int nchunks, cudaStream_t st) {
+  const size_t smem = StateSmem<HPC>::TOTAL;
+  cudaFuncSetAttribute(ssd_state_kernel<T, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  ssd_state_kernel<T, HPC><<<dim3(a.heads / HPC, a.batch), 256, smem, st>>>(a, nchunks);
+  return launch_status("ssd_state_kernel");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -687,10 +726,26 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
     if (int rc = launch_status("ssd_cumsum_kernel")) return rc;
   }
   if (a.phase != 2) {
-    const size_t smem = StateSmem::TOTAL;
-    cudaFuncSetAttribute(ssd_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ssd_state_kernel<T><<<dim3(a.heads, a.batch), 256, smem, st>>>(a, nchunks);
-    if (int rc = launch_status("ssd_state_kernel")) return rc;
+    // heads per CTA of the sequential state kernel: enough to bring the grid down to about one CTA per SM
+    // (its CTAs all run for the whole sequence, so a second, partial wave would double the time), at most 4,
+    // and a divisor of the heads of one B / C group
+    int sm_count = 148;
+    {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    }
+    int shpc = (int)(((int64_t)a.batch * a.heads + sm_count - 1) / sm_count);
+    shpc = shpc < 1 ? 1 : (shpc > 4 ? 4 : shpc);
+    while (hpg % shpc != 0) --shpc;
+    int rc;
+    switch (shpc) {
+      case 1: rc = ssd_state_launch<T, 1>(a, nchunks, st); break;
+      case 2: rc = ssd_state_launch<T, 2>(a, nchunks, st); break;
+      case 3: rc = ssd_state_launch<T, 3>(a, nchunks, st); break;
+      default: rc = ssd_state_launch<T, 4>(a, nchunks, st); break;
+    }
+    if (rc) return rc;
   } else {
     const int64_t total = (int64_t)a.batch * a.heads * kP * kN;
     ssd_fold_init_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a, nchunks);

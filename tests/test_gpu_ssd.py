@@ -34,6 +34,9 @@ CASES = [
     (1, 700, 4, 2, torch.bfloat16),   # ragged last chunk, two groups
     (1, 512, 2, 1, torch.float16),
     (1, 100, 2, 2, torch.bfloat16),   # shorter than one row block
+    (2, 300, 96, 2, torch.bfloat16),  # more (batch, head) pairs than SMs: two heads per state CTA
+    (3, 256, 120, 1, torch.float16),  # three heads per state CTA
+    (5, 256, 128, 1, torch.bfloat16),  # four heads per state CTA
 ]
 
 
