@@ -196,14 +196,18 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
       }
     }
   };
+  // last exponent of the current / previous chunk per head (the decay across the chunk is exp2 of it)
+  float clast[HPC], clast_prev[HPC];
+#pragma unroll
+  for (int hh = 0; hh < HPC; ++hh) clast[hh] = 0.f, clast_prev[hh] = 0.f;
   // fold chunk c's finished accumulators into the running states
-  auto fold_chunk = [&](int c) -> bool {
+  auto fold_chunk = [&](int c, const float (&cl)[HPC]) -> bool {
     const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_acc[c & 1]), (c >> 1) & 1));
     tc::fence_after_sync();
     if (ok) {
 #pragma unroll
       for (int hh = 0; hh < HPC; ++hh) {
-        const float decay = ex2_approx(__ldg(a.ws_cum + vrow0 + ((int64_t)hh * nchunks + c) * kQ + kQ - 1));
+        const float decay = ex2_approx(cl[hh]);
         float v[32];
         tc::tmem_ld32(tmem + lane_base + ((c & 1) * HPC + hh) * 64 + wg * 32, v);
 #pragma unroll
@@ -224,9 +228,18 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
       copy_stage(s + AHEAD);
     }
     cp_async_commit();
-    // ---- a new chunk begins: fold the previous chunk, hand out the states before this one ----------------
-    if (part == 0) {
-      if (c >= 1 && !fail) fail = !fold_chunk(c - 1);
+    if (part == 0) {  // a new chunk begins: its last exponents (loaded early, used by the scaling below)
+#pragma unroll
+      for (int hh = 0; hh < HPC; ++hh) {
+        clast_prev[hh] = clast[hh];
+        clast[hh] = __ldg(a.ws_cum + vrow0 + ((int64_t)hh * nchunks + c) * kQ + kQ - 1);
+      }
+      if (c == 0) emit_state_in(0);
+    }
+    // ---- one stage into a chunk its predecessor's MMAs have surely finished: fold them, hand out the states
+    // ---- before this chunk (its accumulators are the other pair, so the stage already issued is not disturbed)
+    if (part == 1 && c >= 1) {
+      if (!fail) fail = !fold_chunk(c - 1, clast_prev);
       emit_state_in(c);
     }
     asm volatile("cp.async.wait_group %0;\n" ::"n"(AHEAD) : "memory");  // this stage's copies (younger groups may be in flight)
@@ -237,7 +250,7 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
 #pragma unroll
     for (int hh = 0; hh < HPC; ++hh) {
       const float* vcp = sVec + ((c & 1) * HPC + hh) * kQ + part * kStep;
-      const float c_last = __ldg(a.ws_cum + vrow0 + ((int64_t)hh * nchunks + c) * kQ + kQ - 1);
+      const float c_last = clast[hh];
 #pragma unroll
       for (int k = 0; k < (kP / 8) * kStep / 256; ++k) {
         const int u = tid + 256 * k;  // unit of this head: (j / 8) * 64 + pc * 8 + j % 8; the heads' units interleave per 8 steps
@@ -271,7 +284,7 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
       if (part == SPC - 1) tc::commit(tc::smem_u32(&mbar_acc[c & 1]));
     }
   }
-  if (nchunks > 0 && !fail) fail = !fold_chunk(nchunks - 1);
+  if (nchunks > 0 && !fail) fail = !fold_chunk(nchunks - 1, clast);
   // final states in fp32, (p, n) order: to the caller, and kept in scratch for a later phase 2
   if (!fail) {
 #pragma unroll
