@@ -358,10 +358,11 @@ int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* args, ssm_stream_t s
  *   ws_state_in   : (batch, nchunks, heads, headdim * nstate) in io_dtype — the state before every chunk, in
  *                   the operand order of the scan kernel
  * status: optional device int, set non-zero when a bounded device-side wait ran out.
- * phase: 0 runs everything.  1 stops after the per-chunk states and the pass over chunks (it
- * fills the scratch and final_states, writes no Y); 2 redoes only the pass over chunks with
- * the given initial_states and then produces Y from scratch left by phase 1.  A sequence
- * shard uses 1, exchanges final states with its neighbours, then 2.
+ * phase: 0 runs everything.  1 stops after the chunk states (it fills the scratch and
+ * final_states from the given, normally absent, initial_states and writes no Y); 2 adds the
+ * given initial_states on top of what phase 1 left in the scratch (by linearity), writes
+ * the corrected final_states and produces Y.  A sequence shard uses 1, exchanges final
+ * states with its neighbours, then 2.
  * ------------------------------------------------------------------------------------- */
 typedef struct {
   int32_t batch, len, heads, headdim;
