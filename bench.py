@@ -125,33 +125,7 @@ def make_weights(cfg, device, dtype, seed=0):
     return {k_: v.to(device).requires_grad_(True) for k_, v in w.items()}
 
 
-def block_forward(ops, w, cfg, hidden, residual):
-    """hidden (B, L, d_model) activations, residual (B, L, d_model) fp32 stream -> (normed, new_residual).
-
-    The scan-side activations live in (d_inner, B, L) buffers viewed as (B, d_inner, L), so that every
-    projection is one 2-D GEMM over the B*L tokens with no transposing copy on either side."""
-    n, r = cfg["d_state"], cfg["dt_rank"]
-    nb, nl, dm = hidden.shape
-    di = w["in_x"].shape[0]
-    h2 = hidden.reshape(nb * nl, dm)
-
-    def rows(m2d):  # (C, B*L) -> (B, C, L) view
-        return m2d.view(m2d.shape[0], nb, nl).permute(1, 0, 2)
-
-    x = rows(torch.matmul(w["in_x"], h2.t()))
-    z = rows(torch.matmul(w["in_z"], h2.t()))
-    u = ops.dw_causal_conv(x, w["conv_w"], w["conv_b"], "silu")
-    u2 = u.permute(1, 0, 2).reshape(di, nb * nl)                       # (Di, B*L), no copy for the channel-major layout
-    x_dbl = torch.matmul(w["x_proj"], u2)                              # (R + 2N, B*L)
-    dt_low, Bm, Cm = torch.split(x_dbl, [r, n, n], dim=0)
-    delta = rows(torch.matmul(w["dt_proj"], dt_low))                   # (B, Di, L) view
-    Bg = Bm.view(n, nb, nl).permute(1, 0, 2).unsqueeze(1)              # (B, 1, N, L)
-    Cg = Cm.view(n, nb, nl).permute(1, 0, 2).unsqueeze(1)
-    y = ops.selective_scan(u, delta, w["A"], Bg, Cg, D=w["D"], z=z, dt_bias=w["dt_bias"], softplus=True)
-    y2 = y.permute(1, 0, 2).reshape(di, nb * nl)
-    out = torch.matmul(y2.t(), w["out_proj"].t()).view(nb, nl, dm)     # (B, L, d_model)
-    return ops.fused_layer_norm(out, w["norm_w"], None, residual=residual, is_rms=True, eps=1e-5, prenorm=True,
-                                residual_in_fp32=True, return_residual=True)
+from ssm_b200.mixer import mamba1_block_forward as block_forward  # noqa: E402  (the block both arms run)
 
 
 # --------------------------------------------------------------------------------------

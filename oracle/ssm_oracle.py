@@ -356,6 +356,21 @@ def dw_causal_conv(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, act
     return out if first else out.transpose(1, 2)
 
 
+def dw_causal_conv_update(conv_state: Tensor, x: Tensor, weight: Tensor, bias: Optional[Tensor] = None,
+                          activation: str = "silu") -> Tensor:
+    """Decode-time conv of upstream's ``Mamba1.step`` (modules/mamba1.py:345-353): roll the ``(B, C, K)``
+    state left by one in place, append ``x (B, C)``, return ``act(bias + <state, weight>)``."""
+    conv_state.copy_(torch.roll(conv_state, shifts=-1, dims=-1))
+    conv_state[:, :, -1] = x.to(conv_state.dtype)
+    w2 = weight[:, 0, :] if weight.ndim == 3 else weight
+    out = (conv_state.float() * w2.float().unsqueeze(0)).sum(dim=-1)
+    if bias is not None:
+        out = out + bias.float()
+    if str(activation).lower() in ("silu", "swish"):
+        out = torch.nn.functional.silu(out)
+    return out.to(x.dtype)
+
+
 def fused_layer_norm(
     x: Tensor,
     weight: Tensor,

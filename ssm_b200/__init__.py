@@ -6,13 +6,13 @@ upstream ``ssm.ops`` so that its CUDA dispatch uses these kernels."""
 
 from __future__ import annotations
 
-__all__ = ["ops", "backend", "install"]
+__all__ = ["ops", "backend", "install", "mixer", "seqpar"]
 
 
 def __getattr__(name):
     import importlib
 
-    if name in ("ops", "backend"):
+    if name in ("ops", "backend", "mixer", "seqpar"):
         return importlib.import_module(f"{__name__}.{name}")
     if name == "install":
         return importlib.import_module(f"{__name__}.backend").install

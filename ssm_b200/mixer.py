@@ -1,0 +1,138 @@
+"""A Mamba-1 mixer block written against the operator surface (`ssm_b200.ops`, or any namespace
+with the same five functions, e.g. the CPU oracle in tests).
+
+Behavioural spec: the data flow of upstream's block (`src/ssm/modules/mamba1.py:176-256` for the
+mixer, `src/ssm/modules/block.py:85-162` for the add + norm around it), with upstream Mamba's
+parameter layout (x_proj -> dt_rank + 2 d_state, B and C shared by all channels of a token).
+
+What is different from a line-by-line port is the activation layout: the scan-side tensors
+live in ``(d_inner, B, L)`` buffers that the operators see as ``(B, d_inner, L)`` through their
+row strides.  Every projection is then ONE 2-D GEMM over the ``B*L`` tokens and none of the
+``permute(0, 2, 1)`` copies of the reference's forward (mamba1.py:209, 217, 226-230) exist.
+
+`mamba1_block_forward` is the functional form (weights in a dict, operator namespace passed
+in) used by the benchmark on both of its arms; `Mamba1Block` wraps it as an ``nn.Module`` with
+a single-token `step` for decoding (conv-state roll + state step, reference `step`:
+mamba1.py:324-385).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Any, Optional
+
+import torch
+from torch import Tensor, nn
+
+
+def mamba1_block_forward(ops: Any, w: dict, cfg: dict, hidden: Tensor, residual: Optional[Tensor]):
+    """hidden (B, L, d_model) activations, residual (B, L, d_model) fp32 stream or None
+    -> (normed, new_residual): new_residual = residual + mixer(hidden); normed = RMSNorm(new_residual).
+
+    ``w``: in_x, in_z (d_inner, d_model); conv_w (d_inner, K), conv_b; x_proj (R + 2N, d_inner);
+    dt_proj (d_inner, R); dt_bias, A (d_inner, N), D (fp32); out_proj (d_model, d_inner); norm_w.
+    """
+    n, r = cfg["d_state"], cfg["dt_rank"]
+    nb, nl, dm = hidden.shape
+    di = w["in_x"].shape[0]
+    h2 = hidden.reshape(nb * nl, dm)
+
+    def rows(m2d):  # (C, B*L) -> (B, C, L) view
+        return m2d.view(m2d.shape[0], nb, nl).permute(1, 0, 2)
+
+    x = rows(torch.matmul(w["in_x"], h2.t()))
+    z = rows(torch.matmul(w["in_z"], h2.t()))
+    u = ops.dw_causal_conv(x, w["conv_w"], w["conv_b"], "silu")
+    u2 = u.permute(1, 0, 2).reshape(di, nb * nl)                       # (Di, B*L), no copy for the channel-major layout
+    x_dbl = torch.matmul(w["x_proj"], u2)                              # (R + 2N, B*L)
+    dt_low, Bm, Cm = torch.split(x_dbl, [r, n, n], dim=0)
+    delta = rows(torch.matmul(w["dt_proj"], dt_low))                   # (B, Di, L) view
+    Bg = Bm.view(n, nb, nl).permute(1, 0, 2).unsqueeze(1)              # (B, 1, N, L)
+    Cg = Cm.view(n, nb, nl).permute(1, 0, 2).unsqueeze(1)
+    y = ops.selective_scan(u, delta, w["A"], Bg, Cg, D=w["D"], z=z, dt_bias=w["dt_bias"], softplus=True)
+    y2 = y.permute(1, 0, 2).reshape(di, nb * nl)
+    out = torch.matmul(y2.t(), w["out_proj"].t()).view(nb, nl, dm)     # (B, L, d_model)
+    return ops.fused_layer_norm(out, w["norm_w"], None, residual=residual, is_rms=True, eps=cfg.get("eps", 1e-5), prenorm=True,
+                                residual_in_fp32=True, return_residual=True)
+
+
+class Mamba1Block(nn.Module):
+    """Mixer + residual add + RMSNorm on the five operators.  ``forward(hidden, residual)`` returns
+    ``(normed, residual)`` like the reference's fused-add-norm block; ``step`` advances one token."""
+
+    def __init__(self, d_model: int, d_state: int = 16, d_conv: int = 4, expand: int = 2, dt_rank: int | str = "auto",
+                 dt_min: float = 1e-3, dt_max: float = 1e-1, dt_init_floor: float = 1e-4, eps: float = 1e-5,
+                 device=None, dtype=None, ops: Any = None) -> None:
+        super().__init__()
+        if isinstance(dt_rank, str):
+            if dt_rank != "auto":
+                raise ValueError("dt_rank must be an integer or 'auto'.")
+            dt_rank = math.ceil(d_model / 16)
+        if dt_rank <= 0:
+            raise ValueError("dt_rank must be positive when provided as an integer.")
+        if dt_min <= 0 or dt_max <= 0 or dt_min > dt_max:
+            raise ValueError("dt_min and dt_max must be positive with dt_min <= dt_max.")
+        self.d_model, self.d_state, self.d_conv, self.dt_rank = d_model, d_state, d_conv, int(dt_rank)
+        self.d_inner = expand * d_model
+        self.eps = eps
+        self._ops = ops
+        kw = dict(device=device, dtype=dtype)
+        f32 = dict(device=device, dtype=torch.float32)
+        di, r, n = self.d_inner, self.dt_rank, d_state
+
+        def lin(o, i):
+            return nn.Parameter(torch.randn(o, i, **kw) / i ** 0.5)
+
+        self.in_x, self.in_z = lin(di, d_model), lin(di, d_model)
+        self.conv_w = nn.Parameter((torch.rand(di, d_conv, **kw) - 0.5) * (2.0 / d_conv ** 0.5))
+        self.conv_b = nn.Parameter(torch.zeros(di, **kw))
+        self.x_proj = lin(r + 2 * n, di)
+        self.dt_proj = nn.Parameter((torch.rand(di, r, **kw) * 2 - 1) * r ** -0.5)
+        dt = torch.exp(torch.rand(di, **f32) * (math.log(dt_max) - math.log(dt_min)) + math.log(dt_min)).clamp(min=dt_init_floor)
+        self.dt_bias = nn.Parameter(dt + torch.log(-torch.expm1(-dt)))  # inverse softplus of the sampled step
+        self.A_log = nn.Parameter(torch.log(torch.arange(1, n + 1, **f32)).repeat(di, 1))
+        self.D = nn.Parameter(torch.ones(di, **f32))
+        self.out_proj = lin(d_model, di)
+        self.norm_w = nn.Parameter(torch.ones(d_model, **kw))
+
+    def _namespace(self):
+        if self._ops is not None:
+            return self._ops
+        from . import ops  # the CUDA operators; raises if the library has not been built
+
+        return ops
+
+    def _weights(self) -> dict:
+        return dict(in_x=self.in_x, in_z=self.in_z, conv_w=self.conv_w, conv_b=self.conv_b, x_proj=self.x_proj, dt_proj=self.dt_proj,
+                    dt_bias=self.dt_bias, A=-torch.exp(self.A_log), D=self.D, out_proj=self.out_proj, norm_w=self.norm_w)
+
+    def forward(self, hidden: Tensor, residual: Optional[Tensor] = None):
+        if hidden.ndim != 3 or hidden.shape[-1] != self.d_model:
+            raise ValueError("hidden_states must have shape (B, L, d_model).")
+        cfg = dict(d_state=self.d_state, dt_rank=self.dt_rank, eps=self.eps)
+        return mamba1_block_forward(self._namespace(), self._weights(), cfg, hidden, residual)
+
+    def allocate_inference_cache(self, batch_size: int, dtype: Optional[torch.dtype] = None):
+        """(conv_state (B, d_inner, K), ssm_state (B, d_inner, N)), both fp32 and zero-filled."""
+        del dtype  # both states are kept in fp32 whatever the activation dtype
+        dev = self.in_x.device
+        return (torch.zeros(batch_size, self.d_inner, self.d_conv, device=dev, dtype=torch.float32),
+                torch.zeros(batch_size, self.d_inner, self.d_state, device=dev, dtype=torch.float32))
+
+    def step(self, hidden: Tensor, residual: Optional[Tensor], conv_state: Tensor, ssm_state: Tensor):
+        """One token: hidden (B, 1, d_model) -> (normed (B, 1, d_model), new residual); both states are updated in place."""
+        if hidden.ndim != 3 or hidden.shape[1] != 1:
+            raise ValueError("step expects inputs of shape (B, 1, d_model)")
+        ops = self._namespace()
+        n, r = self.d_state, self.dt_rank
+        tok = hidden[:, 0]
+        x, z = tok @ self.in_x.t(), tok @ self.in_z.t()
+        u = ops.dw_causal_conv_update(conv_state, x, self.conv_w, self.conv_b, "silu")
+        xd = u @ self.x_proj.t()
+        delta = xd[:, :r] @ self.dt_proj.t()
+        y = ops.selective_state_step(ssm_state, u, delta, -torch.exp(self.A_log), xd[:, r:r + n].unsqueeze(1), xd[:, r + n:].unsqueeze(1),
+                                     D=self.D, z=z, dt_bias=self.dt_bias, softplus=True)
+        out = (y @ self.out_proj.t()).unsqueeze(1)
+        res1 = None if residual is None else residual
+        return ops.fused_layer_norm(out, self.norm_w, None, residual=res1, is_rms=True, eps=self.eps, prenorm=True,
+                                    residual_in_fp32=True, return_residual=True)

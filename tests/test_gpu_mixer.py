@@ -1,0 +1,83 @@
+"""`ssm_b200.mixer.Mamba1Block` on the CUDA operators against the same block on the CPU oracle."""
+
+from __future__ import annotations
+
+import copy
+
+import pytest
+import torch
+
+from oracle import ssm_oracle as orc
+from tests.gpu_util import FP32_TOL, HALF_TOL, close
+
+pytestmark = pytest.mark.gpu
+
+
+def _pair(d_model, dtype, **kw):
+    from ssm_b200.mixer import Mamba1Block
+
+    torch.manual_seed(d_model)
+    cpu = Mamba1Block(d_model, ops=orc, **kw)
+    gpu = Mamba1Block(d_model, **kw)  # ops=None: the CUDA operators
+    gpu.load_state_dict(copy.deepcopy(cpu.state_dict()))
+    gpu = gpu.cuda()
+    if dtype != torch.float32:
+        for name in ("in_x", "in_z", "conv_w", "conv_b", "x_proj", "dt_proj", "out_proj", "norm_w"):
+            p = getattr(gpu, name)
+            p.data = p.data.to(dtype)
+            getattr(cpu, name).data = p.data.float().cpu()  # the oracle block computes in fp32 from the rounded weights
+    return cpu, gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_block_forward_backward_match_oracle(dtype):
+    cpu, gpu = _pair(64, dtype, d_state=16, d_conv=4, expand=2)
+    gen = torch.Generator().manual_seed(3)
+    hidden = torch.randn(2, 160, 64, generator=gen).to(dtype)
+    residual = torch.randn(2, 160, 64, generator=gen)
+    ho = hidden.float().clone().requires_grad_(True)
+    hg = hidden.cuda().requires_grad_(True)
+    yo, ro = cpu(ho, residual)
+    yg, rg = gpu(hg, residual.cuda())
+    tol = FP32_TOL if dtype == torch.float32 else HALF_TOL
+    close(yg, yo, **tol, what="normed output")
+    close(rg, ro, **tol, what="residual stream")
+    wy = torch.randn(yo.shape, generator=gen).to(dtype).float()
+    names = ["x_proj", "dt_proj", "A_log", "dt_bias", "D", "conv_w", "out_proj"]
+    go = torch.autograd.grad((yo * wy).sum(), [ho] + [getattr(cpu, n) for n in names])
+    gg = torch.autograd.grad((yg.float() * wy.cuda()).sum(), [hg] + [getattr(gpu, n) for n in names])
+    for name, a, b in zip(["hidden"] + names, gg, go):
+        close(a, b, **tol, what=f"grad {name}")
+
+
+def test_step_reproduces_forward_and_replays_under_a_cuda_graph():
+    cpu, gpu = _pair(48, torch.float32, d_state=8, d_conv=4, expand=2)
+    del cpu
+    torch.manual_seed(7)
+    hidden = torch.randn(4, 9, 48, device="cuda")
+    residual = torch.randn(4, 9, 48, device="cuda")
+    with torch.no_grad():
+        y, r = gpu(hidden, residual)
+        conv_state, ssm_state = gpu.allocate_inference_cache(4)
+        for t in range(9):
+            yt, rt = gpu.step(hidden[:, t:t + 1].contiguous(), residual[:, t:t + 1].contiguous(), conv_state, ssm_state)
+            close(yt, y[:, t:t + 1], **FP32_TOL, what=f"step {t}")
+            close(rt, r[:, t:t + 1], **FP32_TOL, what=f"residual {t}")
+        # the same nine steps as graph replays of one captured step
+        conv2, ssm2 = gpu.allocate_inference_cache(4)
+        tok, res = torch.zeros(4, 1, 48, device="cuda"), torch.zeros(4, 1, 48, device="cuda")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):  # warm-up outside capture (allocator, lazy library state)
+                gpu.step(tok, res, conv2.clone(), ssm2.clone())
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out_y, out_r = gpu.step(tok, res, conv2, ssm2)
+        conv2.zero_(), ssm2.zero_()
+        for t in range(9):
+            tok.copy_(hidden[:, t:t + 1]), res.copy_(residual[:, t:t + 1])
+            graph.replay()
+            close(out_y, y[:, t:t + 1], **FP32_TOL, what=f"graph step {t}")
+    close(ssm2, ssm_state, **FP32_TOL, what="state after nine graph replays")
