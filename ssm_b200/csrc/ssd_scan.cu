@@ -17,6 +17,8 @@
 //
 // Exponent differences are always formed before exp (never exp(cum_i) / exp(cum_j)), so long
 // sequences stay finite.  Every wait on an mbarrier is bounded and reports through the status word.
+#include <cuda.h>
+
 #include <type_traits>
 
 #include "common.cuh"
@@ -357,20 +359,26 @@ template <typename T>
 struct ScanSmem {
   static constexpr int C_BYTES = kBlk * kN * 2;     // C rows of the block, K-major [n/8][i][8]            32 KB
   static constexpr int B_BYTES = kQ * kN * 2;       // B rows, K-major [n/8][j][8]; later the masked tile  64 KB
-  static constexpr int X_BYTES = kQ * kP * 2;       // x rows, MN-major [p/8][j][8]                         32 KB (x2)
+  static constexpr int X_BYTES = kQ * kP * 2;       // x rows [j][64 p], 128-byte rows, TMA 128-byte swizzle  32 KB (x2)
   static constexpr int S_BYTES = kP * kN * 2;       // incoming state, MN-major [p/8][n][8]                 16 KB (x2)
   static constexpr int VEC_BYTES = 2 * kQ * 4;      // c and c - log2(delta) of the chunk                     2 KB (x2)
-  static constexpr int Z_BYTES = kBlk * kP * 2;     // z in / y out of one head: [row][8 chunks of 16 B], chunk ^= row & 7   16 KB
+  static constexpr int Z_BYTES = kBlk * kP * 2;     // z in / y out of one head: [row][64 p], same swizzle    16 KB
   static constexpr int W_BYTES = 8 * 128 * 4;       // per warp: the column factors of its (up to) four mask chunks            4 KB
   static constexpr int TOTAL = C_BYTES + B_BYTES + 2 * (X_BYTES + S_BYTES + VEC_BYTES) + Z_BYTES + W_BYTES;
+  static constexpr int ALLOC = TOTAL + 1024;        // the tiles TMA swizzles must start on 1024-byte boundaries
 };
 
 constexpr int kScanThreads = 256;
 
+// tensor maps of one call: x (box of 128 or 256 steps), z and y (boxes of 128 rows); rank 4 (p, head, step, batch)
+struct ScanMaps {
+  CUtensorMap x0, x1, z, y;
+};
+
 // Body for row block MB (0: rows 0..127, steps 0..127; 1: rows 128..255, steps 0..255).
 template <typename T, int MB>
-__device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks, int hpc, int nparts, unsigned char* smraw, uint64_t* mbar,
-                                              uint32_t* tmem_slot) {
+__device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanMaps& maps, int nchunks, int hpc, int nparts, unsigned char* smraw,
+                                              uint64_t* mbar, uint32_t* tmem_slot) {
   using M = ScanSmem<T>;
   constexpr int KJ = (MB + 1) * kBlk;  // steps that can reach this block's rows
   constexpr int NCH = KJ / 64;         // 32-step column chunks per thread (the two warpgroups interleave chunks)
@@ -380,6 +388,10 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
   unsigned char* sS = sX + 2 * M::X_BYTES;     // two buffers
   float* sVec = reinterpret_cast<float*>(sS + 2 * M::S_BYTES);  // two buffers of [c | c - log2 delta]
   unsigned char* sZ = reinterpret_cast<unsigned char*>(sVec) + 2 * M::VEC_BYTES;
+  // mbar: 0 G done; 1 + b MMAs of a head into accumulator pair b done; 3 + b operands of buffer b landed; 5 z tile landed
+  const uint32_t mb_g = tc::smem_u32(&mbar[0]), mb_z = tc::smem_u32(&mbar[5]);
+  auto mb_mma = [&](int bf) { return tc::smem_u32(&mbar[1 + bf]); };
+  auto mb_full = [&](int bf) { return tc::smem_u32(&mbar[3 + bf]); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wg = tid >> 7;                     // column chunks wg, wg + 2, ... in the mask stage; column half in the epilogue
@@ -396,12 +408,11 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
   const int i_chunk = MB * kBlk + i_loc;       // row within the chunk
   const int rc = MB * 4 + (warp & 3);          // this warp's rows as a 32-step chunk index
   constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  const bool has_z = a.z != nullptr;
+  const CUtensorMap* mapx = MB ? &maps.x1 : &maps.x0;
 
   const T* Cg = reinterpret_cast<const T*>(a.Cm);
   const T* Bg = reinterpret_cast<const T*>(a.Bm);
-  const T* Xg = reinterpret_cast<const T*>(a.X);
-  const T* Zg = reinterpret_cast<const T*>(a.z);
-  T* Yg = reinterpret_cast<T*>(a.Y);
 
   // ---- C rows of the block, B rows of the reachable steps: 16 lanes copy one 256-byte row -----------
   {
@@ -419,70 +430,27 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
   }
   cp_async_commit();
 
-  // Per-thread copy plan for one head.  x: 8 lanes copy one 128-byte row; incoming state: a
-  // straight copy (it is stored in operand order); exponent vectors: 16-byte pieces.
-  const int xpc = tid & 7, xr0 = tid >> 3;
-  const int64_t xrow_stride = (int64_t)a.heads * kP;
-  const T* xsrc0 = Xg + ((int64_t)b * a.len + t0) * xrow_stride + xpc * 8;
-  const int64_t sbase = (((int64_t)b * nchunks + c) * a.heads) * (int64_t)(kP * kN) + tid * 8;
-  const int64_t vbase = ((int64_t)b * a.heads * nchunks + c) * kQ;
-  // One head's copies are issued in NCH parts, interleaved with the mask stage, so that the
-  // load/store unit's queue drains while the warp computes instead of stalling the issue.
-  auto prefetch_part = [&](int h, int buf, int part) {
-    constexpr int XP = (KJ / 32) / NCH;  // x passes per part
-    unsigned char* dX = sX + buf * M::X_BYTES + (size_t)xpc * KJ * 16;
-    const T* xs = xsrc0 + (int64_t)h * kP;
-#pragma unroll
-    for (int k = 0; k < XP; ++k) {
-      const int j = xr0 + 32 * (part * XP + k);
-      const bool okt = t0 + j < a.len;
-      cp_async16(dX + (size_t)j * 16, xs + (okt ? (int64_t)j * xrow_stride : 0), okt);
-    }
-    unsigned char* dS = sS + buf * M::S_BYTES + (size_t)tid * 16;
-    const T* ss = reinterpret_cast<const T*>(a.ws_state_in) + sbase + (int64_t)h * (kP * kN);
-#pragma unroll
-    for (int k = 0; k < 4 / NCH; ++k) {
-      const int kk = part * (4 / NCH) + k;
-      cp_async16(dS + (size_t)kk * kScanThreads * 16, ss + kk * kScanThreads * 8, true);
-    }
-    if (part == 0) {
-      float* dV = sVec + buf * (2 * kQ);
-      const int64_t voff = vbase + (int64_t)h * nchunks * kQ;
-      if (tid < KJ / 4) cp_async16(dV + tid * 4, a.ws_cum + voff + tid * 4, true);
-      else if (tid >= 128 && tid < 128 + KJ / 4) cp_async16(dV + kQ + (tid - 128) * 4, a.ws_dt + voff + (tid - 128) * 4, true);
-    }
-  };
+  // One head's operands, by bulk copies issued from one thread: x rows through the tensor map (128-byte rows, swizzled),
+  // the incoming state and the two exponent vectors as contiguous pieces.  Steps beyond the sequence read as zero.
+  constexpr uint32_t kOperandBytes = KJ * kP * 2 + M::S_BYTES + 2 * KJ * 4;
   auto prefetch = [&](int h, int buf) {
-#pragma unroll
-    for (int part = 0; part < NCH; ++part) prefetch_part(h, buf, part);
+    const uint32_t full = mb_full(buf);
+    tc::mbar_expect_tx(full, kOperandBytes);
+    tc::tma_load_4d(tc::smem_u32(sX + buf * M::X_BYTES), mapx, full, 0, h, t0, b);
+    const T* ss = reinterpret_cast<const T*>(a.ws_state_in) + (((int64_t)b * nchunks + c) * a.heads + h) * (int64_t)(kP * kN);
+    tc::bulk_load(tc::smem_u32(sS + buf * M::S_BYTES), ss, M::S_BYTES, full);
+    const int64_t voff = (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
+    float* dV = sVec + buf * (2 * kQ);
+    tc::bulk_load(tc::smem_u32(dV), a.ws_cum + voff, KJ * 4, full);
+    tc::bulk_load(tc::smem_u32(dV + kQ), a.ws_dt + voff, KJ * 4, full);
   };
-  // z / y staging: 8 lanes handle one 128-byte row of the block; slot of (row, 16-byte chunk) is swizzled
-  // so that both these row-wise accesses and the epilogue's one-row-per-thread accesses avoid bank conflicts
-  const int64_t zrow0 = (int64_t)b * a.len + t0 + MB * kBlk;  // token of the block's first row
-  auto z_slot = [&](int row, int chunk) { return sZ + ((size_t)row * 8 + (chunk ^ (row & 7))) * 16; };
-  auto copy_z = [&](int h) {
-    if (!Zg) return;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int row = xr0 + 32 * k;
-      const bool okt = t0 + MB * kBlk + row < a.len;
-      cp_async16(z_slot(row, xpc), Zg + ((zrow0 + (okt ? row : 0)) * a.heads + h) * kP + xpc * 8, okt);
-    }
-  };
-  auto store_y = [&](int h) {
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int row = xr0 + 32 * k;
-      if (t0 + MB * kBlk + row < a.len) {
-        const uint4 v = *reinterpret_cast<const uint4*>(z_slot(row, xpc));
-        *reinterpret_cast<uint4*>(Yg + ((zrow0 + row) * a.heads + h) * kP + xpc * 8) = v;
-      }
-    }
-  };
-  prefetch(h0, 0);
-  cp_async_commit();
+  // slot of (row, 16-byte chunk) in a tile of 128-byte rows written / read by TMA with the 128-byte swizzle
+  auto swz = [&](unsigned char* tile, int row, int chunk) { return tile + ((size_t)row * 8 + (chunk ^ (row & 7))) * 16; };
 
-  asm volatile("cp.async.wait_group 1;\n" ::: "memory");  // C and B have landed (the head's group may still be in flight)
+  __syncthreads();  // barriers initialised (by thread 0 of the kernel prologue) before anyone arms or polls them
+  if (tid == 0) prefetch(h0, 0);
+
+  cp_async_wait_all();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -498,9 +466,9 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
 #pragma unroll
     for (int kk = 0; kk < kN / 16; ++kk)
       tc::mma_ss(tmem, dc0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), db0 + (uint64_t)(kk * ((2 * KJ * 16) >> 4)), idG, kk > 0);
-    tc::commit(tc::smem_u32(&mbar[0]));
+    tc::commit(mb_g);
   }
-  bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar[0]), 0));  // warp-uniform
+  bool ok = __all_sync(0xffffffffu, tc::mbar_wait(mb_g, 0));  // warp-uniform
   tc::fence_after_sync();
 
   // This thread's part of G stays in registers for all heads: row i_loc, chunks wg, wg + 2, ...
@@ -516,7 +484,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
     }
   }
 
-  // epilogue of head h from buffer `buf`: y = Y_intra + exp2(c_i) Y_inter + D x, gated by the z row in
+  // epilogue of head h from accumulator pair `buf`: y = Y_intra + exp2(c_i) Y_inter + D x, gated by the z row in
   // the staging tile, written back to the same slots.  Thread = row i_loc, this warpgroup's 32 columns.
   auto epilogue = [&](int h, int buf, float ct, const uint4 (&xr)[4]) {
     const float escale = ex2_approx(ct);
@@ -535,8 +503,8 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
         const float Dv = (a.D && a.d_has_p) ? __ldg(a.D + h * kP + wg * 32 + q * 8 + e) : Dh;
         f[e] = fmaf(escale, ys[q * 8 + e], yi[q * 8 + e]) + Dv * xv[e];
       }
-      unsigned char* slot = z_slot(i_loc, wg * 4 + q);
-      if (Zg) {
+      unsigned char* slot = swz(sZ, i_loc, wg * 4 + q);
+      if (has_z) {
         float zv[8];
         Vec16<T> zz;
         zz.raw = *reinterpret_cast<const uint4*>(slot);
@@ -548,29 +516,40 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
       o.pack(f);
       *reinterpret_cast<uint4*>(slot) = o.raw;
     }
+    tc::fence_async_smem();  // the staged rows leave through a bulk store
   };
+  const int t_blk = t0 + MB * kBlk;  // first step of this block's rows
 
   float ct_prev = 0.f;   // the previous head's row exponent and x row, carried into its (deferred) epilogue
   uint4 xr_prev[4];
 #pragma unroll
   for (int q = 0; q < 4; ++q) xr_prev[q] = make_uint4(0, 0, 0, 0);
   int fail = 0;
+  int nz = 0;  // z tiles requested so far (parity of the z barrier)
 #pragma unroll 1
   for (int hi = 0; hi < nh; ++hi) {
     const int h = h0 + hi, buf = hi & 1;
-    cp_async_wait_all();  // this thread's copies for head hi
+    ok = !fail && tc::mbar_wait(mb_full(buf), (hi >> 1) & 1);  // this head's operands (no more waiting once a wait ran out)
     // MMAs of the previous head: the masked tile, the other buffer and its accumulators are free / ready
-    if (hi > 0) ok = tc::mbar_wait(tc::smem_u32(&mbar[1 + (buf ^ 1)]), ((hi - 1) >> 1) & 1) && ok;
+    if (hi > 0) ok = tc::mbar_wait(mb_mma(buf ^ 1), ((hi - 1) >> 1) & 1) && ok;
     tc::fence_after_sync();
-    ok = __syncthreads_and(ok);  // every thread's copies and staged y are visible; the verdict on the waits is CTA-wide
+    ok = __syncthreads_and(ok);  // the staged y of the head before last is complete; the verdict on the waits is CTA-wide
     if (!ok) {
       fail = 1;
       break;
     }
-    if (hi >= 2) store_y(h - 2);     // staged by the epilogue of the previous iteration
-    if (hi >= 1) copy_z(h - 1);      // same lanes, same slots: ordered after the reads above
-    cp_async_commit();
-    const bool more = hi + 1 < nh;
+    if (tid == 0) {
+      if (hi >= 2) {  // staged by the epilogue of the previous iteration
+        tc::tma_store_4d(&maps.y, tc::smem_u32(sZ), 0, h - 2, t_blk, b);
+        tc::bulk_commit();
+        tc::bulk_wait_read();  // the tile may be overwritten
+      }
+      if (hi >= 1 && has_z) {
+        tc::mbar_expect_tx(mb_z, M::Z_BYTES);
+        tc::tma_load_4d(tc::smem_u32(sZ), &maps.z, mb_z, 0, h - 1, t_blk, b);
+      }
+      if (hi + 1 < nh) prefetch(h + 1, buf ^ 1);
+    }
 
     // ---- decay mask: G (registers) -> masked tile, K-major over j: unit (i, j/8) at (j/8) * 2048 + i * 16
     const float* vc = sVec + buf * (2 * kQ);
@@ -596,7 +575,6 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
     __syncwarp();
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
-      if (more) prefetch_part(h + 1, buf ^ 1, k);
       const int cc = wg + 2 * k;  // chunk of 32 steps: fully causal (cc < rc), diagonal (cc == rc) or empty (cc > rc) for this warp's rows
       const int jb = cc * 32;
       unsigned char* dst = sBA + ((size_t)(jb / 8) * kBlk + i_loc) * 16;
@@ -645,13 +623,11 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
         }
       }
     }
-    cp_async_commit();
     // this row of x (for D x in the epilogue one iteration later)
     uint4 xr[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) xr[q] = *reinterpret_cast<const uint4*>(sX + buf * M::X_BYTES + ((size_t)(wg * 4 + q) * KJ + i_chunk) * 16);
+    for (int q = 0; q < 4; ++q) xr[q] = *reinterpret_cast<const uint4*>(swz(sX + buf * M::X_BYTES, i_chunk, wg * 4 + q));
 
-    asm volatile("cp.async.wait_group 1;\n" ::: "memory");  // z of the previous head (the next head's operands may still be in flight)
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
@@ -661,66 +637,117 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, int nchunks
     if (tid == 0) {
       // descriptors differ from instruction to instruction only in the start address (16-byte units, low bits)
       const uint64_t da0 = tc::smem_desc(tc::smem_u32(sBA), kBlk * 16, 128);
-      const uint64_t dx0 = tc::smem_desc(tc::smem_u32(sX + buf * M::X_BYTES), 128, KJ * 16);
+      const uint64_t dx0 = tc::smem_desc_sw128(tc::smem_u32(sX + buf * M::X_BYTES), 1024);
       const uint64_t dc0 = tc::smem_desc(tc::smem_u32(sC), kBlk * 16, 128);
       const uint64_t ds0 = tc::smem_desc(tc::smem_u32(sS + buf * M::S_BYTES), 128, kN * 16);
       constexpr uint32_t idY = tc::instr_desc(kBlk, kP, fmt, 0, 1);
       constexpr uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 1);
       const uint32_t dY = tmem + 256 + buf * 128, dS = dY + 64;
 #pragma unroll
-      for (int kk = 0; kk < KJ / 16; ++kk)
-        tc::mma_ss(dY, da0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), dx0 + (uint64_t)(kk * (256 >> 4)), idY, kk > 0);
+      for (int kk = 0; kk < KJ / 16; ++kk)  // 16 steps = 16 rows of 128 bytes of the x tile
+        tc::mma_ss(dY, da0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), dx0 + (uint64_t)(kk * (2048 >> 4)), idY, kk > 0);
 #pragma unroll
       for (int kk = 0; kk < kN / 16; ++kk)
         tc::mma_ss(dS, dc0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), ds0 + (uint64_t)(kk * (256 >> 4)), idS, kk > 0);
-      tc::commit(tc::smem_u32(&mbar[1 + buf]));
+      tc::commit(mb_mma(buf));
     }
     // ---- the previous head's result, while the tensor cores work on this one ---------------------------------
-    if (hi > 0) epilogue(h - 1, buf ^ 1, ct_prev, xr_prev);
+    if (hi > 0) {
+      if (has_z) {
+        ok = tc::mbar_wait(mb_z, nz & 1);
+        ++nz;
+      }
+      if (ok) epilogue(h - 1, buf ^ 1, ct_prev, xr_prev);
+      else fail = 1;  // becomes CTA-wide at the next iteration's barrier (or right after the loop)
+    }
     ct_prev = ct;
 #pragma unroll
     for (int q = 0; q < 4; ++q) xr_prev[q] = xr[q];
   }
+  // leave the loop together: a thread that saw a wait run out above still reaches the same barriers
+  fail = __syncthreads_or(fail);
   if (!fail && nh > 0) {
     const int last = nh - 1, buf = last & 1;
-    ok = tc::mbar_wait(tc::smem_u32(&mbar[1 + buf]), (last >> 1) & 1);
+    ok = tc::mbar_wait(mb_mma(buf), (last >> 1) & 1);
     tc::fence_after_sync();
     ok = __syncthreads_and(ok);
     if (ok) {
-      if (nh >= 2) store_y(h0 + last - 1);
-      copy_z(h0 + last);
-      cp_async_commit();
-      cp_async_wait_all();
-      __syncthreads();
-      epilogue(h0 + last, buf, ct_prev, xr_prev);
-      __syncthreads();
-      store_y(h0 + last);
+      if (tid == 0) {
+        if (nh >= 2) {
+          tc::tma_store_4d(&maps.y, tc::smem_u32(sZ), 0, h0 + last - 1, t_blk, b);
+          tc::bulk_commit();
+          tc::bulk_wait_read();
+        }
+        if (has_z) {
+          tc::mbar_expect_tx(mb_z, M::Z_BYTES);
+          tc::tma_load_4d(tc::smem_u32(sZ), &maps.z, mb_z, 0, h0 + last, t_blk, b);
+        }
+      }
+      if (has_z) ok = tc::mbar_wait(mb_z, nz & 1);
+      ok = __syncthreads_and(ok);  // also orders thread 0's wait on the store's reads before everyone's writes
+      if (ok) {
+        epilogue(h0 + last, buf, ct_prev, xr_prev);
+        __syncthreads();
+        if (tid == 0) {
+          tc::tma_store_4d(&maps.y, tc::smem_u32(sZ), 0, h0 + last, t_blk, b);
+          tc::bulk_commit();
+        }
+      } else {
+        fail = 1;
+      }
     } else {
       fail = 1;
     }
   }
+  if (tid == 0) tc::bulk_wait_all();  // the staging tile must outlive the stores that read it
   if (fail && tid == 0 && a.status) atomicExch(a.status, 2);
-  cp_async_wait_all();
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kScanThreads, 1) ssd_scan_kernel(const ssm_ssd_args a, int nchunks, int hpc, int nparts) {
-  extern __shared__ __align__(128) unsigned char smraw[];
-  __shared__ __align__(8) uint64_t mbar[3];    // 0: G, 1 + b: head MMAs into buffer b
+__global__ void __launch_bounds__(kScanThreads, 1)
+    ssd_scan_kernel(const ssm_ssd_args a, const __grid_constant__ ScanMaps maps, int nchunks, int hpc, int nparts) {
+  extern __shared__ unsigned char smdyn[];
+  unsigned char* smraw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smdyn) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t mbar[6];
   __shared__ uint32_t tmem_slot;
   const int warp = threadIdx.x >> 5;
   if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), 512);
   if (threadIdx.x == 0) {
-    tc::mbar_init(tc::smem_u32(&mbar[0]), 1);
-    tc::mbar_init(tc::smem_u32(&mbar[1]), 1);
-    tc::mbar_init(tc::smem_u32(&mbar[2]), 1);
+    for (int i = 0; i < 6; ++i) tc::mbar_init(tc::smem_u32(&mbar[i]), 1);
   }
   // the heavier blocks (rows 128..255) are scheduled first
-  if ((int)blockIdx.x < (int)(gridDim.x >> 1)) ssd_scan_body<T, 1>(a, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
-  else ssd_scan_body<T, 0>(a, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
+  if ((int)blockIdx.x < (int)(gridDim.x >> 1)) ssd_scan_body<T, 1>(a, maps, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
+  else ssd_scan_body<T, 0>(a, maps, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
   tc::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem_slot, 512);
+}
+
+// ---- tensor maps (driver entry point fetched through the runtime; no link-time dependency on the driver) -------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+// (batch, len, heads, 64) tensor of 16-bit elements seen as rank 4 (p, head, step, batch); box = 64 p of one head x `rows` steps
+static int encode_rows_map(CUtensorMap* m, const void* base, const ssm_ssd_args& a, int rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return ::ssmb::fail(SSM_ERR_DEVICE, "ssd_scan: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[4] = {(cuuint64_t)kP, (cuuint64_t)a.heads, (cuuint64_t)a.len, (cuuint64_t)a.batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)kP * 2, (cuuint64_t)a.heads * kP * 2, (cuuint64_t)a.len * a.heads * kP * 2};
+  const cuuint32_t box[4] = {(cuuint32_t)kP, 1, (cuuint32_t)rows, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = a.io_dtype == SSM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult rc = fn(m, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return ::ssmb::fail(SSM_ERR_DEVICE, "ssd_scan: cuTensorMapEncodeTiled rejected the tensor");
+  return SSM_OK;
 }
 
 template <typename T>
@@ -765,9 +792,14 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
     if (int rc = launch_status("ssd_fold_init_kernel")) return rc;
   }
   if (a.phase != 1) {
-    const size_t smem = ScanSmem<T>::TOTAL;
+    ScanMaps maps;
+    if (int rc = encode_rows_map(&maps.x0, a.X, a, kBlk)) return rc;
+    if (int rc = encode_rows_map(&maps.x1, a.X, a, kQ)) return rc;
+    if (int rc = encode_rows_map(&maps.z, a.z ? a.z : a.X, a, kBlk)) return rc;
+    if (int rc = encode_rows_map(&maps.y, a.Y, a, kBlk)) return rc;
+    const size_t smem = ScanSmem<T>::ALLOC;
     cudaFuncSetAttribute(ssd_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ssd_scan_kernel<T><<<2 * nparts * a.batch * nchunks, kScanThreads, smem, st>>>(a, nchunks, hpc, nparts);
+    ssd_scan_kernel<T><<<2 * nparts * a.batch * nchunks, kScanThreads, smem, st>>>(a, maps, nchunks, hpc, nparts);
     if (int rc = launch_status("ssd_scan_kernel")) return rc;
   }
   return SSM_OK;

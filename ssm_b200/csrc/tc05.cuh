@@ -28,6 +28,19 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;                // base offset 0, layout type 0 (no swizzle)
 }
 
+// Same for an MN-major operand whose rows of 64 elements (128 bytes) were written by TMA with the 128-byte swizzle:
+// K row k of the tile lives at k * 128 bytes, its 16-byte chunk c at position c ^ (k % 8); groups of 8 K rows are
+// sbo_bytes apart (1024 for a dense tile).  The tile must start on a 1024-byte boundary.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;  // leading-dimension offset: unused for a single 64-element block along M / N
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;  // layout type: 128-byte swizzle
+  return d;
+}
+
 // 32-bit instruction descriptor for kind::f16 with fp32 accumulation.
 // fmt: 0 = fp16, 1 = bf16.  major: 0 = K-major, 1 = MN-major.
 __host__ __device__ constexpr uint32_t instr_desc(int m, int n, int fmt, int a_major, int b_major) {
@@ -81,6 +94,33 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
   }
   return false;
 }
+
+// ---- bulk asynchronous copies (TMA); completion is counted in bytes on an mbarrier -----------------------------
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbar), "r"(bytes) : "memory");
+}
+// contiguous global -> shared; both addresses 16-byte aligned, size a multiple of 16
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src), "r"(bytes), "r"(mbar)
+               : "memory");
+}
+// one box of a rank-4 tensor map, global -> shared (no multicast); c0 is the innermost coordinate
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t mbar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n" ::"r"(dst),
+               "l"(tmap), "r"(mbar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+// one box, shared -> global; elements outside the tensor are not written
+__device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n" ::"l"(tmap), "r"(src), "r"(c0), "r"(c1),
+               "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+// the committed stores have finished READING shared memory (their source may be overwritten)
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+// ... and have completed altogether
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 
 // TMEM allocation: executed by one full warp; the base address lands in *slot (shared memory).
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_saddr, uint32_t ncols) {
