@@ -91,25 +91,35 @@ __global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, i
 // is refilled once the MMAs that read it have completed (tcgen05.commit -> mbarrier).
 // ---------------------------------------------------------------------------------------------
 // HPC heads of one B / C group per CTA share the B^T tile of every stage (the grid is sized to about one CTA per SM).
+// Tiles are rows of 128 bytes (64 elements along M / N) written by TMA with the 128-byte swizzle, 64 steps each:
+// B^T as two blocks (states 0..63, 64..127), then one x block per head; blocks are 8 KB apart.
 template <int HPC>
 struct StateSmem {
   static constexpr int kStep = 64;                            // steps per stage
-  static constexpr int A_BYTES = (kN / 8) * kStep * 16;       // 16 KB
-  static constexpr int X_BYTES = (kP / 8) * kStep * 16;       //  8 KB per head
-  static constexpr int STAGE = A_BYTES + HPC * X_BYTES;
+  static constexpr int BLK_BYTES = kStep * 128;               // 8 KB: 64 steps x 64 elements
+  static constexpr int A_BYTES = 2 * BLK_BYTES;               // 16 KB
+  static constexpr int STAGE = A_BYTES + HPC * BLK_BYTES;
   static constexpr int NSTAGE = HPC <= 2 ? 6 : (HPC == 3 ? 5 : 4);
   static constexpr int AHEAD = NSTAGE - 2;                    // stages copied ahead of the one being multiplied
   static constexpr int VEC_BYTES = HPC * kQ * 4;              // c - log2(delta) of a chunk, per head (x2)
   static constexpr int TOTAL = NSTAGE * STAGE + 2 * VEC_BYTES;
+  static constexpr int ALLOC = TOTAL + 1024;
+};
+
+// tensor maps of the state kernel: B rows (box 64 states x 64 steps) and x rows (box 64 p x 64 steps)
+struct StateMaps {
+  CUtensorMap b, x;
 };
 
 template <typename T, int HPC>
-__global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a, int nchunks) {
+__global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a, const __grid_constant__ StateMaps maps, int nchunks) {
   using M = StateSmem<HPC>;
   constexpr int kStep = M::kStep, NS = M::NSTAGE, AHEAD = M::AHEAD;
   constexpr int SPC = kQ / kStep;  // stages per chunk
-  extern __shared__ __align__(128) unsigned char smraw[];
+  extern __shared__ unsigned char smdyn[];
+  unsigned char* smraw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smdyn) + 1023) & ~(uintptr_t)1023);
   float* sVec = reinterpret_cast<float*>(smraw + NS * M::STAGE);  // [2][HPC][kQ]
+  __shared__ __align__(8) uint64_t mbar_full[NS];   // a stage's copies have landed
   __shared__ __align__(8) uint64_t mbar_free[NS];   // the MMAs that read a stage's buffer have completed
   __shared__ __align__(8) uint64_t mbar_acc[2];     // a chunk's accumulators are complete
   __shared__ uint32_t tmem_slot;
@@ -123,58 +133,40 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
 
   if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), kCols);
   if (tid == 0) {
-    for (int i = 0; i < NS; ++i) tc::mbar_init(tc::smem_u32(&mbar_free[i]), 1);
+    for (int i = 0; i < NS; ++i) {
+      tc::mbar_init(tc::smem_u32(&mbar_full[i]), 1);
+      tc::mbar_init(tc::smem_u32(&mbar_free[i]), 1);
+    }
     tc::mbar_init(tc::smem_u32(&mbar_acc[0]), 1);
     tc::mbar_init(tc::smem_u32(&mbar_acc[1]), 1);
   }
-
-  const T* Bg = reinterpret_cast<const T*>(a.Bm);
-  const T* Xg = reinterpret_cast<const T*>(a.X);
-  const int64_t vrow0 = ((int64_t)b * a.heads + h0) * nchunks * kQ;  // exponent vectors of head h0 (next head: + nchunks * kQ)
-  const int nst = SPC * nchunks;
-  // stage s = steps [s * 64, s * 64 + 64): 16 lanes copy one 256-byte row of B, 8 lanes one 128-byte row of x
-  auto copy_stage = [&](int s) {
-    unsigned char* base = smraw + (s % NS) * M::STAGE;
-    const int tq = s * kStep;  // first step of the stage
-    {
-      const int nc = tid & 15, r0 = tid >> 4;
-#pragma unroll
-      for (int k = 0; k < kStep / 16; ++k) {
-        const int j = r0 + 16 * k;
-        const bool okt = tq + j < a.len;
-        cp_async16(base + (size_t)(j >> 3) * (kN * 16) + nc * 128 + (j & 7) * 16, Bg + (((int64_t)b * a.len + (okt ? tq + j : 0)) * a.groups + g) * kN + nc * 8, okt);
-      }
-    }
-    {
-      const int pc = tid & 7, r0 = tid >> 3;
-#pragma unroll
-      for (int hh = 0; hh < HPC; ++hh) {
-#pragma unroll
-        for (int k = 0; k < kStep / 32; ++k) {
-          const int j = r0 + 32 * k;
-          const bool okt = tq + j < a.len;
-          cp_async16(base + M::A_BYTES + (size_t)(j >> 3) * (HPC * kP * 16) + (hh * 8 + pc) * 128 + (j & 7) * 16,
-                     Xg + (((int64_t)b * a.len + (okt ? tq + j : 0)) * a.heads + h0 + hh) * kP + pc * 8, okt);
-        }
-      }
-    }
-    if (s % SPC == 0) {
-      const int c = s / SPC;
-      for (int i = tid; i < HPC * (kQ / 4); i += 256) {
-        const int hh = i / (kQ / 4), q4 = i % (kQ / 4);
-        cp_async16(sVec + ((c & 1) * HPC + hh) * kQ + q4 * 4, a.ws_dt + vrow0 + ((int64_t)hh * nchunks + c) * kQ + q4 * 4, true);
-      }
-    }
-  };
-#pragma unroll
-  for (int s = 0; s < AHEAD; ++s) {
-    if (s < nst) copy_stage(s);
-    cp_async_commit();
-  }
-
   __syncthreads();  // TMEM address and barriers are set up
   const uint32_t tmem = tmem_slot;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+
+  const int64_t vrow0 = ((int64_t)b * a.heads + h0) * nchunks * kQ;  // exponent vectors of head h0 (next head: + nchunks * kQ)
+  const int nst = SPC * nchunks;
+  // stage s = steps [s * 64, s * 64 + 64), issued by one thread: two boxes of B, one box of x per head, and with a
+  // chunk's first stage the exponent vectors of its heads.  Steps beyond the sequence read as zero.
+  auto copy_stage = [&](int s) {
+    const uint32_t base = tc::smem_u32(smraw + (s % NS) * M::STAGE);
+    const uint32_t full = tc::smem_u32(&mbar_full[s % NS]);
+    const bool first = s % SPC == 0;
+    tc::mbar_expect_tx(full, M::STAGE + (first ? HPC * kQ * 4 : 0));
+    tc::tma_load_4d(base, &maps.b, full, 0, g, s * kStep, b);
+    tc::tma_load_4d(base + M::BLK_BYTES, &maps.b, full, 64, g, s * kStep, b);
+#pragma unroll
+    for (int hh = 0; hh < HPC; ++hh) tc::tma_load_4d(base + M::A_BYTES + hh * M::BLK_BYTES, &maps.x, full, 0, h0 + hh, s * kStep, b);
+    if (first) {
+      const int c = s / SPC;
+#pragma unroll
+      for (int hh = 0; hh < HPC; ++hh)
+        tc::bulk_load(tc::smem_u32(sVec + ((c & 1) * HPC + hh) * kQ), a.ws_dt + vrow0 + ((int64_t)hh * nchunks + c) * kQ, kQ * 4, full);
+    }
+  };
+  if (tid == 0) {
+    for (int s = 0; s < AHEAD && s < nst; ++s) copy_stage(s);
+  }
 
   // running states: st[hh][i] = S_{h0 + hh}[n][wg * 32 + i]
   float st[HPC][32];
@@ -224,12 +216,12 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
   for (int s = 0; s < nst; ++s) {
     const int c = s / SPC, part = s % SPC;
     // ---- refill the buffer AHEAD stages ahead; it was last read by the MMAs of stage s + AHEAD - NS ----------
-    if (s + AHEAD < nst) {
+    if (tid == 0 && s + AHEAD < nst) {
       const int sp = s + AHEAD - NS;  // previous user of that buffer
-      if (sp >= 0 && !fail) fail = !__all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_free[(s + AHEAD) % NS]), (sp / NS) & 1));
-      copy_stage(s + AHEAD);
+      bool okf = true;
+      if (sp >= 0) okf = tc::mbar_wait(tc::smem_u32(&mbar_free[(s + AHEAD) % NS]), (sp / NS) & 1);
+      if (okf) copy_stage(s + AHEAD);  // if that wait ran out the stage never lands and the waits below report it
     }
-    cp_async_commit();
     if (part == 0) {  // a new chunk begins: its last exponents (loaded early, used by the scaling below)
 #pragma unroll
       for (int hh = 0; hh < HPC; ++hh) {
@@ -244,20 +236,19 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
       if (!fail) fail = !fold_chunk(c - 1, clast_prev);
       emit_state_in(c);
     }
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(AHEAD) : "memory");  // this stage's copies (younger groups may be in flight)
-    __syncthreads();
+    if (!fail) fail = !__all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_full[s % NS]), (s / NS) & 1));  // this stage's copies
 
-    // ---- scale the x rows in place: w_j x_j -----------------------------------------------------------------
+    // ---- scale the x rows in place: w_j x_j (a row is one step, whatever the swizzle does inside it) ------------
     unsigned char* base = smraw + (s % NS) * M::STAGE;
 #pragma unroll
     for (int hh = 0; hh < HPC; ++hh) {
       const float* vcp = sVec + ((c & 1) * HPC + hh) * kQ + part * kStep;
       const float c_last = clast[hh];
 #pragma unroll
-      for (int k = 0; k < (kP / 8) * kStep / 256; ++k) {
-        const int u = tid + 256 * k;  // unit of this head: (j / 8) * 64 + pc * 8 + j % 8; the heads' units interleave per 8 steps
-        const float w = ex2_approx(c_last - vcp[(u >> 6) * 8 + (u & 7)]);
-        unsigned char* px = base + M::A_BYTES + ((size_t)(u >> 6) * (HPC * 64) + hh * 64 + (u & 63)) * 16;
+      for (int k = 0; k < M::BLK_BYTES / 16 / 256; ++k) {
+        const int u = tid + 256 * k;  // 16-byte unit of this head's tile; 8 units per step
+        const float w = ex2_approx(c_last - vcp[u >> 3]);
+        unsigned char* px = base + M::A_BYTES + hh * M::BLK_BYTES + (size_t)u * 16;
         Vec16<T> v;
         v.raw = *reinterpret_cast<const uint4*>(px);
         float f[8];
@@ -274,14 +265,13 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
     tc::fence_after_sync();
 
     if (tid == 0) {
-      // the heads' x tiles sit side by side along N: one instruction of N = 64 HPC columns serves all of them
+      // M = 128 states = two 64-element blocks, N = 64 HPC = one block per head; blocks 8 KB apart, 8 steps 1 KB apart
       constexpr uint32_t idesc = tc::instr_desc(kN, HPC * kP, fmt, 1, 1);
-      const uint64_t da0 = tc::smem_desc(tc::smem_u32(base), kN * 16, 128);
-      const uint64_t db0 = tc::smem_desc(tc::smem_u32(base + M::A_BYTES), HPC * kP * 16, 128);
+      const uint64_t da0 = tc::smem_desc_sw128(tc::smem_u32(base), M::BLK_BYTES, 1024);
+      const uint64_t db0 = tc::smem_desc_sw128(tc::smem_u32(base + M::A_BYTES), M::BLK_BYTES, 1024);
 #pragma unroll
-      for (int kk = 0; kk < kStep / 16; ++kk)  // two groups of 8 steps per instruction
-        tc::mma_ss(tmem + (c & 1) * HPC * 64, da0 + (uint64_t)(kk * ((2 * kN * 16) >> 4)), db0 + (uint64_t)(kk * ((2 * HPC * kP * 16) >> 4)), idesc,
-                   part > 0 || kk > 0);
+      for (int kk = 0; kk < kStep / 16; ++kk)  // 16 steps = 16 rows of 128 bytes
+        tc::mma_ss(tmem + (c & 1) * HPC * 64, da0 + (uint64_t)(kk * (2048 >> 4)), db0 + (uint64_t)(kk * (2048 >> 4)), idesc, part > 0 || kk > 0);
       tc::commit(tc::smem_u32(&mbar_free[s % NS]));
       if (part == SPC - 1) tc::commit(tc::smem_u32(&mbar_acc[c & 1]));
     }
@@ -300,18 +290,9 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
     }
   }
   if (fail && lane == 0 && a.status) atomicExch(a.status, 1);
-  cp_async_wait_all();
   tc::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem, kCols);
-}
-
-template <typename T, int HPC>
-static int ssd_state_launch(const ssm_ssd_args& a, int nchunks, cudaStream_t st) {
-  const size_t smem = StateSmem<HPC>::TOTAL;
-  cudaFuncSetAttribute(ssd_state_kernel<T, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  ssd_state_kernel<T, HPC><<<dim3(a.heads / HPC, a.batch), 256, smem, st>>>(a, nchunks);
-  return launch_status("ssd_state_kernel");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -637,7 +618,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     if (tid == 0) {
       // descriptors differ from instruction to instruction only in the start address (16-byte units, low bits)
       const uint64_t da0 = tc::smem_desc(tc::smem_u32(sBA), kBlk * 16, 128);
-      const uint64_t dx0 = tc::smem_desc_sw128(tc::smem_u32(sX + buf * M::X_BYTES), 1024);
+      const uint64_t dx0 = tc::smem_desc_sw128(tc::smem_u32(sX + buf * M::X_BYTES), 16, 1024);
       const uint64_t dc0 = tc::smem_desc(tc::smem_u32(sC), kBlk * 16, 128);
       const uint64_t ds0 = tc::smem_desc(tc::smem_u32(sS + buf * M::S_BYTES), 128, kN * 16);
       constexpr uint32_t idY = tc::instr_desc(kBlk, kP, fmt, 0, 1);
@@ -735,12 +716,14 @@ static EncodeTiledFn encode_tiled_fn() {
   }();
   return fn;
 }
-// (batch, len, heads, 64) tensor of 16-bit elements seen as rank 4 (p, head, step, batch); box = 64 p of one head x `rows` steps
-static int encode_rows_map(CUtensorMap* m, const void* base, const ssm_ssd_args& a, int rows) {
+// (batch, len, outer, inner) tensor of 16-bit elements seen as rank 4 (inner, outer, step, batch);
+// box = 64 inner elements of one outer index x `rows` steps
+static int encode_rows_map(CUtensorMap* m, const void* base, const ssm_ssd_args& a, int rows, int inner = kP, int outer = -1) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return ::ssmb::fail(SSM_ERR_DEVICE, "ssd_scan: cuTensorMapEncodeTiled is not available from this driver");
-  const cuuint64_t dims[4] = {(cuuint64_t)kP, (cuuint64_t)a.heads, (cuuint64_t)a.len, (cuuint64_t)a.batch};
-  const cuuint64_t strides[3] = {(cuuint64_t)kP * 2, (cuuint64_t)a.heads * kP * 2, (cuuint64_t)a.len * a.heads * kP * 2};
+  if (outer < 0) outer = a.heads;
+  const cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)a.len, (cuuint64_t)a.batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)inner * 2, (cuuint64_t)outer * inner * 2, (cuuint64_t)a.len * outer * inner * 2};
   const cuuint32_t box[4] = {(cuuint32_t)kP, 1, (cuuint32_t)rows, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dt = a.io_dtype == SSM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -748,6 +731,17 @@ static int encode_rows_map(CUtensorMap* m, const void* base, const ssm_ssd_args&
                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return ::ssmb::fail(SSM_ERR_DEVICE, "ssd_scan: cuTensorMapEncodeTiled rejected the tensor");
   return SSM_OK;
+}
+
+template <typename T, int HPC>
+static int ssd_state_launch(const ssm_ssd_args& a, int nchunks, cudaStream_t st) {
+  StateMaps maps;
+  if (int rc = encode_rows_map(&maps.b, a.Bm, a, StateSmem<HPC>::kStep, kN, a.groups)) return rc;
+  if (int rc = encode_rows_map(&maps.x, a.X, a, StateSmem<HPC>::kStep)) return rc;
+  const size_t smem = StateSmem<HPC>::ALLOC;
+  cudaFuncSetAttribute(ssd_state_kernel<T, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  ssd_state_kernel<T, HPC><<<dim3(a.heads / HPC, a.batch), 256, smem, st>>>(a, maps, nchunks);
+  return launch_status("ssd_state_kernel");
 }
 
 template <typename T>

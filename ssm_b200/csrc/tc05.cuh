@@ -30,11 +30,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
 
 // Same for an MN-major operand whose rows of 64 elements (128 bytes) were written by TMA with the 128-byte swizzle:
 // K row k of the tile lives at k * 128 bytes, its 16-byte chunk c at position c ^ (k % 8); groups of 8 K rows are
-// sbo_bytes apart (1024 for a dense tile).  The tile must start on a 1024-byte boundary.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t sbo_bytes) {
+// sbo_bytes apart (1024 for a dense tile); when M / N spans several 64-element blocks, those are lbo_bytes apart.
+// The tile must start on a 1024-byte boundary.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr >> 4) & 0x3FFF);
-  d |= (uint64_t)1 << 16;  // leading-dimension offset: unused for a single 64-element block along M / N
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)2 << 61;  // layout type: 128-byte swizzle
