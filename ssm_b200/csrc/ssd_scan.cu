@@ -338,8 +338,8 @@ __global__ void __launch_bounds__(256) ssd_fold_init_kernel(const ssm_ssd_args a
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 struct ScanSmem {
-  static constexpr int C_BYTES = kBlk * kN * 2;     // C rows of the block, K-major [n/8][i][8]            32 KB
-  static constexpr int B_BYTES = kQ * kN * 2;       // B rows, K-major [n/8][j][8]; later the masked tile  64 KB
+  static constexpr int C_BYTES = kBlk * kN * 2;     // C rows of the block: two blocks (states 0..63, 64..127) of [i][128 B], swizzled   32 KB
+  static constexpr int B_BYTES = kQ * kN * 2;       // B rows likewise, [j][128 B] per block; later the masked tile, K-major [j/8][i][8]  64 KB
   static constexpr int X_BYTES = kQ * kP * 2;       // x rows [j][64 p], 128-byte rows, TMA 128-byte swizzle  32 KB (x2)
   static constexpr int S_BYTES = kP * kN * 2;       // incoming state, MN-major [p/8][n][8]                 16 KB (x2)
   static constexpr int VEC_BYTES = 2 * kQ * 4;      // c and c - log2(delta) of the chunk                     2 KB (x2)
@@ -354,6 +354,7 @@ constexpr int kScanThreads = 256;
 // tensor maps of one call: x (box of 128 or 256 steps), z and y (boxes of 128 rows); rank 4 (p, head, step, batch)
 struct ScanMaps {
   CUtensorMap x0, x1, z, y;
+  CUtensorMap c, bm;  // C and B rows: rank 4 (state, group, step, batch), boxes of 64 states x 128 steps
 };
 
 // Body for row block MB (0: rows 0..127, steps 0..127; 1: rows 128..255, steps 0..255).
@@ -369,7 +370,8 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   unsigned char* sS = sX + 2 * M::X_BYTES;     // two buffers
   float* sVec = reinterpret_cast<float*>(sS + 2 * M::S_BYTES);  // two buffers of [c | c - log2 delta]
   unsigned char* sZ = reinterpret_cast<unsigned char*>(sVec) + 2 * M::VEC_BYTES;
-  // mbar: 0 G done; 1 + b MMAs of a head into accumulator pair b done; 3 + b operands of buffer b landed; 5 z tile landed
+  // mbar: 0 G done; 1 + b MMAs of a head into accumulator pair b done; 3 + b operands of buffer b landed; 5 z tile landed;
+  // 6 C and B tiles landed
   const uint32_t mb_g = tc::smem_u32(&mbar[0]), mb_z = tc::smem_u32(&mbar[5]);
   auto mb_mma = [&](int bf) { return tc::smem_u32(&mbar[1 + bf]); };
   auto mb_full = [&](int bf) { return tc::smem_u32(&mbar[3 + bf]); };
@@ -392,24 +394,18 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   const bool has_z = a.z != nullptr;
   const CUtensorMap* mapx = MB ? &maps.x1 : &maps.x0;
 
-  const T* Cg = reinterpret_cast<const T*>(a.Cm);
-  const T* Bg = reinterpret_cast<const T*>(a.Bm);
-
-  // ---- C rows of the block, B rows of the reachable steps: 16 lanes copy one 256-byte row -----------
-  {
-    const int nc = tid & 15, r0 = tid >> 4;
-    for (int i = r0; i < kBlk; i += 16) {
-      const int t = t0 + MB * kBlk + i;
-      const bool okt = t < a.len;
-      cp_async16(sC + ((size_t)nc * kBlk + i) * 16, Cg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
-    }
-    for (int j = r0; j < KJ; j += 16) {
-      const int t = t0 + j;
-      const bool okt = t < a.len;
-      cp_async16(sBA + ((size_t)nc * KJ + j) * 16, Bg + (((int64_t)b * a.len + (okt ? t : 0)) * a.groups + g) * kN + nc * 8, okt);
+  // ---- C rows of the block, B rows of the reachable steps, by TMA: per half of the states one block of 128-byte rows
+  const uint32_t mb_cb = tc::smem_u32(&mbar[6]);
+  if (tid == 0) {
+    tc::mbar_expect_tx(mb_cb, M::C_BYTES + KJ * kN * 2);
+#pragma unroll
+    for (int nb2 = 0; nb2 < 2; ++nb2) {
+      tc::tma_load_4d(tc::smem_u32(sC + nb2 * (kBlk * 128)), &maps.c, mb_cb, nb2 * 64, g, t0 + MB * kBlk, b);
+#pragma unroll
+      for (int jb2 = 0; jb2 <= MB; ++jb2)
+        tc::tma_load_4d(tc::smem_u32(sBA + nb2 * (KJ * 128) + jb2 * (kBlk * 128)), &maps.bm, mb_cb, nb2 * 64, g, t0 + jb2 * kBlk, b);
     }
   }
-  cp_async_commit();
 
   // One head's operands, by bulk copies issued from one thread: x rows through the tensor map (128-byte rows, swizzled),
   // the incoming state and the two exponent vectors as contiguous pieces.  Steps beyond the sequence read as zero.
@@ -428,11 +424,9 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   // slot of (row, 16-byte chunk) in a tile of 128-byte rows written / read by TMA with the 128-byte swizzle
   auto swz = [&](unsigned char* tile, int row, int chunk) { return tile + ((size_t)row * 8 + (chunk ^ (row & 7))) * 16; };
 
-  __syncthreads();  // barriers initialised (by thread 0 of the kernel prologue) before anyone arms or polls them
   if (tid == 0) prefetch(h0, 0);
 
-  cp_async_wait_all();
-  tc::fence_async_smem();
+  bool ok = __all_sync(0xffffffffu, tc::mbar_wait(mb_cb, 0));  // C and B have landed
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
@@ -440,16 +434,18 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
   // ---- G = C_m B^T ------------------------------------------------------------------------------------
-  if (tid == 0) {
-    const uint64_t dc0 = tc::smem_desc(tc::smem_u32(sC), kBlk * 16, 128);
-    const uint64_t db0 = tc::smem_desc(tc::smem_u32(sBA), KJ * 16, 128);
+  // K-major operands in 128-byte-swizzled rows: 16 states = 32 bytes further along the row, 64 states = the next block
+  if (tid == 0 && ok) {
+    const uint64_t dc0 = tc::smem_desc_sw128(tc::smem_u32(sC), 16, 1024);
+    const uint64_t db0 = tc::smem_desc_sw128(tc::smem_u32(sBA), 16, 1024);
     constexpr uint32_t idG = tc::instr_desc(kBlk, KJ, fmt, 0, 0);
 #pragma unroll
     for (int kk = 0; kk < kN / 16; ++kk)
-      tc::mma_ss(tmem, dc0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), db0 + (uint64_t)(kk * ((2 * KJ * 16) >> 4)), idG, kk > 0);
+      tc::mma_ss(tmem, dc0 + (uint64_t)(((kk >> 2) * (kBlk * 128) + (kk & 3) * 32) >> 4), db0 + (uint64_t)(((kk >> 2) * (KJ * 128) + (kk & 3) * 32) >> 4), idG,
+                 kk > 0);
     tc::commit(mb_g);
   }
-  bool ok = __all_sync(0xffffffffu, tc::mbar_wait(mb_g, 0));  // warp-uniform
+  ok = __all_sync(0xffffffffu, ok && tc::mbar_wait(mb_g, 0));  // warp-uniform
   tc::fence_after_sync();
 
   // This thread's part of G stays in registers for all heads: row i_loc, chunks wg, wg + 2, ...
@@ -619,7 +615,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
       // descriptors differ from instruction to instruction only in the start address (16-byte units, low bits)
       const uint64_t da0 = tc::smem_desc(tc::smem_u32(sBA), kBlk * 16, 128);
       const uint64_t dx0 = tc::smem_desc_sw128(tc::smem_u32(sX + buf * M::X_BYTES), 16, 1024);
-      const uint64_t dc0 = tc::smem_desc(tc::smem_u32(sC), kBlk * 16, 128);
+      const uint64_t dc0 = tc::smem_desc_sw128(tc::smem_u32(sC), 16, 1024);
       const uint64_t ds0 = tc::smem_desc(tc::smem_u32(sS + buf * M::S_BYTES), 128, kN * 16);
       constexpr uint32_t idY = tc::instr_desc(kBlk, kP, fmt, 0, 1);
       constexpr uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 1);
@@ -629,7 +625,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
         tc::mma_ss(dY, da0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), dx0 + (uint64_t)(kk * (2048 >> 4)), idY, kk > 0);
 #pragma unroll
       for (int kk = 0; kk < kN / 16; ++kk)
-        tc::mma_ss(dS, dc0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), ds0 + (uint64_t)(kk * (256 >> 4)), idS, kk > 0);
+        tc::mma_ss(dS, dc0 + (uint64_t)(((kk >> 2) * (kBlk * 128) + (kk & 3) * 32) >> 4), ds0 + (uint64_t)(kk * (256 >> 4)), idS, kk > 0);
       tc::commit(mb_mma(buf));
     }
     // ---- the previous head's result, while the tensor cores work on this one ---------------------------------
@@ -689,13 +685,14 @@ __global__ void __launch_bounds__(kScanThreads, 1)
     ssd_scan_kernel(const ssm_ssd_args a, const __grid_constant__ ScanMaps maps, int nchunks, int hpc, int nparts) {
   extern __shared__ unsigned char smdyn[];
   unsigned char* smraw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smdyn) + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t mbar[6];
+  __shared__ __align__(8) uint64_t mbar[7];
   __shared__ uint32_t tmem_slot;
   const int warp = threadIdx.x >> 5;
   if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), 512);
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 6; ++i) tc::mbar_init(tc::smem_u32(&mbar[i]), 1);
+    for (int i = 0; i < 7; ++i) tc::mbar_init(tc::smem_u32(&mbar[i]), 1);
   }
+  __syncthreads();  // barriers and the TMEM address are set up before anyone arms or polls them
   // the heavier blocks (rows 128..255) are scheduled first
   if ((int)blockIdx.x < (int)(gridDim.x >> 1)) ssd_scan_body<T, 1>(a, maps, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
   else ssd_scan_body<T, 0>(a, maps, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
@@ -747,12 +744,26 @@ static int ssd_state_launch(const ssm_ssd_args& a, int nchunks, cudaStream_t st)
 template <typename T>
 static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
   const int nchunks = (a.len + kQ - 1) / kQ;
-  // heads per CTA: the largest divisor of the heads of one B / C group that is <= 12, so that a
-  // CTA's heads share their B / C tiles and the grid still has several CTAs per SM to balance
+  // heads per scan CTA (a divisor of the heads of one B / C group, so that a CTA's heads share their G): every CTA
+  // pays a prologue (C / B tiles, G) of about two heads' worth of time, and the grid runs in whole waves of one CTA
+  // per SM; take the divisor with the least (waves x (prologue + heads)).
   const int hpg = a.heads / a.groups;
+  int sm_count = 148;
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
   int hpc = 1;
-  for (int d = 1; d <= 12; ++d)
-    if (hpg % d == 0) hpc = d;
+  {
+    double best = 1e300;
+    for (int d = 1; d <= hpg && d <= 32; ++d) {
+      if (hpg % d) continue;
+      const int64_t ctas = 2ll * a.batch * nchunks * (a.heads / d);
+      const double cost = (double)((ctas + sm_count - 1) / sm_count) * (2.0 + d);
+      if (cost < best) best = cost, hpc = d;
+    }
+  }
   const int nparts = a.heads / hpc;
   if (a.phase != 2) {
     const int warps = a.batch * a.heads * nchunks;
@@ -763,12 +774,6 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
     // heads per CTA of the sequential state kernel: enough to bring the grid down to about one CTA per SM
     // (its CTAs all run for the whole sequence, so a second, partial wave would double the time), at most 4,
     // and a divisor of the heads of one B / C group
-    int sm_count = 148;
-    {
-      int dev = 0;
-      cudaGetDevice(&dev);
-      cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    }
     int shpc = (int)(((int64_t)a.batch * a.heads + sm_count - 1) / sm_count);
     shpc = shpc < 1 ? 1 : (shpc > 4 ? 4 : shpc);
     while (hpg % shpc != 0) --shpc;
@@ -791,6 +796,8 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
     if (int rc = encode_rows_map(&maps.x1, a.X, a, kQ)) return rc;
     if (int rc = encode_rows_map(&maps.z, a.z ? a.z : a.X, a, kBlk)) return rc;
     if (int rc = encode_rows_map(&maps.y, a.Y, a, kBlk)) return rc;
+    if (int rc = encode_rows_map(&maps.c, a.Cm, a, kBlk, kN, a.groups)) return rc;
+    if (int rc = encode_rows_map(&maps.bm, a.Bm, a, kBlk, kN, a.groups)) return rc;
     const size_t smem = ScanSmem<T>::ALLOC;
     cudaFuncSetAttribute(ssd_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ssd_scan_kernel<T><<<2 * nparts * a.batch * nchunks, kScanThreads, smem, st>>>(a, maps, nchunks, hpc, nparts);

@@ -444,7 +444,7 @@ def run_reference(ref) -> Pack:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference", help="root of the upstream b-vitamins/ssm checkout")
+    ap.add_argument("--reference", required=True, help="root of a checkout of upstream b-vitamins/ssm (the fixtures are its test vectors and runs of its Python operators)")
     args = ap.parse_args()
     root = Path(args.reference)
     sys.path.insert(0, str(root / "src"))
