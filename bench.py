@@ -641,6 +641,123 @@ def run_ssd_sp(args):
         dist.destroy_process_group()
 
 
+def run_mamba2_sp(args):
+    """BASELINE config 5: a random-init bf16 Mamba-2 stack (d_model 2560, expand 2, headdim 64, d_state 128, ngroups 1,
+    chunk 256, conv width 4, RMSNorm, vocab 50280 with a tied head) prefilling batch 2 x seqlen 131072 of uniform random
+    token ids, the sequence split into contiguous shards over the ranks: per layer the K-1 trailing conv inputs go to
+    the next rank and the chunk state is handed over (`ssm_b200.seqpar`).  A step is one whole forward; the result is
+    the logits of the last token (on the last rank)."""
+    import torch.distributed as dist
+
+    from ssm_b200 import ops
+    from ssm_b200.mixer import mamba2_block_forward
+
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    under_launcher = "RANK" in os.environ
+    if under_launcher:
+        dist.init_process_group("nccl", device_id=dev)
+    B, Ltot = 2, args.seqlen or 131072
+    layers = args.layers or 64
+    dm, hp, n, k, vocab = 2560, 64, 128, 4, 50280
+    di = 2 * dm
+    nh = di // hp
+    Lq = Ltot // world
+    bf = torch.bfloat16
+    cfg = dict(heads=nh, headdim=hp, d_state=n, groups=1, chunk_size=256, eps=1e-5)
+    gen = torch.Generator(device=dev).manual_seed(1234)  # the same weights on every rank
+
+    def lin(o, i):
+        return (torch.randn(o, i, generator=gen, device=dev) / i ** 0.5).to(bf)
+
+    def layer_weights():
+        return dict(
+            pre_norm_w=torch.ones(dm, device=dev, dtype=bf), in_z=lin(di, dm), in_x=lin(di, dm), in_B=lin(n, dm), in_C=lin(n, dm), in_dt=lin(nh, dm),
+            conv_x=(torch.rand(di, k, generator=gen, device=dev) - 0.5).to(bf), conv_B=(torch.rand(n, k, generator=gen, device=dev) - 0.5).to(bf),
+            conv_C=(torch.rand(n, k, generator=gen, device=dev) - 0.5).to(bf), conv_x_b=torch.zeros(di, device=dev, dtype=bf),
+            conv_B_b=torch.zeros(n, device=dev, dtype=bf), conv_C_b=torch.zeros(n, device=dev, dtype=bf),
+            dt_bias=(torch.rand(nh, generator=gen, device=dev) * 2 - 4).float(), A_log=torch.log(torch.rand(nh, generator=gen, device=dev) * 15 + 1),
+            D=torch.randn(nh, generator=gen, device=dev), norm_w=torch.ones(di, device=dev, dtype=bf), out_proj=lin(dm, di))
+
+    ws = [layer_weights() for _ in range(layers)]
+    emb = (torch.randn(vocab, dm, generator=gen, device=dev) * 0.02).to(bf)
+    final_norm = torch.ones(dm, device=dev, dtype=bf)
+    gi = torch.Generator().manual_seed(99)
+    ids_all = torch.randint(0, vocab, (B, Ltot), generator=gi)
+    ids_host = ids_all[:, rank * Lq:(rank + 1) * Lq].contiguous().pin_memory()
+    if rank == 0:
+        print(f"[mamba2_sp] {layers} layers ready: shard length {Lq}", file=sys.stderr, flush=True)
+
+    @torch.no_grad()
+    def forward(ids):
+        hidden = torch.nn.functional.embedding(ids, emb)
+        residual = None
+        for w in ws:
+            hidden, residual = mamba2_block_forward(ops, w, cfg, hidden, residual, sharded=world > 1)
+        last = ops.fused_layer_norm(hidden[:, -1:].contiguous(), final_norm, None, residual=residual[:, -1:].contiguous(), is_rms=True, eps=1e-5,
+                                    prenorm=True, residual_in_fp32=True)
+        return torch.matmul(last[:, 0], emb.t())  # logits of the shard's last token; the sequence's last token on the last rank
+
+    ids_dev = ids_host.to(dev)
+    tw = time.perf_counter()
+    for i in range(args.warmup):
+        forward(ids_dev)
+        torch.cuda.synchronize()
+        if rank == 0:
+            print(f"[mamba2_sp] warm-up {i}: {time.perf_counter() - tw:.2f} s since start", file=sys.stderr, flush=True)
+
+    def timed(fn):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda: forward(ids_dev))
+    clocks = sampler.stop() if rank == 0 else None
+    out_host = torch.empty(B, vocab, dtype=bf).pin_memory()
+
+    def e2e_step():
+        logits = forward(ids_host.to(dev, non_blocking=True))
+        out_host.copy_(logits, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    ms_e2e = timed(e2e_step)
+    if rank == 0:
+        tokens = B * Ltot
+        gemm_flops = 2.0 * tokens * dm * (2 * di + 2 * n + nh + di) * layers
+        print(json.dumps({
+            "metric": "tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 weights / activations, fp32 residual stream and states", "data": "synthetic (seeded uniform token ids, random-init weights)",
+            "config": {"workload": f"mamba2 prefill: {layers} layers, d_model {dm}, {nh} heads x {hp}, d_state {n}, chunk 256, conv {k}, vocab {vocab}; "
+                                   f"batch {B}, seqlen {Ltot} in {world} contiguous shards",
+                       "parallelism": f"sp{world}: per layer a {k - 1}-token conv halo to the next rank and an all-gather of the chunk state (5.2 MB / rank)",
+                       "l2": "per-layer activations (GBs) exceed the 126 MB L2"},
+            "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": ids_host.numel() * 8,
+                    "d2h_bytes_per_step": out_host.numel() * 2},
+            "gpu_launches": layers * 9 * args.steps,
+            "roofline": {"kernel": "whole forward (projection GEMMs dominate)", "bound": "tensor", "achieved": gemm_flops / (ms * 1e-3) / 1e12 / world,
+                         "peak": None, "unit": "TFLOP/s", "frac": None, "traffic": None, "note": "dense projection flops per GPU over the whole step"},
+            "clocks": clocks}))
+    if under_launcher:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -650,7 +767,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling on a smaller case)")
-    ap.add_argument("--workload", default="mamba1_block", choices=["mamba1_block", "ssd", "decode", "scan_c1", "ssd_sp"])
+    ap.add_argument("--workload", default="mamba1_block", choices=["mamba1_block", "ssd", "decode", "scan_c1", "ssd_sp", "mamba2_sp"])
+    ap.add_argument("--layers", type=int, default=0, help="override the depth of the mamba2_sp workload")
     ap.add_argument("--seqlen", type=int, default=0, help="override the total sequence length of the ssd_sp workload")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -662,6 +780,8 @@ def main():
         run_decode(args)
     elif args.workload == "scan_c1":
         run_scan_c1(args)
+    elif args.workload == "mamba2_sp":
+        run_mamba2_sp(args)
     elif args.workload == "ssd_sp":
         run_ssd_sp(args)
     else:

@@ -136,3 +136,102 @@ class Mamba1Block(nn.Module):
         res1 = None if residual is None else residual
         return ops.fused_layer_norm(out, self.norm_w, None, residual=res1, is_rms=True, eps=self.eps, prenorm=True,
                                     residual_in_fp32=True, return_residual=True)
+
+
+def mamba2_block_forward(ops: Any, w: dict, cfg: dict, hidden: Tensor, residual: Optional[Tensor], group=None, sharded: bool = False):
+    """One Mamba-2 block (upstream Mamba-2 data flow; the reference's ``Mamba2`` has no ``d_state`` axis, so the
+    layout follows upstream): ``residual += hidden; u = RMSNorm(residual); out = mixer(u)`` -> ``(out, residual)``.
+
+    mixer: projections of u to z, x, B, C, dt (separate GEMMs, so every operand of the scan is contiguous);
+    depthwise causal conv + SiLU on x, B and C (channels-last); SSD scan with D skip, dt bias + softplus and
+    the SiLU(z) gate; RMSNorm over d_inner; out projection.
+
+    ``sharded=True``: ``hidden`` is this rank's contiguous shard of the sequence; the conv inputs of the last
+    K-1 tokens go to the next rank and the chunk state is handed over (`ssm_b200.seqpar`), CUDA operators only.
+    ``cfg``: heads, headdim, d_state, groups, chunk_size, eps.
+    """
+    nb, nl, dm = hidden.shape
+    nh, hp, n, g = cfg["heads"], cfg["headdim"], cfg["d_state"], cfg["groups"]
+    eps = cfg.get("eps", 1e-5)
+    u, residual = ops.fused_layer_norm(hidden, w["pre_norm_w"], None, residual=residual, is_rms=True, eps=eps, prenorm=True,
+                                       residual_in_fp32=True, return_residual=True)
+    u2 = u.reshape(nb * nl, dm)
+
+    def proj(name):
+        return torch.matmul(u2, w[name].t()).view(nb, nl, -1)
+
+    def conv(t, name):
+        halo = None
+        if sharded:
+            from . import seqpar
+
+            halo = seqpar.exchange_conv_halo(t, w[name].shape[1], group, channels_first=False)
+        if halo is None:
+            return ops.dw_causal_conv(t, w[name], w[name + "_b"], "silu")
+        return ops.dw_causal_conv(t, w[name], w[name + "_b"], "silu", halo=halo)
+
+    z = proj("in_z").view(nb, nl, nh, hp)
+    x = conv(proj("in_x"), "conv_x").view(nb, nl, nh, hp)
+    Bm = conv(proj("in_B"), "conv_B").view(nb, nl, g, n)
+    Cm = conv(proj("in_C"), "conv_C").view(nb, nl, g, n)
+    dt = proj("in_dt")
+    A = -torch.exp(w["A_log"])
+    if sharded:
+        from . import seqpar
+
+        y, _ = seqpar.ssd_scan_sharded(x, dt, A, Bm, Cm, cfg.get("chunk_size", 256), D=w["D"], z=z, dt_bias=w["dt_bias"], dt_softplus=True,
+                                       group=group)
+    else:
+        y = ops.ssd_scan(x, dt, A, Bm, Cm, cfg.get("chunk_size", 256), D=w["D"], z=z, dt_bias=w["dt_bias"], dt_softplus=True)
+    y = ops.fused_layer_norm(y.reshape(nb, nl, nh * hp), w["norm_w"], None, is_rms=True, eps=eps)
+    out = torch.matmul(y.reshape(nb * nl, nh * hp), w["out_proj"].t()).view(nb, nl, dm)
+    return out, residual
+
+
+class Mamba2Block(nn.Module):
+    """Pre-norm Mamba-2 block on the operators: ``forward(hidden, residual) -> (mixer output, residual stream)``.
+    ``forward(..., sharded=True, group=pg)`` runs it on one contiguous shard of a sequence split over ranks."""
+
+    def __init__(self, d_model: int, d_state: int = 128, d_conv: int = 4, expand: int = 2, headdim: int = 64, ngroups: int = 1,
+                 chunk_size: int = 256, dt_min: float = 1e-3, dt_max: float = 1e-1, dt_init_floor: float = 1e-4, eps: float = 1e-5,
+                 device=None, dtype=None, ops: Any = None) -> None:
+        super().__init__()
+        d_inner = expand * d_model
+        if d_inner % headdim:
+            raise ValueError("expand * d_model must be a multiple of headdim.")
+        heads = d_inner // headdim
+        if heads % ngroups:
+            raise ValueError("Group dimension must divide H.")
+        self.d_model, self.d_inner, self.d_state, self.d_conv = d_model, d_inner, d_state, d_conv
+        self.heads, self.headdim, self.ngroups, self.chunk_size, self.eps = heads, headdim, ngroups, chunk_size, eps
+        self._ops = ops
+        kw = dict(device=device, dtype=dtype)
+        f32 = dict(device=device, dtype=torch.float32)
+        gn = ngroups * d_state
+
+        def lin(o, i):
+            return nn.Parameter(torch.randn(o, i, **kw) / i ** 0.5)
+
+        def conv_w(c):
+            return nn.Parameter((torch.rand(c, d_conv, **kw) - 0.5) * (2.0 / d_conv ** 0.5))
+
+        self.pre_norm_w = nn.Parameter(torch.ones(d_model, **kw))
+        self.in_z, self.in_x, self.in_B, self.in_C, self.in_dt = lin(d_inner, d_model), lin(d_inner, d_model), lin(gn, d_model), lin(gn, d_model), lin(heads, d_model)
+        self.conv_x, self.conv_B, self.conv_C = conv_w(d_inner), conv_w(gn), conv_w(gn)
+        self.conv_x_b, self.conv_B_b, self.conv_C_b = (nn.Parameter(torch.zeros(c, **kw)) for c in (d_inner, gn, gn))
+        dt = torch.exp(torch.rand(heads, **f32) * (math.log(dt_max) - math.log(dt_min)) + math.log(dt_min)).clamp(min=dt_init_floor)
+        self.dt_bias = nn.Parameter(dt + torch.log(-torch.expm1(-dt)))
+        self.A_log = nn.Parameter(torch.log(torch.empty(heads, **f32).uniform_(1.0, 16.0)))
+        self.D = nn.Parameter(torch.ones(heads, **f32))
+        self.norm_w = nn.Parameter(torch.ones(d_inner, **kw))
+        self.out_proj = lin(d_model, d_inner)
+
+    def forward(self, hidden: Tensor, residual: Optional[Tensor] = None, sharded: bool = False, group=None):
+        if hidden.ndim != 3 or hidden.shape[-1] != self.d_model:
+            raise ValueError("hidden_states must have shape (B, L, d_model).")
+        ops = self._ops
+        if ops is None:
+            from . import ops  # the CUDA operators; raises if the library has not been built
+        w = {k: v for k, v in self.named_parameters()}
+        cfg = dict(heads=self.heads, headdim=self.headdim, d_state=self.d_state, groups=self.ngroups, chunk_size=self.chunk_size, eps=self.eps)
+        return mamba2_block_forward(ops, w, cfg, hidden, residual, group=group, sharded=sharded)
