@@ -108,6 +108,7 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32, BwdShap
   const int raw_bc_dtype = bc_vec ? a.bc_dtype : SSM_F32;
 
   const int ntiles = (L + TL - 1) / TL;
+  const float Dv = a.D ? __ldg(a.D + d) : 0.f;
 
   auto fill_raw = [&](int t0) {
     fill_rows_raw<T, RPW, TL>(rawU, gu, b, D, L, drow0, t0, io_vec, lane, a.row_sb, a.row_sd);
@@ -121,7 +122,20 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32, BwdShap
     cp_async_commit();
   };
 
-  if (ntiles > 0) fill_raw((ntiles - 1) * TL);
+  // the checkpoint a tile starts from is fetched one tile ahead
+  float2 hck[NS / 2];
+  auto load_checkpoint = [&](int kt) {
+    const float* ck = a.checkpoints + (row * ntiles + kt) * N;  // TL == checkpoint interval
+#pragma unroll
+    for (int j = 0; j < NS; j += 2) {
+      hck[j / 2].x = (sg * NS + j) < N ? __ldg(ck + sg * NS + j) : 0.f;
+      hck[j / 2].y = (sg * NS + j + 1) < N ? __ldg(ck + sg * NS + j + 1) : 0.f;
+    }
+  };
+  if (ntiles > 0) {
+    fill_raw((ntiles - 1) * TL);
+    load_checkpoint(ntiles - 1);
+  }
 
   for (int k = ntiles - 1; k >= 0; --k) {
     const int t0 = k * TL;
@@ -184,7 +198,6 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32, BwdShap
     float* rU = sU + r * TLP;
     float* rDy = sDy + r * TLP;
     float* rZf = sZf + r * TLP;
-    const float Dv = a.D ? __ldg(a.D + d) : 0.f;
     float* hl = hist + lane * NS;  // this lane's states of slot m live at hl[m * 32 * NS]
 
     auto load_bc = [&](const float* tile, const char* base, int64_t sn, int64_t st, int tt, float (&v)[NS]) {
@@ -215,12 +228,9 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32, BwdShap
     // ---- rebuild the tile's states from the checkpoint -----------------------------------------
     {
       float2 h[NS / 2];
-      const float* ck = a.checkpoints + (row * ntiles + k) * N;  // TL == checkpoint interval
 #pragma unroll
-      for (int j = 0; j < NS; j += 2) {
-        h[j / 2].x = (sg * NS + j) < N ? __ldg(ck + sg * NS + j) : 0.f;
-        h[j / 2].y = (sg * NS + j + 1) < N ? __ldg(ck + sg * NS + j + 1) : 0.f;
-      }
+      for (int j = 0; j < NS / 2; ++j) h[j] = hck[j];
+      if (k > 0) load_checkpoint(k - 1);  // for the next (earlier) tile: its latency hides behind this tile's work
       hist_store(0, h);
 #pragma unroll 2
       for (int tb0 = 0; tb0 < TL; tb0 += TB) {
