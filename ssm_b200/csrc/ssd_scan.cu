@@ -785,10 +785,13 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
       default: rc = ssd_state_launch<T, 4>(a, nchunks, st); break;
     }
     if (rc) return rc;
-  } else {
+  } else if (a.initial_states) {
     const int64_t total = (int64_t)a.batch * a.heads * kP * kN;
     ssd_fold_init_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a, nchunks);
     if (int rc = launch_status("ssd_fold_init_kernel")) return rc;
+  } else if (a.final_states) {  // nothing arrives: the final state is the one phase 1 left in the scratch
+    const cudaError_t e = cudaMemcpyAsync(a.final_states, a.ws_state, sizeof(float) * (size_t)a.batch * a.heads * kP * kN, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return ::ssmb::fail((int)e, "ssd_scan: copying the final state failed");
   }
   if (a.phase != 1) {
     ScanMaps maps;

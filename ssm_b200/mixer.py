@@ -160,20 +160,22 @@ def mamba2_block_forward(ops: Any, w: dict, cfg: dict, hidden: Tensor, residual:
     def proj(name):
         return torch.matmul(u2, w[name].t()).view(nb, nl, -1)
 
-    def conv(t, name):
-        halo = None
-        if sharded:
-            from . import seqpar
+    px, pB, pC = proj("in_x"), proj("in_B"), proj("in_C")
+    halos = [None, None, None]
+    if sharded:
+        from . import seqpar
 
-            halo = seqpar.exchange_conv_halo(t, w[name].shape[1], group, channels_first=False)
+        halos = seqpar.exchange_conv_halos([px, pB, pC], w["conv_x"].shape[1], group)  # one message for the three inputs
+
+    def conv(t, name, halo):
         if halo is None:
             return ops.dw_causal_conv(t, w[name], w[name + "_b"], "silu")
         return ops.dw_causal_conv(t, w[name], w[name + "_b"], "silu", halo=halo)
 
     z = proj("in_z").view(nb, nl, nh, hp)
-    x = conv(proj("in_x"), "conv_x").view(nb, nl, nh, hp)
-    Bm = conv(proj("in_B"), "conv_B").view(nb, nl, g, n)
-    Cm = conv(proj("in_C"), "conv_C").view(nb, nl, g, n)
+    x = conv(px, "conv_x", halos[0]).view(nb, nl, nh, hp)
+    Bm = conv(pB, "conv_B", halos[1]).view(nb, nl, g, n)
+    Cm = conv(pC, "conv_C", halos[2]).view(nb, nl, g, n)
     dt = proj("in_dt")
     A = -torch.exp(w["A_log"])
     if sharded:

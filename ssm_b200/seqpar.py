@@ -31,9 +31,14 @@ def fold_incoming_state(states: Tensor, log_decay: Tensor, rank: int, initial: O
     every shard's total ``sum delta A``.  ``initial`` is the state before shard 0.
     ``S_in[r] = sum_{q<r} exp(sum_{q<m<r} logP_m) S_q  (+ exp(sum_{m<r} logP_m) initial)``.
     """
-    s = torch.zeros_like(states[0]) if initial is None else initial.to(states[0].dtype).clone()
-    for q in range(rank):
-        s = torch.exp(log_decay[q])[..., None, None] * s + states[q]
+    if rank == 0:
+        return torch.zeros_like(states[0]) if initial is None else initial.to(states[0].dtype).clone()
+    # weight of shard q's state (and of the initial state) at the start of shard `rank`: the decay of the shards in between
+    logs = torch.stack([log_decay[q] for q in range(rank)])                                   # (rank, B, H)
+    after = torch.flip(torch.cumsum(torch.flip(logs, [0]), 0), [0]) - logs                    # sum over q < m < rank
+    s = (torch.stack([states[q] for q in range(rank)]) * torch.exp(after)[..., None, None]).sum(0)
+    if initial is not None:
+        s = s + torch.exp(logs.sum(0))[..., None, None] * initial.to(s.dtype)
     return s
 
 
@@ -54,12 +59,16 @@ def ssd_scan_sequence_parallel(
     rank, world = (0, 1) if alone else (dist.get_rank(group), dist.get_world_size(group))
     s_loc, logp = state_phase()
     if world == 1:
-        s_in = torch.zeros_like(s_loc) if initial_states is None else initial_states.to(s_loc.dtype)
-        return finish_phase(s_in)
-    all_s = [torch.empty_like(s_loc) for _ in range(world)]
-    all_p = [torch.empty_like(logp) for _ in range(world)]
-    dist.all_gather(all_s, s_loc.contiguous(), group=group)
-    dist.all_gather(all_p, logp.contiguous(), group=group)
+        return finish_phase(None if initial_states is None else initial_states.to(s_loc.dtype))
+    # one message per rank: the state with its log-decay appended
+    nbh = logp.numel()
+    packed = torch.cat([s_loc.reshape(nbh, -1), logp.reshape(nbh, 1).to(s_loc.dtype)], dim=1).contiguous()
+    gathered = [torch.empty_like(packed) for _ in range(world)]
+    dist.all_gather(gathered, packed, group=group)
+    if rank == 0:
+        return finish_phase(None if initial_states is None else initial_states.to(s_loc.dtype))
+    all_s = [gk[:, :-1].reshape(s_loc.shape) for gk in gathered[:rank]]
+    all_p = [gk[:, -1].reshape(logp.shape) for gk in gathered[:rank]]
     s_in = fold_incoming_state(all_s, all_p, rank, initial_states)
     return finish_phase(s_in)
 
@@ -102,3 +111,22 @@ def exchange_conv_halo(x_shard: Tensor, width: int, group=None, channels_first: 
     for req in dist.batch_isend_irecv(ops_):
         req.wait()
     return recv if rank > 0 else None
+
+
+def exchange_conv_halos(parts, width: int, group=None):
+    """One exchange for several channels-last conv inputs ``(B, L, C_i)`` of the same shard: their last
+    ``width-1`` tokens travel to the next rank as one message.  Returns one halo ``(B, C_i, width-1)`` per
+    part (fp32), or ``None`` for each on rank 0 / without a process group."""
+    alone = not (dist.is_available() and dist.is_initialized())
+    world = 1 if alone else dist.get_world_size(group)
+    if width <= 1 or world == 1:
+        return [None for _ in parts]
+    joined = torch.cat([p[:, -(width - 1):, :] for p in parts], dim=-1)  # (B, K-1, sum C_i)
+    halo = exchange_conv_halo(joined, width, group, channels_first=False)
+    if halo is None:
+        return [None for _ in parts]
+    out, c0 = [], 0
+    for p in parts:
+        out.append(halo[:, c0:c0 + p.shape[-1], :].contiguous())
+        c0 += p.shape[-1]
+    return out
