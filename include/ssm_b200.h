@@ -354,7 +354,11 @@ int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* args, ssm_stream_t s
  *   ws_dt, ws_cum : (batch, heads, nchunks * 256) fp32 each; per chunk ws_cum[i] = log2(e) * sum_{k<=i} delta_k A
  *                   (running decay exponent, base 2) and ws_dt[i] = ws_cum[i] - log2(delta_i)
  *   ws_state      : (batch, heads, headdim, nstate) fp32 — the final state reached from the given (or zero)
- *                   initial state, kept for a later phase-2 call on the same scratch
+ *                   initial state, kept for a later phase-2 call on the same scratch — followed by (batch, heads)
+ *                   fp32, the total log-decay sum(delta A) of the call; the two together (ssm_ssd_shard_summary_floats()
+ *                   floats) are what a sequence shard sends to the other ranks; then, from the next 256-byte boundary,
+ *                   (batch, heads, nchunks) fp32 decay exponents from the start of the call to each chunk.  The whole
+ *                   region takes ssm_ssd_state_scratch_bytes() bytes
  *   ws_state_in   : (batch, nchunks, heads, headdim * nstate) in io_dtype — the state before every chunk, in
  *                   the operand order of the scan kernel
  * status: optional device int, set non-zero when a bounded device-side wait ran out.
@@ -388,7 +392,17 @@ typedef struct {
 
 int ssm_ssd_supported(int32_t headdim, int32_t nstate, int32_t chunk_size, int32_t io_dtype);
 int64_t ssm_ssd_scratch_bytes(int32_t batch, int32_t len, int32_t heads);
+int64_t ssm_ssd_state_scratch_bytes(int32_t batch, int32_t len, int32_t heads);
 int ssm_ssd_fwd(const ssm_ssd_args* args, ssm_stream_t stream);
+
+/* Sequence shards (no reference counterpart: the reference is single-device).  After phase 1 every rank all-gathers its
+ * summary (ws_state: final state from a zero start, then total log-decay; ssm_ssd_shard_summary_floats() floats) into
+ * `gathered` (world x that many floats).  ssm_ssd_fold_shards writes the incoming state (batch, heads, headdim, nstate)
+ * fp32 of shard `rank`:  sum_{q<rank} exp(sum_{q<m<rank} logP_m) S_q  (+ the decayed `initial_states`, nullable),
+ * which is the initial_states of the phase-2 call. */
+int64_t ssm_ssd_shard_summary_floats(int32_t batch, int32_t heads);
+int ssm_ssd_fold_shards(const float* gathered, int32_t world, int32_t rank, int32_t batch, int32_t heads, const float* initial_states,
+                        float* incoming, ssm_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -32,6 +32,11 @@ constexpr int kP = 64;     // head dimension
 constexpr int kN = 128;    // state dimension
 constexpr int kBlk = 128;  // rows per scan CTA
 
+// floats of the shard summary (final state, then total log-decay), rounded up to whole 256-byte lines
+__host__ __device__ inline int64_t ssd_summary_floats_padded(int batch, int heads) {
+  return ((int64_t)batch * heads * (kP * kN + 1) + 63) / 64 * 64;
+}
+
 // ---------------------------------------------------------------------------------------------
 // delta and within-chunk cumulative log-decay; one warp per (batch, head, chunk)
 // ---------------------------------------------------------------------------------------------
@@ -191,9 +196,9 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
     }
   };
   // last exponent of the current / previous chunk per head (the decay across the chunk is exp2 of it)
-  float clast[HPC], clast_prev[HPC];
+  float clast[HPC], clast_prev[HPC], ctot[HPC];
 #pragma unroll
-  for (int hh = 0; hh < HPC; ++hh) clast[hh] = 0.f, clast_prev[hh] = 0.f;
+  for (int hh = 0; hh < HPC; ++hh) clast[hh] = 0.f, clast_prev[hh] = 0.f, ctot[hh] = 0.f;
   // fold chunk c's finished accumulators into the running states
   auto fold_chunk = [&](int c, const float (&cl)[HPC]) -> bool {
     const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_acc[c & 1]), (c >> 1) & 1));
@@ -227,6 +232,10 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
       for (int hh = 0; hh < HPC; ++hh) {
         clast_prev[hh] = clast[hh];
         clast[hh] = __ldg(a.ws_cum + vrow0 + ((int64_t)hh * nchunks + c) * kQ + kQ - 1);
+        // exponent (base 2) of the decay from the start of the sequence to the start of this chunk: what a state
+        // that arrives later (phase 2 of a sequence shard) is multiplied by before it joins this chunk's state
+        if (tid == 0) a.ws_state[ssd_summary_floats_padded(a.batch, a.heads) + ((int64_t)b * a.heads + h0 + hh) * nchunks + c] = ctot[hh];
+        ctot[hh] += clast[hh];
       }
       if (c == 0) emit_state_in(0);
     }
@@ -287,6 +296,9 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
         if (a.final_states) a.final_states[off + (int64_t)i * kN] = st[hh][i];
         a.ws_state[off + (int64_t)i * kN] = st[hh][i];
       }
+      // the shard's total log-decay (natural log) follows the states in the scratch: together they are what a
+      // sequence shard sends to the other ranks
+      if (tid == 0) a.ws_state[(int64_t)a.batch * a.heads * kP * kN + (int64_t)b * a.heads + h0 + hh] = ctot[hh] * kLn2;
     }
   }
   if (fail && lane == 0 && a.status) atomicExch(a.status, 1);
@@ -302,24 +314,36 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) ssd_fold_init_kernel(const ssm_ssd_args a, int nchunks) {
-  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  const int64_t per = (int64_t)kP * kN;
-  const int64_t total = (int64_t)a.batch * a.heads * per;
-  if (i >= total) return;
-  const int64_t bh = i / per;
-  const int q = (int)(i % per);  // ((p / 8) * N + n) * 8 + p % 8
-  const int e = q & 7, n = (q >> 3) % kN, pc = q / (8 * kN);
-  const int pn = (pc * 8 + e) * kN + n;
+  // thread = one 16-byte unit (p / 8, n) of the state before one chunk; blockIdx.y = 0 .. nchunks (the last row: final states)
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;  // unit of one (batch, head): 1024 units each
+  const int64_t units = (int64_t)a.batch * a.heads * (kP * kN / 8);
+  if (i >= units) return;
+  const int64_t bh = i / (kP * kN / 8);
+  const int u = (int)(i % (kP * kN / 8));
+  const int n = u % kN, pc = u / kN;
   const int b = (int)(bh / a.heads), h = (int)(bh % a.heads);
-  const float s0 = a.initial_states ? __ldg(a.initial_states + bh * per + pn) : 0.f;
-  T* sin = reinterpret_cast<T*>(a.ws_state_in);
-  float expo = 0.f;
-  for (int c = 0; c < nchunks; ++c) {
-    const int64_t idx = (((int64_t)b * nchunks + c) * a.heads + h) * per + q;
-    if (a.initial_states) sin[idx] = from_f<T>(to_f<T>(sin[idx]) + ex2_approx(expo) * s0);
-    expo += __ldg(a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ + kQ - 1);
+  const int c = blockIdx.y;
+  const float* s0 = a.initial_states + bh * (int64_t)(kP * kN) + (int64_t)(pc * 8) * kN + n;  // 8 values p = 8 pc .. 8 pc + 7 of state n
+  const float* pre = a.ws_state + ssd_summary_floats_padded(a.batch, a.heads);
+  if (c < nchunks) {
+    const float w = ex2_approx(__ldg(pre + bh * nchunks + c));
+    T* blk = reinterpret_cast<T*>(a.ws_state_in) + (((int64_t)b * nchunks + c) * a.heads + h) * (int64_t)(kP * kN) + (int64_t)u * 8;
+    Vec16<T> v;
+    v.raw = *reinterpret_cast<const uint4*>(blk);
+    float f[8];
+    v.unpack(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = fmaf(w, __ldg(s0 + (int64_t)e * kN), f[e]);
+    v.pack(f);
+    *reinterpret_cast<uint4*>(blk) = v.raw;
+  } else if (a.final_states) {
+    const float w = __expf(__ldg(a.ws_state + (int64_t)a.batch * a.heads * kP * kN + bh));  // total log-decay of the call
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int64_t off = bh * (int64_t)(kP * kN) + (int64_t)(pc * 8 + e) * kN + n;
+      a.final_states[off] = fmaf(w, __ldg(s0 + (int64_t)e * kN), a.ws_state[off]);
+    }
   }
-  if (a.final_states) a.final_states[bh * per + pn] = a.ws_state[bh * per + pn] + ex2_approx(expo) * s0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -741,6 +765,24 @@ static int ssd_state_launch(const ssm_ssd_args& a, int nchunks, cudaStream_t st)
   return launch_status("ssd_state_kernel");
 }
 
+// ---------------------------------------------------------------------------------------------
+// incoming state of sequence shard `rank` from every rank's (final state from a zero start | total log-decay):
+//   S_in = sum_{q < rank} exp(sum_{q < m < rank} logP_m) S_q  (+ exp(sum_{m < rank} logP_m) initial)
+// `gathered`: world x per_rank floats, each rank's block = batch_heads * elems states then batch_heads log-decays.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) ssd_fold_shards_kernel(const float* __restrict__ gathered, int rank, int64_t per_rank, int batch_heads, int elems,
+                                                              const float* __restrict__ initial, float* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= (int64_t)batch_heads * elems) return;
+  const int bh = (int)(i / elems);
+  float s = initial ? __ldg(initial + i) : 0.f;
+  for (int q = 0; q < rank; ++q) {
+    const float* blk = gathered + (int64_t)q * per_rank;
+    s = fmaf(__expf(__ldg(blk + (int64_t)batch_heads * elems + bh)), s, __ldg(blk + i));
+  }
+  out[i] = s;
+}
+
 template <typename T>
 static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
   const int nchunks = (a.len + kQ - 1) / kQ;
@@ -786,8 +828,8 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
     }
     if (rc) return rc;
   } else if (a.initial_states) {
-    const int64_t total = (int64_t)a.batch * a.heads * kP * kN;
-    ssd_fold_init_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a, nchunks);
+    const int64_t units = (int64_t)a.batch * a.heads * (kP * kN / 8);
+    ssd_fold_init_kernel<T><<<dim3((unsigned)((units + 255) / 256), nchunks + 1), 256, 0, st>>>(a, nchunks);
     if (int rc = launch_status("ssd_fold_init_kernel")) return rc;
   } else if (a.final_states) {  // nothing arrives: the final state is the one phase 1 left in the scratch
     const cudaError_t e = cudaMemcpyAsync(a.final_states, a.ws_state, sizeof(float) * (size_t)a.batch * a.heads * kP * kN, cudaMemcpyDeviceToDevice, st);
@@ -817,12 +859,30 @@ extern "C" int ssm_ssd_supported(int32_t headdim, int32_t nstate, int32_t chunk_
   return headdim == kP && nstate == kN && chunk_size == kQ && (io_dtype == SSM_BF16 || io_dtype == SSM_F16);
 }
 
+extern "C" int64_t ssm_ssd_state_scratch_bytes(int32_t batch, int32_t len, int32_t heads) {
+  const int64_t nchunks = (len + kQ - 1) / kQ;
+  return ((ssd_summary_floats_padded(batch, heads) + (int64_t)batch * heads * nchunks) * 4 + 255) / 256 * 256;
+}
+
 extern "C" int64_t ssm_ssd_scratch_bytes(int32_t batch, int32_t len, int32_t heads) {
   const int64_t nchunks = (len + kQ - 1) / kQ;
   const int64_t vec = (int64_t)batch * heads * nchunks * kQ * 4;      // delta, cum (each)
-  const int64_t fin = (int64_t)batch * heads * kP * kN * 4;           // shard-local final state, fp32
+  const int64_t fin = ssm_ssd_state_scratch_bytes(batch, len, heads);  // shard-local final state, total log-decay, per-chunk decay prefixes
   const int64_t st = (int64_t)batch * nchunks * heads * kP * kN * 2;  // state before every chunk, operand dtype
   return 2 * vec + fin + st;
+}
+
+extern "C" int64_t ssm_ssd_shard_summary_floats(int32_t batch, int32_t heads) { return (int64_t)batch * heads * (kP * kN + 1); }
+
+extern "C" int ssm_ssd_fold_shards(const float* gathered, int32_t world, int32_t rank, int32_t batch, int32_t heads, const float* initial_states,
+                                   float* incoming, ssm_stream_t stream) {
+  SSM_REQUIRE(gathered && incoming, SSM_ERR_NULL, "ssd_fold_shards: missing tensor");
+  SSM_REQUIRE(world >= 1 && rank >= 0 && rank < world && batch >= 0 && heads >= 1, SSM_ERR_SHAPE, "ssd_fold_shards: bad shape");
+  const int64_t total = (int64_t)batch * heads * kP * kN;
+  if (total == 0) return SSM_OK;
+  ssd_fold_shards_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      gathered, rank, ssm_ssd_shard_summary_floats(batch, heads), batch * heads, kP * kN, initial_states, incoming);
+  return launch_status("ssd_fold_shards_kernel");
 }
 
 extern "C" int ssm_ssd_fwd(const ssm_ssd_args* a, ssm_stream_t stream) {

@@ -991,7 +991,7 @@ class _SsdWorkspace:
         Y = torch.empty_like(self.X) if want_y else None
         final = torch.empty(nb, nh, npj, nn, dtype=torch.float32, device=dev)
         vec = nb * nh * self.nchunks * self.chunk * 4
-        fin = nb * nh * npj * nn * 4
+        fin = int(L.load().ssm_ssd_state_scratch_bytes(nb, nl, nh))
         a = L.SsdArgs()
         a.batch, a.len, a.heads, a.headdim = nb, nl, nh, npj
         a.nstate, a.groups, a.chunk_size, a.io_dtype = nn, ng, self.chunk, _CODES[self.io]
@@ -1004,6 +1004,13 @@ class _SsdWorkspace:
         a.status = _p(self.status)
         _call(L.load().ssm_ssd_fwd, a)
         return Y, final
+
+    def shard_summary(self) -> Tensor:
+        """Flat fp32 view of what phase 1 left for the other ranks: the final state from a zero start, then (B, H) total log-decay."""
+        nb, nl, nh, _, _, _ = self.shape
+        vec = nb * nh * self.nchunks * self.chunk * 4
+        n = int(L.load().ssm_ssd_shard_summary_floats(nb, nh))
+        return self.ws[2 * vec: 2 * vec + n * 4].view(torch.float32)
 
     def total_log_decay(self) -> Tensor:
         """(B, H) sum over the shard of delta * A, read from the cumulative sums left in scratch."""

@@ -90,6 +90,25 @@ def ssd_scan_sharded(X, dt, A, B, C, chunk_size=256, D=None, z=None, dt_bias=Non
     def finish_phase(s_in):
         return w.run(2, s_in, True)
 
+    alone = not (dist.is_available() and dist.is_initialized())
+    world = 1 if alone else dist.get_world_size(group)
+    if world > 1 and dist.get_backend(group) == "nccl":
+        # fast path: the summary phase 1 leaves in the scratch is gathered as it is and folded by one kernel
+        from . import _lib as L
+
+        rank = dist.get_rank(group)
+        w.run(1, None, False)
+        mine = w.shard_summary()
+        gathered = torch.empty(world * mine.numel(), dtype=torch.float32, device=mine.device)
+        dist.all_gather_into_tensor(gathered, mine, group=group)
+        if rank == 0 and initial_states is None:
+            return finish_phase(None)
+        nb, _, nh, npj, _, nn = w.shape
+        s_in = torch.empty(nb, nh, npj, nn, dtype=torch.float32, device=mine.device)
+        init = None if initial_states is None else initial_states.to(torch.float32).contiguous()
+        L.check(L.load().ssm_ssd_fold_shards(gathered.data_ptr(), world, rank, nb, nh, None if init is None else init.data_ptr(), s_in.data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream))
+        return finish_phase(s_in)
     return ssd_scan_sequence_parallel(state_phase, finish_phase, group, initial_states)
 
 

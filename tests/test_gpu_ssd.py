@@ -136,3 +136,30 @@ def test_two_phase_shards_reproduce_the_unsharded_scan():
     close(torch.cat([outs[0][0], outs[1][0]], 1), Yf, **HALF_TOL, what="Y")
     close(outs[1][1], Sf, **HALF_TOL, what="final state")
     assert int(shards[0][0].status.item()) == 0 and int(shards[1][0].status.item()) == 0
+
+
+def test_shard_summary_and_fold_kernel_match_the_host_fold():
+    """Phase 1 leaves (final state | total log-decay) in the scratch; the fold entry point turns the gathered
+    summaries of all ranks into a rank's incoming state exactly like the host-side fold."""
+    from ssm_b200 import _lib as L
+    from ssm_b200 import ops, seqpar
+
+    world, nb, nh = 3, 2, 3
+    summaries, states, logps = [], [], []
+    for r in range(world):
+        t = {k: (None if v is None else v.cuda()) for k, v in _inputs(nb, 512, nh, 1, torch.bfloat16, seed=40 + r, with_init=False).items()}
+        w = ops._SsdWorkspace(t["X"], t["dt"], t["A"], t["B"], t["C"], t["D"], t["z"], t["dt_bias"], True, 256)
+        _, s_loc = w.run(1, None, False)
+        summary = w.shard_summary().clone()
+        assert summary.numel() == L.load().ssm_ssd_shard_summary_floats(nb, nh)
+        close(summary[: s_loc.numel()].view_as(s_loc), s_loc, **FP32_TOL, what="state part of the summary")
+        close(summary[s_loc.numel():].view(nb, nh), w.total_log_decay(), **FP32_TOL, what="log-decay part of the summary")
+        summaries.append(summary), states.append(s_loc), logps.append(w.total_log_decay())
+    gathered = torch.cat(summaries)
+    init = torch.randn(nb, nh, 64, 128, device="cuda")
+    for r in range(world):
+        for ini in (None, init):
+            out = torch.empty(nb, nh, 64, 128, device="cuda")
+            L.check(L.load().ssm_ssd_fold_shards(gathered.data_ptr(), world, r, nb, nh, None if ini is None else ini.data_ptr(), out.data_ptr(),
+                                                 torch.cuda.current_stream().cuda_stream))
+            close(out, seqpar.fold_incoming_state(states, logps, r, ini), **FP32_TOL, what=f"incoming state of rank {r}")
