@@ -193,12 +193,17 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_fwd_kernel(const ss
   for (int c = 0; c < kNormFwdChunks; ++c) {
     const int ch = c * G + gt;
     if (ch < nchunk) {
-      float o[V];
+      float o[V], wv[V], bv[V];
+#pragma unroll
+      for (int i = 0; i < V; i += 4) {  // weight / bias are fp32 and 16-byte aligned at every chunk (hidden % V == 0, V >= 4)
+        const float4 w4 = __ldg(reinterpret_cast<const float4*>(a.weight + ch * V + i));
+        wv[i] = w4.x, wv[i + 1] = w4.y, wv[i + 2] = w4.z, wv[i + 3] = w4.w;
+        const float4 b4 = a.bias ? __ldg(reinterpret_cast<const float4*>(a.bias + ch * V + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        bv[i] = b4.x, bv[i + 1] = b4.y, bv[i + 2] = b4.z, bv[i + 3] = b4.w;
+      }
 #pragma unroll
       for (int i = 0; i < V; ++i) {
-        const int col = ch * V + i;
-        float y = (s[c][i] - mean) * rstd * __ldg(a.weight + col);
-        if (a.bias) y += __ldg(a.bias + col);
+        float y = fmaf((s[c][i] - mean) * rstd, wv[i], bv[i]);
         if (a.residual && !a.prenorm) y += r[c][i];
         o[i] = y;
       }
@@ -439,7 +444,7 @@ static bool norm_vec_ok(const ssm_norm_args& a, int maxchunks, const void* p1, c
   if (a.hidden > 512 * maxchunks * V) return false;
   auto ok = [](const void* p) { return p == nullptr || aligned_to(p, 16); };
   // residual / residual_out / dresidual rows of fp32 with hidden % V == 0 are 16-byte aligned too
-  return ok(a.x) && ok(a.y) && ok(a.residual) && ok(a.residual_out) && ok(p1) && ok(p2) && ok(p3);
+  return ok(a.x) && ok(a.y) && ok(a.residual) && ok(a.residual_out) && ok(a.weight) && ok(a.bias) && ok(p1) && ok(p2) && ok(p3);
 }
 
 static int norm_group(const ssm_norm_args& a, int maxchunks) {
