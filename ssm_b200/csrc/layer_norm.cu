@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_fwd_kernel(const ss
 }
 
 template <typename T, int G>
-__global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_bwd_kernel(const ssm_norm_bwd_args g) {
+__global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 128 ? 4 : 1) norm_bwd_kernel(const ssm_norm_bwd_args g) {
   using Cfg = NormCfg<T, G>;
   constexpr int V = Cfg::V;
   const ssm_norm_args& a = g.fwd;
