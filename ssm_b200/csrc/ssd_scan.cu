@@ -374,6 +374,9 @@ struct ScanSmem {
 };
 
 constexpr int kScanThreads = 256;
+// Thread that issues the bulk copies (TMA): lane 0 of the warp with the least mask work (rows 0..31 of the block, odd
+// chunks), so that its issue time hides behind the other warps' mask stage; thread 0 issues the MMAs.
+constexpr int kCopyThread = 128;
 
 // tensor maps of one call: x (box of 128 or 256 steps), z and y (boxes of 128 rows); rank 4 (p, head, step, batch)
 struct ScanMaps {
@@ -420,7 +423,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
 
   // ---- C rows of the block, B rows of the reachable steps, by TMA: per half of the states one block of 128-byte rows
   const uint32_t mb_cb = tc::smem_u32(&mbar[6]);
-  if (tid == 0) {
+  if (tid == kCopyThread) {
     tc::mbar_expect_tx(mb_cb, M::C_BYTES + KJ * kN * 2);
 #pragma unroll
     for (int nb2 = 0; nb2 < 2; ++nb2) {
@@ -448,7 +451,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   // slot of (row, 16-byte chunk) in a tile of 128-byte rows written / read by TMA with the 128-byte swizzle
   auto swz = [&](unsigned char* tile, int row, int chunk) { return tile + ((size_t)row * 8 + (chunk ^ (row & 7))) * 16; };
 
-  if (tid == 0) prefetch(h0, 0);
+  if (tid == kCopyThread) prefetch(h0, 0);
 
   bool ok = __all_sync(0xffffffffu, tc::mbar_wait(mb_cb, 0));  // C and B have landed
   tc::fence_before_sync();
@@ -539,7 +542,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
       fail = 1;
       break;
     }
-    if (tid == 0) {
+    if (tid == kCopyThread) {
       if (hi >= 2) {  // staged by the epilogue of the previous iteration
         tc::tma_store_4d(&maps.y, tc::smem_u32(sZ), 0, h - 2, t_blk, b);
         tc::bulk_commit();
@@ -673,7 +676,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     tc::fence_after_sync();
     ok = __syncthreads_and(ok);
     if (ok) {
-      if (tid == 0) {
+      if (tid == kCopyThread) {
         if (nh >= 2) {
           tc::tma_store_4d(&maps.y, tc::smem_u32(sZ), 0, h0 + last - 1, t_blk, b);
           tc::bulk_commit();
@@ -689,7 +692,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
       if (ok) {
         epilogue(h0 + last, buf, ct_prev, xr_prev);
         __syncthreads();
-        if (tid == 0) {
+        if (tid == kCopyThread) {
           tc::tma_store_4d(&maps.y, tc::smem_u32(sZ), 0, h0 + last, t_blk, b);
           tc::bulk_commit();
         }
@@ -700,7 +703,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
       fail = 1;
     }
   }
-  if (tid == 0) tc::bulk_wait_all();  // the staging tile must outlive the stores that read it
+  if (tid == kCopyThread) tc::bulk_wait_all();  // the staging tile must outlive the stores that read it
   if (fail && tid == 0 && a.status) atomicExch(a.status, 2);
 }
 
