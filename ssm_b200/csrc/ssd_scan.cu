@@ -3,26 +3,26 @@
 //   delta_t = softplus?(dt_t + dt_bias);  S_t = exp(delta_t A) S_{t-1} + delta_t x_t B_t^T;  y_t = S_t C_t + D x_t;  y_t *= silu(z_t)
 //
 // evaluated chunk by chunk (Q = 256 steps) in the dual, matrix form, with every contraction on
-// the tcgen05 tensor cores (bf16 / fp16 operands from shared memory, fp32 accumulators in TMEM):
+// the tcgen05 tensor cores (bf16 / fp16 operands in shared memory, staged by TMA, fp32 accumulators in TMEM):
 //
 //   ssd_cumsum_kernel   per chunk the running decay exponent  c_i = log2(e) sum_{k<=i} delta_k A  and  c_i - log2(delta_i)
-//   ssd_state_kernel    per (batch, head), chunks in order: local state  S_c = sum_j exp2(c_last - c_j) delta_j x_j B_j^T   [N x P GEMM, K = Q]
-//                       folded into the running state in registers; the state before every chunk (kept in
-//                       the operand dtype for the GEMM below) and the final state in fp32
-//   ssd_fold_init_kernel  (sequence shards only) adds a late-arriving incoming state to those by linearity
-//   ssd_scan_kernel     per (batch, chunk, head), one warpgroup per 128-row block:  G = C B^T  (TMEM), the decay mask
-//                       exp(cum_i - cum_j) delta_j [j <= i] applied on the TMEM -> register path and
-//                       re-packed as the A operand of  Y_intra = (G o L) X, plus  Y_inter = C S_in;
-//                       y = Y_intra + exp(cum_i) Y_inter + D x, gated, stored.
+//   ssd_state_kernel    per (batch, a few heads), chunks in order: local state  S_c = sum_j exp2(c_last - c_j) delta_j x_j B_j^T
+//                       [N x P GEMM, K = Q] folded into the running state in registers; writes the state before every
+//                       chunk (in the operand dtype and order of the GEMM below), the final state in fp32, and what a
+//                       sequence shard hands to the other ranks
+//   ssd_fold_shards_kernel / ssd_fold_init_kernel   (sequence shards only) fold the other ranks' summaries into this
+//                       shard's incoming state, and add that late-arriving state to the per-chunk states by linearity
+//   ssd_scan_kernel     per (batch, chunk, 128-row block, part of a head group):  G = C B^T once (TMEM -> registers), then per
+//                       head the decay mask exp2(c_i - c_j) delta_j [j <= i] re-packed as the A operand of
+//                       Y_intra = (G o L) X, plus  Y_inter = C S_in;  y = Y_intra + exp2(c_i) Y_inter + D x, gated, stored.
 //
-// Exponent differences are always formed before exp (never exp(cum_i) / exp(cum_j)), so long
+// Exponent differences are always formed before exp2 (never exp2(c_i) / exp2(c_j)), so long
 // sequences stay finite.  Every wait on an mbarrier is bounded and reports through the status word.
 #include <cuda.h>
 
 #include <type_traits>
 
 #include "common.cuh"
-#include "scan_common.cuh"
 #include "tc05.cuh"
 
 namespace ssmb {

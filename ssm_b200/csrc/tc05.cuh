@@ -1,13 +1,15 @@
 // Thin wrappers over the Blackwell tensor-core (tcgen05) and tensor-memory (TMEM) PTX used by
 // the state-space-dual kernels: shared-memory matrix descriptors, the instruction descriptor,
-// MMA issue, commit to an mbarrier, TMEM allocation and TMEM -> register loads.
+// MMA issue, commit to an mbarrier, TMEM allocation and TMEM -> register loads, and the bulk
+// asynchronous copies (TMA) that fill the operand tiles.
 //
-// Operand tiles are kept in the un-swizzled canonical layouts, in units of 16 bytes (8
-// 16-bit elements):
+// Tiles that threads write themselves are kept in the un-swizzled canonical layouts, in units of
+// 16 bytes (8 16-bit elements):
 //   K-major  (the 8 elements of a unit run along K):   unit(mn, kc) at  kc * LBO + (mn / 8) * SBO + (mn % 8) * 16
 //   MN-major (the 8 elements of a unit run along M/N): unit(mc, k)  at  mc * SBO + (k / 8) * LBO + (k % 8) * 16
 // One instruction consumes K = 16, i.e. two K units (K-major) or two groups of eight K rows
 // (MN-major); both are a descriptor advance of 2 * LBO.
+// Tiles that TMA writes are rows of 128 bytes with the 128-byte swizzle (smem_desc_sw128 below).
 #pragma once
 
 #include <cuda_runtime.h>
