@@ -302,8 +302,8 @@ def run_gpu(args):
         "roofline": {"kernel": "scan_bwd_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": peak_kind,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch captured with ncu at batch 2
-                     # (profiles/scan_kernels_ncu_batch2.md: 173.64 MB), scaled by the batch ratio
-                     "traffic": 173.64e6 * B / 2, "bytes_per_launch": bwd_bytes, "ms_per_launch": bwd_ms,
+                     # (profiles/scan_kernels_ncu_batch2.md: 127.68 + 44.90 MB), scaled by the batch ratio
+                     "traffic": 172.58e6 * B / 2, "bytes_per_launch": bwd_bytes, "ms_per_launch": bwd_ms,
                      "note": "instruction/latency-bound kernel (one ex2 and ~34 warp instructions per 32 (row,state,step)); not HBM-bound on this part"},
         "kernels": {"scan_fwd_kernel": {"ms_per_launch": fwd_ms, "bytes_per_launch": fwd_bytes,
                                         "achieved_gbs": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak}},
