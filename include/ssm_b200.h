@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define SSM_B200_ABI_VERSION 1
+#define SSM_B200_ABI_VERSION 2
 
 /* element types of activation tensors */
 enum { SSM_F32 = 0, SSM_BF16 = 1, SSM_F16 = 2 };
@@ -116,6 +116,7 @@ typedef struct {
   int64_t dc_sb, dc_sg, dc_sn, dc_st;
   float* dD;       /* nullable */
   float* ddt_bias; /* nullable */
+  float* dinitial_state; /* nullable: (batch, dim, nstate) fp32, written: gradient of fwd.initial_state (additive extension) */
 } ssm_scan_bwd_args;
 
 int ssm_selective_scan_bwd(const ssm_scan_bwd_args* args, ssm_stream_t stream);
@@ -311,6 +312,7 @@ typedef struct {
   float* dweight;
   float* dbias; /* nullable */
   float* partial;
+  const void* dresidual_out; /* nullable: gradient arriving through residual_out, (rows, hidden) of fwd.resout_dtype; added to dx and dresidual */
 } ssm_norm_bwd_args;
 
 int64_t ssm_norm_bwd_scratch_floats(int64_t rows, int32_t hidden);
@@ -329,7 +331,8 @@ int ssm_fused_add_norm_bwd(const ssm_norm_bwd_args* args, ssm_stream_t stream);
  *  - hidden <= 8192 (larger rows are rejected with SSM_ERR_TOO_LARGE); the array takes
  *    9.25 MiB on every GPU that loads the library, for the life of the process;
  *  - the first call on each device looks up the array's device address (with that device
- *    current) and remembers it; make that first call outside any stream capture;
+ *    current) and remembers it; make that first call outside any stream capture.  The tensors
+ *    must live on the current device (checked: SSM_ERR_DEVICE otherwise);
  *  - all calls on a device share the one array.  Nothing in it has to start at zero (every
  *    launch overwrites the part it later reads), but two calls whose kernels overlap on
  *    the GPU (different streams, no ordering) race on it: serialise them on one stream or

@@ -13,6 +13,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libssm_b200.so"
 
 F32, BF16, F16 = 0, 1, 2
+ABI_VERSION = 2  # SSM_B200_ABI_VERSION of include/ssm_b200.h this binding mirrors
 i32, i64, vp, fp = C.c_int32, C.c_int64, C.c_void_p, C.c_void_p
 
 
@@ -37,7 +38,7 @@ class ScanBwdArgs(C.Structure):
         ("dA", fp), ("dB", fp), ("dC", fp),
         ("db_sb", i64), ("db_sg", i64), ("db_sn", i64), ("db_st", i64),
         ("dc_sb", i64), ("dc_sg", i64), ("dc_sn", i64), ("dc_st", i64),
-        ("dD", fp), ("ddt_bias", fp),
+        ("dD", fp), ("ddt_bias", fp), ("dinitial_state", fp),
     ]
 
 
@@ -116,7 +117,7 @@ class NormArgs(C.Structure):
 
 
 class NormBwdArgs(C.Structure):
-    _fields_ = [("fwd", NormArgs), ("dy", vp), ("dx", vp), ("dresidual", vp), ("dweight", fp), ("dbias", fp), ("partial", fp)]
+    _fields_ = [("fwd", NormArgs), ("dy", vp), ("dx", vp), ("dresidual", vp), ("dweight", fp), ("dbias", fp), ("partial", fp), ("dresidual_out", vp)]
 
 
 class SsdArgs(C.Structure):
@@ -177,7 +178,7 @@ def load() -> C.CDLL:
         except AttributeError as exc:
             raise RuntimeError(f"{LIB_PATH} does not export {name}; rebuild the library") from exc
         fn.restype, fn.argtypes = res, args
-    if lib.ssm_b200_abi_version() != 1:
+    if lib.ssm_b200_abi_version() != ABI_VERSION:
         raise RuntimeError("libssm_b200.so has an unexpected ABI version; rebuild the library")
     _lib = lib
     return lib

@@ -284,6 +284,12 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 
 #pragma unroll
           for (int i = 0; i < V; ++i) dsv[i] = (dy[c][i] * w[c][i] - s[c][i] * c1 - c2) * rstd;
           const int64_t off = row * a.hidden + (int64_t)ch * V;
+          if (g.dresidual_out) {  // gradient arriving through the x + residual output reaches x and residual unchanged
+            float gro[V];
+            load_dyn_vec<V>(g.dresidual_out, off, a.resout_dtype, gro);
+#pragma unroll
+            for (int i = 0; i < V; ++i) dsv[i] += gro[i], dy[c][i] += gro[i];
+          }
           Vec16<T> v;
           v.pack(dsv);
           v.store_stream(reinterpret_cast<T*>(g.dx) + off);
@@ -421,9 +427,10 @@ __global__ void __launch_bounds__(128) norm_scalar_kernel(const ssm_norm_bwd_arg
     for (int c = threadIdx.x; c < a.hidden; c += 128) {
       const float xh = (norm_s_at<T>(a, base + c) - mean) * rstd;
       const float dyv = to_f<T>(reinterpret_cast<const T*>(g.dy)[base + c]);
-      const float ds = (dyv * __ldg(a.weight + c) - xh * c1 - c2) * rstd;
+      const float gro = g.dresidual_out ? load_dyn(g.dresidual_out, base + c, a.resout_dtype) : 0.f;
+      const float ds = (dyv * __ldg(a.weight + c) - xh * c1 - c2) * rstd + gro;
       reinterpret_cast<T*>(g.dx)[base + c] = from_f<T>(ds);
-      if (g.dresidual) store_dyn(g.dresidual, base + c, a.res_dtype, a.prenorm ? ds : dyv);
+      if (g.dresidual) store_dyn(g.dresidual, base + c, a.res_dtype, a.prenorm ? ds : dyv + gro);
     }
   }
 }
@@ -494,7 +501,7 @@ static int norm_fwd_t(const ssm_norm_args& a, cudaStream_t st) {
 template <typename T>
 static int norm_bwd_t(const ssm_norm_bwd_args& g, cudaStream_t st) {
   const ssm_norm_args& a = g.fwd;
-  if (!norm_vec_ok(a, kNormBwdChunks, g.dy, g.dx, g.dresidual)) {
+  if (!norm_vec_ok(a, kNormBwdChunks, g.dy, g.dx, g.dresidual) || !aligned_to(g.dresidual_out, 16)) {
     cudaMemsetAsync(g.dweight, 0, sizeof(float) * a.hidden, st);
     if (g.dbias) cudaMemsetAsync(g.dbias, 0, sizeof(float) * a.hidden, st);
     norm_scalar_kernel<T, true><<<(unsigned)a.rows, 128, 0, st>>>(g);
@@ -564,7 +571,7 @@ static int norm_bwd_launch_capped(const ssm_norm_bwd_args& g, cudaStream_t st, i
 template <typename T>
 static int norm_bwd_noalloc_t(const ssm_norm_bwd_args& g, float* scratch, cudaStream_t st) {
   const ssm_norm_args& a = g.fwd;
-  if (!norm_vec_ok(a, kNormBwdChunks, g.dy, g.dx, g.dresidual)) {
+  if (!norm_vec_ok(a, kNormBwdChunks, g.dy, g.dx, g.dresidual) || !aligned_to(g.dresidual_out, 16)) {
     // rows that cannot be vectorised take the scalar kernel, which needs no scratch at all
     cudaMemsetAsync(g.dweight, 0, sizeof(float) * a.hidden, st);
     if (g.dbias) cudaMemsetAsync(g.dbias, 0, sizeof(float) * a.hidden, st);
@@ -614,6 +621,7 @@ extern "C" int ssm_fused_add_norm_bwd(const ssm_norm_bwd_args* g, ssm_stream_t s
   }
   SSM_REQUIRE(a->x && a->weight && g->dy && g->dx && g->partial, SSM_ERR_NULL, "fused_layer_norm_backward: missing pointer");
   SSM_REQUIRE(!a->residual == !g->dresidual || !g->dresidual, SSM_ERR_NULL, "fused_layer_norm_backward: dresidual without residual");
+  SSM_REQUIRE(!g->dresidual_out || valid_dtype(a->resout_dtype), SSM_ERR_DTYPE, "fused_layer_norm_backward: dresidual_out needs resout_dtype");
   switch (a->io_dtype) {
     case SSM_F32: return norm_bwd_t<float>(*g, st);
     case SSM_BF16: return norm_bwd_t<__nv_bfloat16>(*g, st);
@@ -636,6 +644,16 @@ extern "C" int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* g, ssm_st
   }
   SSM_REQUIRE(a->x && a->weight && g->dy && g->dx, SSM_ERR_NULL, "fused_layer_norm_backward_noalloc: missing pointer");
   SSM_REQUIRE(a->residual || !g->dresidual, SSM_ERR_NULL, "fused_layer_norm_backward_noalloc: dresidual without residual");
+  SSM_REQUIRE(!g->dresidual_out || valid_dtype(a->resout_dtype), SSM_ERR_DTYPE, "fused_layer_norm_backward_noalloc: dresidual_out needs resout_dtype");
+  {
+    // the built-in scratch is looked up for the CURRENT device; tensors that live on another one would be paired with the wrong GPU's array
+    int cur = -1;
+    cudaPointerAttributes attr{};
+    if (cudaGetDevice(&cur) == cudaSuccess && cudaPointerGetAttributes(&attr, g->dy) == cudaSuccess && attr.type == cudaMemoryTypeDevice)
+      SSM_REQUIRE(attr.device == cur, SSM_ERR_DEVICE, "fused_layer_norm_backward_noalloc: the tensors are not on the current device");
+    else
+      (void)cudaGetLastError();
+  }
   float* scratch = nullptr;
   if (int rc = noalloc_scratch_address(&scratch)) return rc;
   switch (a->io_dtype) {

@@ -477,6 +477,14 @@ __global__ void __launch_bounds__(BwdShape<T, NS, LPR, SHARED>::NW * 32, BwdShap
 
   dDacc = group_sum<LPR, 1>(dDacc);
   dBiasAcc = group_sum<LPR, 1>(dBiasAcc);
+  if (g.dinitial_state && row_ok) {  // what the adjoint carries past step 0 is the gradient of the state before it
+#pragma unroll
+    for (int j = 0; j < NS; j += 2) {
+      const int n = sg * NS + j;
+      if (n < N) g.dinitial_state[row * N + n] = carry[j / 2].x;
+      if (n + 1 < N) g.dinitial_state[row * N + n + 1] = carry[j / 2].y;
+    }
+  }
   if (row_ok) {
 #pragma unroll
     for (int j = 0; j < NS; j += 2) {

@@ -7,8 +7,6 @@
 // across the LPR lanes of the row, amortised over TB steps.  B and C tiles are read from
 // global memory once per CTA (ROWS channel rows share them), u / delta / z once, out
 // written once; the next tile's loads (cp.async) overlap the current tile's recurrence.
-#include <cstdlib>
-
 #pragma once
 
 #include "scan_common.cuh"
@@ -282,20 +280,6 @@ static int fwd_lpr(int n) { return n <= 4 ? 1 : n <= 8 ? 2 : n <= 16 ? 4 : n <= 
 template <typename T>
 int dispatch_fwd(const ssm_scan_fwd_args& a, const ScanFlags& fl, cudaStream_t st) {
   const int n = a.nstate;
-#ifdef SSM_SCAN_EXPERIMENT
-  if (const char* v = getenv("SSM_SCAN_FWD_VARIANT")) {
-    const int id = atoi(v);
-    if (n == 16) {
-      if (id == 441) return launch_fwd<T, 4, 4, 1>(a, fl, st);
-      if (id == 442) return launch_fwd<T, 4, 4, 2>(a, fl, st);
-      if (id == 444) return launch_fwd<T, 4, 4, 4>(a, fl, st);
-      if (id == 281) return launch_fwd<T, 2, 8, 1>(a, fl, st);
-      if (id == 282) return launch_fwd<T, 2, 8, 2>(a, fl, st);
-      if (id == 821) return launch_fwd<T, 8, 2, 1>(a, fl, st);
-      if (id == 822) return launch_fwd<T, 8, 2, 2>(a, fl, st);
-    }
-  }
-#endif
   switch (fwd_lpr(n)) {
     case 1: return launch_fwd<T, 4, 1>(a, fl, st);
     case 2: return launch_fwd<T, 4, 2>(a, fl, st);

@@ -91,6 +91,67 @@ def _rows_like(t: Optional[Tensor], ref: Tensor) -> Optional[Tensor]:
     return out
 
 
+def _guard(ctx, *tensors: Optional[Tensor]) -> None:
+    """Remember the version counters of the tensors a backward pass will read again; `_check_guard`
+    raises if one of them was modified in place in between (what autograd does for saved tensors)."""
+    ctx._guarded = [(t, t._version) for t in tensors if t is not None]
+
+
+def _check_guard(ctx) -> None:
+    for t, v in getattr(ctx, "_guarded", ()):
+        if t._version != v:
+            raise RuntimeError("one of the tensors needed for the backward pass of an ssm_b200 operator has been modified in place "
+                               f"(shape {tuple(t.shape)}, version {t._version}, expected {v})")
+
+
+class _DeviceStatus:
+    """The device word that the tensor-core kernels set when one of their bounded waits runs out, with a pinned host
+    mirror.  After every launch the word is copied to the mirror asynchronously on the launching stream; `poll` reads
+    the mirror once that copy has finished, so a timed-out wait surfaces at the next call without the hot path ever
+    synchronising.  `poll(sync=True)` waits for the last launch first."""
+
+    _per_device: dict[int, "_DeviceStatus"] = {}
+
+    def __init__(self, device: torch.device):
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event: Optional[torch.cuda.Event] = None
+
+    @classmethod
+    def of(cls, device: torch.device) -> "_DeviceStatus":
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        st = cls._per_device.get(idx)
+        if st is None:
+            st = cls._per_device[idx] = cls(torch.device("cuda", idx))
+        return st
+
+    def after_launch(self) -> None:
+        if torch.cuda.is_current_stream_capturing():
+            return
+        self.host.copy_(self.word, non_blocking=True)
+        self.event = torch.cuda.Event()
+        self.event.record()
+
+    def poll(self, sync: bool = False) -> None:
+        if self.event is None or torch.cuda.is_current_stream_capturing():
+            return
+        if sync:
+            self.event.synchronize()
+        elif not self.event.query():
+            return
+        code = int(self.host[0])
+        if code:
+            self.host.zero_()
+            self.word.zero_()
+            self.event = None
+            raise RuntimeError(f"ssd_scan: a bounded device-side wait ran out in an earlier launch (status {code}); its outputs are invalid")
+
+
+def ssd_check_status(device: Optional[torch.device] = None) -> None:
+    """Wait for the last tensor-core SSD launch on ``device`` and raise if one of its bounded waits ran out."""
+    _DeviceStatus.of(torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)).poll(sync=True)
+
+
 def _call(fn, args) -> None:
     try:
         L.check(fn(C.byref(args), _stream()))
@@ -217,10 +278,16 @@ def _scan_forward(ctx: _ScanCtx, want_last: bool, want_ckpt: bool, last_dtype: t
     return out, last, ck
 
 
-def _scan_backward(ctx: _ScanCtx, ck: Tensor, grad_out: Tensor, grad_last: Optional[Tensor], B_like: Tensor, C_like: Tensor):
+def _scan_backward(ctx: _ScanCtx, ck: Tensor, grad_out: Tensor, grad_last: Optional[Tensor], B_like: Tensor, C_like: Tensor,
+                   want_dinit: bool = False):
     nb, nd, nl, nn = ctx.shape
     lib = L.load()
     dev = ctx.u.device
+    dinit = None
+    if want_dinit:
+        # an empty sequence hands the gradient of the last state straight to the initial state
+        dinit = torch.zeros(nb, nd, nn, dtype=torch.float32, device=dev) if (nl == 0 and grad_last is None) else \
+            (grad_last.detach().float().clone() if nl == 0 else torch.empty(nb, nd, nn, dtype=torch.float32, device=dev))
     du = torch.empty_like(ctx.u)
     ddelta = torch.empty_like(ctx.u)
     dz = torch.empty_like(ctx.u) if ctx.z is not None else None
@@ -240,6 +307,7 @@ def _scan_backward(ctx: _ScanCtx, ck: Tensor, grad_out: Tensor, grad_last: Optio
     g.dA, g.dB, g.dC, g.dD, g.ddt_bias = _p(dA), _p(dB), _p(dC), _p(dD), _p(dbias)
     g.db_sb, g.db_sg, g.db_sn, g.db_st = ctx.sB
     g.dc_sb, g.dc_sg, g.dc_sn, g.dc_st = ctx.sC
+    g.dinitial_state = _p(dinit)
     _call(lib.ssm_selective_scan_bwd, g)
 
     def fold(grad: Tensor, like: Tensor) -> Tensor:
@@ -248,6 +316,8 @@ def _scan_backward(ctx: _ScanCtx, ck: Tensor, grad_out: Tensor, grad_last: Optio
             grad = grad.view(like.shape[0], like.shape[1], rep, *like.shape[2:]).sum(2)
         return grad.to(like.dtype)
 
+    if want_dinit:
+        return du, ddelta, dA, fold(dB, B_like), fold(dC, C_like), dD, dz, dbias, dinit
     return du, ddelta, dA, fold(dB, B_like), fold(dC, C_like), dD, dz, dbias
 
 
@@ -255,22 +325,26 @@ class _SelectiveScanFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, u, delta, A, B, C_, D, z, dt_bias, softplus, return_last_state, initial_state, keep_state_fp32):
         sc = _ScanCtx(u, delta, A, B, C_, D, z, dt_bias, softplus, initial_state)
-        needs = any(t is not None and t.requires_grad for t in (u, delta, A, B, C_, D, z, dt_bias))
+        needs = any(t is not None and t.requires_grad for t in (u, delta, A, B, C_, D, z, dt_bias, initial_state))
         last_dtype = torch.float32 if keep_state_fp32 else u.dtype
         out, last, ck = _scan_forward(sc, return_last_state, needs, last_dtype)
         ctx.sc, ctx.ck = sc, ck
-        ctx.like = (B, C_, A, D, z, dt_bias, delta)
+        ctx.like = (B, C_, A, D, z, dt_bias, delta, initial_state)
+        _guard(ctx, u, delta, A, B, C_, D, z, dt_bias, initial_state)
         if return_last_state:
             return out, last
         return out
 
     @staticmethod
     def backward(ctx, grad_out, grad_last=None):
+        _check_guard(ctx)
         sc: _ScanCtx = ctx.sc
-        B, C_, A, D, z, dt_bias, delta = ctx.like
+        B, C_, A, D, z, dt_bias, delta, init = ctx.like
         if grad_out is None:
             grad_out = torch.zeros_like(sc.u)
-        du, ddelta, dA, dB, dC, dD, dz, dbias = _scan_backward(sc, ctx.ck, grad_out, grad_last, B, C_)
+        want_dinit = init is not None and init.requires_grad
+        res = _scan_backward(sc, ctx.ck, grad_out, grad_last, B, C_, want_dinit)
+        du, ddelta, dA, dB, dC, dD, dz, dbias = res[:8]
         return (
             du,
             ddelta.to(delta.dtype),
@@ -280,7 +354,7 @@ class _SelectiveScanFn(torch.autograd.Function):
             None if D is None else dD.to(D.dtype),
             None if z is None else dz.to(z.dtype),
             None if dt_bias is None else dbias.to(dt_bias.dtype),
-            None, None, None, None,
+            None, None, res[8].to(init.dtype) if want_dinit else None, None,
         )
 
 
@@ -300,9 +374,9 @@ def selective_scan(
 ):
     """Mamba-1 selective scan (upstream ``ssm.ops.selective_scan``, reference.py:87-194).
 
-    Extensions: ``initial_state`` ``(B, D, N)`` starts the recurrence from a given state (no
-    gradient flows into it); ``keep_state_fp32`` returns the last state in fp32 instead of
-    ``u.dtype``.
+    Extensions: ``initial_state`` ``(B, D, N)`` starts the recurrence from a given state (it
+    receives a gradient like any other input); ``keep_state_fp32`` returns the last state in
+    fp32 instead of ``u.dtype``.
     """
     res = _SelectiveScanFn.apply(u, delta, A, B, C, D, z, dt_bias, softplus, return_last_state, initial_state, keep_state_fp32)
     return res
@@ -406,10 +480,12 @@ class _StateStepFn(torch.autograd.Function):
         y = _step_forward(sc, new)
         ctx.sc, ctx.old = sc, old
         ctx.like = (state, dt, A, B, C_, D, z, dt_bias)
+        _guard(ctx, x, dt, A, B, C_, D, z, dt_bias)
         return y, new.to(state.dtype)
 
     @staticmethod
     def backward(ctx, gy, gstate):
+        _check_guard(ctx)
         sc: _StepCtx = ctx.sc
         state, dt, A, B, C_, D, z, dt_bias = ctx.like
         nb, nd, nn = sc.shape
@@ -658,10 +734,12 @@ class _ChunkScanFn(torch.autograd.Function):
         Y, _ = _chunk_forward(cc)
         ctx.cc = cc
         ctx.like = (dt, A, B, C_, D, z, initial_states)
+        _guard(ctx, X, dt, A, B, C_, D, z, initial_states)
         return Y
 
     @staticmethod
     def backward(ctx, gY):
+        _check_guard(ctx)
         cc: _ChunkCtx = ctx.cc
         dt, A, B, C_, D, z, init = ctx.like
         nb, nl, nh, npj = cc.shape
@@ -772,10 +850,12 @@ class _ConvFn(torch.autograd.Function):
         a.y = _p(y)
         _call(L.load().ssm_dw_causal_conv_fwd, a)
         ctx.cc, ctx.like = cc, (weight, bias)
+        _guard(ctx, x, weight, bias)
         return y
 
     @staticmethod
     def backward(ctx, gy):
+        _check_guard(ctx)
         cc: _ConvCtx = ctx.cc
         weight, bias = ctx.like
         dev = cc.x.device
@@ -867,15 +947,19 @@ class _NormFn(torch.autograd.Function):
         a.resout_dtype = _CODES[residual_dtype] if return_residual else 0
         _call(L.load().ssm_fused_add_norm_fwd, a)
         ctx.nc, ctx.like = nc, (weight, bias, residual)
+        ctx.res_dtype = residual_dtype
+        _guard(ctx, x, weight, bias, residual)
         if return_residual:
-            ctx.mark_non_differentiable(ro)
             return y, ro
         return y
 
     @staticmethod
-    def backward(ctx, gy, *unused):
+    def backward(ctx, gy, gro=None):
+        _check_guard(ctx)
         nc: _NormCtx = ctx.nc
         weight, bias, residual = ctx.like
+        if gy is None:
+            gy = torch.zeros_like(nc.x)
         lib = L.load()
         dev = nc.x.device
         hidden = nc.x.shape[2]
@@ -889,6 +973,11 @@ class _NormFn(torch.autograd.Function):
         nc.fill(g.fwd)
         go = _c(gy.to(nc.x.dtype))
         g.dy, g.dx, g.dresidual, g.dweight, g.dbias, g.partial = _p(go), _p(dx), _p(dres), _p(dw), _p(db), _p(partial)
+        gr = None
+        if gro is not None:  # gradient arriving through the x + residual output: added to dx and dresidual inside the kernel
+            gr = _c(gro.to(ctx.res_dtype))
+            g.fwd.resout_dtype = _CODES[ctx.res_dtype]
+            g.dresidual_out = _p(gr)
         _call(lib.ssm_fused_add_norm_bwd, g)
         return (
             dx, dw.to(weight.dtype), None if bias is None else db.to(bias.dtype),
@@ -911,8 +1000,8 @@ def fused_layer_norm(
     """Residual add fused with LayerNorm / RMSNorm (upstream ``ssm.ops.fused_layer_norm``,
     reference.py:540-609).  All arithmetic is fp32, which is what upstream does for fp32, bf16
     and fp16 inputs whatever ``residual_in_fp32`` says.  Extension: ``return_residual`` also
-    returns ``x + residual`` (fp32 when ``residual_in_fp32``, else ``x.dtype``); that second
-    output is not differentiable."""
+    returns ``x + residual`` (fp32 when ``residual_in_fp32``, else ``x.dtype``), the residual
+    stream a stack of blocks passes on; gradients flow back through both outputs."""
     rd = torch.float32 if residual_in_fp32 else x.dtype
     return _NormFn.apply(x, weight, bias, residual, is_rms, eps, prenorm, return_residual, rd)
 
@@ -982,7 +1071,9 @@ class _SsdWorkspace:
         self.softplus = int(bool(dt_softplus))
         self.nchunks = (nl + self.chunk - 1) // self.chunk
         self.ws = torch.empty(int(lib.ssm_ssd_scratch_bytes(nb, nl, nh)), dtype=torch.uint8, device=X.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=X.device)
+        self._status = _DeviceStatus.of(X.device)
+        self._status.poll()  # a wait that ran out in an earlier launch surfaces here, without a synchronisation
+        self.status = self._status.word
 
     def run(self, phase: int, initial_states: Optional[Tensor], want_y: bool):
         nb, nl, nh, npj, ng, nn = self.shape
@@ -1003,6 +1094,7 @@ class _SsdWorkspace:
         a.ws_dt, a.ws_cum, a.ws_state, a.ws_state_in = base, base + vec, base + 2 * vec, base + 2 * vec + fin
         a.status = _p(self.status)
         _call(L.load().ssm_ssd_fwd, a)
+        self._status.after_launch()
         return Y, final
 
     def shard_summary(self) -> Tensor:
@@ -1037,20 +1129,22 @@ class _SsdFn(torch.autograd.Function):
     def forward(ctx, X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states, chunk_size, check_status):
         _ssd_check(X, dt, A, B, C_, D, z, dt_bias, initial_states)
         ctx.args = (X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states)
+        _guard(ctx, X, dt, A, B, C_, D, z, dt_bias, initial_states)
         if ssd_tensor_core_supported(X, B, chunk_size):
-            Y, final, status = _ssd_tensor_core(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states, int(chunk_size))
-            if check_status and int(status.item()) != 0:
-                raise RuntimeError(f"ssd_scan: a bounded device-side wait ran out (status {int(status.item())})")
+            Y, final, _ = _ssd_tensor_core(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states, int(chunk_size))
+            if check_status:
+                ssd_check_status(X.device)
             return Y, final
         with torch.no_grad():
             return _ssd_via_scan(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states)
 
     @staticmethod
     def backward(ctx, gY, gfinal):
+        _check_guard(ctx)
         X, dt, A, B, C_, D, z, dt_bias, dt_softplus, init = ctx.args
-        leaves = [None if t is None else t.detach().requires_grad_(t.requires_grad) for t in (X, dt, A, B, C_, D, z, dt_bias)]
+        leaves = [None if t is None else t.detach().requires_grad_(t.requires_grad) for t in (X, dt, A, B, C_, D, z, dt_bias, init)]
         with torch.enable_grad():
-            Y, final = _ssd_via_scan(*leaves, dt_softplus, init)
+            Y, final = _ssd_via_scan(*leaves[:8], dt_softplus, leaves[8])
         live = [t for t in leaves if t is not None and t.requires_grad]
         outs, gouts = [Y], [gY if gY is not None else torch.zeros_like(Y)]
         if gfinal is not None:
@@ -1058,7 +1152,7 @@ class _SsdFn(torch.autograd.Function):
             gouts.append(gfinal)
         grads = iter(torch.autograd.grad(outs, live, gouts, allow_unused=True))
         res = [next(grads) if (t is not None and t.requires_grad) else None for t in leaves]
-        return (*res, None, None, None, None)
+        return (*res[:8], None, res[8], None, None)
 
 
 def ssd_scan(
@@ -1083,7 +1177,8 @@ def ssd_scan(
     on channel ``h*P+p`` with per-head ``dt`` and ``A``.  For headdim 64, d_state 128, chunk 256 and
     bf16 / fp16 operands the forward runs as chunked GEMMs on the tcgen05 tensor cores; any other
     shape or dtype, and every backward pass, goes through the selective-scan kernels on the
-    flattened channels.  ``check_status`` synchronises and raises if a device-side wait timed out.
+    flattened channels.  A bounded device-side wait that runs out (it never should) is reported by the next
+    ``ssd_scan`` call on the device, or at once by ``check_status=True`` / :func:`ssd_check_status`, which synchronise.
     """
     Y, final = _SsdFn.apply(X, dt, A, B, C, D, z, dt_bias, dt_softplus, initial_states, chunk_size, check_status)
     return (Y, final) if return_final_states else Y
@@ -1098,5 +1193,6 @@ __all__ = [
     "dw_causal_conv_update",
     "fused_layer_norm",
     "ssd_scan",
+    "ssd_check_status",
     "ssd_tensor_core_supported",
 ]

@@ -80,6 +80,8 @@ def ssd_scan_sharded(X, dt, A, B, C, chunk_size=256, D=None, z=None, dt_bias=Non
 
     if not ops.ssd_tensor_core_supported(X, B, chunk_size):
         raise ValueError("ssd_scan_sharded needs the tensor-core shape (headdim 64, d_state 128, chunk 256, bf16/fp16)")
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (X, dt, A, B, C, D, z, dt_bias, initial_states)):
+        raise RuntimeError("ssd_scan_sharded is forward-only: call it under torch.no_grad() (its outputs carry no autograd history)")
     ops._ssd_check(X, dt, A, B, C, D, z, dt_bias, None)
     w = ops._SsdWorkspace(X, dt, A, B, C, D, z, dt_bias, dt_softplus, chunk_size)
 

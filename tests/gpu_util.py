@@ -1,11 +1,24 @@
-"""Helpers shared by the GPU parity tests."""
+"""Helpers shared by the GPU parity tests.
+
+Comparison bars.  Element-wise tensors (outputs, final states, gradients that have the shape
+of an activation) are held to the stated bars as they are: fp32 ``rtol 1e-4 / atol 1e-5``;
+bf16 / fp16 I/O ``rtol 2e-2`` against the fp32 computation on the same rounded inputs, with a
+small absolute term for values that cancel to nearly zero.  Only contractions over thousands
+of terms -- parameter gradients summed over batch and time (``dA, dB, dC, dD, ddt_bias``, conv
+and norm ``dweight / dbias``) and the outputs of the tensor-core SSD path, each a 256-term
+bf16 product sum -- get the absolute term scaled by the magnitude of the expected tensor
+(``reduced=True``): their rounding error grows with the size of the terms, not of the result.
+"""
 
 from __future__ import annotations
 
 import torch
 
 FP32_TOL = dict(rtol=1e-4, atol=1e-5)  # fp32 bar for outputs, final states and gradients
-HALF_TOL = dict(rtol=2e-2, atol=2e-2)  # bf16 / fp16 I/O against the fp32 computation
+HALF_TOL = dict(rtol=2e-2, atol=2e-3)  # bf16 / fp16 I/O against the fp32 computation
+
+# names of operator arguments whose gradient is a sum over batch and / or time
+REDUCED = frozenset({"A", "B", "C", "D", "dt_bias", "weight", "bias", "A_log"})
 
 
 def dev(t):
@@ -25,14 +38,16 @@ def leaf(t, grad=True):
     return t
 
 
-def close(got, want, rtol, atol, what=""):
-    """allclose with the absolute term scaled by the magnitude of the expected tensor, so that
-    reductions over thousands of terms are judged relative to their own scale."""
+def close(got, want, rtol, atol, what="", reduced=False):
+    """``|got - want| <= atol + rtol * |want|`` element by element.  ``reduced=True`` scales the
+    absolute term by ``max(1, max|want|)`` (contractions over many terms; see the module text)."""
     got = got.detach().float().cpu()
     want = want.detach().float().cpu()
     assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
     ok = torch.isfinite(want)
-    scale = max(1.0, float(want[ok].abs().max())) if ok.any() else 1.0
+    scale = 1.0
+    if reduced and ok.any():
+        scale = max(1.0, float(want[ok].abs().max()))
     err = (got[ok] - want[ok]).abs()
     bound = atol * scale + rtol * want[ok].abs()
     bad = err > bound

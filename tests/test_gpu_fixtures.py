@@ -1,5 +1,8 @@
 """GPU parity against the golden fixtures (upstream's own vectors and recorded runs of
-upstream's Python operators): outputs, final states and gradients, through the C ABI."""
+upstream's Python operators): outputs, final states and gradients, through the C ABI.
+
+Vectors that carry their own bar (``rtol`` in the case options: upstream's stored known-answer files, whose bars are
+tighter than the fp32 bar used elsewhere) are judged with the absolute term scaled by the tensor's magnitude."""
 
 from __future__ import annotations
 
@@ -7,7 +10,7 @@ import pytest
 import torch
 
 from tests.fixtures import cases, tol
-from tests.gpu_util import close, leaf
+from tests.gpu_util import REDUCED, close, leaf
 
 pytestmark = pytest.mark.gpu
 
@@ -26,7 +29,7 @@ def _grads(case, outs, weights, leaves):
     got = torch.autograd.grad(total, list(live.values()), allow_unused=True)
     for (k, _), g in zip(live.items(), got):
         assert g is not None, f"no gradient for {k}"
-        close(g, case.grads[k], **tol(case, grad=True), what=f"{case.name} d{k}")
+        close(g, case.grads[k], **tol(case, grad=True), what=f"{case.name} d{k}", reduced=k in REDUCED or "rtol" in case.opts)
 
 
 @pytest.mark.parametrize("case", _all("scan"))
@@ -37,9 +40,9 @@ def test_selective_scan(case):
     y, last = ops.selective_scan(i["u"], i["delta"], i["A"], i["B"], i["C"], D=i.get("D"), z=i.get("z"),
                                  dt_bias=i.get("dt_bias"), softplus=case.opts["softplus"], return_last_state=True)
     assert y.dtype == i["u"].dtype and last.dtype == i["u"].dtype
-    close(y, case.outs["out"], **tol(case), what=f"{case.name} out")
+    close(y, case.outs["out"], **tol(case), what=f"{case.name} out", reduced="rtol" in case.opts)
     if "last_state" in case.outs:
-        close(last, case.outs["last_state"], **tol(case), what=f"{case.name} last_state")
+        close(last, case.outs["last_state"], **tol(case), what=f"{case.name} last_state", reduced="rtol" in case.opts)
     if "grad_out" in case.ins:
         _grads(case, (y, last), (case.ins["grad_out"], case.ins["grad_last_state"]), i)
     else:
@@ -53,8 +56,8 @@ def test_selective_state_step(case):
     i = {k: leaf(v, grad=False) for k, v in case.ins.items()}
     y = ops.selective_state_step(i["state"], i["x"], i["dt"], i["A"], i["B"], i["C"], D=i.get("D"), z=i.get("z"),
                                  dt_bias=i.get("dt_bias"), softplus=case.opts["softplus"])
-    close(y, case.outs["y"], **tol(case), what=f"{case.name} y")
-    close(i["state"], case.outs["state"], **tol(case), what=f"{case.name} state")
+    close(y, case.outs["y"], **tol(case), what=f"{case.name} y", reduced="rtol" in case.opts)
+    close(i["state"], case.outs["state"], **tol(case), what=f"{case.name} state", reduced="rtol" in case.opts)
 
 
 @pytest.mark.parametrize("case", _all("chunk"))
@@ -69,7 +72,7 @@ def test_ssd_chunk_scan(case):
         meta = {"seq_lens": i["seq_lens"]}
     Y = ops.ssd_chunk_scan(i["X"], i["dt"], i["A"], i["B"], i["C"], case.opts["chunk_size"], D=i.get("D"), z=i.get("z"),
                            seq_meta=meta, initial_states=i.get("initial_states"))
-    close(Y, case.outs["Y"], **tol(case), what=f"{case.name} Y")
+    close(Y, case.outs["Y"], **tol(case), what=f"{case.name} Y", reduced="rtol" in case.opts)
     if "grad_out" in case.ins:
         _grads(case, (Y,), (case.ins["grad_out"],), i)
 
@@ -81,7 +84,7 @@ def test_dw_causal_conv(case):
     i = {k: leaf(v) for k, v in case.ins.items()}
     y = ops.dw_causal_conv(i["x"], i["weight"], bias=i.get("bias"), activation=case.opts["activation"])
     assert y.shape == i["x"].shape and y.dtype == i["x"].dtype
-    close(y, case.outs["y"], **tol(case), what=f"{case.name} y")
+    close(y, case.outs["y"], **tol(case), what=f"{case.name} y", reduced="rtol" in case.opts)
     w = case.ins["grad_out"] if "grad_out" in case.ins else torch.ones_like(y)
     _grads(case, (y,), (w,), i)
 
@@ -95,9 +98,9 @@ def test_fused_layer_norm(case):
     y, res = ops.fused_layer_norm(i["x"], i["weight"], i.get("bias"), residual=i.get("residual"), is_rms=o["is_rms"],
                                   eps=o["eps"], prenorm=o["prenorm"], residual_in_fp32=o.get("residual_in_fp32", True),
                                   return_residual=True)
-    close(y, case.outs["y"], **tol(case), what=f"{case.name} y")
+    close(y, case.outs["y"], **tol(case), what=f"{case.name} y", reduced="rtol" in case.opts)
     if "residual_out" in case.outs:
-        close(res, case.outs["residual_out"], **tol(case), what=f"{case.name} residual_out")
+        close(res, case.outs["residual_out"], **tol(case), what=f"{case.name} residual_out", reduced="rtol" in case.opts)
     w = case.ins["grad_out"] if "grad_out" in case.ins else torch.ones_like(y)
     _grads(case, (y,), (w,), i)
 
@@ -113,9 +116,9 @@ def test_ssd_scan(case):
                           return_final_states=True)
     heads = o.get("heads")
     if heads is not None:  # mamba-ssm vector: only the listed heads follow the exact recurrence
-        close(Y[:, :, heads], case.outs["y"][:, :, heads], **tol(case), what=f"{case.name} y")
-        close(fin[:, heads], case.outs["final_states"][:, heads], **tol(case), what=f"{case.name} final")
+        close(Y[:, :, heads], case.outs["y"][:, :, heads], **tol(case), what=f"{case.name} y", reduced="rtol" in case.opts)
+        close(fin[:, heads], case.outs["final_states"][:, heads], **tol(case), what=f"{case.name} final", reduced="rtol" in case.opts)
         return
-    close(Y, case.outs["y"], **tol(case), what=f"{case.name} y")
-    close(fin, case.outs["final_states"], **tol(case), what=f"{case.name} final")
+    close(Y, case.outs["y"], **tol(case), what=f"{case.name} y", reduced="rtol" in case.opts)
+    close(fin, case.outs["final_states"], **tol(case), what=f"{case.name} final", reduced="rtol" in case.opts)
     _grads(case, (Y, fin), (case.ins["grad_out"], case.ins["grad_final_states"]), i)

@@ -11,6 +11,9 @@ from tests.gpu_util import FP32_TOL, HALF_TOL, close
 
 pytestmark = pytest.mark.gpu
 
+# every output element of the tensor-core path is a 256-term product sum of bf16-rounded operands
+SSD_TOL = dict(rtol=2e-2, atol=2e-2)
+
 
 def _inputs(nb, nl, nh, ng, dtype, seed, with_init=True):
     gen = torch.Generator().manual_seed(seed)
@@ -52,8 +55,8 @@ def test_tensor_core_ssd_matches_oracle(nb, nl, nh, ng, dtype):
     Yg, Sg = ops.ssd_scan(g["X"], g["dt"], g["A"], g["B"], g["C"], 256, D=g["D"], z=g["z"], dt_bias=g["dt_bias"], dt_softplus=True,
                           initial_states=g["initial_states"], return_final_states=True, check_status=True)
     assert Yg.dtype == dtype and Sg.dtype == torch.float32
-    close(Yg, Yo, **HALF_TOL, what="Y")
-    close(Sg, So, **HALF_TOL, what="final state")
+    close(Yg, Yo, **SSD_TOL, what="Y", reduced=True)
+    close(Sg, So, **SSD_TOL, what="final state", reduced=True)
 
 
 def test_tensor_core_ssd_without_optionals_and_matrix_D():
@@ -65,8 +68,8 @@ def test_tensor_core_ssd_without_optionals_and_matrix_D():
     Yo, So = orc.ssd_scan(t["X"], dtp, t["A"], t["B"], t["C"], 256, D=Dm, return_final_states=True)
     Yg, Sg = ops.ssd_scan(t["X"].cuda(), dtp.cuda(), t["A"].cuda(), t["B"].cuda(), t["C"].cuda(), 256, D=Dm.cuda(),
                           return_final_states=True, check_status=True)
-    close(Yg, Yo, **HALF_TOL, what="Y")
-    close(Sg, So, **HALF_TOL, what="final state")
+    close(Yg, Yo, **SSD_TOL, what="Y", reduced=True)
+    close(Sg, So, **SSD_TOL, what="final state", reduced=True)
 
 
 def test_tensor_core_ssd_strong_decay_takes_the_exact_mask_form():
@@ -81,8 +84,8 @@ def test_tensor_core_ssd_strong_decay_takes_the_exact_mask_form():
     Yg, Sg = ops.ssd_scan(t["X"].cuda(), dtp.cuda(), A.cuda(), t["B"].cuda(), t["C"].cuda(), 256, D=t["D"].cuda(), z=t["z"].cuda(),
                           initial_states=t["initial_states"].cuda(), return_final_states=True, check_status=True)
     assert torch.isfinite(Yg.float()).all() and torch.isfinite(Sg).all()
-    close(Yg, Yo, **HALF_TOL, what="Y")
-    close(Sg, So, **HALF_TOL, what="final state")
+    close(Yg, Yo, **SSD_TOL, what="Y", reduced=True)
+    close(Sg, So, **SSD_TOL, what="final state", reduced=True)
 
 
 def test_tensor_core_ssd_agrees_with_scan_kernel_path_and_has_gradients():
@@ -93,16 +96,16 @@ def test_tensor_core_ssd_agrees_with_scan_kernel_path_and_has_gradients():
     Y1, S1 = ops.ssd_scan(t["X"], t["dt"], t["A"], t["B"], t["C"], 256, D=t["D"], z=t["z"], dt_bias=t["dt_bias"], dt_softplus=True,
                           initial_states=t["initial_states"], return_final_states=True, check_status=True)
     Y2, S2 = ops._ssd_via_scan(t["X"], t["dt"], t["A"], t["B"], t["C"], t["D"], t["z"], t["dt_bias"], True, t["initial_states"])
-    close(Y1, Y2, **HALF_TOL, what="Y")
-    close(S1, S2, **HALF_TOL, what="final state")
+    close(Y1, Y2, **SSD_TOL, what="Y", reduced=True)
+    close(S1, S2, **SSD_TOL, what="final state", reduced=True)
     # chaining: second half started from the first half's final state
     h = 512
     Ya, Sa = ops.ssd_scan(t["X"][:, :h], t["dt"][:, :h], t["A"], t["B"][:, :h], t["C"][:, :h], 256, D=t["D"], z=t["z"][:, :h],
                           dt_bias=t["dt_bias"], dt_softplus=True, initial_states=t["initial_states"], return_final_states=True)
     Yb, Sb = ops.ssd_scan(t["X"][:, h:], t["dt"][:, h:], t["A"], t["B"][:, h:], t["C"][:, h:], 256, D=t["D"], z=t["z"][:, h:],
                           dt_bias=t["dt_bias"], dt_softplus=True, initial_states=Sa, return_final_states=True)
-    close(torch.cat([Ya, Yb], 1), Y1, **HALF_TOL, what="chained Y")
-    close(Sb, S1, **HALF_TOL, what="chained state")
+    close(torch.cat([Ya, Yb], 1), Y1, **SSD_TOL, what="chained Y", reduced=True)
+    close(Sb, S1, **SSD_TOL, what="chained state", reduced=True)
     # gradients flow (through the scan-kernel backward)
     X = t["X"].clone().requires_grad_(True)
     A = t["A"].clone().requires_grad_(True)
@@ -133,8 +136,8 @@ def test_two_phase_shards_reproduce_the_unsharded_scan():
     for r, (w, _, _) in enumerate(shards):
         s_in = seqpar.fold_incoming_state(states, logp, r, t["initial_states"])
         outs.append(w.run(2, s_in, True))
-    close(torch.cat([outs[0][0], outs[1][0]], 1), Yf, **HALF_TOL, what="Y")
-    close(outs[1][1], Sf, **HALF_TOL, what="final state")
+    close(torch.cat([outs[0][0], outs[1][0]], 1), Yf, **SSD_TOL, what="Y", reduced=True)
+    close(outs[1][1], Sf, **SSD_TOL, what="final state", reduced=True)
     assert int(shards[0][0].status.item()) == 0 and int(shards[1][0].status.item()) == 0
 
 

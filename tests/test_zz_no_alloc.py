@@ -76,7 +76,7 @@ def test_noalloc_backward_matches_regular_entry_point(shape, hidden, dtype, rdty
             if w_ is None:
                 assert g_ is None
                 continue
-            close(g_, w_, **(FP32_TOL if name in ("dweight", "dbias") else tol), what=f"call {call} {name}")
+            close(g_, w_, **(FP32_TOL if name in ("dweight", "dbias") else tol), what=f"call {call} {name}", reduced=name in ("dweight", "dbias"))
         assert torch.equal(got[0], want[0]), "dx must be bit-identical"
 
 
