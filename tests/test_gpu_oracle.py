@@ -323,43 +323,6 @@ def test_norm_matches_oracle(nb, nl, nd, dtype, rdtype, prenorm, is_rms):
     _grad_check((yg,), (yo,), (wy,), lg, lo, tol, "norm")
 
 
-def test_backend_object_serves_upstream_calling_convention():
-    """The ten callables upstream's facade invokes on its CUDA extension module."""
-    from ssm_b200.backend import Backend
-
-    be = Backend()
-    gen = torch.Generator().manual_seed(2)
-    nb, nd, nl, nn = 2, 6, 20, 4
-    u, delta = _rand(gen, nb, nd, nl), _rand(gen, nb, nd, nl, scale=0.5)
-    A, Bm, Cm = -torch.exp(_rand(gen, nd, nn, scale=0.5)), _rand(gen, nd, nn), _rand(gen, nd, nn)
-    D, z, bias = _rand(gen, nd), _rand(gen, nb, nd, nl), _rand(gen, nd, scale=0.5)
-    c = lambda t: t.cuda()  # noqa: E731
-    out, last, cache = be.selective_scan(c(u), c(delta), c(A), c(Bm), c(Cm), c(D), c(z), c(bias), True, True)
-    lo = {k: v.clone().requires_grad_(True) for k, v in dict(u=u, delta=delta, A=A, B=Bm, C=Cm, D=D, z=z, dt_bias=bias).items()}
-    yo, so = orc.selective_scan(lo["u"], lo["delta"], lo["A"], lo["B"], lo["C"], D=lo["D"], z=lo["z"], dt_bias=lo["dt_bias"],
-                                softplus=True, return_last_state=True)
-    close(out, yo, **FP32_TOL, what="out")
-    close(last, so, **FP32_TOL, what="last")
-    go, gl = _rand(gen, *yo.shape), _rand(gen, *so.shape)
-    grads = be.selective_scan_backward(c(go), c(gl), c(u), c(delta), c(A), c(Bm), c(Cm), c(D), c(z), c(bias), True, out, cache)
-    want = torch.autograd.grad((yo * go).sum() + (so * gl).sum(), list(lo.values()))
-    assert len(grads) == 8
-    for g, w_, k in zip(grads, want, lo):
-        close(g, w_, **FP32_TOL, what=f"d{k}", reduced=k in REDUCED)
-    out2, last2, _ = be.selective_scan(c(u), c(delta), c(A), c(Bm), c(Cm))
-    assert last2.numel() == 0 and out2.shape == u.shape
-    x = _rand(gen, 2, 6, 10)
-    wt = torch.rand(6, 4, generator=gen) - 0.5
-    y = be.dw_causal_conv(c(x), c(wt), None, "silu")
-    dx, dw, db = be.dw_causal_conv_backward(torch.ones_like(y), c(x), c(wt), None, "silu")
-    assert db is None and dx.shape == x.shape and dw.shape == wt.shape
-    xn, wn = _rand(gen, 2, 3, 16), _rand(gen, 16)
-    yn = be.fused_layer_norm(c(xn), c(wn), None, None, True, 1e-5, True, True)
-    close(yn, orc.fused_layer_norm(xn, wn, None, is_rms=True), **FP32_TOL, what="rms")
-    g4 = be.fused_layer_norm_backward(torch.ones_like(yn), c(xn), c(wn), None, None, True, 1e-5, True, True)
-    assert len(g4) == 4 and g4[2].numel() == 0 and g4[3].numel() == 0
-
-
 def test_channel_major_row_layout_matches_dense():
     """(D, B, L) buffers viewed as (B, D, L) are addressed in place by the scan and the conv (forward
     and backward) and give the dense-layout results."""
