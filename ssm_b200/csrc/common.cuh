@@ -131,6 +131,13 @@ __device__ __forceinline__ float softplus_fast(float x) {
   const float l = t < 0.0625f ? series : lg2_approx(1.f + t) * kLn2;
   return fmaxf(x, 0.f) + l;
 }
+// softplus for kernels whose inputs and outputs are 16-bit: log2(1 + 2^(x log2 e)) ln 2 on the special-function unit, no
+// series for small arguments.  The absolute error is that of forming 1 + t in fp32 (6e-8), i.e. a relative error of
+// 6e-8 / softplus(x): below the spacing of bf16 / fp16 values down to softplus(x) = 1e-5.
+__device__ __forceinline__ float softplus_half_io(float x) {
+  const float t = ex2_approx(fminf(x, 88.f) * kLog2e);
+  return x > 20.f ? x : lg2_approx(1.f + t) * kLn2;
+}
 // 1 - exp(-x) for x >= 0 without cancellation for small x (it is sigmoid(pre) when
 // x = softplus(pre), i.e. the derivative of softplus).
 __device__ __forceinline__ float one_minus_exp_neg(float x) {

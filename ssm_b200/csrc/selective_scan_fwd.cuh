@@ -10,6 +10,7 @@
 #pragma once
 
 #include "scan_common.cuh"
+#include "selective_scan_fwd_tiles.cuh"
 
 namespace ssmb {
 
@@ -280,6 +281,7 @@ static int fwd_lpr(int n) { return n <= 4 ? 1 : n <= 8 ? 2 : n <= 16 ? 4 : n <= 
 template <typename T>
 int dispatch_fwd(const ssm_scan_fwd_args& a, const ScanFlags& fl, cudaStream_t st) {
   const int n = a.nstate;
+  if (fwd_tiles_ok(a, fl)) return dispatch_fwd_tiles<T>(a, fl, st);  // selective_scan_fwd_tiles.cuh; the general kernel below otherwise
   switch (fwd_lpr(n)) {
     case 1: return launch_fwd<T, 4, 1>(a, fl, st);
     case 2: return launch_fwd<T, 4, 2>(a, fl, st);
