@@ -25,12 +25,11 @@ import torch
 from torch import Tensor, nn
 
 
-def mamba1_block_forward(ops: Any, w: dict, cfg: dict, hidden: Tensor, residual: Optional[Tensor]):
-    """hidden (B, L, d_model) activations, residual (B, L, d_model) fp32 stream or None
-    -> (normed, new_residual): new_residual = residual + mixer(hidden); normed = RMSNorm(new_residual).
+def mamba1_mixer_forward(ops: Any, w: dict, cfg: dict, hidden: Tensor) -> Tensor:
+    """The Mamba-1 mixer alone: hidden (B, L, d_model) -> (B, L, d_model), before any residual add or norm.
 
     ``w``: in_x, in_z (d_inner, d_model); conv_w (d_inner, K), conv_b; x_proj (R + 2N, d_inner);
-    dt_proj (d_inner, R); dt_bias, A (d_inner, N), D (fp32); out_proj (d_model, d_inner); norm_w.
+    dt_proj (d_inner, R); dt_bias, A (d_inner, N), D (fp32); out_proj (d_model, d_inner).
     """
     n, r = cfg["d_state"], cfg["dt_rank"]
     nb, nl, dm = hidden.shape
@@ -51,9 +50,31 @@ def mamba1_block_forward(ops: Any, w: dict, cfg: dict, hidden: Tensor, residual:
     Cg = Cm.view(n, nb, nl).permute(1, 0, 2).unsqueeze(1)
     y = ops.selective_scan(u, delta, w["A"], Bg, Cg, D=w["D"], z=z, dt_bias=w["dt_bias"], softplus=True)
     y2 = y.permute(1, 0, 2).reshape(di, nb * nl)
-    out = torch.matmul(y2.t(), w["out_proj"].t()).view(nb, nl, dm)     # (B, L, d_model)
+    return torch.matmul(y2.t(), w["out_proj"].t()).view(nb, nl, dm)     # (B, L, d_model)
+
+
+def mamba1_block_forward(ops: Any, w: dict, cfg: dict, hidden: Tensor, residual: Optional[Tensor]):
+    """hidden (B, L, d_model) activations, residual (B, L, d_model) fp32 stream or None
+    -> (normed, new_residual): new_residual = residual + mixer(hidden); normed = RMSNorm(new_residual).
+
+    ``w``: the mixer weights of :func:`mamba1_mixer_forward` plus norm_w.
+    """
+    out = mamba1_mixer_forward(ops, w, cfg, hidden)
     return ops.fused_layer_norm(out, w["norm_w"], None, residual=residual, is_rms=True, eps=cfg.get("eps", 1e-5), prenorm=True,
                                 residual_in_fp32=True, return_residual=True)
+
+
+def mamba1_mixer_step(ops: Any, w: dict, cfg: dict, tok: Tensor, conv_state: Tensor, ssm_state: Tensor) -> Tensor:
+    """One decode token through the Mamba-1 mixer: tok (B, d_model) -> (B, d_model); ``conv_state (B, d_inner, K)`` and
+    ``ssm_state (B, d_inner, N)`` (both fp32) are updated in place (reference step: modules/mamba1.py:324-385)."""
+    n, r = cfg["d_state"], cfg["dt_rank"]
+    x, z = tok @ w["in_x"].t(), tok @ w["in_z"].t()
+    u = ops.dw_causal_conv_update(conv_state, x, w["conv_w"], w["conv_b"], "silu")
+    xd = u @ w["x_proj"].t()
+    delta = xd[:, :r] @ w["dt_proj"].t()
+    y = ops.selective_state_step(ssm_state, u, delta, w["A"], xd[:, r:r + n].unsqueeze(1), xd[:, r + n:].unsqueeze(1),
+                                 D=w["D"], z=z, dt_bias=w["dt_bias"], softplus=True)
+    return y @ w["out_proj"].t()
 
 
 class Mamba1Block(nn.Module):
@@ -112,6 +133,14 @@ class Mamba1Block(nn.Module):
         cfg = dict(d_state=self.d_state, dt_rank=self.dt_rank, eps=self.eps)
         return mamba1_block_forward(self._namespace(), self._weights(), cfg, hidden, residual)
 
+    def mixer_forward(self, u: Tensor) -> Tensor:
+        """The mixer alone (no residual add, no norm): u (B, L, d_model) -> (B, L, d_model)."""
+        return mamba1_mixer_forward(self._namespace(), self._weights(), dict(d_state=self.d_state, dt_rank=self.dt_rank), u)
+
+    def mixer_step(self, tok: Tensor, cache) -> Tensor:
+        """The mixer alone on one token: tok (B, d_model) -> (B, d_model); ``cache`` from `allocate_inference_cache`."""
+        return mamba1_mixer_step(self._namespace(), self._weights(), dict(d_state=self.d_state, dt_rank=self.dt_rank), tok, cache[0], cache[1])
+
     def allocate_inference_cache(self, batch_size: int, dtype: Optional[torch.dtype] = None):
         """(conv_state (B, d_inner, K), ssm_state (B, d_inner, N)), both fp32 and zero-filled."""
         del dtype  # both states are kept in fp32 whatever the activation dtype
@@ -124,15 +153,8 @@ class Mamba1Block(nn.Module):
         if hidden.ndim != 3 or hidden.shape[1] != 1:
             raise ValueError("step expects inputs of shape (B, 1, d_model)")
         ops = self._namespace()
-        n, r = self.d_state, self.dt_rank
-        tok = hidden[:, 0]
-        x, z = tok @ self.in_x.t(), tok @ self.in_z.t()
-        u = ops.dw_causal_conv_update(conv_state, x, self.conv_w, self.conv_b, "silu")
-        xd = u @ self.x_proj.t()
-        delta = xd[:, :r] @ self.dt_proj.t()
-        y = ops.selective_state_step(ssm_state, u, delta, -torch.exp(self.A_log), xd[:, r:r + n].unsqueeze(1), xd[:, r + n:].unsqueeze(1),
-                                     D=self.D, z=z, dt_bias=self.dt_bias, softplus=True)
-        out = (y @ self.out_proj.t()).unsqueeze(1)
+        cfg = dict(d_state=self.d_state, dt_rank=self.dt_rank)
+        out = mamba1_mixer_step(ops, self._weights(), cfg, hidden[:, 0], conv_state, ssm_state).unsqueeze(1)
         res1 = None if residual is None else residual
         return ops.fused_layer_norm(out, self.norm_w, None, residual=res1, is_rms=True, eps=self.eps, prenorm=True,
                                     residual_in_fp32=True, return_residual=True)
@@ -150,11 +172,17 @@ def mamba2_block_forward(ops: Any, w: dict, cfg: dict, hidden: Tensor, residual:
     K-1 tokens go to the next rank and the chunk state is handed over (`ssm_b200.seqpar`), CUDA operators only.
     ``cfg``: heads, headdim, d_state, groups, chunk_size, eps.
     """
-    nb, nl, dm = hidden.shape
-    nh, hp, n, g = cfg["heads"], cfg["headdim"], cfg["d_state"], cfg["groups"]
     eps = cfg.get("eps", 1e-5)
     u, residual = ops.fused_layer_norm(hidden, w["pre_norm_w"], None, residual=residual, is_rms=True, eps=eps, prenorm=True,
                                        residual_in_fp32=True, return_residual=True)
+    return mamba2_mixer_forward(ops, w, cfg, u, group=group, sharded=sharded), residual
+
+
+def mamba2_mixer_forward(ops: Any, w: dict, cfg: dict, u: Tensor, group=None, sharded: bool = False) -> Tensor:
+    """The Mamba-2 mixer alone on normed activations u (B, L, d_model) -> (B, L, d_model); see `mamba2_block_forward`."""
+    nb, nl, dm = u.shape
+    nh, hp, n, g = cfg["heads"], cfg["headdim"], cfg["d_state"], cfg["groups"]
+    eps = cfg.get("eps", 1e-5)
     u2 = u.reshape(nb * nl, dm)
 
     def proj(name):
@@ -186,8 +214,31 @@ def mamba2_block_forward(ops: Any, w: dict, cfg: dict, hidden: Tensor, residual:
     else:
         y = ops.ssd_scan(x, dt, A, Bm, Cm, cfg.get("chunk_size", 256), D=w["D"], z=z, dt_bias=w["dt_bias"], dt_softplus=True)
     y = ops.fused_layer_norm(y.reshape(nb, nl, nh * hp), w["norm_w"], None, is_rms=True, eps=eps)
-    out = torch.matmul(y.reshape(nb * nl, nh * hp), w["out_proj"].t()).view(nb, nl, dm)
-    return out, residual
+    return torch.matmul(y.reshape(nb * nl, nh * hp), w["out_proj"].t()).view(nb, nl, dm)
+
+
+def mamba2_mixer_step(ops: Any, w: dict, cfg: dict, tok: Tensor, conv_states: tuple, ssm_state: Tensor) -> Tensor:
+    """One decode token through the Mamba-2 mixer: tok (B, d_model), normed -> (B, d_model).  ``conv_states``: the rolling
+    windows of the x, B and C convolutions ((B, C_i, K) fp32 each); ``ssm_state (B, H, P, N)`` fp32; all updated in place."""
+    nb = tok.shape[0]
+    nh, hp, n, g = cfg["heads"], cfg["headdim"], cfg["d_state"], cfg["groups"]
+    eps = cfg.get("eps", 1e-5)
+    z = tok @ w["in_z"].t()
+    x = ops.dw_causal_conv_update(conv_states[0], tok @ w["in_x"].t(), w["conv_x"], w["conv_x_b"], "silu")
+    Bm = ops.dw_causal_conv_update(conv_states[1], tok @ w["in_B"].t(), w["conv_B"], w["conv_B_b"], "silu").view(nb, g, n)
+    Cm = ops.dw_causal_conv_update(conv_states[2], tok @ w["in_C"].t(), w["conv_C"], w["conv_C_b"], "silu").view(nb, g, n)
+    dt = tok @ w["in_dt"].t()
+    A = -torch.exp(w["A_log"])
+    if hasattr(ops, "selective_state_step_heads"):
+        y = ops.selective_state_step_heads(ssm_state, x.view(nb, nh, hp), dt, A, Bm, Cm, D=w["D"], z=z.view(nb, nh, hp),
+                                           dt_bias=w["dt_bias"], softplus=True).reshape(nb, nh * hp)
+    else:  # operator namespaces without the per-head form (the CPU oracle): the same step on the flattened channels
+        flat = ssm_state.view(nb, nh * hp, n)
+        rep = lambda v: v[:, None].expand(nh, hp).reshape(-1)  # noqa: E731
+        y = ops.selective_state_step(flat, x, dt.repeat_interleave(hp, dim=1), A[:, None, None].expand(nh, hp, n).reshape(nh * hp, n), Bm, Cm,
+                                     D=rep(w["D"]), z=z, dt_bias=rep(w["dt_bias"]), softplus=True)
+    y = ops.fused_layer_norm(y.view(nb, 1, nh * hp), w["norm_w"], None, is_rms=True, eps=eps)
+    return y.view(nb, nh * hp) @ w["out_proj"].t()
 
 
 class Mamba2Block(nn.Module):
@@ -228,12 +279,34 @@ class Mamba2Block(nn.Module):
         self.norm_w = nn.Parameter(torch.ones(d_inner, **kw))
         self.out_proj = lin(d_model, d_inner)
 
+    def _namespace(self):
+        if self._ops is not None:
+            return self._ops
+        from . import ops  # the CUDA operators; raises if the library has not been built
+
+        return ops
+
+    def _cfg(self) -> dict:
+        return dict(heads=self.heads, headdim=self.headdim, d_state=self.d_state, groups=self.ngroups, chunk_size=self.chunk_size, eps=self.eps)
+
     def forward(self, hidden: Tensor, residual: Optional[Tensor] = None, sharded: bool = False, group=None):
         if hidden.ndim != 3 or hidden.shape[-1] != self.d_model:
             raise ValueError("hidden_states must have shape (B, L, d_model).")
-        ops = self._ops
-        if ops is None:
-            from . import ops  # the CUDA operators; raises if the library has not been built
         w = {k: v for k, v in self.named_parameters()}
-        cfg = dict(heads=self.heads, headdim=self.headdim, d_state=self.d_state, groups=self.ngroups, chunk_size=self.chunk_size, eps=self.eps)
-        return mamba2_block_forward(ops, w, cfg, hidden, residual, group=group, sharded=sharded)
+        return mamba2_block_forward(self._namespace(), w, self._cfg(), hidden, residual, group=group, sharded=sharded)
+
+    def mixer_forward(self, u: Tensor, sharded: bool = False, group=None) -> Tensor:
+        """The mixer alone on normed activations: u (B, L, d_model) -> (B, L, d_model)."""
+        return mamba2_mixer_forward(self._namespace(), {k: v for k, v in self.named_parameters()}, self._cfg(), u, group=group, sharded=sharded)
+
+    def allocate_inference_cache(self, batch_size: int, dtype: Optional[torch.dtype] = None):
+        """((conv windows of x, B, C: (B, C_i, K)), ssm_state (B, H, P, N)), all fp32 and zero-filled."""
+        del dtype
+        dev = self.in_x.device
+        gn = self.ngroups * self.d_state
+        z = lambda c: torch.zeros(batch_size, c, self.d_conv, device=dev, dtype=torch.float32)  # noqa: E731
+        return ((z(self.d_inner), z(gn), z(gn)), torch.zeros(batch_size, self.heads, self.headdim, self.d_state, device=dev, dtype=torch.float32))
+
+    def mixer_step(self, tok: Tensor, cache) -> Tensor:
+        """The mixer alone on one normed token: tok (B, d_model) -> (B, d_model); ``cache`` from `allocate_inference_cache`."""
+        return mamba2_mixer_step(self._namespace(), {k: v for k, v in self.named_parameters()}, self._cfg(), tok, cache[0], cache[1])
