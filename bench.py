@@ -120,6 +120,22 @@ def time_cuda(fn, steps, warmup=3):
     return e0.elapsed_time(e1) / steps
 
 
+def graph_time(fn, reps=4, iters=10):
+    """Milliseconds per call of `fn` when `reps` calls are captured into one CUDA graph and replayed: device time only, none of
+    the host-side launch work that an eager loop over a short kernel would measure."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(2):
+            fn(i)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(reps):
+            fn(i)
+    return time_cuda(graph.replay, iters, 2) / reps
+
+
 class CallTimer:
     """CUDA-event timing and counting of selected host entry points inside a timed region (on the launching stream)."""
 
@@ -428,15 +444,13 @@ def bench_prefill_scan(iters=100):
                  B=torch.randn(nb, 1, nn, nl, device=dev), C=torch.randn(nb, 1, nn, nl, device=dev), z=torch.randn(nb, nd, nl, device=dev))
             for _ in range(nsets)]
     A, D = -torch.exp(torch.randn(nd, nn, device=dev) * 0.5), torch.randn(nd, device=dev)
-    it = [0]
 
     @torch.no_grad()
-    def step():
-        s = sets[it[0] % nsets]
-        it[0] += 1
+    def step(i):
+        s = sets[i % nsets]
         return ops.selective_scan(s["u"], s["delta"], A, s["B"], s["C"], D=D, z=s["z"], softplus=True, return_last_state=True)
 
-    ms = time_cuda(step, iters, 10)
+    ms = graph_time(step, reps=nsets, iters=max(2, iters // nsets))  # device time: the kernel is shorter than its eager host call
     by = 3 * nb * nd * nl * 4 + 2 * nb * nn * nl * 4 + nd * nn * 4 + nd * 4 + nb * nd * nl * 4 + nb * nd * nn * 4
     return {"ms": ms, "bytes": by}
 
@@ -495,6 +509,49 @@ def bench_mamba1_block(batch=8, steps=10, warmup=3, timer=None):
     if own:
         timer.restore()
     return res
+
+
+def bench_conv_norm():
+    """The depthwise causal conv (channel-major (8, 1536, 4096) bf16 rows, width 4, SiLU) and the fused add + RMSNorm ((32768, 768) bf16 with
+    an fp32 residual stream in and out), forward and backward, as CUDA-graph replays over two alternating input sets."""
+    from ssm_b200 import ops
+
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(5)
+    kw = dict(generator=g, device=dev)
+    bf = torch.bfloat16
+    B, D, Lq, dm = 8, 1536, 4096, 768
+    xs = [torch.randn(D, B, Lq, **kw).to(bf).permute(1, 0, 2).requires_grad_(True) for _ in range(2)]
+    gys = [torch.randn(D, B, Lq, **kw).to(bf).permute(1, 0, 2) for _ in range(2)]
+    cw, cb = (torch.rand(D, 4, **kw) - 0.5).requires_grad_(True), torch.zeros(D, device=dev, requires_grad=True)
+    nx = [torch.randn(B, Lq, dm, **kw).to(bf).requires_grad_(True) for _ in range(2)]
+    nr = [torch.randn(B, Lq, dm, **kw).requires_grad_(True) for _ in range(2)]
+    ngy = [torch.randn(B, Lq, dm, **kw).to(bf) for _ in range(2)]
+    ngr = [torch.randn(B, Lq, dm, **kw) for _ in range(2)]
+    nw = torch.ones(dm, device=dev, dtype=bf, requires_grad=True)
+
+    def conv_fwd(i):
+        with torch.no_grad():
+            return ops.dw_causal_conv(xs[i % 2], cw, cb, "silu")
+
+    def conv_both(i):
+        y = ops.dw_causal_conv(xs[i % 2], cw, cb, "silu")
+        return torch.autograd.grad(y, (xs[i % 2], cw, cb), gys[i % 2])
+
+    def norm_fwd(i):
+        with torch.no_grad():
+            return ops.fused_layer_norm(nx[i % 2], nw, None, residual=nr[i % 2], is_rms=True, prenorm=True, return_residual=True)
+
+    def norm_both(i):
+        y, ro = ops.fused_layer_norm(nx[i % 2], nw, None, residual=nr[i % 2], is_rms=True, prenorm=True, return_residual=True)
+        return torch.autograd.grad((y, ro), (nx[i % 2], nr[i % 2], nw), (ngy[i % 2], ngr[i % 2]))
+
+    cf, cfb, nf, nfb = graph_time(conv_fwd), graph_time(conv_both), graph_time(norm_fwd), graph_time(norm_both)
+    el_c, el_n = B * D * Lq, B * Lq * dm
+    return {"conv_fwd_ms": cf, "conv_bwd_ms": cfb - cf, "norm_fwd_ms": nf, "norm_bwd_ms": nfb - nf,
+            "conv_fwd_bytes": 2 * el_c * 2, "conv_bwd_bytes": 3 * el_c * 2,
+            "norm_fwd_bytes": el_n * (2 + 4 + 2 + 4),            # x, fp32 residual in; y, fp32 residual stream out
+            "norm_bwd_bytes": el_n * (2 + 4 + 2 + 4 + 2 + 4)}    # x, residual, dy, d(residual stream) in; dx, dresidual out
 
 
 def bench_ssd(batch=8, steps=20):
@@ -569,8 +626,16 @@ def bench_decode(steps=1000):
         it[0] += 1
         return ops.selective_state_step_heads(st2[it[0] % 2], x2, dt2, A2, B2, C2, D=D2, z=z2, softplus=True)
 
-    res = {"layer_eager_us": time_cuda(layer_step, steps, 20) * 1e3, "state_kernels_us": time_cuda(state_kernels, steps, 20) * 1e3,
-           "mamba2_step_us": time_cuda(m2_step, min(steps, 200), 5) * 1e3}
+    def state_kernels_i(i):
+        it[0] = i
+        state_kernels()
+
+    def m2_step_i(i):
+        it[0] = i
+        m2_step()
+
+    res = {"layer_eager_us": time_cuda(layer_step, steps, 20) * 1e3, "state_kernels_us": graph_time(state_kernels_i, reps=2 * nbuf, iters=50) * 1e3,
+           "mamba2_step_us": graph_time(m2_step_i, reps=4, iters=20) * 1e3}
     # CUDA-graph replay of the whole layer step (one fixed pair of state buffers, as a decoder has)
     try:
         it[0] = 0
@@ -613,22 +678,22 @@ def bench_chunk_scan(steps=20):
                              Bm=torch.randn(B, Lq, H, P, **kw).to(bf), Cm=torch.randn(B, Lq, H, P, **kw).to(bf), z=torch.randn(B, Lq, H, P, **kw).to(bf),
                              gY=torch.randn(B, Lq, H, P, **kw).to(bf)))
         A, D = -torch.exp(torch.randn(H, P, **kw) * 0.5), torch.randn(H, **kw)
-        it = [0]
+        for st in sets:
+            for k_ in ("Bm", "Cm", "z"):
+                st[k_].requires_grad_(True)
 
-        def fwd():
-            s = sets[it[0] % 3]
-            it[0] += 1
+        def fwd(i):
+            s = sets[i % 3]
             with torch.no_grad():
                 return ops.ssd_chunk_scan(s["X"], s["dt"], A, s["Bm"], s["Cm"], chunk, D=D, z=s["z"])
 
-        def fwd_bwd():
-            s = sets[it[0] % 3]
-            it[0] += 1
-            s["X"].grad = None
-            ops.ssd_chunk_scan(s["X"], s["dt"], A, s["Bm"], s["Cm"], chunk, D=D, z=s["z"]).backward(s["gY"])
+        def fwd_bwd(i):
+            s = sets[i % 3]
+            Y = ops.ssd_chunk_scan(s["X"], s["dt"], A, s["Bm"], s["Cm"], chunk, D=D, z=s["z"])
+            return torch.autograd.grad(Y, (s["X"], s["Bm"], s["Cm"], s["z"]), s["gY"])
 
-        f = time_cuda(fwd, steps, 3)
-        fb = time_cuda(fwd_bwd, steps, 3)
+        f = graph_time(fwd, reps=3, iters=max(2, steps // 3))
+        fb = graph_time(fwd_bwd, reps=3, iters=max(2, steps // 3))
         el = B * Lq * H * P
         out[name] = {"fwd_ms": f, "bwd_ms": fb - f, "fwd_bytes": 5 * el * 2 + B * Lq * H * 2, "bwd_bytes": 6 * el * 2 + B * Lq * H * 2 + B * Lq * H * 4}
     return out
@@ -647,8 +712,11 @@ def operator_table(args):
     t["c2_clocks"] = json.dumps(sampler.stop())
     t["c2_step_ms"] = c2["step_ms"]
     t["c2_tokens_per_s"] = c2["tokens"] / (c2["step_ms"] * 1e-3)
-    for tag in ("scan_fwd", "scan_bwd", "conv_fwd", "conv_bwd", "norm_fwd", "norm_bwd"):
+    for tag in ("scan_fwd", "scan_bwd"):
         t[f"c2_{tag}_ms"], t[f"c2_{tag}_frac"] = c2[tag + "_ms"], frac(c2[tag + "_bytes"], c2[tag + "_ms"])
+    cn = bench_conv_norm()  # short kernels: device time from CUDA-graph replays, not from events around eager host calls
+    for tag in ("conv_fwd", "conv_bwd", "norm_fwd", "norm_bwd"):
+        t[f"c2_{tag}_ms"], t[f"c2_{tag}_frac"] = cn[tag + "_ms"], frac(cn[tag + "_bytes"], cn[tag + "_ms"])
     # the scan is bound by the special-function unit, not by HBM: one ex2 per (row, state, step) plus softplus / SiLU per (row, step)
     b, d, l, n = BLOCK_CFG["batch"], BLOCK_CFG["d_inner"], BLOCK_CFG["seqlen"], BLOCK_CFG["d_state"]
     xu_floor_ms = b * d * l * (n + 4) / (148 * 16 * 1.965e9) * 1e3

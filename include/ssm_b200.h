@@ -219,8 +219,11 @@ typedef struct {
   float* ddt;
   ssm_bcast4 dA, dB, dC, dD, dz, dinitial; /* ptr as float*; NULL to skip where fwd's is NULL */
   float* history;
+  float* scratch; /* nullable: ssm_chunk_scan_bwd_scratch_floats() floats; with it the chunks run in parallel, without it one thread
+                     per (batch, head, proj) walks the whole sequence */
 } ssm_chunk_bwd_args;
 
+int64_t ssm_chunk_scan_bwd_scratch_floats(int32_t batch, int32_t len, int32_t heads, int32_t proj, int32_t chunk_size);
 int ssm_chunk_scan_bwd(const ssm_chunk_bwd_args* args, ssm_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------

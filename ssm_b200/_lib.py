@@ -81,7 +81,7 @@ class ChunkBwdArgs(C.Structure):
         ("fwd", ChunkArgs),
         ("dY", vp), ("dX", vp), ("ddt", fp),
         ("dA", Bcast4), ("dB", Bcast4), ("dC", Bcast4), ("dD", Bcast4), ("dz", Bcast4), ("dinitial", Bcast4),
-        ("history", fp),
+        ("history", fp), ("scratch", fp),
     ]
 
 
@@ -142,6 +142,7 @@ ENTRY_POINTS = {
     "ssm_selective_state_step_bwd": (C.c_int, [C.POINTER(StepBwdArgs), vp]),
     "ssm_chunk_scan_scratch_floats": (C.c_int64, [i32, i32, i32, i32, i32]),
     "ssm_chunk_scan_fwd": (C.c_int, [C.POINTER(ChunkArgs), vp]),
+    "ssm_chunk_scan_bwd_scratch_floats": (C.c_int64, [i32, i32, i32, i32, i32]),
     "ssm_chunk_scan_bwd": (C.c_int, [C.POINTER(ChunkBwdArgs), vp]),
     "ssm_dw_causal_conv_fwd": (C.c_int, [C.POINTER(ConvArgs), vp]),
     "ssm_dw_causal_conv_bwd": (C.c_int, [C.POINTER(ConvBwdArgs), vp]),

@@ -15,7 +15,7 @@
 namespace ssmb {
 
 constexpr int kNormFwdChunks = 4;  // 16-byte chunks of x per thread, forward
-constexpr int kNormBwdChunks = 2;  // backward keeps three more row-sized arrays in registers
+constexpr int kNormBwdChunks = 2;  // widest backward configuration: 512 threads x 2 chunks
 constexpr int kNormBwdMaxCtas = 592;  // 4 per SM on a 148-SM part
 
 // V consecutive elements of run-time type -> fp32
@@ -214,24 +214,32 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_fwd_kernel(const ss
   }
 }
 
-template <typename T, int G>
-__global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 128 ? 4 : 1) norm_bwd_kernel(const ssm_norm_bwd_args g) {
+// MC = 16-byte chunks of a row per thread.  A row of up to 32 * MC chunks is owned by ONE warp (G = 32): every reduction is
+// a shuffle tree and four rows are in flight per CTA; wider rows take 128 or 512 threads with block-wide reductions.
+template <typename T, int G, int MC>
+__global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 128 ? (MC <= 2 ? 4 : (MC == 3 ? 3 : 2)) : 1) norm_bwd_kernel(const ssm_norm_bwd_args g) {
   using Cfg = NormCfg<T, G>;
   constexpr int V = Cfg::V;
+  constexpr int kNormBwdChunks = MC;
   const ssm_norm_args& a = g.fwd;
   __shared__ float scratch[32];
   const int gt = threadIdx.x % G, slot = threadIdx.x / G;
   const int nchunk = a.hidden / V;
   const float inv = 1.f / (float)a.hidden;
-  float dw[kNormBwdChunks][V], db[kNormBwdChunks][V], w[kNormBwdChunks][V];
+  float dw[kNormBwdChunks][V], db[kNormBwdChunks][V];
 #pragma unroll
   for (int c = 0; c < kNormBwdChunks; ++c)
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-      const int col = (c * G + gt) * V + i;
-      dw[c][i] = 0.f, db[c][i] = 0.f;
-      w[c][i] = col < a.hidden ? __ldg(a.weight + col) : 0.f;
+    for (int i = 0; i < V; ++i) dw[c][i] = 0.f, db[c][i] = 0.f;
+  // the weights of this thread's columns are re-read from L1 for every row (16-byte loads) instead of occupying registers
+  auto load_w = [&](int c, float (&wv)[V]) {
+    const int ch = c * G + gt;
+#pragma unroll
+    for (int i = 0; i < V; i += 4) {
+      const float4 w4 = ch < nchunk ? __ldg(reinterpret_cast<const float4*>(a.weight + ch * V + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      wv[i] = w4.x, wv[i + 1] = w4.y, wv[i + 2] = w4.z, wv[i + 3] = w4.w;
     }
+  };
   const int64_t npass = (a.rows + Cfg::RPC - 1) / Cfg::RPC;
   for (int64_t pass = blockIdx.x; pass < npass; pass += gridDim.x) {
     const int64_t row = pass * Cfg::RPC + slot;
@@ -251,6 +259,9 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 
         Vec16<T> v;
         v.load_stream(reinterpret_cast<const T*>(g.dy) + row * a.hidden + (int64_t)ch * V);
         v.unpack(dy[c]);
+        // the gradient arriving through the x + residual output travels with the other loads of the row (the residual values in
+        // r[] are dead once the row sum is formed)
+        if (g.dresidual_out) load_dyn_vec<V>(g.dresidual_out, row * a.hidden + (int64_t)ch * V, a.resout_dtype, r[c]);
       } else {
 #pragma unroll
         for (int i = 0; i < V; ++i) dy[c][i] = 0.f;
@@ -260,11 +271,13 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 
     norm_stats<T, G, kNormBwdChunks>(a, gt, nchunk, s, scratch, mean, rstd);
     float c1 = 0.f, c2 = 0.f;
 #pragma unroll
-    for (int c = 0; c < kNormBwdChunks; ++c)
+    for (int c = 0; c < kNormBwdChunks; ++c) {
+      float wv[V];
+      load_w(c, wv);
 #pragma unroll
       for (int i = 0; i < V; ++i) {
         const float xh = (s[c][i] - mean) * rstd;
-        const float wdy = dy[c][i] * w[c][i];
+        const float wdy = dy[c][i] * wv[i];
         s[c][i] = xh;  // keep xhat
         c1 = fmaf(wdy, xh, c1);
         c2 += wdy;
@@ -273,6 +286,7 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 
           db[c][i] += dy[c][i];
         }
       }
+    }
     c1 = group_allsum<G>(c1, scratch) * inv;
     c2 = a.is_rms ? 0.f : group_allsum<G>(c2, scratch) * inv;
     if (live) {
@@ -280,15 +294,14 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 
       for (int c = 0; c < kNormBwdChunks; ++c) {
         const int ch = c * G + gt;
         if (ch < nchunk) {
-          float dsv[V];
+          float dsv[V], wv[V];
+          load_w(c, wv);
 #pragma unroll
-          for (int i = 0; i < V; ++i) dsv[i] = (dy[c][i] * w[c][i] - s[c][i] * c1 - c2) * rstd;
+          for (int i = 0; i < V; ++i) dsv[i] = (dy[c][i] * wv[i] - s[c][i] * c1 - c2) * rstd;
           const int64_t off = row * a.hidden + (int64_t)ch * V;
           if (g.dresidual_out) {  // gradient arriving through the x + residual output reaches x and residual unchanged
-            float gro[V];
-            load_dyn_vec<V>(g.dresidual_out, off, a.resout_dtype, gro);
 #pragma unroll
-            for (int i = 0; i < V; ++i) dsv[i] += gro[i], dy[c][i] += gro[i];
+            for (int i = 0; i < V; ++i) dsv[i] += r[c][i], dy[c][i] += r[c][i];
           }
           Vec16<T> v;
           v.pack(dsv);
@@ -474,14 +487,38 @@ static int norm_fwd_launch(const ssm_norm_args& a, cudaStream_t st) {
   norm_fwd_kernel<T, G><<<grid, Cfg::BLOCK, 0, st>>>(a);
   return launch_status("norm_fwd_kernel");
 }
-template <typename T, int G>
-static int norm_bwd_launch(const ssm_norm_bwd_args& g, cudaStream_t st) {
+template <typename T, int G, int MC>
+static int norm_bwd_launch(const ssm_norm_bwd_args& g, cudaStream_t st, int max_ctas = kNormBwdMaxCtas) {
   using Cfg = NormCfg<T, G>;
-  const int nctas = norm_bwd_ctas(g.fwd, Cfg::RPC);
-  norm_bwd_kernel<T, G><<<nctas, Cfg::BLOCK, 0, st>>>(g);
+  // persistent grid: exactly one resident wave (a second, partial wave would double the time)
+  static const int resident = [] {
+    int per_sm = 1, sms = 148, dev = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, norm_bwd_kernel<T, G, MC>, Cfg::BLOCK, 0);
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return (per_sm < 1 ? 1 : per_sm) * sms;
+  }();
+  int nctas = norm_bwd_ctas(g.fwd, Cfg::RPC);
+  if (nctas > max_ctas) nctas = max_ctas;
+  if (nctas > resident) nctas = resident;
+  norm_bwd_kernel<T, G, MC><<<nctas, Cfg::BLOCK, 0, st>>>(g);
   if (int rc = launch_status("norm_bwd_kernel")) return rc;
   norm_fold_kernel<<<(g.fwd.hidden + 31) / 32, 32 * kFoldLanes, 0, st>>>(g.partial, nctas, g.fwd.hidden, g.dweight, g.dbias);
   return launch_status("norm_fold_kernel");
+}
+
+// rows of up to 128 chunks go to one warp each (1 .. 4 chunks per lane), wider ones to 128 or 512 threads
+template <typename T>
+static int norm_bwd_dispatch(const ssm_norm_bwd_args& g, cudaStream_t st, int max_ctas) {
+  const int V = 16 / (int)sizeof(T);
+  const int nchunk = g.fwd.hidden / V;
+  if (nchunk <= 32) return norm_bwd_launch<T, 32, 1>(g, st, max_ctas);
+  if (nchunk <= 64) return norm_bwd_launch<T, 32, 2>(g, st, max_ctas);
+  if (nchunk <= 96) return norm_bwd_launch<T, 32, 3>(g, st, max_ctas);
+  if (nchunk <= 128) return norm_bwd_launch<T, 32, 4>(g, st, max_ctas);
+  if (nchunk <= 256) return norm_bwd_launch<T, 128, 2>(g, st, max_ctas);
+  if (nchunk <= 512) return norm_bwd_launch<T, 128, 4>(g, st, max_ctas);
+  return norm_bwd_launch<T, 512, 2>(g, st, max_ctas);
 }
 
 template <typename T>
@@ -507,11 +544,7 @@ static int norm_bwd_t(const ssm_norm_bwd_args& g, cudaStream_t st) {
     norm_scalar_kernel<T, true><<<(unsigned)a.rows, 128, 0, st>>>(g);
     return launch_status("norm_scalar_kernel");
   }
-  switch (norm_group(a, kNormBwdChunks)) {
-    case 32: return norm_bwd_launch<T, 32>(g, st);
-    case 128: return norm_bwd_launch<T, 128>(g, st);
-    default: return norm_bwd_launch<T, 512>(g, st);
-  }
+  return norm_bwd_dispatch<T>(g, st, kNormBwdMaxCtas);
 }
 
 
@@ -557,17 +590,6 @@ static int noalloc_scratch_address(float** out) {
   return SSM_OK;
 }
 
-template <typename T, int G>
-static int norm_bwd_launch_capped(const ssm_norm_bwd_args& g, cudaStream_t st, int max_ctas) {
-  using Cfg = NormCfg<T, G>;
-  int nctas = norm_bwd_ctas(g.fwd, Cfg::RPC);
-  if (nctas > max_ctas) nctas = max_ctas;
-  norm_bwd_kernel<T, G><<<nctas, Cfg::BLOCK, 0, st>>>(g);
-  if (int rc = launch_status("norm_bwd_kernel")) return rc;
-  norm_fold_kernel<<<(g.fwd.hidden + 31) / 32, 32 * kFoldLanes, 0, st>>>(g.partial, nctas, g.fwd.hidden, g.dweight, g.dbias);
-  return launch_status("norm_fold_kernel");
-}
-
 template <typename T>
 static int norm_bwd_noalloc_t(const ssm_norm_bwd_args& g, float* scratch, cudaStream_t st) {
   const ssm_norm_args& a = g.fwd;
@@ -580,11 +602,7 @@ static int norm_bwd_noalloc_t(const ssm_norm_bwd_args& g, float* scratch, cudaSt
   }
   ssm_norm_bwd_args h = g;
   h.partial = scratch;
-  switch (norm_group(a, kNormBwdChunks)) {
-    case 32: return norm_bwd_launch_capped<T, 32>(h, st, kNoAllocCtas);
-    case 128: return norm_bwd_launch_capped<T, 128>(h, st, kNoAllocCtas);
-    default: return norm_bwd_launch_capped<T, 512>(h, st, kNoAllocCtas);
-  }
+  return norm_bwd_dispatch<T>(h, st, kNoAllocCtas);
 }
 
 }  // namespace ssmb

@@ -4,28 +4,37 @@
 //   s_t = exp(dt_t A) s_{t-1} + dt_t B_t X_t;   y_t = s_t C_t + D X_t;   y_t *= silu(z_t)
 //
 // Each (batch, head, proj) lane is an independent scalar recurrence, so with (head, proj)
-// fastest in memory consecutive threads read consecutive addresses at every step.  The
-// sequence axis is split into chunks that run in parallel in three phases: (1) every chunk
-// integrates from a zero state and records its decay product, (2) a short serial pass
-// over chunks turns those into each chunk's incoming state, (3) every chunk is replayed
-// from its true incoming state and writes Y.  Without scratch memory a single serial pass
-// is used instead.
+// fastest in memory consecutive threads read consecutive addresses at every step; the kernels
+// are HBM-bound streams.  The sequence axis is split into chunks that run in parallel:
+//   forward   (1) every chunk integrates from a zero state and records its decay product,
+//             (2) a short serial pass over chunks turns those into each chunk's incoming state,
+//             (3) every chunk is replayed from its true incoming state and writes Y;
+//   backward  the same three phases give every chunk its incoming state, their mirror image
+//             gives every chunk the adjoint that enters it from the right
+//             (g_t = C_t dy_t + exp(dt_{t+1} A) g_{t+1} is a linear recurrence too), and one
+//             final pass per chunk replays the states into the history scratch and walks back
+//             through them producing every gradient.
+// Every thread keeps raw pointers that advance by one time stride per step, and the loads of
+// eight steps are issued before the first of them is used, so that enough bytes are in flight.
+// Without scratch memory a single serial pass is used instead.
 #include "common.cuh"
 
 namespace ssmb {
 
 constexpr int kChunkThreads = 128;
+constexpr int kChunkUnroll = 8;
 
-__device__ __forceinline__ float bc4_load_f32(const ssm_bcast4& p, int b, int t, int h, int q) {
-  return __ldg(reinterpret_cast<const float*>(p.ptr) + (int64_t)b * p.sb + (int64_t)t * p.st + (int64_t)h * p.sh + (int64_t)q * p.sq);
+__device__ __forceinline__ int64_t bc4_off(const ssm_bcast4& p, int b, int t, int h, int q) {
+  return (int64_t)b * p.sb + (int64_t)t * p.st + (int64_t)h * p.sh + (int64_t)q * p.sq;
 }
-__device__ __forceinline__ float bc4_load(const ssm_bcast4& p, int dtype, int b, int t, int h, int q) {
-  return load_dyn(p.ptr, (int64_t)b * p.sb + (int64_t)t * p.st + (int64_t)h * p.sh + (int64_t)q * p.sq, dtype);
+__device__ __forceinline__ float bc4_load_f32(const ssm_bcast4& p, int b, int t, int h, int q) {
+  return __ldg(reinterpret_cast<const float*>(p.ptr) + bc4_off(p, b, t, h, q));
 }
 __device__ __forceinline__ float* bc4_ptr(const ssm_bcast4& p, int b, int t, int h, int q) {
-  return const_cast<float*>(reinterpret_cast<const float*>(p.ptr)) + (int64_t)b * p.sb + (int64_t)t * p.st + (int64_t)h * p.sh +
-         (int64_t)q * p.sq;
+  return const_cast<float*>(reinterpret_cast<const float*>(p.ptr)) + bc4_off(p, b, t, h, q);
 }
+// true when every (b, t, h, q) of a gradient buffer is a distinct element (no broadcast axis): plain stores suffice
+__device__ __forceinline__ bool bc4_dense(const ssm_bcast4& p) { return p.sb != 0 && p.st != 0 && p.sh != 0 && p.sq != 0; }
 
 __device__ __forceinline__ int chunk_valid_len(const ssm_chunk_args& a, int b) {
   if (!a.seq_lens) return a.len;
@@ -33,62 +42,110 @@ __device__ __forceinline__ int chunk_valid_len(const ssm_chunk_args& a, int b) {
   return (int)(v < 0 ? 0 : (v > a.len ? a.len : v));
 }
 
-// One step of the recurrence for lane (b, h, q) at time t; returns the gated output.
-template <typename T>
-__device__ __forceinline__ float chunk_step(const ssm_chunk_args& a, int b, int t, int h, int q, float Av, float& s) {
-  const int64_t HP = (int64_t)a.heads * a.proj;
-  const float x = to_f<T>(reinterpret_cast<const T*>(a.X)[((int64_t)b * a.len + t) * HP + (int64_t)h * a.proj + q]);
-  const float dt = to_f<T>(reinterpret_cast<const T*>(a.dt)[((int64_t)b * a.len + t) * a.heads + h]);
-  const float Bv = bc4_load(a.Bm, a.par_dtype, b, t, h, q);
-  const float Cv = bc4_load(a.Cm, a.par_dtype, b, t, h, q);
-  s = fmaf(ex2_approx(dt * Av * kLog2e), s, dt * Bv * x);
-  float y = s * Cv;
-  if (a.D.ptr) y = fmaf(bc4_load_f32(a.D, 0, 0, h, q), x, y);
-  if (a.z.ptr) y *= silu_fast(bc4_load(a.z, a.par_dtype, b, t, h, q));
-  return y;
+// A time-strided stream of one lane: element offset at the lane's first step, stride per step (0: constant in time).
+template <typename E>
+struct Stream {
+  const E* p;
+  int64_t st;
+  __device__ __forceinline__ float at(int k) const { return to_f<E>(__ldg(p + (int64_t)k * st)); }
+};
+// B / C / z stream of element type PT at (b, t, h, q)
+template <typename PT>
+__device__ __forceinline__ Stream<PT> par_stream(const ssm_bcast4& c, int b, int t, int h, int q) {
+  return {reinterpret_cast<const PT*>(c.ptr) + bc4_off(c, b, t, h, q), c.st};
 }
 
-// mode 0: serial over the whole sequence (no scratch).  mode 1: phase 1.  mode 3: phase 3.
-template <typename T, int MODE>
+// per-lane context shared by all kernels
+template <typename T>
+struct Lane {
+  int b, h, q, hp, HP, valid;
+  float Av, Dv;
+  __device__ __forceinline__ bool init(const ssm_chunk_args& a) {
+    HP = a.heads * a.proj;
+    hp = blockIdx.x * kChunkThreads + threadIdx.x;
+    if (hp >= HP) return false;
+    h = hp / a.proj, q = hp % a.proj;
+    b = blockIdx.z;
+    valid = chunk_valid_len(a, b);
+    Av = bc4_load_f32(a.A, 0, 0, h, q) * kLog2e;
+    Dv = a.D.ptr ? bc4_load_f32(a.D, 0, 0, h, q) : 0.f;
+    return true;
+  }
+  __device__ __forceinline__ Stream<T> x(const ssm_chunk_args& a, int t) const {
+    return {reinterpret_cast<const T*>(a.X) + ((int64_t)b * a.len + t) * HP + hp, HP};
+  }
+  __device__ __forceinline__ Stream<T> dt(const ssm_chunk_args& a, int t) const {
+    return {reinterpret_cast<const T*>(a.dt) + ((int64_t)b * a.len + t) * a.heads + h, a.heads};
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------------
+// mode 0: serial over the whole sequence (no scratch).  mode 1: phase 1 (local state + decay).  mode 3: phase 3.
+template <typename T, typename PT, int MODE>
 __global__ void __launch_bounds__(kChunkThreads) chunk_fwd_kernel(const ssm_chunk_args a, int nchunks) {
-  const int HP = a.heads * a.proj;
-  const int hp = blockIdx.x * kChunkThreads + threadIdx.x;
-  if (hp >= HP) return;
-  const int h = hp / a.proj, q = hp % a.proj;
+  Lane<T> ln;
+  if (!ln.init(a)) return;
   const int c = MODE == 0 ? 0 : blockIdx.y;
-  const int b = blockIdx.z;
-  const int valid = chunk_valid_len(a, b);
   const int t0 = MODE == 0 ? 0 : c * a.chunk_size;
   const int t1 = MODE == 0 ? a.len : min(a.len, t0 + a.chunk_size);
-  const float Av = bc4_load_f32(a.A, 0, 0, h, q);
-  float* P = a.scratch;                                     // [batch][nchunks][HP] decay products
-  float* S = a.scratch ? a.scratch + (int64_t)a.batch * nchunks * HP : nullptr;  // local end state, then incoming state
-  const int64_t slot = ((int64_t)b * nchunks + c) * HP + hp;
-  T* Y = reinterpret_cast<T*>(a.Y);
+  const int te = max(t0, min(t1, ln.valid));
+  float* P = a.scratch;                                                             // [batch][nchunks][HP] decay products
+  float* S = a.scratch ? a.scratch + (int64_t)a.batch * nchunks * ln.HP : nullptr;  // local end state, then incoming state
+  const int64_t slot = ((int64_t)ln.b * nchunks + c) * ln.HP + ln.hp;
+  const Stream<T> sx = ln.x(a, t0), sdt = ln.dt(a, t0);
+  const Stream<PT> sB = par_stream<PT>(a.Bm, ln.b, t0, ln.h, ln.q);
+  const int n = te - t0;
   if (MODE == 1) {
     float s = 0.f, sumdt = 0.f;
-    const int te = min(t1, valid);
-    for (int t = t0; t < te; ++t) {
-      const float x = to_f<T>(reinterpret_cast<const T*>(a.X)[((int64_t)b * a.len + t) * HP + hp]);
-      const float dt = to_f<T>(reinterpret_cast<const T*>(a.dt)[((int64_t)b * a.len + t) * a.heads + h]);
-      const float Bv = bc4_load(a.Bm, a.par_dtype, b, t, h, q);
-      s = fmaf(ex2_approx(dt * Av * kLog2e), s, dt * Bv * x);
-      sumdt += dt;
+    int k = 0;
+    for (; k + kChunkUnroll <= n; k += kChunkUnroll) {
+      float x[kChunkUnroll], d[kChunkUnroll], bv[kChunkUnroll];
+#pragma unroll
+      for (int i = 0; i < kChunkUnroll; ++i) x[i] = sx.at(k + i), d[i] = sdt.at(k + i), bv[i] = sB.at(k + i);
+#pragma unroll
+      for (int i = 0; i < kChunkUnroll; ++i) {
+        s = fmaf(ex2_approx(d[i] * ln.Av), s, d[i] * bv[i] * x[i]);
+        sumdt += d[i];
+      }
     }
-    P[slot] = ex2_approx(sumdt * Av * kLog2e);
+    for (; k < n; ++k) {
+      const float d = sdt.at(k);
+      s = fmaf(ex2_approx(d * ln.Av), s, d * sB.at(k) * sx.at(k));
+      sumdt += d;
+    }
+    P[slot] = ex2_approx(sumdt * ln.Av);
     S[slot] = s;
     return;
   }
+  const Stream<PT> sC = par_stream<PT>(a.Cm, ln.b, t0, ln.h, ln.q);
+  const bool has_z = a.z.ptr != nullptr;
+  const Stream<PT> sz = has_z ? par_stream<PT>(a.z, ln.b, t0, ln.h, ln.q) : Stream<PT>{nullptr, 0};
+  T* Y = reinterpret_cast<T*>(a.Y) + ((int64_t)ln.b * a.len + t0) * ln.HP + ln.hp;
   float s;
-  if (MODE == 0) s = a.initial.ptr ? bc4_load_f32(a.initial, b, 0, h, q) : 0.f;
+  if (MODE == 0) s = a.initial.ptr ? bc4_load_f32(a.initial, ln.b, 0, ln.h, ln.q) : 0.f;
   else s = S[slot];
-  const int te = min(t1, valid);
-  for (int t = t0; t < te; ++t) {
-    const float y = chunk_step<T>(a, b, t, h, q, Av, s);
-    Y[((int64_t)b * a.len + t) * HP + hp] = from_f<T>(y);
+  auto step = [&](float x, float d, float bv, float cv, float zv) {
+    s = fmaf(ex2_approx(d * ln.Av), s, d * bv * x);
+    float y = fmaf(ln.Dv, x, s * cv);
+    if (has_z) y *= silu_fast(zv);
+    return y;
+  };
+  int k = 0;
+  for (; k + kChunkUnroll <= n; k += kChunkUnroll) {
+    float x[kChunkUnroll], d[kChunkUnroll], bv[kChunkUnroll], cv[kChunkUnroll], zv[kChunkUnroll];
+#pragma unroll
+    for (int i = 0; i < kChunkUnroll; ++i) {
+      x[i] = sx.at(k + i), d[i] = sdt.at(k + i), bv[i] = sB.at(k + i), cv[i] = sC.at(k + i);
+      zv[i] = has_z ? sz.at(k + i) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < kChunkUnroll; ++i) Y[(int64_t)(k + i) * ln.HP] = from_f<T>(step(x[i], d[i], bv[i], cv[i], zv[i]));
   }
-  for (int t = max(te, t0); t < t1; ++t) Y[((int64_t)b * a.len + t) * HP + hp] = from_f<T>(0.f);
-  if (MODE == 0 && a.final_state) a.final_state[(int64_t)b * HP + hp] = s;
+  for (; k < n; ++k) Y[(int64_t)k * ln.HP] = from_f<T>(step(sx.at(k), sdt.at(k), sB.at(k), sC.at(k), has_z ? sz.at(k) : 0.f));
+  for (int t = te; t < t1; ++t) Y[(int64_t)(t - t0) * ln.HP] = from_f<T>(0.f);
+  if (MODE == 0 && a.final_state) a.final_state[(int64_t)ln.b * ln.HP + ln.hp] = s;
 }
 
 // phase 2: serial over chunks; S[c] <- state entering chunk c
@@ -110,67 +167,189 @@ __global__ void __launch_bounds__(kChunkThreads) chunk_carry_kernel(const ssm_ch
   if (a.final_state) a.final_state[(int64_t)b * HP + hp] = s;
 }
 
-// Backward: one thread per (batch, head, proj); forward replay into `history`, then the
-// reverse recurrence  g_t = C_t dyg_t + exp(dt_{t+1} A) g_{t+1}.
-template <typename T>
-__global__ void __launch_bounds__(kChunkThreads) chunk_bwd_kernel(const ssm_chunk_bwd_args g) {
+// ---------------------------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------------------------
+// dy_t = dout_t * silu(z_t) (or dout_t)
+__device__ __forceinline__ float gated_dy(float dout, bool has_z, float zv) { return has_z ? dout * silu_fast(zv) : dout; }
+
+// reverse phase 1: per chunk, the adjoint that leaves the chunk on its left side when nothing enters on the right:
+//   carry <- exp(dt_t A) (C_t dy_t + carry), t from the chunk's last valid step down to its first
+template <typename T, typename PT>
+__global__ void __launch_bounds__(kChunkThreads) chunk_bwd_local_kernel(const ssm_chunk_bwd_args g, int nchunks) {
+  const ssm_chunk_args& a = g.fwd;
+  Lane<T> ln;
+  if (!ln.init(a)) return;
+  const int c = blockIdx.y;
+  const int t0 = c * a.chunk_size, t1 = min(a.len, t0 + a.chunk_size);
+  const int te = max(t0, min(t1, ln.valid));
+  const int n = te - t0;
+  float* R = g.scratch + 2 * (int64_t)a.batch * nchunks * ln.HP;  // [batch][nchunks][HP] local adjoint, then the adjoint entering each chunk
+  const int64_t slot = ((int64_t)ln.b * nchunks + c) * ln.HP + ln.hp;
+  const Stream<T> sdt = ln.dt(a, t0);
+  const Stream<T> sdy = {reinterpret_cast<const T*>(g.dY) + ((int64_t)ln.b * a.len + t0) * ln.HP + ln.hp, ln.HP};
+  const Stream<PT> sC = par_stream<PT>(a.Cm, ln.b, t0, ln.h, ln.q);
+  const bool has_z = a.z.ptr != nullptr;
+  const Stream<PT> sz = has_z ? par_stream<PT>(a.z, ln.b, t0, ln.h, ln.q) : Stream<PT>{nullptr, 0};
+  float carry = 0.f;
+  int k = n;
+  for (; k - kChunkUnroll >= 0; k -= kChunkUnroll) {
+    float d[kChunkUnroll], dy[kChunkUnroll], cv[kChunkUnroll];
+#pragma unroll
+    for (int i = 0; i < kChunkUnroll; ++i) {
+      const int kk = k - 1 - i;
+      d[i] = sdt.at(kk), cv[i] = sC.at(kk);
+      dy[i] = gated_dy(sdy.at(kk), has_z, has_z ? sz.at(kk) : 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < kChunkUnroll; ++i) carry = ex2_approx(d[i] * ln.Av) * fmaf(cv[i], dy[i], carry);
+  }
+  for (; k > 0; --k) {
+    const int kk = k - 1;
+    carry = ex2_approx(sdt.at(kk) * ln.Av) * fmaf(sC.at(kk), gated_dy(sdy.at(kk), has_z, has_z ? sz.at(kk) : 0.f), carry);
+  }
+  R[slot] = carry;
+}
+
+// reverse phase 2: serial over chunks from the right; R[c] <- adjoint entering chunk c from chunk c + 1
+__global__ void __launch_bounds__(kChunkThreads) chunk_bwd_carry_kernel(const ssm_chunk_bwd_args g, int nchunks) {
   const ssm_chunk_args& a = g.fwd;
   const int HP = a.heads * a.proj;
   const int hp = blockIdx.x * kChunkThreads + threadIdx.x;
   if (hp >= HP) return;
-  const int h = hp / a.proj, q = hp % a.proj;
   const int b = blockIdx.z;
-  const int valid = chunk_valid_len(a, b);
-  const float Av = bc4_load_f32(a.A, 0, 0, h, q);
-  const float s0 = a.initial.ptr ? bc4_load_f32(a.initial, b, 0, h, q) : 0.f;
-  const T* X = reinterpret_cast<const T*>(a.X);
-  const T* DT = reinterpret_cast<const T*>(a.dt);
-  const T* dY = reinterpret_cast<const T*>(g.dY);
-  T* dX = reinterpret_cast<T*>(g.dX);
-  float s = s0;
-  for (int t = 0; t < valid; ++t) {
-    const int64_t e = ((int64_t)b * a.len + t) * HP + hp;
-    const float x = to_f<T>(X[e]);
-    const float dt = to_f<T>(DT[((int64_t)b * a.len + t) * a.heads + h]);
-    const float Bv = bc4_load(a.Bm, a.par_dtype, b, t, h, q);
-    s = fmaf(ex2_approx(dt * Av * kLog2e), s, dt * Bv * x);
-    g.history[e] = s;
+  const float* P = g.scratch;
+  float* R = g.scratch + 2 * (int64_t)a.batch * nchunks * HP;
+  float carry = 0.f;
+  for (int c = nchunks - 1; c >= 0; --c) {
+    const int64_t slot = ((int64_t)b * nchunks + c) * HP + hp;
+    const float local = R[slot];
+    R[slot] = carry;
+    carry = fmaf(P[slot], carry, local);
   }
-  const float Dv = a.D.ptr ? bc4_load_f32(a.D, 0, 0, h, q) : 0.f;
-  float carry = 0.f;  // exp(dt_{t+1} A) g_{t+1}
+  if (g.dinitial.ptr) {
+    const int h = hp / a.proj, q = hp % a.proj;
+    atomicAdd(bc4_ptr(g.dinitial, b, 0, h, q), carry);
+  }
+}
+
+// sum over the lanes of a warp that share a head, then one atomic per group (proj a multiple of 32: the whole warp)
+__device__ __forceinline__ void add_reduced(float* dst, float v, bool whole_warp) {
+  if (whole_warp) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) atomicAdd(dst, v);
+  } else {
+    atomicAdd(dst, v);
+  }
+}
+
+// final pass: MODE 0 = one thread walks the whole sequence (no scratch); MODE 1 = one chunk per blockIdx.y, states and
+// adjoints entering the chunk taken from the scratch.
+template <typename T, typename PT, int MODE>
+__global__ void __launch_bounds__(kChunkThreads) chunk_bwd_kernel(const ssm_chunk_bwd_args g, int nchunks) {
+  const ssm_chunk_args& a = g.fwd;
+  Lane<T> ln;
+  if (!ln.init(a)) return;
+  const int c = MODE == 0 ? 0 : blockIdx.y;
+  const int t0 = MODE == 0 ? 0 : c * a.chunk_size;
+  const int t1 = MODE == 0 ? a.len : min(a.len, t0 + a.chunk_size);
+  const int te = max(t0, min(t1, ln.valid));
+  const int n = te - t0;
+  const int64_t slot = ((int64_t)ln.b * nchunks + c) * ln.HP + ln.hp;
+  float s0, carry;
+  if (MODE == 0) {
+    s0 = a.initial.ptr ? bc4_load_f32(a.initial, ln.b, 0, ln.h, ln.q) : 0.f;
+    carry = 0.f;
+  } else {
+    s0 = g.scratch[(int64_t)a.batch * nchunks * ln.HP + slot];
+    carry = g.scratch[2 * (int64_t)a.batch * nchunks * ln.HP + slot];
+  }
+  const Stream<T> sx = ln.x(a, t0), sdt = ln.dt(a, t0);
+  const Stream<T> sdy = {reinterpret_cast<const T*>(g.dY) + ((int64_t)ln.b * a.len + t0) * ln.HP + ln.hp, ln.HP};
+  const Stream<PT> sB = par_stream<PT>(a.Bm, ln.b, t0, ln.h, ln.q);
+  const Stream<PT> sC = par_stream<PT>(a.Cm, ln.b, t0, ln.h, ln.q);
+  const bool has_z = a.z.ptr != nullptr;
+  const Stream<PT> sz = has_z ? par_stream<PT>(a.z, ln.b, t0, ln.h, ln.q) : Stream<PT>{nullptr, 0};
+  float* hist = g.history + ((int64_t)ln.b * a.len + t0) * ln.HP + ln.hp;
+  T* dX = reinterpret_cast<T*>(g.dX) + ((int64_t)ln.b * a.len + t0) * ln.HP + ln.hp;
+
+  // ---- states of the chunk, into the history ---------------------------------------------------------------
+  {
+    float s = s0;
+    int k = 0;
+    for (; k + kChunkUnroll <= n; k += kChunkUnroll) {
+      float x[kChunkUnroll], d[kChunkUnroll], bv[kChunkUnroll];
+#pragma unroll
+      for (int i = 0; i < kChunkUnroll; ++i) x[i] = sx.at(k + i), d[i] = sdt.at(k + i), bv[i] = sB.at(k + i);
+#pragma unroll
+      for (int i = 0; i < kChunkUnroll; ++i) {
+        s = fmaf(ex2_approx(d[i] * ln.Av), s, d[i] * bv[i] * x[i]);
+        hist[(int64_t)(k + i) * ln.HP] = s;
+      }
+    }
+    for (; k < n; ++k) {
+      const float d = sdt.at(k);
+      s = fmaf(ex2_approx(d * ln.Av), s, d * sB.at(k) * sx.at(k));
+      hist[(int64_t)k * ln.HP] = s;
+    }
+  }
+  for (int t = te; t < t1; ++t) dX[(int64_t)(t - t0) * ln.HP] = from_f<T>(0.f);
+
+  // ---- reverse recurrence  g_t = C_t dy_t + exp(dt_{t+1} A) g_{t+1} -------------------------------------------
+  const bool dense_b = bc4_dense(g.dB), dense_c = bc4_dense(g.dC), dense_z = has_z && bc4_dense(g.dz);
+  const bool warp_heads = (a.proj & 31) == 0;  // a warp's 32 lanes share their head: (b, t, h) sums reduce in the warp first
   float dA_acc = 0.f, dD_acc = 0.f;
-  for (int t = a.len - 1; t >= valid; --t) dX[((int64_t)b * a.len + t) * HP + hp] = from_f<T>(0.f);
-  for (int t = valid - 1; t >= 0; --t) {
-    const int64_t e = ((int64_t)b * a.len + t) * HP + hp;
-    const float x = to_f<T>(X[e]);
-    const float dt = to_f<T>(DT[((int64_t)b * a.len + t) * a.heads + h]);
-    const float Bv = bc4_load(a.Bm, a.par_dtype, b, t, h, q);
-    const float Cv = bc4_load(a.Cm, a.par_dtype, b, t, h, q);
-    const float st = g.history[e];
-    const float sp = t > 0 ? g.history[e - HP] : s0;
-    const float dout = to_f<T>(dY[e]);
+  const float A_nat = ln.Av * kLn2;
+  auto back = [&](int k, float x, float d, float bv, float cv, float zv, float dout, float st, float sp) {
+    const int t = t0 + k;
     float dyv = dout;
-    if (a.z.ptr) {
-      const float zv = bc4_load(a.z, a.par_dtype, b, t, h, q);
-      const float sg = sigmoid_f(zv);
-      const float yfull = fmaf(Dv, x, st * Cv);
-      atomicAdd(bc4_ptr(g.dz, b, t, h, q), dout * yfull * sg * (1.f + zv * (1.f - sg)));
+    if (has_z) {
+      const float sg = sigmoid_fast(zv);
+      const float yfull = fmaf(ln.Dv, x, st * cv);
+      const float dzv = dout * yfull * sg * (1.f + zv * (1.f - sg));
+      if (dense_z) *bc4_ptr(g.dz, ln.b, t, ln.h, ln.q) = dzv;
+      else if (a.z.sq == 0) add_reduced(bc4_ptr(g.dz, ln.b, t, ln.h, 0), dzv, warp_heads);
+      else atomicAdd(bc4_ptr(g.dz, ln.b, t, ln.h, ln.q), dzv);
       dyv = dout * zv * sg;
     }
-    const float da = expf(dt * Av);
-    const float G = fmaf(Cv, dyv, carry);
-    atomicAdd(bc4_ptr(g.dC, b, t, h, q), dyv * st);
-    atomicAdd(bc4_ptr(g.dB, b, t, h, q), G * dt * x);
-    dX[e] = from_f<T>(fmaf(dyv, Dv, G * dt * Bv));
+    const float da = ex2_approx(d * ln.Av);
+    const float G = fmaf(cv, dyv, carry);
+    if (dense_c) *bc4_ptr(g.dC, ln.b, t, ln.h, ln.q) = dyv * st;
+    else atomicAdd(bc4_ptr(g.dC, ln.b, t, ln.h, ln.q), dyv * st);
+    if (dense_b) *bc4_ptr(g.dB, ln.b, t, ln.h, ln.q) = G * d * x;
+    else atomicAdd(bc4_ptr(g.dB, ln.b, t, ln.h, ln.q), G * d * x);
+    dX[(int64_t)k * ln.HP] = from_f<T>(fmaf(dyv, ln.Dv, G * d * bv));
     const float gsa = G * sp * da;
-    atomicAdd(g.ddt + ((int64_t)b * a.len + t) * a.heads + h, fmaf(G, Bv * x, gsa * Av));
-    dA_acc = fmaf(gsa, dt, dA_acc);
+    add_reduced(g.ddt + ((int64_t)ln.b * a.len + t) * a.heads + ln.h, fmaf(G, bv * x, gsa * A_nat), warp_heads);
+    dA_acc = fmaf(gsa, d, dA_acc);
     dD_acc = fmaf(dyv, x, dD_acc);
     carry = G * da;
+  };
+  int k = n;
+  for (; k - kChunkUnroll >= 0; k -= kChunkUnroll) {
+    float x[kChunkUnroll], d[kChunkUnroll], bv[kChunkUnroll], cv[kChunkUnroll], zv[kChunkUnroll], dout[kChunkUnroll], st[kChunkUnroll + 1];
+#pragma unroll
+    for (int i = 0; i < kChunkUnroll; ++i) {
+      const int kk = k - 1 - i;
+      x[i] = sx.at(kk), d[i] = sdt.at(kk), bv[i] = sB.at(kk), cv[i] = sC.at(kk), dout[i] = sdy.at(kk);
+      zv[i] = has_z ? sz.at(kk) : 0.f;
+      st[i] = hist[(int64_t)kk * ln.HP];
+    }
+    st[kChunkUnroll] = k - kChunkUnroll > 0 ? hist[(int64_t)(k - kChunkUnroll - 1) * ln.HP] : s0;
+#pragma unroll
+    for (int i = 0; i < kChunkUnroll; ++i) back(k - 1 - i, x[i], d[i], bv[i], cv[i], zv[i], dout[i], st[i], st[i + 1]);
   }
-  atomicAdd(bc4_ptr(g.dA, 0, 0, h, q), dA_acc);
-  if (g.dD.ptr) atomicAdd(bc4_ptr(g.dD, 0, 0, h, q), dD_acc);
-  if (g.dinitial.ptr) atomicAdd(bc4_ptr(g.dinitial, b, 0, h, q), carry);
+  for (; k > 0; --k) {
+    const int kk = k - 1;
+    back(kk, sx.at(kk), sdt.at(kk), sB.at(kk), sC.at(kk), has_z ? sz.at(kk) : 0.f, sdy.at(kk), hist[(int64_t)kk * ln.HP],
+         kk > 0 ? hist[(int64_t)(kk - 1) * ln.HP] : s0);
+  }
+  atomicAdd(bc4_ptr(g.dA, 0, 0, ln.h, ln.q), dA_acc);
+  if (g.dD.ptr) {
+    if (a.D.sq == 0) add_reduced(bc4_ptr(g.dD, 0, 0, ln.h, 0), dD_acc, warp_heads);
+    else atomicAdd(bc4_ptr(g.dD, 0, 0, ln.h, ln.q), dD_acc);
+  }
+  if (MODE == 0 && g.dinitial.ptr) atomicAdd(bc4_ptr(g.dinitial, ln.b, 0, ln.h, ln.q), carry);
 }
 
 static int chunk_validate(const ssm_chunk_args* a) {
@@ -182,22 +361,45 @@ static int chunk_validate(const ssm_chunk_args* a) {
   return SSM_OK;
 }
 
-template <typename T>
-static int chunk_fwd_t(const ssm_chunk_args& a, cudaStream_t st) {
+template <typename T, typename PT>
+static int chunk_fwd_t(const ssm_chunk_args& a, cudaStream_t st, bool through_phase2_only = false) {
   const int HP = a.heads * a.proj;
   const unsigned gx = (HP + kChunkThreads - 1) / kChunkThreads;
   const int nchunks = (a.len + a.chunk_size - 1) / a.chunk_size;
   if (!a.scratch || nchunks <= 1) {
-    chunk_fwd_kernel<T, 0><<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(a, 1);
+    chunk_fwd_kernel<T, PT, 0><<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(a, 1);
     return launch_status("chunk_fwd_kernel<serial>");
   }
   SSM_REQUIRE(nchunks <= 65535, SSM_ERR_TOO_LARGE, "ssd_chunk_scan: more than 65535 chunks");
-  chunk_fwd_kernel<T, 1><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(a, nchunks);
+  chunk_fwd_kernel<T, PT, 1><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(a, nchunks);
   if (int rc = launch_status("chunk_fwd_kernel<local>")) return rc;
   chunk_carry_kernel<<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(a, nchunks);
   if (int rc = launch_status("chunk_carry_kernel")) return rc;
-  chunk_fwd_kernel<T, 3><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(a, nchunks);
+  if (through_phase2_only) return SSM_OK;
+  chunk_fwd_kernel<T, PT, 3><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(a, nchunks);
   return launch_status("chunk_fwd_kernel<apply>");
+}
+
+template <typename T, typename PT>
+static int chunk_bwd_t(const ssm_chunk_bwd_args& g, cudaStream_t st) {
+  const ssm_chunk_args& a = g.fwd;
+  const int HP = a.heads * a.proj;
+  const unsigned gx = (HP + kChunkThreads - 1) / kChunkThreads;
+  const int nchunks = (a.len + a.chunk_size - 1) / a.chunk_size;
+  if (!g.scratch || nchunks <= 1 || nchunks > 65535) {
+    chunk_bwd_kernel<T, PT, 0><<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(g, 1);
+    return launch_status("chunk_bwd_kernel<serial>");
+  }
+  // states entering every chunk (forward phases 1 and 2 on the backward call's scratch; no final state, no Y)
+  ssm_chunk_args f = a;
+  f.scratch = g.scratch, f.final_state = nullptr;
+  if (int rc = chunk_fwd_t<T, PT>(f, st, true)) return rc;
+  chunk_bwd_local_kernel<T, PT><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
+  if (int rc = launch_status("chunk_bwd_local_kernel")) return rc;
+  chunk_bwd_carry_kernel<<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
+  if (int rc = launch_status("chunk_bwd_carry_kernel")) return rc;
+  chunk_bwd_kernel<T, PT, 1><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
+  return launch_status("chunk_bwd_kernel");
 }
 
 }  // namespace ssmb
@@ -210,16 +412,25 @@ extern "C" int64_t ssm_chunk_scan_scratch_floats(int32_t batch, int32_t len, int
   return 2 * (int64_t)batch * nchunks * heads * proj;
 }
 
+extern "C" int64_t ssm_chunk_scan_bwd_scratch_floats(int32_t batch, int32_t len, int32_t heads, int32_t proj, int32_t chunk_size) {
+  if (chunk_size < 1) return 0;
+  const int64_t nchunks = (len + (int64_t)chunk_size - 1) / chunk_size;
+  return 3 * (int64_t)batch * nchunks * heads * proj;  // decay products, states entering, adjoints entering every chunk
+}
+
 extern "C" int ssm_chunk_scan_fwd(const ssm_chunk_args* a, ssm_stream_t stream) {
   if (int rc = chunk_validate(a)) return rc;
   if (a->batch == 0 || a->heads == 0 || a->proj == 0) return SSM_OK;
   SSM_REQUIRE(a->A.ptr && a->Bm.ptr && a->Cm.ptr, SSM_ERR_NULL, "ssd_chunk_scan: A, B and C are required");
   SSM_REQUIRE(a->len == 0 || (a->X && a->dt && a->Y), SSM_ERR_NULL, "ssd_chunk_scan: X, dt and Y are required");
+  SSM_REQUIRE(a->par_dtype == a->io_dtype || a->par_dtype == SSM_F32, SSM_ERR_UNSUPPORTED,
+              "ssd_chunk_scan: B, C and z must have the element type of X, or float32");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool same = a->par_dtype == a->io_dtype;
   switch (a->io_dtype) {
-    case SSM_F32: return chunk_fwd_t<float>(*a, st);
-    case SSM_BF16: return chunk_fwd_t<__nv_bfloat16>(*a, st);
-    default: return chunk_fwd_t<__half>(*a, st);
+    case SSM_F32: return chunk_fwd_t<float, float>(*a, st);
+    case SSM_BF16: return same ? chunk_fwd_t<__nv_bfloat16, __nv_bfloat16>(*a, st) : chunk_fwd_t<__nv_bfloat16, float>(*a, st);
+    default: return same ? chunk_fwd_t<__half, __half>(*a, st) : chunk_fwd_t<__half, float>(*a, st);
   }
 }
 
@@ -232,13 +443,13 @@ extern "C" int ssm_chunk_scan_bwd(const ssm_chunk_bwd_args* g, ssm_stream_t stre
   SSM_REQUIRE(g->dY && g->dX && g->ddt && g->dA.ptr && g->dB.ptr && g->dC.ptr && g->history, SSM_ERR_NULL,
               "ssd_chunk_scan_backward: missing gradient buffer");
   SSM_REQUIRE(!a->z.ptr || g->dz.ptr, SSM_ERR_NULL, "ssd_chunk_scan_backward: dz is required when z is given");
+  SSM_REQUIRE(a->par_dtype == a->io_dtype || a->par_dtype == SSM_F32, SSM_ERR_UNSUPPORTED,
+              "ssd_chunk_scan_backward: B, C and z must have the element type of X, or float32");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int HP = a->heads * a->proj;
-  const dim3 grid((HP + kChunkThreads - 1) / kChunkThreads, 1, a->batch);
+  const bool same = a->par_dtype == a->io_dtype;
   switch (a->io_dtype) {
-    case SSM_F32: chunk_bwd_kernel<float><<<grid, kChunkThreads, 0, st>>>(*g); break;
-    case SSM_BF16: chunk_bwd_kernel<__nv_bfloat16><<<grid, kChunkThreads, 0, st>>>(*g); break;
-    default: chunk_bwd_kernel<__half><<<grid, kChunkThreads, 0, st>>>(*g); break;
+    case SSM_F32: return chunk_bwd_t<float, float>(*g, st);
+    case SSM_BF16: return same ? chunk_bwd_t<__nv_bfloat16, __nv_bfloat16>(*g, st) : chunk_bwd_t<__nv_bfloat16, float>(*g, st);
+    default: return same ? chunk_bwd_t<__half, __half>(*g, st) : chunk_bwd_t<__half, float>(*g, st);
   }
-  return launch_status("chunk_bwd_kernel");
 }

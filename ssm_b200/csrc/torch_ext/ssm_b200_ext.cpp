@@ -404,8 +404,8 @@ struct ChunkCtx {
     }
     if (init_.has_value()) TORCH_CHECK(init_->dim() == 3 && init_->size(0) == nb && init_->size(1) == nh && init_->size(2) == np, "initial_states must have shape (B, H, P).");
     // B, C and z share one run-time element type inside the kernel
-    at::ScalarType pd = B_.scalar_type();
-    const bool same = C_.scalar_type() == pd && (!z_.has_value() || z_->scalar_type() == pd) && io_dtype_ok(B_);
+    at::ScalarType pd = X_.scalar_type();  // the kernels take X's element type or fp32
+    const bool same = B_.scalar_type() == pd && C_.scalar_type() == pd && (!z_.has_value() || z_->scalar_type() == pd);
     if (!same) pd = at::kFloat;
     par = pd == at::kFloat ? SSM_F32 : pd == at::kBFloat16 ? SSM_BF16 : SSM_F16;
     B = B_.detach().to(pd).contiguous(), C = C_.detach().to(pd).contiguous();
@@ -459,7 +459,9 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, OptTensor, OptTensor, OptTens
   Tensor gy = like(grad_output, c.X);
   ssm_chunk_bwd_args g{};
   c.fill(g.fwd);
+  Tensor scratch = at::empty({std::max<int64_t>(1, ssm_chunk_scan_bwd_scratch_floats((int)c.nb, (int)c.nl, (int)c.nh, (int)c.np, c.chunk))}, f32);
   g.dY = gy.data_ptr(), g.dX = dX.data_ptr(), g.ddt = ddt.data_ptr<float>(), g.history = hist.data_ptr<float>();
+  g.scratch = scratch.data_ptr<float>();
   set_bc4(g.dA, dA, c.kA), set_bc4(g.dB, dB, c.kB), set_bc4(g.dC, dC, c.kC), set_bc4(g.dD, dD, c.kD), set_bc4(g.dz, dz, c.kz),
       set_bc4(g.dinitial, dI, Kind::BHP);
   run(ssm_chunk_scan_bwd(&g, stream_of(c.X)));

@@ -691,7 +691,7 @@ class _ChunkCtx:
             raise ValueError("initial_states must have shape (B, H, P).")
         # B, C and z share one run-time dtype in the kernel
         par = [t for t in (B, C_, z) if t is not None]
-        pd = par[0].dtype if all(t.dtype == par[0].dtype for t in par) and par[0].dtype in _CODES else torch.float32
+        pd = X.dtype if all(t.dtype == X.dtype for t in par) else torch.float32  # the kernels take X's element type or fp32
         self.par = _CODES[pd]
         self.B, self.C = _c(B.to(pd)), _c(C_.to(pd))
         self.z = None if z is None else _c(z.to(pd))
@@ -753,7 +753,8 @@ class _ChunkScanFn(torch.autograd.Function):
         g = L.ChunkBwdArgs()
         cc.fill(g.fwd)
         gy = _c(gY.to(cc.X.dtype))
-        g.dY, g.dX, g.ddt, g.history = _p(gy), _p(dX), _p(ddt), _p(hist)
+        scratch = torch.empty(max(1, int(lib.ssm_chunk_scan_bwd_scratch_floats(nb, nl, nh, npj, cc.chunk))), dtype=torch.float32, device=dev)
+        g.dY, g.dX, g.ddt, g.history, g.scratch = _p(gy), _p(dX), _p(ddt), _p(hist), _p(scratch)
         _set_bc4(g.dA, *_bc4(dA, cc.kA))
         _set_bc4(g.dB, *_bc4(dB, cc.kB))
         _set_bc4(g.dC, *_bc4(dC, cc.kC))
