@@ -397,6 +397,11 @@ typedef struct {
 } ssm_ssd_args;
 
 int ssm_ssd_supported(int32_t headdim, int32_t nstate, int32_t chunk_size, int32_t io_dtype);
+
+/* Self-test of the bounded device-side waits (no counterpart upstream).  Launches one warp that waits on a barrier nothing
+ * arms, with a limit of `probes` probes of about a microsecond each (1 .. 100000); when the limit runs out the kernel
+ * writes 3 to *status (device int) and returns normally -- the error path of ssm_ssd_fwd's kernels, without a fault. */
+int ssm_ssd_wait_selftest(int32_t* status, int32_t probes, ssm_stream_t stream);
 int64_t ssm_ssd_scratch_bytes(int32_t batch, int32_t len, int32_t heads);
 int64_t ssm_ssd_state_scratch_bytes(int32_t batch, int32_t len, int32_t heads);
 int ssm_ssd_fwd(const ssm_ssd_args* args, ssm_stream_t stream);

@@ -152,6 +152,7 @@ ENTRY_POINTS = {
     "ssm_fused_add_norm_bwd": (C.c_int, [C.POINTER(NormBwdArgs), vp]),
     "ssm_fused_add_norm_bwd_noalloc": (C.c_int, [C.POINTER(NormBwdArgs), vp]),
     "ssm_ssd_supported": (C.c_int, [i32, i32, i32, i32]),
+    "ssm_ssd_wait_selftest": (C.c_int, [vp, i32, vp]),
     "ssm_ssd_scratch_bytes": (C.c_int64, [i32, i32, i32]),
     "ssm_ssd_state_scratch_bytes": (C.c_int64, [i32, i32, i32]),
     "ssm_ssd_fwd": (C.c_int, [C.POINTER(SsdArgs), vp]),

@@ -786,6 +786,17 @@ __global__ void __launch_bounds__(256) ssd_fold_shards_kernel(const float* __res
   out[i] = s;
 }
 
+// Self-test of the bounded waits: one warp waits on an mbarrier that nothing ever arms, with a limit of `probes` probes
+// (about a microsecond each).  The wait runs out, the kernel records status 3 and returns normally: the path every
+// kernel above takes if one of its copies or MMAs never completes, exercised without a fault.
+__global__ void __launch_bounds__(32) ssd_wait_selftest_kernel(int32_t* status, int probes) {
+  __shared__ __align__(8) uint64_t mbar;
+  if (threadIdx.x == 0) tc::mbar_init(tc::smem_u32(&mbar), 1);
+  __syncwarp();
+  const bool ok = tc::mbar_wait(tc::smem_u32(&mbar), 0, probes);
+  if (!ok && threadIdx.x == 0 && status) atomicExch(status, 3);
+}
+
 template <typename T>
 static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
   const int nchunks = (a.len + kQ - 1) / kQ;
@@ -886,6 +897,13 @@ extern "C" int ssm_ssd_fold_shards(const float* gathered, int32_t world, int32_t
   ssd_fold_shards_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       gathered, rank, ssm_ssd_shard_summary_floats(batch, heads), batch * heads, kP * kN, initial_states, incoming);
   return launch_status("ssd_fold_shards_kernel");
+}
+
+extern "C" int ssm_ssd_wait_selftest(int32_t* status, int32_t probes, ssm_stream_t stream) {
+  SSM_REQUIRE(status != nullptr, SSM_ERR_NULL, "ssd_wait_selftest: status is NULL");
+  SSM_REQUIRE(probes >= 1 && probes <= 100000, SSM_ERR_SHAPE, "ssd_wait_selftest: probes must be in [1, 100000]");
+  ssd_wait_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status, probes);
+  return launch_status("ssd_wait_selftest_kernel");
 }
 
 extern "C" int ssm_ssd_fwd(const ssm_ssd_args* a, ssm_stream_t stream) {

@@ -81,8 +81,8 @@ __device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count) {
 
 // Bounded wait on an mbarrier phase; returns false if the limit ran out (the caller records
 // the failure in the status word and unwinds, it never spins forever).
-__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
-  for (int it = 0; it < 200000; ++it) {  // each probe suspends for at most about a microsecond
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity, int limit = 200000) {
+  for (int it = 0; it < limit; ++it) {  // each probe suspends for at most about a microsecond
     uint32_t ok;
     asm volatile(
         "{\n\t"

@@ -152,6 +152,16 @@ def ssd_check_status(device: Optional[torch.device] = None) -> None:
     _DeviceStatus.of(torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)).poll(sync=True)
 
 
+def ssd_wait_selftest(probes: int = 100, device: Optional[torch.device] = None) -> None:
+    """Launch the library's wait self-test on ``device``: a warp waits on a barrier nothing arms and gives up after ``probes``
+    probes, recording status 3 like a tensor-core kernel whose copy never landed.  The next ``ssd_scan`` call (or
+    :func:`ssd_check_status`) then raises; the device and the context stay usable."""
+    st = _DeviceStatus.of(torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device))
+    with torch.cuda.device(st.word.device):
+        L.check(L.load().ssm_ssd_wait_selftest(st.word.data_ptr(), int(probes), _stream()))
+        st.after_launch()
+
+
 def _call(fn, args) -> None:
     try:
         L.check(fn(C.byref(args), _stream()))
@@ -1195,5 +1205,6 @@ __all__ = [
     "fused_layer_norm",
     "ssd_scan",
     "ssd_check_status",
+    "ssd_wait_selftest",
     "ssd_tensor_core_supported",
 ]

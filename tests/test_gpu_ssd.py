@@ -166,3 +166,25 @@ def test_shard_summary_and_fold_kernel_match_the_host_fold():
             L.check(L.load().ssm_ssd_fold_shards(gathered.data_ptr(), world, r, nb, nh, None if ini is None else ini.data_ptr(), out.data_ptr(),
                                                  torch.cuda.current_stream().cuda_stream))
             close(out, seqpar.fold_incoming_state(states, logps, r, ini), **FP32_TOL, what=f"incoming state of rank {r}")
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
+    """The library's self-test makes a bounded device wait run out (a barrier nothing arms, 100 probes).  The status word is
+    reported without a synchronisation by the next call, or at once by `ssd_check_status`; afterwards the same operator runs
+    and matches the oracle again."""
+    from ssm_b200 import ops
+
+    t = {k: (None if v is None else v.cuda()) for k, v in _inputs(1, 256, 2, 1, torch.bfloat16, seed=3, with_init=False).items()}
+    ops.ssd_check_status()  # clean before
+    ops.ssd_wait_selftest(100)
+    with pytest.raises(RuntimeError, match="bounded device-side wait ran out"):
+        ops.ssd_check_status()
+    ops.ssd_check_status()  # the report cleared the word
+    # the lazy path: the next operator call surfaces an earlier failure without synchronising for it
+    ops.ssd_wait_selftest(100)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="status 3"):
+        ops.ssd_scan(t["X"], t["dt"], t["A"], t["B"], t["C"], 256, dt_softplus=True)
+    Yg = ops.ssd_scan(t["X"], t["dt"], t["A"], t["B"], t["C"], 256, dt_softplus=True, check_status=True)
+    Yo = orc.ssd_scan(t["X"].cpu(), t["dt"].cpu(), t["A"].cpu(), t["B"].cpu(), t["C"].cpu(), 256, dt_softplus=True)
+    close(Yg, Yo, **SSD_TOL, what="Y after the reported failure", reduced=True)

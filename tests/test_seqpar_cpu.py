@@ -99,3 +99,52 @@ def test_fold_matches_sequential_chain():
     for r in range(R):
         torch.testing.assert_close(seqpar.fold_incoming_state(states, logp, r, init), s)
         s = seqpar.outgoing_state(s, states[r], logp[r])
+
+
+def _failing_worker(rank, world, port, out):
+    """Rank 1 raises before it joins the hand-off; the others must come back with an error instead of waiting forever."""
+    import datetime
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    try:
+        from ssm_b200 import seqpar
+
+        torch.set_num_threads(1)
+        nb, nh, npj, nn = 1, 2, 4, 8
+
+        def state_phase():
+            if rank == 1:
+                raise ValueError("injected failure on rank 1 before the hand-off")
+            return torch.ones(nb, nh, npj, nn), torch.zeros(nb, nh)
+
+        def finish_phase(s_in):
+            return torch.zeros(nb, 4, nh, npj), torch.ones(nb, nh, npj, nn)
+
+        seqpar.ssd_scan_sequence_parallel(state_phase, finish_phase, None, None)
+        out.put((rank, "completed"))
+    except ValueError as exc:
+        out.put((rank, f"raised: {exc}"))
+    except Exception as exc:  # noqa: BLE001  (the surviving ranks: a timed-out or broken collective)
+        out.put((rank, f"collective failed: {type(exc).__name__}"))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+def test_a_rank_that_raises_before_the_handoff_does_not_hang_the_others():
+    world = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=90) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert res[1].startswith("raised: injected failure")
+    for r in (0, 2):
+        assert res[r].startswith("collective failed"), res
