@@ -85,9 +85,16 @@ typedef struct {
    * a (D, B, L) buffer viewed as (B, D, L) is {len, batch*len}, which lets the projections
    * around the scan be plain 2-D GEMMs with no transposing copies. */
   int64_t row_sb, row_sd;
+  /* Optional time-parallel execution for calls whose (batch x dim) rows alone cannot fill the GPU (e.g. batch 1): the sequence
+   * is cut into split_segments pieces that are integrated in parallel and stitched by a short serial pass (the block-level
+   * prefix over the (A, B u) recurrence).  split_scratch: 2 * batch * dim * split_segments * nstate floats.  NULL or
+   * split_segments <= 1: one pass over the whole sequence.  ssm_scan_split_segments() suggests the count. */
+  float* split_scratch;
+  int32_t split_segments, reserved1;
 } ssm_scan_fwd_args;
 
 int ssm_scan_checkpoint_interval(void);
+int ssm_scan_split_segments(int32_t batch, int32_t dim, int32_t len, int32_t nstate);
 int ssm_selective_scan_fwd(const ssm_scan_fwd_args* args, ssm_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------

@@ -28,6 +28,7 @@ class ScanFwdArgs(C.Structure):
         ("D", fp), ("dt_bias", fp), ("initial_state", fp),
         ("out", vp), ("last_state", vp), ("checkpoints", fp),
         ("row_sb", i64), ("row_sd", i64),
+        ("split_scratch", fp), ("split_segments", i32), ("reserved1", i32),
     ]
 
 
@@ -136,6 +137,7 @@ ENTRY_POINTS = {
     "ssm_b200_abi_version": (C.c_int, []),
     "ssm_b200_last_error": (C.c_char_p, []),
     "ssm_scan_checkpoint_interval": (C.c_int, []),
+    "ssm_scan_split_segments": (C.c_int, [i32, i32, i32, i32]),
     "ssm_selective_scan_fwd": (C.c_int, [C.POINTER(ScanFwdArgs), vp]),
     "ssm_selective_scan_bwd": (C.c_int, [C.POINTER(ScanBwdArgs), vp]),
     "ssm_selective_state_step": (C.c_int, [C.POINTER(StepArgs), vp]),

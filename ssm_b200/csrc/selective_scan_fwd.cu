@@ -1,6 +1,7 @@
 // C-ABI entry point of the selective-scan forward; the kernels live in selective_scan_fwd.cuh and are
 // instantiated per element type in selective_scan_fwd_*.cu.
 #include "scan_common.cuh"
+#include "selective_scan_fwd_tiles.cuh"
 
 namespace ssmb {
 template <typename T>
@@ -40,6 +41,11 @@ int ssmb::scan_validate(const ssm_scan_fwd_args* a, ScanFlags* fl, int rows_per_
 }
 
 extern "C" int ssm_scan_checkpoint_interval(void) { return kScanCkpt; }
+
+extern "C" int ssm_scan_split_segments(int32_t batch, int32_t dim, int32_t len, int32_t nstate) {
+  if (batch <= 0 || dim <= 0 || len <= 0 || nstate > 32) return 1;  // the split lives in the tile kernel (d_state <= 32)
+  return ssmb::fwd_split_segments(batch, dim, len);
+}
 
 extern "C" int ssm_selective_scan_fwd(const ssm_scan_fwd_args* a, ssm_stream_t stream) {
   ScanFlags fl{};

@@ -53,8 +53,12 @@ struct FwdStepOps {  // everything of one step that does not depend on the state
   float2 da0, da1, db0, db1, c0, c1;
 };
 
-template <typename T, int NG>
-__global__ void __launch_bounds__(NG * 32, NG <= 4 ? 3 : 1) scan_fwd_tiles_kernel(const ssm_scan_fwd_args a, const ScanFlags fl) {
+// MODE 0: the whole sequence per CTA.  MODE 1 / 2: the sequence is cut into gridDim.z segments of `seg_tiles` tiles that run in
+// parallel (for calls whose rows alone cannot fill the machine): pass 1 integrates every segment from a zero state (segment 0:
+// from the initial state) and leaves its end state and decay product exp(A sum delta) in `split`; after the serial combine
+// (scan_split_combine_kernel) pass 2 replays every segment from its true incoming state and produces the outputs.
+template <typename T, int NG, int MODE>
+__global__ void __launch_bounds__(NG * 32, NG <= 4 ? 3 : 1) scan_fwd_tiles_kernel(const ssm_scan_fwd_args a, const ScanFlags fl, int seg_tiles) {
   using M = FwdTiles<T, NG>;
   constexpr int NP = M::NP, TL = M::TL, TLP = M::TLP, V = M::V, NT = M::NT;
   constexpr int CH = TL / V;  // 16-byte chunks per row and tile
@@ -91,11 +95,27 @@ __global__ void __launch_bounds__(NG * 32, NG <= 4 ? 3 : 1) scan_fwd_tiles_kerne
     h[j / 2].x = (n < N && a.initial_state) ? __ldg(a.initial_state + row * N + n) : 0.f;
     h[j / 2].y = (n + 1 < N && a.initial_state) ? __ldg(a.initial_state + row * N + n + 1) : 0.f;
   }
+  const int seg = MODE == 0 ? 0 : blockIdx.z, nseg = MODE == 0 ? 1 : gridDim.z;
+  // split scratch: [2][batch][dim][nseg][N]: end state / incoming state, then decay product
+  float* split_h = MODE == 0 ? nullptr : a.split_scratch + ((row * nseg + seg) * (int64_t)N);
+  float* split_p = MODE == 0 ? nullptr : split_h + (int64_t)a.batch * D * nseg * N;
+  if (MODE == 1 && seg > 0) h[0] = h[1] = make_float2(0.f, 0.f);
+  if (MODE == 2 && seg > 0) {  // segment 0 starts from the call's initial state, loaded above
+#pragma unroll
+    for (int j = 0; j < 4; j += 2) {
+      const int n = grp * 4 + j;
+      h[j / 2].x = n < N ? split_h[n] : 0.f;
+      h[j / 2].y = n + 1 < N ? split_h[n + 1] : 0.f;
+    }
+  }
+  float sumdl = 0.f;  // MODE 1: sum of this row's delta over the segment
 
   const int64_t boff = bc_row_offset(b, min(d0, D - 1), fl.rows_per_group, a.b_sb, a.b_sg);
   const int64_t coff = bc_row_offset(b, min(d0, D - 1), fl.rows_per_group, a.c_sb, a.c_sg);
 
   const int ntiles = (L + TL - 1) / TL;
+  const int k_begin = MODE == 0 ? 0 : seg * seg_tiles;
+  const int k_end = MODE == 0 ? ntiles : min(ntiles, k_begin + seg_tiles);
 
   // ---- B / C tiles travel through registers: one 16-byte chunk (8 or 4 steps of one state) per thread and slot, fetched a
   // ---- tile ahead with a plain vector load and written to the fp32 [step][state] tiles when its tile starts
@@ -169,16 +189,16 @@ __global__ void __launch_bounds__(NG * 32, NG <= 4 ? 3 : 1) scan_fwd_tiles_kerne
     cp_async_commit();
   };
 
-  if (ntiles > 0) {
-    fill_raw(0);
-    bc_fetch(0);
+  if (k_begin < k_end) {
+    fill_raw(k_begin);
+    bc_fetch(k_begin);
   }
 
-  for (int k = 0; k < ntiles; ++k) {
+  for (int k = k_begin; k < k_end; ++k) {
     const int t0 = k * TL;
     cp_async_wait_all();
     __syncthreads();  // raw tile k has landed for every thread; the other raw buffer, the fp32 tiles and the partials are free
-    if (k + 1 < ntiles) fill_raw(k + 1);
+    if (k + 1 < k_end) fill_raw(k + 1);
 
     const T* rawU = rawrows + (k & 1) * (3 * ROWS * TL);
     const T* rawD = rawU + ROWS * TL;
@@ -217,11 +237,11 @@ __global__ void __launch_bounds__(NG * 32, NG <= 4 ? 3 : 1) scan_fwd_tiles_kerne
       }
     }
     bc_store();
-    if (k + 1 < ntiles) bc_fetch(k + 1);  // lands while this tile is being processed
+    if (k + 1 < k_end) bc_fetch(k + 1);  // lands while this tile is being processed
     __syncthreads();  // fp32 tiles ready
 
     // ---- recurrence over the tile ----------------------------------------------------------
-    if (a.checkpoints && row_ok) {
+    if (MODE != 1 && a.checkpoints && row_ok) {
       float* ck = a.checkpoints + (row * ntiles + k) * N + grp * 4;
       if (grp * 4 + 3 < N && (N & 3) == 0) {
         *reinterpret_cast<float4*>(ck) = make_float4(h[0].x, h[0].y, h[1].x, h[1].y);
@@ -248,6 +268,7 @@ __global__ void __launch_bounds__(NG * 32, NG <= 4 ? 3 : 1) scan_fwd_tiles_kerne
         o.db0 = __fmul2_rn(du2, make_float2(b4.x, b4.y));
         o.db1 = __fmul2_rn(du2, make_float2(b4.z, b4.w));
         o.c0 = make_float2(c4.x, c4.y), o.c1 = make_float2(c4.z, c4.w);
+        if (MODE == 1) sumdl += dd4.x;
         return o;
       };
       FwdStepOps cur[4], nxt[4];
@@ -264,15 +285,18 @@ __global__ void __launch_bounds__(NG * 32, NG <= 4 ? 3 : 1) scan_fwd_tiles_kerne
         for (int i = 0; i < 4; ++i) {
           h[0] = __ffma2_rn(cur[i].da0, h[0], cur[i].db0);
           h[1] = __ffma2_rn(cur[i].da1, h[1], cur[i].db1);
-          const float2 acc = __ffma2_rn(cur[i].c1, h[1], __fmul2_rn(cur[i].c0, h[0]));
-          p[i] = acc.x + acc.y;
+          if (MODE != 1) {
+            const float2 acc = __ffma2_rn(cur[i].c1, h[1], __fmul2_rn(cur[i].c0, h[0]));
+            p[i] = acc.x + acc.y;
+          }
         }
-        *reinterpret_cast<float4*>(pP + q) = make_float4(p[0], p[1], p[2], p[3]);
+        if (MODE != 1) *reinterpret_cast<float4*>(pP + q) = make_float4(p[0], p[1], p[2], p[3]);
 #pragma unroll
         for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
       }
     }
     __syncthreads();  // every state group's partial sums are in place
+    if (MODE == 1) continue;  // pass 1 of a split call produces no output
 
     // ---- epilogue: add the state groups' partial sums, skip term, gate, store ---------------------
     for (int c = tid; c < ROWS * CH; c += NT) {
@@ -311,7 +335,18 @@ __global__ void __launch_bounds__(NG * 32, NG <= 4 ? 3 : 1) scan_fwd_tiles_kerne
     }
   }
 
-  if (a.last_state && row_ok) {
+  if (MODE == 1) {
+    if (row_ok) {
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        const int n = grp * 4 + j;
+        if (n < N) split_h[n] = h[j / 2].x, split_p[n] = ex2_approx(sumdl * A2[j / 2].x);
+        if (n + 1 < N) split_h[n + 1] = h[j / 2].y, split_p[n + 1] = ex2_approx(sumdl * A2[j / 2].y);
+      }
+    }
+    return;
+  }
+  if (a.last_state && row_ok && seg == nseg - 1) {
 #pragma unroll
     for (int j = 0; j < 4; j += 2) {
       const int n = grp * 4 + j;
@@ -321,14 +356,61 @@ __global__ void __launch_bounds__(NG * 32, NG <= 4 ? 3 : 1) scan_fwd_tiles_kerne
   }
 }
 
+// Serial pass over the segments of a split call: split_h[s] <- state entering segment s.  One thread per (row, state).
+static __global__ void __launch_bounds__(128) scan_split_combine_kernel(float* __restrict__ split, int64_t rows_states, int nstate, int nseg) {
+  const int64_t i = (int64_t)blockIdx.x * 128 + threadIdx.x;
+  if (i >= rows_states) return;
+  const int64_t row = i / nstate;
+  const int n = (int)(i % nstate);
+  float* hs = split + row * nseg * nstate + n;
+  const float* ps = hs + rows_states * nseg;
+  float h = 0.f;  // segment 0 was integrated from the call's initial state already
+  for (int s_ = 0; s_ < nseg; ++s_) {
+    const float local = hs[(int64_t)s_ * nstate];
+    hs[(int64_t)s_ * nstate] = h;
+    h = s_ == 0 ? local : fmaf(ps[(int64_t)s_ * nstate], h, local);
+  }
+}
+
+// Segments of a split call: enough to offer every SM about three CTAs, every segment at least two tiles long; 1 = no split.
+static inline int fwd_split_segments(int batch, int dim, int len) {
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t ctas = (int64_t)batch * ((dim + kTileRows - 1) / kTileRows);
+  const int tiles = (len + kScanCkpt - 1) / kScanCkpt;
+  if (ctas >= sms || tiles < 8) return 1;
+  int64_t want = (3 * sms + ctas - 1) / ctas;
+  const int most = tiles / 2;
+  if (want > most) want = most;
+  return want < 2 ? 1 : (int)want;
+}
+
 template <typename T, int NG>
 static int launch_fwd_tiles(const ssm_scan_fwd_args& a, const ScanFlags& fl, cudaStream_t st) {
   using M = FwdTiles<T, NG>;
-  dim3 grid((a.dim + kTileRows - 1) / kTileRows, a.batch);
-  auto kern = scan_fwd_tiles_kernel<T, NG>;
-  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)M::kBytes);
-  kern<<<grid, NG * 32, M::kBytes, st>>>(a, fl);
-  return launch_status("scan_fwd_tiles_kernel");
+  const int ntiles = (a.len + kScanCkpt - 1) / kScanCkpt;
+  const int nseg = a.split_scratch && a.split_segments > 1 ? a.split_segments : 1;
+  const unsigned gx = (a.dim + kTileRows - 1) / kTileRows;
+  if (nseg <= 1) {
+    auto kern = scan_fwd_tiles_kernel<T, NG, 0>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)M::kBytes);
+    kern<<<dim3(gx, a.batch), NG * 32, M::kBytes, st>>>(a, fl, ntiles);
+    return launch_status("scan_fwd_tiles_kernel");
+  }
+  const int seg_tiles = (ntiles + nseg - 1) / nseg;
+  const int used = (ntiles + seg_tiles - 1) / seg_tiles;  // segments that hold at least one tile
+  auto k1 = scan_fwd_tiles_kernel<T, NG, 1>;
+  auto k2 = scan_fwd_tiles_kernel<T, NG, 2>;
+  cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)M::kBytes);
+  cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)M::kBytes);
+  k1<<<dim3(gx, a.batch, used), NG * 32, M::kBytes, st>>>(a, fl, seg_tiles);
+  if (int rc = launch_status("scan_fwd_tiles_kernel<local>")) return rc;
+  const int64_t rs = (int64_t)a.batch * a.dim * a.nstate;
+  scan_split_combine_kernel<<<(unsigned)((rs + 127) / 128), 128, 0, st>>>(a.split_scratch, rs, a.nstate, used);
+  if (int rc = launch_status("scan_split_combine_kernel")) return rc;
+  k2<<<dim3(gx, a.batch, used), NG * 32, M::kBytes, st>>>(a, fl, seg_tiles);
+  return launch_status("scan_fwd_tiles_kernel<final>");
 }
 
 // True when the tile kernel covers this call: vectorisable rows and coefficients and a CTA's 32 rows inside one

@@ -162,6 +162,12 @@ std::tuple<Tensor, Tensor, Tensor> selective_scan(const Tensor& u, const Tensor&
   a.last_state = return_last_state ? last.data_ptr() : nullptr;
   a.last_dtype = a.io_dtype;
   a.checkpoints = cache.data_ptr<float>();
+  const int nseg = ssm_scan_split_segments((int)c.nb, (int)c.nd, (int)c.nl, (int)c.nn);  // > 1: cut the sequence into parallel segments
+  Tensor split;
+  if (nseg > 1) {
+    split = at::empty({2 * c.nb * c.nd * nseg * c.nn}, c.u.options().dtype(at::kFloat));
+    a.split_scratch = split.data_ptr<float>(), a.split_segments = nseg;
+  }
   run(ssm_selective_scan_fwd(&a, stream_of(c.u)));
   return {out, last, cache};
 }

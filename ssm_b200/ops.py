@@ -283,6 +283,11 @@ def _scan_forward(ctx: _ScanCtx, want_last: bool, want_ckpt: bool, last_dtype: t
     a = L.ScanFwdArgs()
     ctx.fill(a)
     a.out, a.last_state, a.checkpoints = _p(out), _p(last), _p(ck)
+    nseg = int(lib.ssm_scan_split_segments(nb, nd, nl, nn))  # > 1: too few rows to fill the GPU, the sequence is cut into parallel segments
+    split = None
+    if nseg > 1:
+        split = torch.empty(2 * nb * nd * nseg * nn, dtype=torch.float32, device=ctx.u.device)
+        a.split_scratch, a.split_segments = _p(split), nseg
     a.last_dtype = _CODES[last_dtype] if want_last else 0
     _call(lib.ssm_selective_scan_fwd, a)
     return out, last, ck

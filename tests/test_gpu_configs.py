@@ -248,3 +248,38 @@ def test_in_place_edit_between_forward_and_backward_is_detected():
     xin.add_(1.0)
     with pytest.raises(RuntimeError, match="modified in place"):
         y.sum().backward()
+
+
+@pytest.mark.parametrize("nb,nd,nl,dtype", [(1, 96, 2048, torch.float32), (2, 64, 1000, torch.bfloat16), (1, 32, 4096, torch.float32)])
+def test_time_parallel_split_of_a_small_grid_matches_oracle(nb, nd, nl, dtype):
+    """Few rows, long sequence: the forward cuts the sequence into parallel segments (local pass, serial combine, final
+    pass).  Output, final state and -- through the checkpoints it writes -- every gradient must match the oracle."""
+    from ssm_b200 import _lib, ops
+
+    assert _lib.load().ssm_scan_split_segments(nb, nd, nl, 16) > 1
+    gen = torch.Generator().manual_seed(nl + nd)
+    ins = dict(u=torch.randn(nb, nd, nl, generator=gen).to(dtype), delta=(torch.randn(nb, nd, nl, generator=gen) - 2).to(dtype),
+               A=-torch.exp(torch.randn(nd, 16, generator=gen) * 0.5), B=torch.randn(nb, 1, 16, nl, generator=gen).to(dtype),
+               C=torch.randn(nb, 1, 16, nl, generator=gen).to(dtype), D=torch.randn(nd, generator=gen), z=torch.randn(nb, nd, nl, generator=gen).to(dtype),
+               init=torch.randn(nb, nd, 16, generator=gen) * 0.5)
+    tol = FP32_TOL if dtype == torch.float32 else HALF_TOL
+    lg = {k: v.clone().cuda().requires_grad_(True) for k, v in ins.items()}
+    yg, sg = ops.selective_scan(lg["u"], lg["delta"], lg["A"], lg["B"], lg["C"], D=lg["D"], z=lg["z"], softplus=True, return_last_state=True,
+                                initial_state=lg["init"], keep_state_fp32=True)
+    # the same recurrence (reference.py:173-188) started from `init`, in fp32 on the CPU
+    f = {k: v.float() for k, v in ins.items()}
+    lo = {k: v.clone().requires_grad_(True) for k, v in f.items()}
+    h, ys = lo["init"], []
+    dl = F.softplus(lo["delta"])
+    for i in range(nl):
+        h = torch.exp(dl[:, :, i, None] * lo["A"][None]) * h + (dl[:, :, i] * lo["u"][:, :, i])[..., None] * lo["B"][:, 0, :, i][:, None, :]
+        ys.append((h * lo["C"][:, 0, :, i][:, None, :]).sum(-1))
+    yo = (torch.stack(ys, -1) + lo["D"][None, :, None] * lo["u"]) * F.silu(lo["z"])
+    close(yg, yo, **tol, what="y")
+    close(sg, h, **FP32_TOL if dtype == torch.float32 else tol, what="last state")
+    gen2 = torch.Generator().manual_seed(1)
+    wy, ws = torch.randn(nb, nd, nl, generator=gen2).to(dtype).float(), torch.randn(nb, nd, 16, generator=gen2)  # weights the output dtype can hold
+    go = torch.autograd.grad((yo * wy).sum() + (h * ws).sum(), list(lo.values()))
+    gg = torch.autograd.grad((yg.float() * wy.cuda()).sum() + (sg * ws.cuda()).sum(), list(lg.values()))
+    for k, a_, b_ in zip(ins, gg, go):
+        close(a_, b_, **tol, what=f"d{k}", reduced=k in REDUCED)
