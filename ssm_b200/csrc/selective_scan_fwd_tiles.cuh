@@ -372,7 +372,7 @@ static __global__ void __launch_bounds__(128) scan_split_combine_kernel(float* _
   }
 }
 
-// Segments of a split call: enough to offer every SM about three CTAs, every segment at least two tiles long; 1 = no split.
+// Segments of a split call: enough to offer every SM about two CTAs, every segment at least four tiles long; 1 = no split.
 static inline int fwd_split_segments(int batch, int dim, int len) {
   int sms = 148, dev = 0;
   cudaGetDevice(&dev);
@@ -380,8 +380,8 @@ static inline int fwd_split_segments(int batch, int dim, int len) {
   const int64_t ctas = (int64_t)batch * ((dim + kTileRows - 1) / kTileRows);
   const int tiles = (len + kScanCkpt - 1) / kScanCkpt;
   if (ctas >= sms || tiles < 8) return 1;
-  int64_t want = (3 * sms + ctas - 1) / ctas;
-  const int most = tiles / 2;
+  int64_t want = (2 * sms + ctas - 1) / ctas;
+  const int most = tiles / 4;
   if (want > most) want = most;
   return want < 2 ? 1 : (int)want;
 }
