@@ -828,7 +828,7 @@ def run_single(args):
         val = r["layer_graph_us"] or r["layer_eager_us"]
         ms, value, unit, metric, hib = val * 1e-3, val, "us/step", "decode_step_us", False
         ach = r["state_kernels_bytes"] / (r["state_kernels_us"] * 1e-6) / 1e9
-        roof = {"kernel": "conv_update_kernel + step_fwd_vec_kernel (Mamba-1 state 256 x 5120 x 16, conv window 256 x 5120 x 4)", "bound": "hbm",
+        roof = {"kernel": "conv_update_kernel + step_fwd_fast_kernel (Mamba-1 state 256 x 5120 x 16, conv window 256 x 5120 x 4)", "bound": "hbm",
                 "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": kind, "traffic": None,
                 "us_per_launch_pair": r["state_kernels_us"], "layer_eager_us": r["layer_eager_us"], "layer_graph_us": r["layer_graph_us"],
                 "mamba2_step_us": r["mamba2_step_us"], "mamba2_step_frac": r["mamba2_step_bytes"] / (r["mamba2_step_us"] * 1e-6) / 1e9 / peak}

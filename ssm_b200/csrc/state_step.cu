@@ -123,6 +123,91 @@ __global__ void __launch_bounds__(kStepThreads) step_fwd_vec_kernel(const ssm_st
   }
 }
 
+// Four consecutive B or C values of compile-time element type BT as fp32 (one 8- or 16-byte load).
+template <typename BT>
+__device__ __forceinline__ void load_bc4(const void* base, int64_t off, float (&v)[4]) {
+  if constexpr (sizeof(BT) == 4) {
+    const float4 q = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off));
+    v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+  } else {
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const BT*>(base) + off));
+    const BT* e = reinterpret_cast<const BT*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = to_f<BT>(e[i]);
+  }
+}
+
+// The same fast path with B / C rows read as vectors: unit state stride, every (batch, group) row of B and C aligned to the
+// vector, element type BT known at compile time.  This is the layout decoding uses (B, C of shape (batch, groups, nstate));
+// it replaces 2 x nstate scalar loads with run-time type dispatch per thread by 2 x nstate / 4 vector loads.
+template <typename T, typename BT, int NV, int LPR>
+__global__ void __launch_bounds__(kStepThreads) step_fwd_fast_kernel(const ssm_step_args a) {
+  const int64_t gid = (int64_t)blockIdx.x * kStepThreads + threadIdx.x;
+  const int64_t rows = (int64_t)a.batch * a.dim;
+  const int64_t row_raw = gid / LPR;
+  const bool live = row_raw < rows;
+  const int64_t row = live ? row_raw : rows - 1;
+  const int sg = (int)(gid % LPR);
+  const int b = (int)(row / a.dim), d = (int)(row % a.dim);
+  constexpr int N = 4 * NV * LPR;
+  const int head = a.param_heads > 0 ? d / (a.dim / a.param_heads) : d;
+  const int64_t prow = a.param_heads > 0 ? (int64_t)b * a.param_heads + head : row;
+  float* st = a.state + row * N;
+  float4 s[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) s[v] = __ldcs(reinterpret_cast<const float4*>(st + (sg + v * LPR) * 4));
+  const int g = d / (a.dim / a.bc_groups);
+  const int64_t boff = (int64_t)b * a.b_sb + (int64_t)g * a.b_sg;
+  const int64_t coff = (int64_t)b * a.c_sb + (int64_t)g * a.c_sg;
+  float Bv[NV][4], Cv[NV][4], An[NV][4];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int n0 = (sg + v * LPR) * 4;
+    load_bc4<BT>(a.Bm, boff + n0, Bv[v]);
+    load_bc4<BT>(a.Cm, coff + n0, Cv[v]);
+    if (a.param_heads == 0) {
+      const float4 q = __ldg(reinterpret_cast<const float4*>(a.A + (int64_t)d * N + n0));
+      An[v][0] = q.x * kLog2e, An[v][1] = q.y * kLog2e, An[v][2] = q.z * kLog2e, An[v][3] = q.w * kLog2e;
+    }
+  }
+  const float x = to_f<T>(reinterpret_cast<const T*>(a.x)[row]);
+  float dt = to_f<T>(reinterpret_cast<const T*>(a.dt)[prow]);
+  if (a.dt_bias) dt += __ldg(a.dt_bias + head);
+  if (a.dt_softplus) dt = softplus_fast(dt);
+  const float dtx = dt * x;
+  float y = 0.f;
+  if (a.param_heads > 0) {  // one decay for the whole head: a single ex2 per thread
+    const float da = ex2_approx(dt * __ldg(a.A + head) * kLog2e);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      float sv[4] = {s[v].x, s[v].y, s[v].z, s[v].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        sv[i] = fmaf(da, sv[i], dtx * Bv[v][i]);
+        y = fmaf(Cv[v][i], sv[i], y);
+      }
+      if (live) __stcs(reinterpret_cast<float4*>(st + (sg + v * LPR) * 4), make_float4(sv[0], sv[1], sv[2], sv[3]));
+    }
+  } else {
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      float sv[4] = {s[v].x, s[v].y, s[v].z, s[v].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        sv[i] = fmaf(ex2_approx(dt * An[v][i]), sv[i], dtx * Bv[v][i]);
+        y = fmaf(Cv[v][i], sv[i], y);
+      }
+      if (live) __stcs(reinterpret_cast<float4*>(st + (sg + v * LPR) * 4), make_float4(sv[0], sv[1], sv[2], sv[3]));
+    }
+  }
+  y = group_sum<LPR, 1>(y);
+  if (sg == 0 && live) {
+    if (a.D) y = fmaf(__ldg(a.D + head), x, y);
+    if (a.z) y *= silu_fast(to_f<T>(reinterpret_cast<const T*>(a.z)[row]));
+    reinterpret_cast<T*>(a.out)[row] = from_f<T>(y);
+  }
+}
+
 // Backward of the plain step.  One group of LPR lanes per row, parameter gradients by atomics.
 template <typename T, int LPR>
 __global__ void __launch_bounds__(kStepThreads) step_bwd_kernel(const ssm_step_bwd_args g) {
@@ -223,9 +308,39 @@ static int step_fwd_vec_launch(const ssm_step_args& a, cudaStream_t st) {
   return launch_status("step_fwd_vec_kernel");
 }
 
+template <typename T, typename BT, int NV, int LPR>
+static int step_fwd_fast_launch(const ssm_step_args& a, cudaStream_t st) {
+  const int64_t threads = (int64_t)a.batch * a.dim * LPR;
+  step_fwd_fast_kernel<T, BT, NV, LPR><<<(unsigned)((threads + kStepThreads - 1) / kStepThreads), kStepThreads, 0, st>>>(a);
+  return launch_status("step_fwd_fast_kernel");
+}
+template <typename T, typename BT>
+static int step_fwd_fast_n(const ssm_step_args& a, cudaStream_t st) {
+  switch (a.nstate) {
+    case 16: return step_fwd_fast_launch<T, BT, 4, 1>(a, st);
+    case 32: return step_fwd_fast_launch<T, BT, 4, 2>(a, st);
+    case 64: return step_fwd_fast_launch<T, BT, 4, 4>(a, st);
+    case 128: return step_fwd_fast_launch<T, BT, 4, 8>(a, st);
+    default: return step_fwd_fast_launch<T, BT, 4, 16>(a, st);
+  }
+}
+
 template <typename T>
 static int step_fwd_t(const ssm_step_args& a, cudaStream_t st) {
   if (aligned_to(a.state, 16) && aligned_to(a.A, 16)) {
+    // vector loads of B / C: unit state stride and rows that start on a vector boundary
+    const int bcb = dtype_size(a.bc_dtype);
+    const int64_t per = 16 / bcb / (bcb == 4 ? 1 : 2);  // elements per load: 4 (one 16-byte or one 8-byte load)
+    const bool n_ok = a.nstate == 16 || a.nstate == 32 || a.nstate == 64 || a.nstate == 128 || a.nstate == 256;
+    const bool bc_ok = a.b_sn == 1 && a.c_sn == 1 && a.b_sb % per == 0 && a.b_sg % per == 0 && a.c_sb % per == 0 && a.c_sg % per == 0 &&
+                       aligned_to(a.Bm, 4 * bcb) && aligned_to(a.Cm, 4 * bcb);
+    if (n_ok && bc_ok) {
+      switch (a.bc_dtype) {
+        case SSM_F32: return step_fwd_fast_n<T, float>(a, st);
+        case SSM_BF16: return step_fwd_fast_n<T, __nv_bfloat16>(a, st);
+        default: return step_fwd_fast_n<T, __half>(a, st);
+      }
+    }
     switch (a.nstate) {
       case 4: return step_fwd_vec_launch<T, 1, 1>(a, st);
       case 8: return step_fwd_vec_launch<T, 2, 1>(a, st);
