@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define SSM_B200_ABI_VERSION 2
+#define SSM_B200_ABI_VERSION 3
 
 /* element types of activation tensors */
 enum { SSM_F32 = 0, SSM_BF16 = 1, SSM_F16 = 2 };
@@ -380,11 +380,25 @@ int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* args, ssm_stream_t s
  * given initial_states on top of what phase 1 left in the scratch (by linearity), writes
  * the corrected final_states and produces Y.  A sequence shard uses 1, exchanges final
  * states with its neighbours, then 2.
+ * dt_mode: 0 = dt is (batch, len, heads) in io_dtype and goes through dt_bias / dt_softplus.  1 = dt is fp32 and holds
+ * the step sizes as they are used (dt_bias and dt_softplus are ignored).  3 = as 1, and the step size enters the
+ * decay exp(dt A) only: the inputs are added with unit weight, S_t = exp(dt_t A) S_{t-1} + x_t B_t^T.  Modes 1 and 3
+ * are what the backward pass uses to run the adjoint recurrence through the same kernels.
+ * row_dots: (batch, len, heads) fp32, zero-filled by the caller.  When given, z is not a gate: Y is written ungated and
+ * row_dots[b, t, h] receives sum_p y[p] z[p], with y taken before the D x term and before rounding to io_dtype (the
+ * backward pass forms dy . y and d(dt x) . x this way).
+ * row_scale: (batch, len, heads) fp32 positive weights: output row t of head h is multiplied by row_scale[b, t, h],
+ * applied to the decay mask before it is rounded to the operand dtype (so a pass weighted this way rounds the same
+ * masked tile as the forward pass, whose mask carries dt of the source step).
+ * ws_state_in_f32: optional (batch, nchunks, heads, headdim * nstate) fp32: ws_state_in before rounding, same element order.
+ * bc_width: stored width of the rows of Bm and Cm.  0 or nstate: (batch, len, groups, nstate).  64: (batch, len, groups, 64),
+ * read as nstate-wide rows whose upper part is zero (the tensor-map copies fill what lies outside the tensor with
+ * zeros) -- how the backward pass feeds x and dy in the places of B and C.
  * ------------------------------------------------------------------------------------- */
 typedef struct {
   int32_t batch, len, heads, headdim;
   int32_t nstate, groups, chunk_size, io_dtype;
-  int32_t dt_softplus, d_has_p, phase, reserved1;
+  int32_t dt_softplus, d_has_p, phase, dt_mode;
   const void* X;
   const void* dt;
   const float* A;
@@ -401,6 +415,11 @@ typedef struct {
   float* ws_state;
   void* ws_state_in;
   int32_t* status; /* nullable */
+  float* row_dots; /* nullable */
+  const float* row_scale; /* nullable */
+  int32_t bc_width;       /* 0 (= nstate) or 64 */
+  int32_t reserved2;
+  float* ws_state_in_f32; /* nullable */
 } ssm_ssd_args;
 
 int ssm_ssd_supported(int32_t headdim, int32_t nstate, int32_t chunk_size, int32_t io_dtype);
@@ -421,6 +440,47 @@ int ssm_ssd_fwd(const ssm_ssd_args* args, ssm_stream_t stream);
 int64_t ssm_ssd_shard_summary_floats(int32_t batch, int32_t heads);
 int ssm_ssd_fold_shards(const float* gathered, int32_t world, int32_t rank, int32_t batch, int32_t heads, const float* initial_states,
                         float* incoming, ssm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Backward of the state-space-dual scan in the dual form (no counterpart upstream, whose Mamba-2 scan has no d_state
+ * axis).  Its contractions are four more runs of ssm_ssd_fwd (dt_mode 1 / 3, row_dots, row_scale, bc_width above) on
+ * transformed operands; the entry points below are the bandwidth passes around them.  `len` is the sequence length
+ * rounded up to whole chunks (the length of the work tensors dy, dy_rev, y_plain, dx_rev), `len_valid` the length
+ * of the caller's tensors (gY, z, X, dX, dz); work rows beyond len_valid are written as zeros.
+ *   ssm_ssd_bwd_gate    dy = gY * silu(z) (gY when z is NULL), in time order and time-reversed (dy_rev)
+ *   ssm_ssd_bwd_finish  dz = gY (y_plain + D x) silu'(z);  dX = reversed(dx_rev) + D dy;  dD (heads) or (heads, headdim)
+ *                       += sum dy x (zero-filled by the caller; NULL when D is NULL)
+ *   ssm_time_flip       dst[b, len - 1 - t] = src[b, t] for rows of row_bytes bytes (a multiple of 16); src has len_valid rows
+ *   ssm_ssd_bwd_group_sum  out[b, t, g, :] = sum over the heads h of group g of weight[b, t, h] * y[b, ts, h, :]
+ *                       (ts = len - 1 - t when reversed, else t; weight nullable; y (batch, len, heads, nstate);
+ *                       out (batch, len_out, groups, nstate) in out_dtype = io_dtype or SSM_F32)
+ *   ssm_ssd_state_dot   out[b, c, h] = <fwd_states[b, c, h, :], adj_states[b, nchunks - c, h, :]> for c >= 1, 0 for c = 0;
+ *                       both (batch, nchunks, heads, elems) in io_dtype or SSM_F32 (ws_state_in / ws_state_in_f32 of two
+ *                       ssm_ssd_fwd runs)
+ * --------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t batch, len, len_valid, heads;
+  int32_t headdim, io_dtype, d_has_p, reserved0;
+  const void* gY;      /* (batch, len_valid, heads, headdim); nullable in finish when z is NULL */
+  const void* z;       /* nullable */
+  const void* X;       /* finish */
+  const void* y_plain; /* finish, with z: output of the forward pass without skip and gate, (batch, len, ...) */
+  const void* dx_rev;  /* finish: output of the adjoint pass, time-reversed, (batch, len, ...) */
+  const float* D;      /* nullable */
+  void* dy;            /* gate: out; finish: in */
+  void* dy_rev;        /* gate: out */
+  void* dX;            /* finish: out */
+  void* dz;            /* finish: out, with z */
+  float* dD;           /* finish: accumulated, nullable */
+} ssm_ssd_bwd_args;
+
+int ssm_ssd_bwd_gate(const ssm_ssd_bwd_args* args, ssm_stream_t stream);
+int ssm_ssd_bwd_finish(const ssm_ssd_bwd_args* args, ssm_stream_t stream);
+int ssm_time_flip(const void* src, void* dst, int32_t batch, int32_t len, int32_t len_valid, int64_t row_bytes, ssm_stream_t stream);
+int ssm_ssd_bwd_group_sum(const void* y, const float* weight, void* out, int32_t batch, int32_t len, int32_t len_out, int32_t heads, int32_t groups,
+                          int32_t nstate, int32_t reversed, int32_t io_dtype, int32_t out_dtype, ssm_stream_t stream);
+int ssm_ssd_state_dot(const void* fwd_states, const void* adj_states, float* out, int32_t batch, int32_t nchunks, int32_t heads, int32_t elems,
+                      int32_t io_dtype, ssm_stream_t stream);
 
 #ifdef __cplusplus
 }

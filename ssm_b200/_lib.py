@@ -13,7 +13,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libssm_b200.so"
 
 F32, BF16, F16 = 0, 1, 2
-ABI_VERSION = 2  # SSM_B200_ABI_VERSION of include/ssm_b200.h this binding mirrors
+ABI_VERSION = 3  # SSM_B200_ABI_VERSION of include/ssm_b200.h this binding mirrors
 i32, i64, vp, fp = C.c_int32, C.c_int64, C.c_void_p, C.c_void_p
 
 
@@ -125,10 +125,21 @@ class SsdArgs(C.Structure):
     _fields_ = [
         ("batch", i32), ("len", i32), ("heads", i32), ("headdim", i32),
         ("nstate", i32), ("groups", i32), ("chunk_size", i32), ("io_dtype", i32),
-        ("dt_softplus", i32), ("d_has_p", i32), ("phase", i32), ("reserved1", i32),
+        ("dt_softplus", i32), ("d_has_p", i32), ("phase", i32), ("dt_mode", i32),
         ("X", vp), ("dt", vp), ("A", fp), ("Bm", vp), ("Cm", vp), ("D", fp), ("z", vp), ("dt_bias", fp),
         ("initial_states", fp), ("Y", vp), ("final_states", fp),
         ("ws_dt", fp), ("ws_cum", fp), ("ws_state", fp), ("ws_state_in", vp), ("status", vp),
+        ("row_dots", fp), ("row_scale", fp), ("bc_width", i32), ("reserved2", i32),
+        ("ws_state_in_f32", fp),
+    ]
+
+
+class SsdBwdArgs(C.Structure):
+    _fields_ = [
+        ("batch", i32), ("len", i32), ("len_valid", i32), ("heads", i32),
+        ("headdim", i32), ("io_dtype", i32), ("d_has_p", i32), ("reserved0", i32),
+        ("gY", vp), ("z", vp), ("X", vp), ("y_plain", vp), ("dx_rev", vp), ("D", fp),
+        ("dy", vp), ("dy_rev", vp), ("dX", vp), ("dz", vp), ("dD", fp),
     ]
 
 
@@ -157,6 +168,11 @@ ENTRY_POINTS = {
     "ssm_ssd_wait_selftest": (C.c_int, [vp, i32, vp]),
     "ssm_ssd_scratch_bytes": (C.c_int64, [i32, i32, i32]),
     "ssm_ssd_state_scratch_bytes": (C.c_int64, [i32, i32, i32]),
+    "ssm_ssd_bwd_gate": (C.c_int, [C.POINTER(SsdBwdArgs), vp]),
+    "ssm_ssd_bwd_finish": (C.c_int, [C.POINTER(SsdBwdArgs), vp]),
+    "ssm_time_flip": (C.c_int, [vp, vp, i32, i32, i32, C.c_int64, vp]),
+    "ssm_ssd_bwd_group_sum": (C.c_int, [vp, fp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
+    "ssm_ssd_state_dot": (C.c_int, [vp, vp, fp, i32, i32, i32, i32, i32, vp]),
     "ssm_ssd_fwd": (C.c_int, [C.POINTER(SsdArgs), vp]),
     "ssm_ssd_shard_summary_floats": (C.c_int64, [i32, i32]),
     "ssm_ssd_fold_shards": (C.c_int, [vp, i32, i32, i32, i32, vp, vp, vp]),

@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, i
   const float Ah = __ldg(a.A + h);
   const float bias = a.dt_bias ? __ldg(a.dt_bias + h) : 0.f;
   const T* dt = reinterpret_cast<const T*>(a.dt);
+  const float* dt_ready = reinterpret_cast<const float*>(a.dt);  // dt_mode & 1: fp32 step sizes, already activated
   float* odt = a.ws_dt + ((int64_t)b * a.heads + h) * nchunks * kQ + (int64_t)c * kQ;
   float* ocum = a.ws_cum + ((int64_t)b * a.heads + h) * nchunks * kQ + (int64_t)c * kQ;
   float d[kQ / 32], run = 0.f;
@@ -58,8 +59,13 @@ __global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, i
     const int t = c * kQ + i;
     float v = 0.f;
     if (t < a.len) {
-      v = to_f<T>(dt[((int64_t)b * a.len + t) * a.heads + h]) + bias;
-      if (a.dt_softplus) v = softplus_f(v);
+      const int64_t at = ((int64_t)b * a.len + t) * a.heads + h;
+      if (a.dt_mode & 1) {
+        v = __ldg(dt_ready + at);
+      } else {
+        v = to_f<T>(dt[at]) + bias;
+        if (a.dt_softplus) v = softplus_f(v);
+      }
     }
     d[k] = v;
     run += v * Ah;
@@ -78,7 +84,9 @@ __global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, i
     acc += d[k] * Ah;
     const float c2 = acc * kLog2e;
     ocum[i] = c2;                      // running decay exponent, base 2
-    odt[i] = c2 - lg2_approx(d[k]);    // the same with delta folded in: exp2(x - odt[j]) = exp2(x - c2_j) * delta_j  (delta 0 -> +inf -> weight 0)
+    // the same with delta folded in: exp2(x - odt[j]) = exp2(x - c2_j) * delta_j  (delta 0 -> +inf -> weight 0);
+    // dt_mode & 2: the inputs enter with unit weight, only the decay uses delta
+    odt[i] = (a.dt_mode & 2) ? c2 : c2 - lg2_approx(d[k]);
   }
 }
 
@@ -192,6 +200,15 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
         Vec16<T> o;
         o.pack(*reinterpret_cast<const float(*)[8]>(&st[hh][q * 8]));
         *reinterpret_cast<uint4*>(blk + ((size_t)(wg * 4 + q) * kN + n) * 8) = o.raw;
+      }
+      if (a.ws_state_in_f32) {  // the same tile unrounded (the backward pass forms <adjoint state, state> from it)
+        float* blk32 = a.ws_state_in_f32 + (((int64_t)b * nchunks + c) * a.heads + h0 + hh) * (int64_t)(kP * kN);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float4* dst = reinterpret_cast<float4*>(blk32 + ((size_t)(wg * 4 + q) * kN + n) * 8);
+          dst[0] = make_float4(st[hh][q * 8], st[hh][q * 8 + 1], st[hh][q * 8 + 2], st[hh][q * 8 + 3]);
+          dst[1] = make_float4(st[hh][q * 8 + 4], st[hh][q * 8 + 5], st[hh][q * 8 + 6], st[hh][q * 8 + 7]);
+        }
       }
     }
   };
@@ -496,6 +513,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     tc::tmem_ld32(tmem + lane_base + 256 + buf * 128 + wg * 32, yi);
     tc::tmem_ld32(tmem + lane_base + 320 + buf * 128 + wg * 32, ys);
     const float Dh = (a.D && !a.d_has_p) ? __ldg(a.D + h) : 0.f;
+    float dot = 0.f;  // row_dots: this thread's 32 columns of  sum_p y[p] z[p]  (y before the skip term and unrounded)
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float f[8], xv[8];
@@ -505,7 +523,8 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const float Dv = (a.D && a.d_has_p) ? __ldg(a.D + h * kP + wg * 32 + q * 8 + e) : Dh;
-        f[e] = fmaf(escale, ys[q * 8 + e], yi[q * 8 + e]) + Dv * xv[e];
+        f[e] = fmaf(escale, ys[q * 8 + e], yi[q * 8 + e]);
+        xv[e] *= Dv;
       }
       unsigned char* slot = swz(sZ, i_loc, wg * 4 + q);
       if (has_z) {
@@ -513,12 +532,25 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
         Vec16<T> zz;
         zz.raw = *reinterpret_cast<const uint4*>(slot);
         zz.unpack(zv);
+        if (a.row_dots) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] *= silu_fast(zv[e]);
+          for (int e = 0; e < 8; ++e) dot = fmaf(f[e], zv[e], dot), f[e] += xv[e];
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = (f[e] + xv[e]) * silu_fast(zv[e]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += xv[e];
       }
       Vec16<T> o;
       o.pack(f);
       *reinterpret_cast<uint4*>(slot) = o.raw;
+    }
+    if (a.row_dots && has_z) {
+      const int t = t0 + MB * kBlk + i_loc;
+      // two threads (column halves) add to one zero-initialised word: the sum does not depend on their order
+      if (t < a.len) atomicAdd(a.row_dots + ((int64_t)b * a.len + t) * a.heads + h, dot);
     }
     tc::fence_async_smem();  // the staged rows leave through a bulk store
   };
@@ -530,9 +562,16 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   for (int q = 0; q < 4; ++q) xr_prev[q] = make_uint4(0, 0, 0, 0);
   int fail = 0;
   int nz = 0;  // z tiles requested so far (parity of the z barrier)
+  // optional weight of this thread's row (folded into the row exponent, so it scales the mask before rounding and
+  // the carried-state term alike); fetched one head ahead
+  const int t_row = t0 + MB * kBlk + i_loc;
+  const float* rs_ptr = (a.row_scale && t_row < a.len) ? a.row_scale + ((int64_t)b * a.len + t_row) * a.heads : nullptr;
+  float rs_next = (rs_ptr && nh > 0) ? __ldg(rs_ptr + h0) : 1.f;
 #pragma unroll 1
   for (int hi = 0; hi < nh; ++hi) {
     const int h = h0 + hi, buf = hi & 1;
+    const float rs_cur = rs_next;
+    if (rs_ptr && hi + 1 < nh) rs_next = __ldg(rs_ptr + h + 1);
     ok = !fail && tc::mbar_wait(mb_full(buf), (hi >> 1) & 1);  // this head's operands (no more waiting once a wait ran out)
     // MMAs of the previous head: the masked tile, the other buffer and its accumulators are free / ready
     if (hi > 0) ok = tc::mbar_wait(mb_mma(buf ^ 1), ((hi - 1) >> 1) & 1) && ok;
@@ -558,7 +597,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     // ---- decay mask: G (registers) -> masked tile, K-major over j: unit (i, j/8) at (j/8) * 2048 + i * 16
     const float* vc = sVec + buf * (2 * kQ);
     const float* vcp = vc + kQ;
-    const float ct = vc[i_chunk];
+    const float ct = a.row_scale ? vc[i_chunk] + lg2_approx(rs_cur) : vc[i_chunk];
     // The weight exp2(c_i - c'_j) of a 32-step chunk factors as exp2(c_i - r) * exp2(r - c'_j) with r = c at the
     // chunk's first step (row factor <= 1 for causal rows, column factor bounded by the decay inside the chunk).
     // Each lane forms one column factor per chunk, each thread one row factor per chunk: 2 ex2 per 32 elements
@@ -760,7 +799,7 @@ static int encode_rows_map(CUtensorMap* m, const void* base, const ssm_ssd_args&
 template <typename T, int HPC>
 static int ssd_state_launch(const ssm_ssd_args& a, int nchunks, cudaStream_t st) {
   StateMaps maps;
-  if (int rc = encode_rows_map(&maps.b, a.Bm, a, StateSmem<HPC>::kStep, kN, a.groups)) return rc;
+  if (int rc = encode_rows_map(&maps.b, a.Bm, a, StateSmem<HPC>::kStep, a.bc_width ? a.bc_width : kN, a.groups)) return rc;
   if (int rc = encode_rows_map(&maps.x, a.X, a, StateSmem<HPC>::kStep)) return rc;
   const size_t smem = StateSmem<HPC>::ALLOC;
   cudaFuncSetAttribute(ssd_state_kernel<T, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -855,8 +894,10 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
     if (int rc = encode_rows_map(&maps.x1, a.X, a, kQ)) return rc;
     if (int rc = encode_rows_map(&maps.z, a.z ? a.z : a.X, a, kBlk)) return rc;
     if (int rc = encode_rows_map(&maps.y, a.Y, a, kBlk)) return rc;
-    if (int rc = encode_rows_map(&maps.c, a.Cm, a, kBlk, kN, a.groups)) return rc;
-    if (int rc = encode_rows_map(&maps.bm, a.Bm, a, kBlk, kN, a.groups)) return rc;
+    // narrower stored rows (bc_width 64): the copies of the upper 64 states start outside the tensor and bring zeros
+    const int bcw = a.bc_width ? a.bc_width : kN;
+    if (int rc = encode_rows_map(&maps.c, a.Cm, a, kBlk, bcw, a.groups)) return rc;
+    if (int rc = encode_rows_map(&maps.bm, a.Bm, a, kBlk, bcw, a.groups)) return rc;
     const size_t smem = ScanSmem<T>::ALLOC;
     cudaFuncSetAttribute(ssd_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ssd_scan_kernel<T><<<2 * nparts * a.batch * nchunks, kScanThreads, smem, st>>>(a, maps, nchunks, hpc, nparts);
@@ -914,6 +955,8 @@ extern "C" int ssm_ssd_fwd(const ssm_ssd_args* a, ssm_stream_t stream) {
               "ssd_scan: the tensor-core path is built for headdim 64, d_state 128, chunk 256, bf16 / fp16");
   if (a->batch == 0 || a->len == 0) return SSM_OK;
   SSM_REQUIRE(a->phase >= 0 && a->phase <= 2, SSM_ERR_SHAPE, "ssd_scan: phase must be 0, 1 or 2");
+  SSM_REQUIRE(a->dt_mode >= 0 && a->dt_mode <= 3 && a->dt_mode != 2, SSM_ERR_SHAPE, "ssd_scan: dt_mode must be 0, 1 or 3");
+  SSM_REQUIRE(a->bc_width == 0 || a->bc_width == kN || a->bc_width == 64, SSM_ERR_SHAPE, "ssd_scan: bc_width must be 0, 64 or nstate");
   SSM_REQUIRE(a->X && a->dt && a->A && a->Bm && a->Cm && (a->Y || a->phase == 1), SSM_ERR_NULL, "ssd_scan: missing tensor");
   SSM_REQUIRE(a->ws_dt && a->ws_cum && a->ws_state && a->ws_state_in, SSM_ERR_NULL, "ssd_scan: missing scratch");
   SSM_REQUIRE(aligned_to(a->X, 16) && aligned_to(a->Bm, 16) && aligned_to(a->Cm, 16) && (!a->Y || aligned_to(a->Y, 16)) && aligned_to(a->ws_state_in, 16) &&

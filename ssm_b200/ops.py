@@ -19,6 +19,7 @@ import math
 from typing import Any, Optional
 
 import torch
+import torch.nn.functional as F
 
 from . import _lib as L
 
@@ -1074,24 +1075,29 @@ class _SsdWorkspace:
     """Scratch and bookkeeping of one tensor-core SSD call, kept so that a sequence shard can run
     the state phase, exchange states, and then finish from the same scratch."""
 
-    def __init__(self, X, dt, A, B, C_, D, z, dt_bias, dt_softplus, chunk_size):
+    def __init__(self, X, dt, A, B, C_, D, z, dt_bias, dt_softplus, chunk_size, dt_mode: int = 0, bc_width: int = 0):
         nb, nl, nh, npj = X.shape
-        self.shape = (nb, nl, nh, npj, B.shape[2], B.shape[3])
+        # bc_width: B and C are stored bc_width (< d_state) wide and read as d_state-wide rows with zeros above
+        self.bc_width = int(bc_width)
+        self.shape = (nb, nl, nh, npj, B.shape[2], 2 * B.shape[3] if bc_width else B.shape[3])
         lib = L.load()
         io = X.dtype
-        self.io, self.chunk = io, int(chunk_size)
-        self.X, self.dt, self.B, self.C = _c(X), _c(dt.to(io)), _c(B.to(io)), _c(C_.to(io))
+        self.io, self.chunk, self.dt_mode = io, int(chunk_size), int(dt_mode)
+        self.X, self.B, self.C = _c(X), _c(B.to(io)), _c(C_.to(io))
+        # dt_mode 1 / 3: dt holds the fp32 step sizes as they are used (no bias, no softplus); 3 also gives the inputs unit weight
+        self.dt = _c(dt.float()) if dt_mode else _c(dt.to(io))
         self.z = None if z is None else _c(z.to(io))
-        self.A, self.D, self.bias = _f32(A), _f32(D), _f32(dt_bias)
+        self.A, self.D, self.bias = _f32(A), _f32(D), (None if dt_mode else _f32(dt_bias))
         self.d_has_p = int(D is not None and D.ndim == 2)
-        self.softplus = int(bool(dt_softplus))
+        self.softplus = int(bool(dt_softplus) and not dt_mode)
         self.nchunks = (nl + self.chunk - 1) // self.chunk
         self.ws = torch.empty(int(lib.ssm_ssd_scratch_bytes(nb, nl, nh)), dtype=torch.uint8, device=X.device)
         self._status = _DeviceStatus.of(X.device)
         self._status.poll()  # a wait that ran out in an earlier launch surfaces here, without a synchronisation
         self.status = self._status.word
 
-    def run(self, phase: int, initial_states: Optional[Tensor], want_y: bool):
+    def run(self, phase: int, initial_states: Optional[Tensor], want_y: bool, row_dots: Optional[Tensor] = None,
+            row_scale: Optional[Tensor] = None, keep_states_f32: bool = False):
         nb, nl, nh, npj, ng, nn = self.shape
         dev = self.X.device
         init32 = _f32(initial_states)
@@ -1102,16 +1108,31 @@ class _SsdWorkspace:
         a = L.SsdArgs()
         a.batch, a.len, a.heads, a.headdim = nb, nl, nh, npj
         a.nstate, a.groups, a.chunk_size, a.io_dtype = nn, ng, self.chunk, _CODES[self.io]
-        a.dt_softplus, a.d_has_p, a.phase = self.softplus, self.d_has_p, phase
+        a.dt_softplus, a.d_has_p, a.phase, a.dt_mode = self.softplus, self.d_has_p, phase, self.dt_mode
         a.X, a.dt, a.A, a.Bm, a.Cm = _p(self.X), _p(self.dt), _p(self.A), _p(self.B), _p(self.C)
         a.D, a.z, a.dt_bias, a.initial_states = _p(self.D), _p(self.z), _p(self.bias), _p(init32)
         a.Y, a.final_states = _p(Y), _p(final)
         base = self.ws.data_ptr()
         a.ws_dt, a.ws_cum, a.ws_state, a.ws_state_in = base, base + vec, base + 2 * vec, base + 2 * vec + fin
         a.status = _p(self.status)
+        a.row_dots = _p(row_dots)  # (B, L, H) fp32 zeros: z is then a dot-product partner, not a gate
+        a.row_scale = _p(row_scale)  # (B, L, H) fp32 weights of the output rows
+        a.bc_width = self.bc_width
+        self.states_f32 = None
+        if keep_states_f32:  # (B, nchunks, H, P * N): the state before every chunk, unrounded
+            self.states_f32 = torch.empty(nb, self.nchunks, nh, npj * nn, dtype=torch.float32, device=dev)
+        a.ws_state_in_f32 = _p(self.states_f32)
         _call(L.load().ssm_ssd_fwd, a)
         self._status.after_launch()
         return Y, final
+
+    def states_before_chunks(self) -> Tensor:
+        """(B, nchunks, H, P * N) in the operand dtype: the state before every chunk as the last run left it in the
+        scratch (element order of the scan kernel's operand tile, the same for every tile)."""
+        nb, nl, nh, npj, _, nn = self.shape
+        vec = nb * nh * self.nchunks * self.chunk * 4
+        fin = int(L.load().ssm_ssd_state_scratch_bytes(nb, nl, nh))
+        return self.ws[2 * vec + fin:].view(self.io).view(nb, self.nchunks, nh, npj * nn)
 
     def shard_summary(self) -> Tensor:
         """Flat fp32 view of what phase 1 left for the other ranks: the final state from a zero start, then (B, H) total log-decay."""
@@ -1140,12 +1161,140 @@ def ssd_tensor_core_supported(X: Tensor, B: Tensor, chunk_size: int) -> bool:
                 and L.load().ssm_ssd_supported(X.shape[3], B.shape[3], int(chunk_size), _CODES[X.dtype]))
 
 
+
+def _ssd_dual_run(X, delta, A, B, C_, init, chunk, dt_mode, partner=None, row_scale=None, bc_width=0, keep_states_f32=False):
+    """One pass of the tensor-core kernels on ready-made fp32 step sizes; returns (Y, final_states, workspace, dots).
+    With ``partner (B, L, H, P)`` the pass also returns ``dots[b, t, h] = sum_p y[p] partner[p]`` from the fp32 accumulators."""
+    w = _SsdWorkspace(X, delta, A, B, C_, None, partner, None, False, chunk, dt_mode=dt_mode, bc_width=bc_width)
+    dots = None if partner is None else torch.zeros(X.shape[:3], dtype=torch.float32, device=X.device)
+    Y, final = w.run(0, init, True, row_dots=dots, row_scale=None if row_scale is None else _c(row_scale.float()),
+                     keep_states_f32=keep_states_f32)
+    return Y, final, w, dots
+
+
+def _time_flip(t: Tensor, length: int) -> Tensor:
+    """``out[b, length - 1 - i] = t[b, i]`` for a contiguous ``(B, L, ...)`` tensor with ``L <= length``; rows beyond ``L`` are zero."""
+    t = _c(t)
+    out = torch.empty((t.shape[0], length, *t.shape[2:]), dtype=t.dtype, device=t.device)
+    row = t[0, 0].numel() * t.element_size() if t.shape[1] else 0
+    L.check(L.load().ssm_time_flip(_p(t), _p(out), t.shape[0], length, t.shape[1], row, _stream()))
+    return out
+
+
+def _ssd_backward_dual(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, init, chunk, gY, gfinal):
+    """Gradients of the state-space-dual scan in the dual (chunked GEMM) form, every contraction on the tcgen05 kernels
+    of the forward pass.  With ``a_t = delta_t A`` and the adjoint state ``G_t = C_t dy_t^T + exp(a_{t+1}) G_{t+1}``:
+
+    * ``d(delta x)_t = G_t B_t`` is the forward recurrence run on the time-reversed sequence with ``B`` and ``C``
+      exchanged, ``dy`` as the input, unit input weight and the decays shifted by one step; its final state is the
+      gradient of the initial state (up to the first decay);
+    * ``dC_t = S_t dy_t`` (and ``dB_t = delta_t G_t x_t`` on the reversed sequence) is the same recurrence with the roles
+      of the head and state axes exchanged: per head, ``x`` and ``dy`` take the places of ``B`` and ``C`` (64 wide, read as
+      128 with zeros above) and the two halves of ``B`` are the inputs of two heads of 64;
+    * the gradient of the decay exponent obeys ``da_{t+1} = da_t + d(delta x)_t . (delta x)_t - dy_t . y_t`` (``y`` without
+      the skip term); the running sum restarts at every chunk from ``<G, S>`` of the two passes' chunk states.  The
+      adjoint pass weights its rows by ``delta`` so that it rounds the same masked tiles as the forward pass; the two
+      dot products come from the passes' fp32 accumulators.
+
+    The passes over ``(B, L, H, P)`` around the four runs are the kernels of ``csrc/ssd_bwd.cu``; only ``(B, L, H)``-sized
+    bookkeeping of the step sizes is PyTorch.  Returns the nine gradients."""
+    lib = L.load()
+    nb, nl, nh, npj = X.shape
+    ng, nn = B.shape[2], B.shape[3]
+    rep = nh // ng
+    io, dev = X.dtype, X.device
+    code = _CODES[io]
+    f32 = torch.float32
+    A32 = A.float()
+    pre_act = dt.float() if dt_bias is None else dt.float() + dt_bias.float()
+    delta = F.softplus(pre_act) if dt_softplus else pre_act
+    pad = (-nl) % chunk  # whole chunks, so that the chunks of the reversed sequence are the chunks of the forward one
+    lp = nl + pad
+    nchunks = lp // chunk
+    Xc, Bc, Cc = _c(X), _c(B.to(io)), _c(C_.to(io))
+    zc = None if z is None else _c(z.to(io))
+    gy = torch.zeros_like(Xc) if gY is None else _c(gY.to(io))
+    D32 = _f32(D)
+    if pad:
+        delta = F.pad(delta, (0, 0, 0, pad))
+        Xp, Bp, Cp = F.pad(Xc, (0, 0, 0, 0, 0, pad)), F.pad(Bc, (0, 0, 0, 0, 0, pad)), F.pad(Cc, (0, 0, 0, 0, 0, pad))
+    else:
+        delta, Xp, Bp, Cp = _c(delta), Xc, Bc, Cc
+    # dy = gY silu(z), in time order and reversed
+    dy = torch.empty(nb, lp, nh, npj, dtype=io, device=dev)
+    dy_r = torch.empty_like(dy)
+    g = L.SsdBwdArgs()
+    g.batch, g.len, g.len_valid, g.heads, g.headdim, g.io_dtype = nb, lp, nl, nh, npj, code
+    g.d_has_p = int(D is not None and D.ndim == 2)
+    g.gY, g.z, g.dy, g.dy_rev = _p(gy), _p(zc), _p(dy), _p(dy_r)
+    _call(lib.ssm_ssd_bwd_gate, g)
+    # (1) forward again without skip and gate: y, dy . y, and the state before every chunk
+    y_plain, _, w_fwd, u = _ssd_dual_run(Xp, delta, A32, Bp, Cp, init, chunk, 1, partner=dy, keep_states_f32=True)
+    # (2) adjoint recurrence on the reversed sequence, rows weighted by delta of the source step: the output is the x
+    # gradient without the skip term, and the masked tiles round exactly like those of pass (1), which lets (4) telescope
+    X_r, B_r, C_r = _time_flip(Xc, lp), _time_flip(Bc, lp), _time_flip(Cc, lp)
+    delta_r = torch.zeros_like(delta)
+    delta_r[:, 1:] = delta.flip(1)[:, :-1]
+    g_init = None if gfinal is None else gfinal.float()
+    dx_r, fin_r, w_adj, qd_r = _ssd_dual_run(dy_r, delta_r, A32, C_r, B_r, g_init, chunk, 3, partner=X_r, row_scale=delta.flip(1),
+                                                keep_states_f32=True)
+    dinit = torch.exp(delta[:, 0] * A32)[..., None, None] * fin_r
+    # dz, dX (+ D dy), dD
+    dX = torch.empty_like(Xc)
+    dz = None if zc is None else torch.empty_like(zc)
+    dD = None if D is None else torch.zeros(D.shape, dtype=f32, device=dev)
+    g.X, g.y_plain, g.dx_rev, g.D, g.dX, g.dz, g.dD = _p(Xc), _p(y_plain), _p(dx_r), _p(D32), _p(dX), _p(dz), _p(dD)
+    _call(lib.ssm_ssd_bwd_finish, g)
+    del y_plain, dx_r
+
+    # (3) dC and dB: head and state axes exchanged, one group per head, the halves of B (C) as the inputs of two heads
+    def halves(t):  # (B, L, G, N) -> (B, L, 2 H, N / 2)
+        return (t.repeat_interleave(rep, 2) if rep > 1 else t).reshape(nb, lp, 2 * nh, nn // 2)
+
+    def state_t(s):  # (B, H, P, N) fp32 -> (B, 2 H, N / 2, N): transposed, the P axis zero-padded to N
+        return None if s is None else F.pad(s.float().transpose(2, 3).reshape(nb, 2 * nh, nn // 2, npj), (0, nn - npj))
+
+    def group_sum(y, weight, reversed_, like):
+        out_dtype = io if like.dtype == io else f32
+        out = torch.empty(nb, nl, ng, nn, dtype=out_dtype, device=dev)
+        L.check(lib.ssm_ssd_bwd_group_sum(_p(y), _p(weight), _p(out), nb, lp, nl, nh, ng, nn, int(reversed_), code, _CODES[out_dtype], _stream()))
+        return out
+
+    A2 = A32.repeat_interleave(2)
+    yc = _ssd_dual_run(halves(Bp), delta.repeat_interleave(2, 2), A2, Xp, dy, state_t(init), chunk, 1, bc_width=npj)[0]
+    dC = group_sum(yc, None, False, C_)
+    del yc
+    yb = _ssd_dual_run(halves(C_r), delta_r.repeat_interleave(2, 2), A2, dy_r, X_r, state_t(g_init), chunk, 3, bc_width=npj)[0]
+    dB = group_sum(yb, delta, True, B)
+    del yb
+    # (4) decay exponent: chunk-local running sums started from <adjoint state, state> at the chunk boundaries
+    qd = qd_r.flip(1)  # (B, L, H): delta_t d(delta x)_t . x_t
+    q = torch.where(delta > 0, qd / delta, torch.zeros_like(qd))
+    r = qd - u
+    start = torch.empty(nb, nchunks, nh, dtype=f32, device=dev)
+    L.check(lib.ssm_ssd_state_dot(_p(w_fwd.states_f32), _p(w_adj.states_f32), _p(start), nb, nchunks, nh, npj * nn, _CODES[f32], _stream()))
+    if nchunks > 1:
+        start[:, 1:] *= torch.exp(delta[:, chunk::chunk] * A32)  # decay of the first step of chunks 1 ..
+    if init is not None:
+        start[:, 0] = (dinit * init.float()).sum((-1, -2))
+    rc = r.view(nb, nchunks, chunk, nh)
+    da = (start[:, :, None] + torch.cumsum(rc, 2) - rc).reshape(nb, lp, nh)
+    ddelta = (q + A32 * da)[:, :nl]
+    dA = (delta * da).sum((0, 1))
+    if dt_softplus:
+        ddelta = ddelta * torch.sigmoid(pre_act)
+    dbias = None if dt_bias is None else ddelta.sum((0, 1))
+    return dX, ddelta, dA, dB, dC, dD, dz, dbias, dinit
+
+
 class _SsdFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states, chunk_size, check_status):
+    def forward(ctx, X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states, chunk_size, check_status, dual_backward):
         _ssd_check(X, dt, A, B, C_, D, z, dt_bias, initial_states)
         ctx.args = (X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states)
         _guard(ctx, X, dt, A, B, C_, D, z, dt_bias, initial_states)
+        ctx.chunk = int(chunk_size)
+        ctx.dual = bool(dual_backward) and ssd_tensor_core_supported(X, B, chunk_size)
         if ssd_tensor_core_supported(X, B, chunk_size):
             Y, final, _ = _ssd_tensor_core(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, initial_states, int(chunk_size))
             if check_status:
@@ -1158,6 +1307,12 @@ class _SsdFn(torch.autograd.Function):
     def backward(ctx, gY, gfinal):
         _check_guard(ctx)
         X, dt, A, B, C_, D, z, dt_bias, dt_softplus, init = ctx.args
+        if ctx.dual:
+            with torch.no_grad():
+                grads = _ssd_backward_dual(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, init, ctx.chunk, gY, gfinal)
+            srcs = (X, dt, A, B, C_, D, z, dt_bias, init)
+            res = [None if (t is None or g is None or not t.requires_grad) else g.to(t.dtype).reshape(t.shape) for t, g in zip(srcs, grads)]
+            return (*res[:8], None, res[8], None, None, None)
         leaves = [None if t is None else t.detach().requires_grad_(t.requires_grad) for t in (X, dt, A, B, C_, D, z, dt_bias, init)]
         with torch.enable_grad():
             Y, final = _ssd_via_scan(*leaves[:8], dt_softplus, leaves[8])
@@ -1168,7 +1323,7 @@ class _SsdFn(torch.autograd.Function):
             gouts.append(gfinal)
         grads = iter(torch.autograd.grad(outs, live, gouts, allow_unused=True))
         res = [next(grads) if (t is not None and t.requires_grad) else None for t in leaves]
-        return (*res[:8], None, res[8], None, None)
+        return (*res[:8], None, res[8], None, None, None)
 
 
 def ssd_scan(
@@ -1185,18 +1340,23 @@ def ssd_scan(
     initial_states: Optional[Tensor] = None,
     return_final_states: bool = False,
     check_status: bool = False,
+    backward: str = "dual",
 ):
     """Extension: state-space-dual scan with a ``d_state`` axis (Mamba-2 layout).
 
     ``X (B,L,H,P)``, ``dt (B,L,H)``, ``A (H,)``, ``B/C (B,L,G,N)``, ``D (H,)|(H,P)``, ``z (B,L,H,P)``,
     state ``(B,H,P,N)`` fp32.  It is upstream's ``selective_scan`` recurrence (reference.py:173-188)
     on channel ``h*P+p`` with per-head ``dt`` and ``A``.  For headdim 64, d_state 128, chunk 256 and
-    bf16 / fp16 operands the forward runs as chunked GEMMs on the tcgen05 tensor cores; any other
-    shape or dtype, and every backward pass, goes through the selective-scan kernels on the
-    flattened channels.  A bounded device-side wait that runs out (it never should) is reported by the next
+    bf16 / fp16 operands the forward runs as chunked GEMMs on the tcgen05 tensor cores, and so does the
+    backward (``backward="dual"``: four more runs of the same kernels on transformed operands; its
+    gradients carry the rounding of 16-bit operands, about 0.3 % of each contraction).  Any other shape or
+    dtype, and ``backward="scan"``, goes through the selective-scan kernels on the flattened channels
+    (fp32 arithmetic, an order of magnitude slower at these shapes).  A bounded device-side wait that runs out (it never should) is reported by the next
     ``ssd_scan`` call on the device, or at once by ``check_status=True`` / :func:`ssd_check_status`, which synchronise.
     """
-    Y, final = _SsdFn.apply(X, dt, A, B, C, D, z, dt_bias, dt_softplus, initial_states, chunk_size, check_status)
+    if backward not in ("dual", "scan"):
+        raise ValueError('backward must be "dual" or "scan".')
+    Y, final = _SsdFn.apply(X, dt, A, B, C, D, z, dt_bias, dt_softplus, initial_states, chunk_size, check_status, backward == "dual")
     return (Y, final) if return_final_states else Y
 
 

@@ -8,6 +8,12 @@ of terms -- parameter gradients summed over batch and time (``dA, dB, dC, dD, dd
 and norm ``dweight / dbias``) and the outputs of the tensor-core SSD path, each a 256-term
 bf16 product sum -- get the absolute term scaled by the magnitude of the expected tensor
 (``reduced=True``): their rounding error grows with the size of the terms, not of the result.
+
+The dual-form (tensor-core) backward of the SSD scan adds one more kind: gradients that sum
+terms of both signs over batch and time (``dA``, ``ddt_bias``) out of 16-bit-operand
+contractions.  Each term carries about 0.3 % of its own size, so the sum is held to a fraction
+of the sum of the terms' magnitudes (``close_sum``), which is what conditions it -- the result
+itself may cancel to far less.
 """
 
 from __future__ import annotations
@@ -58,3 +64,19 @@ def close(got, want, rtol, atol, what="", reduced=False):
             f"(got {float(got[ok][i]):.6e}, want {float(want[ok][i]):.6e}, bound {float(bound[i]):.3e})"
         )
     assert torch.isfinite(got[ok]).all(), f"{what}: non-finite values"
+
+
+def close_sum(got, want, abs_terms, frac, what=""):
+    """``|got - want| <= frac * abs_terms`` element by element: for a sum of signed terms, ``abs_terms`` being (an estimate
+    of) the sum of their magnitudes."""
+    got = got.detach().float().cpu()
+    want = want.detach().float().cpu()
+    abs_terms = abs_terms.detach().float().cpu()
+    assert got.shape == want.shape == abs_terms.shape, f"{what}: shapes {tuple(got.shape)}, {tuple(want.shape)}, {tuple(abs_terms.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    err = (got - want).abs()
+    bad = err > frac * abs_terms
+    if bad.any():
+        i = int(torch.argmax(err / abs_terms.clamp_min(1e-30)))
+        raise AssertionError(f"{what}: {int(bad.sum())}/{bad.numel()} off; worst |err|={float(err.flatten()[i]):.3e} "
+                             f"(got {float(got.flatten()[i]):.6e}, want {float(want.flatten()[i]):.6e}, sum of |terms| {float(abs_terms.flatten()[i]):.3e})")

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
         assert name in _lib.ENTRY_POINTS, f"{name} has no ctypes prototype"
-    assert lib.ssm_b200_abi_version() == 2
+    assert lib.ssm_b200_abi_version() == 3
     assert lib.ssm_scan_checkpoint_interval() == 32
 
 

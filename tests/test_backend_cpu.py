@@ -19,7 +19,7 @@ def test_extension_exports_the_ten_upstream_names_with_their_keywords():
     from ssm_b200 import backend
 
     ext = backend.load_extension()
-    assert ext.abi_version() == 2
+    assert ext.abi_version() == 3
     for name in backend.NAMES:
         assert callable(getattr(ext, name)), name
     # keyword names and defaults of src/ssm/ops/cuda/bindings.cpp:96-152, as pybind records them

@@ -13,7 +13,7 @@ import torch
 import torch.nn.functional as F
 
 from oracle import ssm_oracle as orc
-from tests.gpu_util import FP32_TOL, HALF_TOL, REDUCED, close
+from tests.gpu_util import FP32_TOL, HALF_TOL, REDUCED, close, close_sum
 
 pytestmark = pytest.mark.gpu
 
@@ -120,37 +120,66 @@ def test_ssd_long_shard_shape_direct_and_two_phase():
     close(S2, S, **SSD_TOL, what="two-phase final state", reduced=True)
 
 
-def test_ssd_gradients_at_the_tensor_core_shape():
-    """headdim 64 / d_state 128 / bf16: every gradient of ssd_scan (dX, ddt, dA, dB, dC, dD, dz, ddt_bias, dinitial) against
-    the oracle's autograd, with a final-state term in the loss."""
+SSD_GRAD_CASES = [
+    # batch, len, heads, groups, dtype, gate, initial state, D per (head, p)
+    pytest.param(1, 384, 2, 1, torch.bfloat16, True, True, False, id="L384-pad-z-init"),
+    pytest.param(2, 1024, 4, 2, torch.bfloat16, True, True, False, id="L1024-groups-z-init"),
+    pytest.param(1, 512, 2, 2, torch.bfloat16, False, False, False, id="L512-plain"),
+    pytest.param(1, 700, 4, 1, torch.float16, True, True, True, id="L700-fp16-Dhp"),
+]
+
+
+@pytest.mark.parametrize("backward", ["dual", "scan"])
+@pytest.mark.parametrize("nb,nl,nh,ng,dtype,use_z,use_init,d_hp", SSD_GRAD_CASES)
+def test_ssd_gradients_at_the_tensor_core_shape(nb, nl, nh, ng, dtype, use_z, use_init, d_hp, backward):
+    """headdim 64 / d_state 128, 16-bit operands: every gradient of ssd_scan (dX, ddt, dA, dB, dC, dD, dz, ddt_bias, dinitial)
+    against the oracle's autograd, with a final-state term in the loss.  ``scan`` = fp32 selective-scan kernels on the
+    flattened channels (element-wise bars); ``dual`` = the chunked GEMM form on the tensor cores (every gradient is a
+    16-bit-operand contraction: the tensor-core bar; the decay-path sums dA and ddt_bias against the sum of their terms'
+    magnitudes, ddt with the absolute term at 5 % of its largest entry, since it holds |A| times the 0.3 % noise of
+    <adjoint state, state>)."""
     from ssm_b200 import ops
 
-    gen = torch.Generator().manual_seed(17)
-    nb, nl, nh = 1, 384, 2
-    bf = torch.bfloat16
-    ins = dict(X=torch.randn(nb, nl, nh, 64, generator=gen).to(bf), dt=(torch.randn(nb, nl, nh, generator=gen) - 3).to(bf),
-               A=-torch.exp(torch.rand(nh, generator=gen) * 2.77), B=(torch.randn(nb, nl, 1, 128, generator=gen) / 128 ** 0.5).to(bf),
-               C=(torch.randn(nb, nl, 1, 128, generator=gen) / 128 ** 0.5).to(bf), D=torch.randn(nh, generator=gen),
-               z=torch.randn(nb, nl, nh, 64, generator=gen).to(bf), dt_bias=torch.randn(nh, generator=gen) * 0.3,
-               initial_states=torch.randn(nb, nh, 64, 128, generator=gen) * 0.5)
-    wy = torch.randn(nb, nl, nh, 64, generator=gen).to(bf).float()
+    gen = torch.Generator().manual_seed(17 + nl)
+    ins = dict(X=torch.randn(nb, nl, nh, 64, generator=gen).to(dtype), dt=(torch.randn(nb, nl, nh, generator=gen) - 3).to(dtype),
+               A=-torch.exp(torch.rand(nh, generator=gen) * 2.77), B=(torch.randn(nb, nl, ng, 128, generator=gen) / 128 ** 0.5).to(dtype),
+               C=(torch.randn(nb, nl, ng, 128, generator=gen) / 128 ** 0.5).to(dtype),
+               D=torch.randn(nh, 64, generator=gen) if d_hp else torch.randn(nh, generator=gen),
+               z=torch.randn(nb, nl, nh, 64, generator=gen).to(dtype) if use_z else None, dt_bias=torch.randn(nh, generator=gen) * 0.3,
+               initial_states=torch.randn(nb, nh, 64, 128, generator=gen) * 0.5 if use_init else None)
+    wy = torch.randn(nb, nl, nh, 64, generator=gen).to(dtype).float()
     wf = torch.randn(nb, nh, 64, 128, generator=gen)
-    lo = {k: v.clone().requires_grad_(True) for k, v in ins.items()}
-    lg = {k: v.clone().cuda().requires_grad_(True) for k, v in ins.items()}
+    names = [k for k, v in ins.items() if v is not None]
+    lo = {k: (None if v is None else v.clone().requires_grad_(True)) for k, v in ins.items()}
+    lg = {k: (None if v is None else v.clone().cuda().requires_grad_(True)) for k, v in ins.items()}
     assert ops.ssd_tensor_core_supported(lg["X"], lg["B"], 256)
 
-    def run(ops_, t, dev):
+    def run(ops_, t, dev, **kw):
         Y, fin = ops_.ssd_scan(t["X"], t["dt"], t["A"], t["B"], t["C"], 256, D=t["D"], z=t["z"], dt_bias=t["dt_bias"], dt_softplus=True,
-                               initial_states=t["initial_states"], return_final_states=True)
-        return Y, fin, torch.autograd.grad((Y.float() * wy.to(dev)).sum() + (fin * wf.to(dev)).sum(), list(t.values()))
+                               initial_states=t["initial_states"], return_final_states=True, **kw)
+        return Y, fin, torch.autograd.grad((Y.float() * wy.to(dev)).sum() + (fin * wf.to(dev)).sum(), [t[k] for k in names])
 
-    Yg, Sg, gg = run(ops, lg, "cuda")
+    Yg, Sg, gg = run(ops, lg, "cuda", backward=backward)
+    ops.ssd_check_status()
     Yo, So, go = run(orc, lo, "cpu")
     close(Yg, Yo, **SSD_TOL, what="Y", reduced=True)
     close(Sg, So, **SSD_TOL, what="final state", reduced=True)
-    for k, a, b in zip(ins, gg, go):
-        # ddt sums 64 bf16-rounded per-channel terms per (token, head): a contraction like the parameter gradients
-        close(a, b, **HALF_TOL, what=f"d{k}", reduced=k in REDUCED or k == "dt")
+    want = dict(zip(names, go))
+    for k, a in zip(names, gg):
+        b = want[k]
+        if backward == "scan":
+            # ddt sums 64 rounded per-channel terms per (token, head): a contraction like the parameter gradients
+            close(a, b, **HALF_TOL, what=f"d{k}", reduced=k in REDUCED or k == "dt")
+        elif k in ("A", "dt_bias"):
+            pre = ins["dt"].float() + ins["dt_bias"]
+            delta, sig = torch.nn.functional.softplus(pre), torch.sigmoid(pre)
+            draw = want["dt"].float()
+            terms = draw.abs().sum((0, 1)) if k == "dt_bias" else (delta * draw.abs() / sig).sum((0, 1)) / ins["A"].abs()
+            close_sum(a, b, terms, 5e-2, what=f"d{k}")
+        elif k == "dt":
+            close(a, b, rtol=2e-2, atol=5e-2, what="ddt", reduced=True)
+        else:
+            close(a, b, **SSD_TOL, what=f"d{k}", reduced=True)
 
 
 def test_decode_step_configuration():
