@@ -573,7 +573,15 @@ def bench_ssd(batch=8, steps=20):
         return ops.ssd_scan(t["X"], t["dt"], A, t["Bm"], t["Cm"], 256, D=D, z=t["z"], dt_softplus=True, return_final_states=True)
 
     ms = time_cuda(step, steps, 3)
-    return {"ms": ms, "bytes": ssd_bytes(B, Lq, H), "flops": ssd_flops(B, Lq, H), "tokens": B * Lq}
+    # backward in the dual form (four more runs of the tensor-core kernels on transformed operands): gradients of every
+    # input for a given output gradient, forward excluded from the timed region
+    lv = {k: v.clone().requires_grad_(True) for k, v in t.items()}
+    Ag, Dg = A.clone().requires_grad_(True), D.clone().requires_grad_(True)
+    gy = torch.randn(B, Lq, H, P, **kw).to(bf)
+    Y = ops.ssd_scan(lv["X"], lv["dt"], Ag, lv["Bm"], lv["Cm"], 256, D=Dg, z=lv["z"], dt_softplus=True)
+    leaves = [lv["X"], lv["dt"], Ag, lv["Bm"], lv["Cm"], Dg, lv["z"]]
+    bwd_ms = time_cuda(lambda: torch.autograd.grad(Y, leaves, gy, retain_graph=True), max(3, steps // 4), 2)
+    return {"ms": ms, "bwd_ms": bwd_ms, "bytes": ssd_bytes(B, Lq, H), "flops": ssd_flops(B, Lq, H), "tokens": B * Lq}
 
 
 def bench_decode(steps=1000):
@@ -725,6 +733,7 @@ def operator_table(args):
     c3 = bench_ssd()
     t["c3_ssd_ms"], t["c3_ssd_frac"], t["c3_ssd_tflops"] = c3["ms"], frac(c3["bytes"], c3["ms"]), c3["flops"] / (c3["ms"] * 1e-3) / 1e12
     t["c3_ssd_tokens_per_s"] = c3["tokens"] / (c3["ms"] * 1e-3)
+    t["c3_ssd_bwd_ms"] = c3["bwd_ms"]
     c4 = bench_decode()
     t["c4a_step_us"], t["c4a_step_frac"] = c4["state_kernels_us"], frac(c4["state_kernels_bytes"], c4["state_kernels_us"] * 1e-3)
     t["c4b_step_us"], t["c4b_step_frac"] = c4["mamba2_step_us"], frac(c4["mamba2_step_bytes"], c4["mamba2_step_us"] * 1e-3)
@@ -820,7 +829,7 @@ def run_single(args):
         ach = r["bytes"] / (ms * 1e-3) / 1e9
         roof = {"kernel": "ssm_ssd_fwd (cumsum + state + scan kernels)", "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                 "peak_kind": kind, "traffic": TRAFFIC_PER_TOKEN_HEAD * r["tokens"] * 48, "bytes_per_launch": r["bytes"],
-                "tensor_tflops": r["flops"] / (ms * 1e-3) / 1e12}
+                "tensor_tflops": r["flops"] / (ms * 1e-3) / 1e12, "bwd_ms": r["bwd_ms"]}
         extra["gpu_launches"] = 3 * steps
         work = f"ssd chunk scan fwd: batch {args.batch or 8}, seqlen 8192, 48 heads x 64, d_state 128, ngroups 1, chunk 256"
     elif wl == "decode":

@@ -454,6 +454,8 @@ int ssm_ssd_fold_shards(const float* gathered, int32_t world, int32_t rank, int3
  *   ssm_ssd_bwd_group_sum  out[b, t, g, :] = sum over the heads h of group g of weight[b, t, h] * y[b, ts, h, :]
  *                       (ts = len - 1 - t when reversed, else t; weight nullable; y (batch, len, heads, nstate);
  *                       out (batch, len_out, groups, nstate) in out_dtype = io_dtype or SSM_F32)
+ *   ssm_ssd_bwd_spread  dst[r, h, :] = src[r, h / (heads / groups), :] for `rows` rows r: (rows, groups, row_bytes) ->
+ *                       (rows, heads, row_bytes), the row of a B / C group handed to each of its heads
  *   ssm_ssd_state_dot   out[b, c, h] = <fwd_states[b, c, h, :], adj_states[b, nchunks - c, h, :]> for c >= 1, 0 for c = 0;
  *                       both (batch, nchunks, heads, elems) in io_dtype or SSM_F32 (ws_state_in / ws_state_in_f32 of two
  *                       ssm_ssd_fwd runs)
@@ -479,6 +481,7 @@ int ssm_ssd_bwd_finish(const ssm_ssd_bwd_args* args, ssm_stream_t stream);
 int ssm_time_flip(const void* src, void* dst, int32_t batch, int32_t len, int32_t len_valid, int64_t row_bytes, ssm_stream_t stream);
 int ssm_ssd_bwd_group_sum(const void* y, const float* weight, void* out, int32_t batch, int32_t len, int32_t len_out, int32_t heads, int32_t groups,
                           int32_t nstate, int32_t reversed, int32_t io_dtype, int32_t out_dtype, ssm_stream_t stream);
+int ssm_ssd_bwd_spread(const void* src, void* dst, int64_t rows, int32_t heads, int32_t groups, int64_t row_bytes, ssm_stream_t stream);
 int ssm_ssd_state_dot(const void* fwd_states, const void* adj_states, float* out, int32_t batch, int32_t nchunks, int32_t heads, int32_t elems,
                       int32_t io_dtype, ssm_stream_t stream);
 

@@ -172,6 +172,7 @@ ENTRY_POINTS = {
     "ssm_ssd_bwd_finish": (C.c_int, [C.POINTER(SsdBwdArgs), vp]),
     "ssm_time_flip": (C.c_int, [vp, vp, i32, i32, i32, C.c_int64, vp]),
     "ssm_ssd_bwd_group_sum": (C.c_int, [vp, fp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
+    "ssm_ssd_bwd_spread": (C.c_int, [vp, vp, C.c_int64, i32, i32, C.c_int64, vp]),
     "ssm_ssd_state_dot": (C.c_int, [vp, vp, fp, i32, i32, i32, i32, i32, vp]),
     "ssm_ssd_fwd": (C.c_int, [C.POINTER(SsdArgs), vp]),
     "ssm_ssd_shard_summary_floats": (C.c_int64, [i32, i32]),

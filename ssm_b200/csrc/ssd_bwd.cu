@@ -196,6 +196,17 @@ __global__ void __launch_bounds__(256) ssd_bwd_group_sum_kernel(const T* __restr
   }
 }
 
+// dst[r, h, :] = src[r, h / rep, :] for rows r = (batch, step): the rows of a B / C group handed to each of its heads
+__global__ void __launch_bounds__(256) ssd_bwd_spread_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int64_t rows, int heads, int rep,
+                                                             int units) {
+  const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= rows * heads * units) return;
+  const int u = (int)(idx % units);
+  const int h = (int)((idx / units) % heads);
+  const int64_t r = idx / ((int64_t)units * heads);
+  dst[idx] = __ldg(src + (r * (heads / rep) + h / rep) * units + u);
+}
+
 // one warp per (batch, chunk c >= 1, head): out[b, c, h] = <fwd[b, c, h, :], adj[b, nchunks - c, h, :]>; out[b, 0, h] = 0
 template <typename T>
 __global__ void __launch_bounds__(128) ssd_state_dot_kernel(const T* __restrict__ fwd, const T* __restrict__ adj, float* __restrict__ out, int batch,
@@ -336,6 +347,18 @@ extern "C" int ssm_ssd_bwd_group_sum(const void* y, const float* weight, void* o
   }
 #undef SSM_GS
   return launch_status("ssd_bwd_group_sum_kernel");
+}
+
+extern "C" int ssm_ssd_bwd_spread(const void* src, void* dst, int64_t rows, int32_t heads, int32_t groups, int64_t row_bytes, ssm_stream_t stream) {
+  SSM_REQUIRE(rows >= 0 && heads >= 1 && groups >= 1 && heads % groups == 0 && row_bytes >= 0, SSM_ERR_SHAPE, "ssd_bwd_spread: bad shape");
+  if (rows == 0 || row_bytes == 0) return SSM_OK;
+  SSM_REQUIRE(src && dst, SSM_ERR_NULL, "ssd_bwd_spread: missing tensor");
+  SSM_REQUIRE(row_bytes % 16 == 0 && aligned_to(src, 16) && aligned_to(dst, 16), SSM_ERR_ALIGN, "ssd_bwd_spread: rows must be whole 16-byte units");
+  const int64_t total = rows * heads * (row_bytes / 16);
+  SSM_REQUIRE((total + 255) / 256 < (1ll << 31), SSM_ERR_TOO_LARGE, "ssd_bwd_spread: too large for one launch");
+  ssd_bwd_spread_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), rows, heads, heads / groups, (int)(row_bytes / 16));
+  return launch_status("ssd_bwd_spread_kernel");
 }
 
 extern "C" int ssm_ssd_state_dot(const void* fwd_states, const void* adj_states, float* out, int32_t batch, int32_t nchunks, int32_t heads, int32_t elems,

@@ -513,18 +513,18 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     tc::tmem_ld32(tmem + lane_base + 256 + buf * 128 + wg * 32, yi);
     tc::tmem_ld32(tmem + lane_base + 320 + buf * 128 + wg * 32, ys);
     const float Dh = (a.D && !a.d_has_p) ? __ldg(a.D + h) : 0.f;
+    const bool dots = a.row_dots != nullptr;
     float dot = 0.f;  // row_dots: this thread's 32 columns of  sum_p y[p] z[p]  (y before the skip term and unrounded)
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      float f[8], xv[8];
+      float f[8], xv[8], dv[8];
       Vec16<T> xx;
       xx.raw = xr[q];
       xx.unpack(xv);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        const float Dv = (a.D && a.d_has_p) ? __ldg(a.D + h * kP + wg * 32 + q * 8 + e) : Dh;
+        dv[e] = (a.D && a.d_has_p) ? __ldg(a.D + h * kP + wg * 32 + q * 8 + e) : Dh;
         f[e] = fmaf(escale, ys[q * 8 + e], yi[q * 8 + e]);
-        xv[e] *= Dv;
       }
       unsigned char* slot = swz(sZ, i_loc, wg * 4 + q);
       if (has_z) {
@@ -532,22 +532,22 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
         Vec16<T> zz;
         zz.raw = *reinterpret_cast<const uint4*>(slot);
         zz.unpack(zv);
-        if (a.row_dots) {
+        if (dots) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(f[e], zv[e], dot), f[e] += xv[e];
+          for (int e = 0; e < 8; ++e) dot = fmaf(f[e], zv[e], dot), f[e] = fmaf(dv[e], xv[e], f[e]);
         } else {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = (f[e] + xv[e]) * silu_fast(zv[e]);
+          for (int e = 0; e < 8; ++e) f[e] = fmaf(dv[e], xv[e], f[e]) * silu_fast(zv[e]);
         }
       } else {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] += xv[e];
+        for (int e = 0; e < 8; ++e) f[e] = fmaf(dv[e], xv[e], f[e]);
       }
       Vec16<T> o;
       o.pack(f);
       *reinterpret_cast<uint4*>(slot) = o.raw;
     }
-    if (a.row_dots && has_z) {
+    if (dots && has_z) {
       const int t = t0 + MB * kBlk + i_loc;
       // two threads (column halves) add to one zero-initialised word: the sum does not depend on their order
       if (t < a.len) atomicAdd(a.row_dots + ((int64_t)b * a.len + t) * a.heads + h, dot);
@@ -562,16 +562,9 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   for (int q = 0; q < 4; ++q) xr_prev[q] = make_uint4(0, 0, 0, 0);
   int fail = 0;
   int nz = 0;  // z tiles requested so far (parity of the z barrier)
-  // optional weight of this thread's row (folded into the row exponent, so it scales the mask before rounding and
-  // the carried-state term alike); fetched one head ahead
-  const int t_row = t0 + MB * kBlk + i_loc;
-  const float* rs_ptr = (a.row_scale && t_row < a.len) ? a.row_scale + ((int64_t)b * a.len + t_row) * a.heads : nullptr;
-  float rs_next = (rs_ptr && nh > 0) ? __ldg(rs_ptr + h0) : 1.f;
 #pragma unroll 1
   for (int hi = 0; hi < nh; ++hi) {
     const int h = h0 + hi, buf = hi & 1;
-    const float rs_cur = rs_next;
-    if (rs_ptr && hi + 1 < nh) rs_next = __ldg(rs_ptr + h + 1);
     ok = !fail && tc::mbar_wait(mb_full(buf), (hi >> 1) & 1);  // this head's operands (no more waiting once a wait ran out)
     // MMAs of the previous head: the masked tile, the other buffer and its accumulators are free / ready
     if (hi > 0) ok = tc::mbar_wait(mb_mma(buf ^ 1), ((hi - 1) >> 1) & 1) && ok;
@@ -597,7 +590,13 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     // ---- decay mask: G (registers) -> masked tile, K-major over j: unit (i, j/8) at (j/8) * 2048 + i * 16
     const float* vc = sVec + buf * (2 * kQ);
     const float* vcp = vc + kQ;
-    const float ct = a.row_scale ? vc[i_chunk] + lg2_approx(rs_cur) : vc[i_chunk];
+    float ct = vc[i_chunk];
+    if (a.row_scale) {
+      // optional weight of this thread's row, folded into the row exponent: it scales the mask before rounding and the
+      // carried-state term alike
+      const int t_row = t0 + MB * kBlk + i_loc;
+      ct += lg2_approx(t_row < a.len ? __ldg(a.row_scale + ((int64_t)b * a.len + t_row) * a.heads + h) : 1.f);
+    }
     // The weight exp2(c_i - c'_j) of a 32-step chunk factors as exp2(c_i - r) * exp2(r - c'_j) with r = c at the
     // chunk's first step (row factor <= 1 for causal rows, column factor bounded by the decay inside the chunk).
     // Each lane forms one column factor per chunk, each thread one row factor per chunk: 2 ex2 per 32 elements

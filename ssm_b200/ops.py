@@ -1248,8 +1248,12 @@ def _ssd_backward_dual(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, init, chunk,
     del y_plain, dx_r
 
     # (3) dC and dB: head and state axes exchanged, one group per head, the halves of B (C) as the inputs of two heads
-    def halves(t):  # (B, L, G, N) -> (B, L, 2 H, N / 2)
-        return (t.repeat_interleave(rep, 2) if rep > 1 else t).reshape(nb, lp, 2 * nh, nn // 2)
+    def halves(t):  # (B, L, G, N) -> (B, L, 2 H, N / 2): every head gets its group's row, the two halves as two heads
+        if rep == 1:
+            return t.reshape(nb, lp, 2 * nh, nn // 2)
+        out = torch.empty(nb, lp, 2 * nh, nn // 2, dtype=io, device=dev)
+        L.check(lib.ssm_ssd_bwd_spread(_p(t), _p(out), nb * lp, nh, ng, nn * t.element_size(), _stream()))
+        return out
 
     def state_t(s):  # (B, H, P, N) fp32 -> (B, 2 H, N / 2, N): transposed, the P axis zero-padded to N
         return None if s is None else F.pad(s.float().transpose(2, 3).reshape(nb, 2 * nh, nn // 2, npj), (0, nn - npj))
