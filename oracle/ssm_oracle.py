@@ -428,8 +428,17 @@ def ssd_scan(
     dt_softplus: bool = False,
     initial_states: Optional[Tensor] = None,
     return_final_states: bool = False,
+    cu_seqlens: Optional[Tensor] = None,
+    seq_reset: bool = True,
+    return_varlen_states: bool = False,
 ):
     """State-space-dual scan with a ``d_state`` axis (Mamba-2 layout).
+
+    ``cu_seqlens (S + 1,)`` marks ``S`` sequences packed along ``L`` of a batch of one.  The
+    ``varlen_states (S, H, P, N)`` are the states after the last token of every sequence, each
+    scanned from zero.  With ``seq_reset`` the state behind ``Y`` restarts at every boundary too;
+    without it ``Y`` runs through the boundaries, which is what upstream mamba-ssm computes when
+    it is given ``cu_seqlens`` but no ``seq_idx`` (its ``combined_varlen`` vector).
 
     ``X (B,L,H,P)``, ``dt (B,L,H)``, ``A (H,)``, ``B/C (B,L,G,N)`` with ``G | H``,
     ``D (H,)`` or ``(H,P)``, ``z (B,L,H,P)``, state ``(B,H,P,N)`` in fp32.  It is the
@@ -464,10 +473,31 @@ def ssd_scan(
         s = initial_states.to(wd)
     else:
         s = torch.zeros(nb, nh, npj, nn, dtype=wd)
+    starts, ends = set(), {}
+    if cu_seqlens is not None:
+        cu = [int(v) for v in torch.as_tensor(cu_seqlens).tolist()]
+        if nb != 1:
+            raise ValueError("cu_seqlens needs a batch of one (sequences packed along L).")
+        if len(cu) < 2 or cu[0] != 0 or cu[-1] != nl or any(b < a for a, b in zip(cu, cu[1:])):
+            raise ValueError("cu_seqlens must rise from 0 to L.")
+        starts = set(cu[1:-1])
+        ends = {e - 1: k for k, e in enumerate(cu[1:]) if e > cu[k]}
+    sr = torch.zeros_like(s)  # the per-sequence state: always restarts at a boundary
+    varlen = [torch.zeros(nh, npj, nn, dtype=wd) for _ in range(len(ends) and len(cu) - 1)]
     rows = []
     for t in range(nl):
         d_t = dtw[:, t]
-        s = torch.exp(d_t * Aw[None])[:, :, None, None] * s + (d_t[:, :, None] * Xw[:, t])[..., None] * Bw[:, t][:, :, None, :]
+        if t in starts:
+            sr = torch.zeros_like(sr)
+            if seq_reset:
+                s = torch.zeros_like(s)
+        decay = torch.exp(d_t * Aw[None])[:, :, None, None]
+        inp = (d_t[:, :, None] * Xw[:, t])[..., None] * Bw[:, t][:, :, None, :]
+        s = decay * s + inp
+        if cu_seqlens is not None:
+            sr = decay * sr + inp
+            if t in ends:
+                varlen[ends[t]] = sr[0]
         rows.append((s * Cw[:, t][:, :, None, :]).sum(-1))
     Y = torch.stack(rows, dim=1) if rows else torch.zeros(nb, 0, nh, npj, dtype=wd)
     if D is not None:
@@ -476,9 +506,15 @@ def ssd_scan(
     if z is not None:
         Y = Y * F.silu(z.to(wd))
     Y = Y.to(X.dtype)
+    out = [Y]
     if return_final_states:
-        return Y, s.to(torch.float32) if wd != torch.float64 else s
-    return Y
+        out.append(s.to(torch.float32) if wd != torch.float64 else s)
+    if return_varlen_states:
+        if cu_seqlens is None:
+            raise ValueError("return_varlen_states needs cu_seqlens.")
+        v = torch.stack(varlen) if varlen else torch.zeros(0, nh, npj, nn, dtype=wd)
+        out.append(v.to(torch.float32) if wd != torch.float64 else v)
+    return out[0] if len(out) == 1 else tuple(out)
 
 
 def softplus_threshold() -> float:

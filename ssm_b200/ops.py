@@ -1345,6 +1345,9 @@ def ssd_scan(
     return_final_states: bool = False,
     check_status: bool = False,
     backward: str = "dual",
+    cu_seqlens: Optional[Tensor] = None,
+    seq_reset: bool = True,
+    return_varlen_states: bool = False,
 ):
     """Extension: state-space-dual scan with a ``d_state`` axis (Mamba-2 layout).
 
@@ -1353,15 +1356,52 @@ def ssd_scan(
     on channel ``h*P+p`` with per-head ``dt`` and ``A``.  For headdim 64, d_state 128, chunk 256 and
     bf16 / fp16 operands the forward runs as chunked GEMMs on the tcgen05 tensor cores, and so does the
     backward (``backward="dual"``: four more runs of the same kernels on transformed operands; its
-    gradients carry the rounding of 16-bit operands, about 0.3 % of each contraction).  Any other shape or
+    gradients carry the rounding of 16-bit operands, about 0.3 % of each contraction).  ``cu_seqlens (S + 1,)``
+    marks ``S`` sequences packed along ``L`` of a batch of one: ``return_varlen_states`` adds the state after the last
+    token of every sequence ``(S, H, P, N)``, each scanned from zero, and with ``seq_reset`` (default) ``Y`` restarts at
+    every boundary too (without it ``Y`` runs through, as upstream mamba-ssm does when given no ``seq_idx``).  Any other shape or
     dtype, and ``backward="scan"``, goes through the selective-scan kernels on the flattened channels
     (fp32 arithmetic, an order of magnitude slower at these shapes).  A bounded device-side wait that runs out (it never should) is reported by the next
     ``ssd_scan`` call on the device, or at once by ``check_status=True`` / :func:`ssd_check_status`, which synchronise.
     """
     if backward not in ("dual", "scan"):
         raise ValueError('backward must be "dual" or "scan".')
-    Y, final = _SsdFn.apply(X, dt, A, B, C, D, z, dt_bias, dt_softplus, initial_states, chunk_size, check_status, backward == "dual")
-    return (Y, final) if return_final_states else Y
+    dual = backward == "dual"
+    if cu_seqlens is None:
+        if return_varlen_states:
+            raise ValueError("return_varlen_states needs cu_seqlens.")
+        Y, final = _SsdFn.apply(X, dt, A, B, C, D, z, dt_bias, dt_softplus, initial_states, chunk_size, check_status, dual)
+        return (Y, final) if return_final_states else Y
+    # packed sequences: every sequence is its own scan from a zero state (chunks counted from its first token), so the
+    # kernels see plain dense problems; the boundaries are host integers (one read of cu_seqlens)
+    if X.ndim != 4 or X.shape[0] != 1:
+        raise ValueError("cu_seqlens needs a batch of one (sequences packed along L).")
+    if initial_states is not None and seq_reset:
+        raise ValueError("initial_states cannot be combined with sequences that restart at cu_seqlens.")
+    cu = [int(v) for v in torch.as_tensor(cu_seqlens).tolist()]
+    if len(cu) < 2 or cu[0] != 0 or cu[-1] != X.shape[1] or any(b < a for a, b in zip(cu, cu[1:])):
+        raise ValueError("cu_seqlens must rise from 0 to L.")
+    cut = lambda t, a, b: None if t is None else t[:, a:b]  # noqa: E731
+    parts, states = [], []
+    for a, b in zip(cu, cu[1:]):
+        if b == a:
+            states.append(torch.zeros(X.shape[2], X.shape[3], B.shape[3], dtype=torch.float32, device=X.device))
+            continue
+        y_k, s_k = _SsdFn.apply(cut(X, a, b), cut(dt, a, b), A, cut(B, a, b), cut(C, a, b), D, cut(z, a, b), dt_bias, dt_softplus, None,
+                                chunk_size, check_status, dual)
+        parts.append(y_k)
+        states.append(s_k[0])
+    varlen = torch.stack(states)
+    if seq_reset:
+        Y, final = (torch.cat(parts, 1) if parts else torch.empty_like(X)), varlen[-1:].clone()
+    else:  # upstream mamba-ssm given cu_seqlens without seq_idx: Y runs through the boundaries, only the states are per sequence
+        Y, final = _SsdFn.apply(X, dt, A, B, C, D, z, dt_bias, dt_softplus, initial_states, chunk_size, check_status, dual)
+    out = [Y]
+    if return_final_states:
+        out.append(final)
+    if return_varlen_states:
+        out.append(varlen)
+    return out[0] if len(out) == 1 else tuple(out)
 
 
 __all__ = [

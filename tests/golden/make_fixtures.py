@@ -177,6 +177,22 @@ def pack_upstream_kats(ref_root: Path) -> Pack:
     pk.put(case, "out", "y", _rec(c["outputs"]["y"]))
     pk.put(case, "out", "final_states", _rec(c["outputs"]["final_states"]))
 
+    # Packed sequences [0, 3, 6] (scripts/refresh_mamba_goldens.py:609-632: cu_seqlens without seq_idx, dt_softplus off).
+    # mamba-ssm clamps dt to its dt_limit (0, inf), so the stored dt is clamped the same way; its y runs through the
+    # boundary (no seq_idx), only the varlen states are per sequence.  Head 1 has A > 0: not a known answer.
+    c = up["ssd_combined"]["combined_varlen"]
+    case = "ssdvarlen/mamba_combined_varlen"
+    for k, v in c["inputs"].items():
+        if k == "chunk_size":
+            continue
+        t = _rec(v)
+        pk.put(case, "in", k, t.clamp_min(0) if k == "dt" else t)
+    pk.put(case, "in", "cu_seqlens", np.asarray([0, 3, 6], dtype=np.int64))
+    pk.opts(case, chunk_size=int(c["inputs"]["chunk_size"]), dt_softplus=False, heads=[0], seq_reset=False,
+            source=src + ":ssd_combined.combined_varlen", rtol=5e-3, atol=2e-2)
+    pk.put(case, "out", "y", _rec(c["outputs"]["y"]))
+    pk.put(case, "out", "varlen_states", _rec(c["outputs"]["varlen_states"]))
+
     for name, act in (("channels_first_silu", "silu"), ("channels_last_identity", "identity")):
         c = up["dw_causal_conv"][name]
         case = f"conv/mamba_{name}"

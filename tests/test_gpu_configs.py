@@ -182,6 +182,40 @@ def test_ssd_gradients_at_the_tensor_core_shape(nb, nl, nh, ng, dtype, use_z, us
             close(a, b, **SSD_TOL, what=f"d{k}", reduced=True)
 
 
+def test_ssd_packed_sequences_on_the_tensor_cores():
+    """Three sequences (one of them empty) packed along L at headdim 64 / d_state 128: outputs, per-sequence states and
+    the gradients of X, B, C and z against the oracle; every sequence runs as its own tensor-core scan."""
+    from ssm_b200 import ops
+
+    gen = torch.Generator().manual_seed(23)
+    nl, nh = 900, 2
+    bf = torch.bfloat16
+    ins = dict(X=torch.randn(1, nl, nh, 64, generator=gen).to(bf), dt=(torch.randn(1, nl, nh, generator=gen) - 3).to(bf),
+               A=-torch.exp(torch.rand(nh, generator=gen) * 2.77), B=(torch.randn(1, nl, 1, 128, generator=gen) / 128 ** 0.5).to(bf),
+               C=(torch.randn(1, nl, 1, 128, generator=gen) / 128 ** 0.5).to(bf), D=torch.randn(nh, generator=gen),
+               z=torch.randn(1, nl, nh, 64, generator=gen).to(bf))
+    cu = torch.tensor([0, 300, 300, 812, 900])
+    wy = torch.randn(1, nl, nh, 64, generator=gen).to(bf).float()
+    ws = torch.randn(4, nh, 64, 128, generator=gen)
+    names = ["X", "B", "C", "z"]
+
+    def run(ops_, t, dev_):
+        Y, st = ops_.ssd_scan(t["X"], t["dt"], t["A"], t["B"], t["C"], 256, D=t["D"], z=t["z"], dt_softplus=True,
+                              cu_seqlens=cu.to(dev_), return_varlen_states=True)
+        return Y, st, torch.autograd.grad((Y.float() * wy.to(dev_)).sum() + (st * ws.to(dev_)).sum(), [t[k] for k in names])
+
+    lo = {k: v.clone().requires_grad_(k in names) for k, v in ins.items()}
+    lg = {k: v.clone().cuda().requires_grad_(k in names) for k, v in ins.items()}
+    Yg, Sg, gg = run(ops, lg, "cuda")
+    ops.ssd_check_status()
+    Yo, So, go = run(orc, lo, "cpu")
+    close(Yg, Yo, **SSD_TOL, what="Y", reduced=True)
+    close(Sg, So, **SSD_TOL, what="varlen states", reduced=True)
+    assert float(Sg[1].abs().max()) == 0.0
+    for k, a, b in zip(names, gg, go):
+        close(a, b, **SSD_TOL, what=f"d{k}", reduced=True)
+
+
 def test_decode_step_configuration():
     """One Mamba-1 decode step at batch 256, d_inner 5120, d_state 16 (fp32 state, bf16 activations, B / C shared by the
     channels of a row) with the conv-window update in front of it, whole configuration against the oracle."""

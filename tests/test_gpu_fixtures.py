@@ -122,3 +122,17 @@ def test_ssd_scan(case):
     close(Y, case.outs["y"], **tol(case), what=f"{case.name} y", reduced="rtol" in case.opts)
     close(fin, case.outs["final_states"], **tol(case), what=f"{case.name} final", reduced="rtol" in case.opts)
     _grads(case, (Y, fin), (case.ins["grad_out"], case.ins["grad_final_states"]), i)
+
+
+@pytest.mark.parametrize("case", _all("ssdvarlen"))
+def test_ssd_scan_packed_sequences(case):
+    """mamba-ssm's ``combined_varlen`` vector (cu_seqlens without seq_idx: y runs through the boundary, states per sequence)."""
+    from ssm_b200 import ops
+
+    i = {k: dev(v) for k, v in case.ins.items()}
+    o = case.opts
+    Y, states = ops.ssd_scan(i["X"], i["dt"], i["A"], i["B"], i["C"], o["chunk_size"], dt_softplus=o["dt_softplus"],
+                             cu_seqlens=i["cu_seqlens"], seq_reset=o["seq_reset"], return_varlen_states=True)
+    heads = o["heads"]
+    close(Y[:, :, heads], case.outs["y"][:, :, heads], **tol(case), what=f"{case.name} y", reduced=True)
+    close(states[:, heads], case.outs["varlen_states"][:, heads], **tol(case), what=f"{case.name} varlen states", reduced=True)

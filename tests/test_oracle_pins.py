@@ -119,3 +119,36 @@ def test_ssd_scan(case):
     _close(Y, case.outs["y"], **tol(case))
     _close(fin, case.outs["final_states"], **tol(case))
     _check_grads(case, (Y, fin), (i["grad_out"].detach(), i["grad_final_states"].detach()), i)
+
+
+@pytest.mark.parametrize("case", _all("ssdvarlen"))
+def test_ssd_scan_packed_sequences(case):
+    """mamba-ssm's ``combined_varlen`` vector: cu_seqlens without seq_idx, so y runs through the boundary and only the
+    states are per sequence (``seq_reset=False``)."""
+    i = {k: v for k, v in case.ins.items()}
+    o = case.opts
+    Y, states = orc.ssd_scan(i["X"], i["dt"], i["A"], i["B"], i["C"], o["chunk_size"], dt_softplus=o["dt_softplus"],
+                             cu_seqlens=i["cu_seqlens"], seq_reset=o["seq_reset"], return_varlen_states=True)
+    heads = o["heads"]
+    _close(Y[:, :, heads], case.outs["y"][:, :, heads], **tol(case))
+    _close(states[:, heads], case.outs["varlen_states"][:, heads], **tol(case))
+
+
+def test_ssd_scan_packed_sequences_restart():
+    """With ``seq_reset`` a packed call equals the separate calls, sequence by sequence; an empty sequence has a zero state."""
+    gen = torch.Generator().manual_seed(5)
+    nl, nh, npj, nn = 11, 2, 3, 4
+    X, dt = torch.randn(1, nl, nh, npj, generator=gen), torch.rand(1, nl, nh, generator=gen) * 0.5
+    A, Bm, Cm = -torch.rand(nh, generator=gen) - 0.1, torch.randn(1, nl, 1, nn, generator=gen), torch.randn(1, nl, 1, nn, generator=gen)
+    cu = torch.tensor([0, 4, 4, 9, 11])
+    Y, fin, states = orc.ssd_scan(X, dt, A, Bm, Cm, 4, cu_seqlens=cu, return_final_states=True, return_varlen_states=True)
+    assert states.shape == (4, nh, npj, nn) and float(states[1].abs().max()) == 0.0
+    for k, (a, b) in enumerate(((0, 4), (4, 4), (4, 9), (9, 11))):
+        if b == a:
+            continue
+        y_k, s_k = orc.ssd_scan(X[:, a:b], dt[:, a:b], A, Bm[:, a:b], Cm[:, a:b], 4, return_final_states=True)
+        _close(Y[:, a:b], y_k, rtol=1e-6, atol=1e-6)
+        _close(states[k], s_k[0], rtol=1e-6, atol=1e-6)
+    _close(fin[0], states[-1], rtol=0, atol=0)
+    with pytest.raises(ValueError):
+        orc.ssd_scan(X, dt, A, Bm, Cm, 4, cu_seqlens=torch.tensor([0, 5, 10]))
