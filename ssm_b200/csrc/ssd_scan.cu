@@ -385,12 +385,15 @@ struct ScanSmem {
   static constexpr int S_BYTES = kP * kN * 2;       // incoming state, MN-major [p/8][n][8]                 16 KB (x2)
   static constexpr int VEC_BYTES = 2 * kQ * 4;      // c and c - log2(delta) of the chunk                     2 KB (x2)
   static constexpr int Z_BYTES = kBlk * kP * 2;     // z in / y out of one head: [row][64 p], same swizzle    16 KB
-  static constexpr int W_BYTES = 8 * 128 * 4;       // per warp: the column factors of its (up to) four mask chunks            4 KB
+  static constexpr int W_BYTES = 1024 * 4;          // per warp: the column factors of its mask chunks (16 warps x 64)          4 KB
   static constexpr int TOTAL = C_BYTES + B_BYTES + 2 * (X_BYTES + S_BYTES + VEC_BYTES) + Z_BYTES + W_BYTES;
   static constexpr int ALLOC = TOTAL + 1024;        // the tiles TMA swizzles must start on 1024-byte boundaries
 };
 
-constexpr int kScanThreads = 256;
+constexpr int kScanThreads = 512;
+constexpr int kScanWG = kScanThreads / 128;  // warpgroups: each owns every kScanWG-th 32-step column chunk of the mask and kP / kScanWG output columns
+constexpr int kEC = kP / kScanWG;             // epilogue columns per thread
+constexpr int kEU = kEC / 8;                  // ... in 16-byte units
 // Thread that issues the bulk copies (TMA): lane 0 of the warp with the least mask work (rows 0..31 of the block, odd
 // chunks), so that its issue time hides behind the other warps' mask stage; thread 0 issues the MMAs.
 constexpr int kCopyThread = 128;
@@ -407,7 +410,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
                                               uint64_t* mbar, uint32_t* tmem_slot) {
   using M = ScanSmem<T>;
   constexpr int KJ = (MB + 1) * kBlk;  // steps that can reach this block's rows
-  constexpr int NCH = KJ / 64;         // 32-step column chunks per thread (the two warpgroups interleave chunks)
+  constexpr int NCH = KJ / (32 * kScanWG);  // 32-step column chunks per thread (the warpgroups interleave chunks)
   unsigned char* sC = smraw;
   unsigned char* sBA = sC + M::C_BYTES;
   unsigned char* sX = sBA + M::B_BYTES;        // two buffers
@@ -421,8 +424,8 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   auto mb_full = [&](int bf) { return tc::smem_u32(&mbar[3 + bf]); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wg = tid >> 7;                     // column chunks wg, wg + 2, ... in the mask stage; column half in the epilogue
-  float* sW = reinterpret_cast<float*>(sZ + M::Z_BYTES) + warp * 128;  // this warp's column factors
+  const int wg = tid >> 7;                     // column chunks wg, wg + kScanWG, ... in the mask stage; column slice in the epilogue
+  float* sW = reinterpret_cast<float*>(sZ + M::Z_BYTES) + warp * (NCH * 32);  // this warp's column factors
   const int half_grid = gridDim.x >> 1;
   const int rem = (int)blockIdx.x % half_grid;
   const int part = rem % nparts, bc = rem / nparts;
@@ -492,11 +495,11 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   ok = __all_sync(0xffffffffu, ok && tc::mbar_wait(mb_g, 0));  // warp-uniform
   tc::fence_after_sync();
 
-  // This thread's part of G stays in registers for all heads: row i_loc, chunks wg, wg + 2, ...
+  // This thread's part of G stays in registers for all heads: row i_loc, chunks wg, wg + kScanWG, ...
   float vG[NCH][32];
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
-    const int cc = wg + 2 * k;
+    const int cc = wg + kScanWG * k;
     if (ok && cc <= rc) {
       tc::tmem_ld32(tmem + lane_base + cc * 32, vG[k]);
     } else {
@@ -507,26 +510,26 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
 
   // epilogue of head h from accumulator pair `buf`: y = Y_intra + exp2(c_i) Y_inter + D x, gated by the z row in
   // the staging tile, written back to the same slots.  Thread = row i_loc, this warpgroup's 32 columns.
-  auto epilogue = [&](int h, int buf, float ct, const uint4 (&xr)[4]) {
+  auto epilogue = [&](int h, int buf, float ct, const uint4 (&xr)[kEU]) {
     const float escale = ex2_approx(ct);
-    float yi[32], ys[32];
-    tc::tmem_ld32(tmem + lane_base + 256 + buf * 128 + wg * 32, yi);
-    tc::tmem_ld32(tmem + lane_base + 320 + buf * 128 + wg * 32, ys);
+    float yi[kEC], ys[kEC];
+    tc::tmem_ld16(tmem + lane_base + 256 + buf * 128 + wg * kEC, yi);
+    tc::tmem_ld16(tmem + lane_base + 320 + buf * 128 + wg * kEC, ys);
     const float Dh = (a.D && !a.d_has_p) ? __ldg(a.D + h) : 0.f;
     const bool dots = a.row_dots != nullptr;
     float dot = 0.f;  // row_dots: this thread's 32 columns of  sum_p y[p] z[p]  (y before the skip term and unrounded)
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < kEU; ++q) {
       float f[8], xv[8], dv[8];
       Vec16<T> xx;
       xx.raw = xr[q];
       xx.unpack(xv);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        dv[e] = (a.D && a.d_has_p) ? __ldg(a.D + h * kP + wg * 32 + q * 8 + e) : Dh;
+        dv[e] = (a.D && a.d_has_p) ? __ldg(a.D + h * kP + wg * kEC + q * 8 + e) : Dh;
         f[e] = fmaf(escale, ys[q * 8 + e], yi[q * 8 + e]);
       }
-      unsigned char* slot = swz(sZ, i_loc, wg * 4 + q);
+      unsigned char* slot = swz(sZ, i_loc, wg * kEU + q);
       if (has_z) {
         float zv[8];
         Vec16<T> zz;
@@ -557,9 +560,9 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   const int t_blk = t0 + MB * kBlk;  // first step of this block's rows
 
   float ct_prev = 0.f;   // the previous head's row exponent and x row, carried into its (deferred) epilogue
-  uint4 xr_prev[4];
+  uint4 xr_prev[kEU];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) xr_prev[q] = make_uint4(0, 0, 0, 0);
+  for (int q = 0; q < kEU; ++q) xr_prev[q] = make_uint4(0, 0, 0, 0);
   int fail = 0;
   int nz = 0;  // z tiles requested so far (parity of the z barrier)
 #pragma unroll 1
@@ -605,7 +608,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     bool fast[NCH];
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
-      const int cc = wg + 2 * k;
+      const int cc = wg + kScanWG * k;
       arow[k] = 0.f, fast[k] = false;
       if (cc <= rc) {
         const float r = vc[cc * 32];
@@ -617,7 +620,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     __syncwarp();
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
-      const int cc = wg + 2 * k;  // chunk of 32 steps: fully causal (cc < rc), diagonal (cc == rc) or empty (cc > rc) for this warp's rows
+      const int cc = wg + kScanWG * k;  // chunk of 32 steps: fully causal (cc < rc), diagonal (cc == rc) or empty (cc > rc) for this warp's rows
       const int jb = cc * 32;
       unsigned char* dst = sBA + ((size_t)(jb / 8) * kBlk + i_loc) * 16;
       if (cc > rc) {
@@ -666,9 +669,9 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
       }
     }
     // this row of x (for D x in the epilogue one iteration later)
-    uint4 xr[4];
+    uint4 xr[kEU];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) xr[q] = *reinterpret_cast<const uint4*>(swz(sX + buf * M::X_BYTES, i_chunk, wg * 4 + q));
+    for (int q = 0; q < kEU; ++q) xr[q] = *reinterpret_cast<const uint4*>(swz(sX + buf * M::X_BYTES, i_chunk, wg * kEU + q));
 
     tc::fence_async_smem();
     tc::fence_before_sync();
@@ -704,7 +707,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     }
     ct_prev = ct;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) xr_prev[q] = xr[q];
+    for (int q = 0; q < kEU; ++q) xr_prev[q] = xr[q];
   }
   // leave the loop together: a thread that saw a wait run out above still reaches the same barriers
   fail = __syncthreads_or(fail);
