@@ -211,7 +211,7 @@ def test_ssd_packed_sequences_on_the_tensor_cores():
     Yo, So, go = run(orc, lo, "cpu")
     close(Yg, Yo, **SSD_TOL, what="Y", reduced=True)
     close(Sg, So, **SSD_TOL, what="varlen states", reduced=True)
-    assert float(Sg[1].abs().max()) == 0.0
+    assert float(Sg[1].detach().abs().max()) == 0.0
     for k, a, b in zip(names, gg, go):
         close(a, b, **SSD_TOL, what=f"d{k}", reduced=True)
 

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from tests.fixtures import cases, tol
-from tests.gpu_util import REDUCED, close, leaf
+from tests.gpu_util import REDUCED, close, dev, leaf
 
 pytestmark = pytest.mark.gpu
 
