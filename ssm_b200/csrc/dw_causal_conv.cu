@@ -291,16 +291,20 @@ __device__ __forceinline__ void load_x_cl(const ssm_conv_args& a, const T* __res
   }
 }
 
+// Channels-last forward: thread = V channels, walking `tile` consecutive steps with the K - 1 previous inputs in registers.
+// Four steps' loads are issued before their results are formed, so every thread keeps four 16-byte loads in flight; the
+// host picks `tile` so that narrow tensors (the 128-channel B / C inputs of a Mamba-2 layer) still fill the machine.
 template <typename T, int KM>
-__global__ void __launch_bounds__(kConvThreads) conv_cl_fwd_kernel(const ssm_conv_args a, int vec) {
+__global__ void __launch_bounds__(kConvThreads) conv_cl_fwd_kernel(const ssm_conv_args a, int vec, int tile) {
   constexpr int KH = KM - 1;
   constexpr int V = 16 / sizeof(T);
+  constexpr int U = 4;  // steps per batch of loads
   const int C = a.channels, L = a.len, K = a.width;
   const int c0 = (blockIdx.x * kConvThreads + threadIdx.x) * V;
   if (c0 >= C) return;
   const int nvalid = min(V, C - c0);
   const int b = blockIdx.z;
-  const int ts = blockIdx.y * kConvTimeTile, te = min(L, ts + kConvTimeTile);
+  const int ts = blockIdx.y * tile, te = min(L, ts + tile);
   const T* __restrict__ x = reinterpret_cast<const T*>(a.x) + (int64_t)b * L * C + c0;
   T* __restrict__ y = reinterpret_cast<T*>(a.y) + (int64_t)b * L * C + c0;
   float wr[KM][V], bias[V];
@@ -320,27 +324,36 @@ __global__ void __launch_bounds__(kConvThreads) conv_cl_fwd_kernel(const ssm_con
       for (int i = 0; i < V; ++i) hist[m][i] = 0.f;
     }
   }
-  for (int t = ts; t < te; ++t) {
-    float cur[V], out[V];
-    load_group<T, V>(x + (int64_t)t * C, vec, nvalid, cur);
+  for (int t = ts; t < te; t += U) {
+    float cur[U][V];
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-      float acc = fmaf(wr[0][i], cur[i], bias[i]);
-#pragma unroll
-      for (int m = 1; m < KM; ++m)
-        if (m < K) acc = fmaf(wr[m][i], hist[m - 1][i], acc);
-      out[i] = a.silu ? silu_fast(acc) : acc;
+    for (int j = 0; j < U; ++j) {
+      if (t + j < te) load_group<T, V>(x + (int64_t)(t + j) * C, vec, nvalid, cur[j]);
     }
-    store_group<T, V>(y + (int64_t)t * C, vec, nvalid, out);
 #pragma unroll
-    for (int m = KH - 1; m >= 1; --m)
-      if (m < K - 1) {
+    for (int j = 0; j < U; ++j) {
+      if (t + j < te) {
+        float out[V];
 #pragma unroll
-        for (int i = 0; i < V; ++i) hist[m][i] = hist[m - 1][i];
+        for (int i = 0; i < V; ++i) {
+          float acc = fmaf(wr[0][i], cur[j][i], bias[i]);
+#pragma unroll
+          for (int m = 1; m < KM; ++m)
+            if (m < K) acc = fmaf(wr[m][i], hist[m - 1][i], acc);
+          out[i] = a.silu ? silu_fast(acc) : acc;
+        }
+        store_group<T, V>(y + (int64_t)(t + j) * C, vec, nvalid, out);
+#pragma unroll
+        for (int m = KH - 1; m >= 1; --m)
+          if (m < K - 1) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) hist[m][i] = hist[m - 1][i];
+          }
+        if (KH > 0) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) hist[0][i] = cur[j][i];
+        }
       }
-    if (KH > 0) {
-#pragma unroll
-      for (int i = 0; i < V; ++i) hist[0][i] = cur[i];
     }
   }
 }
@@ -486,8 +499,18 @@ static int conv_validate(const ssm_conv_args* a) {
   return SSM_OK;
 }
 
-static dim3 conv_cl_grid(const ssm_conv_args& a, int V) {
-  return dim3(((a.channels + V - 1) / V + kConvThreads - 1) / kConvThreads, (a.len + kConvTimeTile - 1) / kConvTimeTile, a.batch);
+static dim3 conv_cl_grid(const ssm_conv_args& a, int V, int tile = kConvTimeTile) {
+  return dim3(((a.channels + V - 1) / V + kConvThreads - 1) / kConvThreads, (a.len + tile - 1) / tile, a.batch);
+}
+
+// Steps per thread of the channels-last forward: the full tile when the tensor is wide enough to occupy the GPU, shorter
+// walks (down to 8 steps: every walk re-reads K - 1 earlier inputs) when channels x batch alone would leave it idle.
+static int conv_cl_fwd_tile(const ssm_conv_args& a, int V) {
+  const int64_t lanes = (int64_t)((a.channels + V - 1) / V) * a.batch;  // threads per time tile
+  int tile = kConvTimeTile;
+  while (tile > 8 && lanes * ((a.len + tile - 1) / tile) < 148 * 1024) tile >>= 1;
+  while ((a.len + tile - 1) / tile > 65535) tile <<= 1;  // grid.y
+  return tile;
 }
 
 template <typename T, int KM>
@@ -498,7 +521,8 @@ static int conv_fwd_launch(const ssm_conv_args& a, cudaStream_t st) {
     conv_cf_fwd_kernel<T, KM><<<(unsigned)((int64_t)a.batch * a.channels), kConvThreads, 0, st>>>(a, vec);
   } else {
     const int vec = (a.channels % V == 0) && aligned_to(a.x, 16) && aligned_to(a.y, 16);
-    conv_cl_fwd_kernel<T, KM><<<conv_cl_grid(a, V), kConvThreads, 0, st>>>(a, vec);
+    const int tile = conv_cl_fwd_tile(a, V);
+    conv_cl_fwd_kernel<T, KM><<<conv_cl_grid(a, V, tile), kConvThreads, 0, st>>>(a, vec, tile);
   }
   return launch_status("dw_causal_conv_fwd");
 }

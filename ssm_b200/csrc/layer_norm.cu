@@ -164,10 +164,13 @@ __device__ __forceinline__ void norm_stats(const ssm_norm_args& a, int gt, int n
   rstd = rsqrtf(group_allsum<G>(q, scratch) * inv + a.eps);
 }
 
-template <typename T, int G>
+// MC = 16-byte chunks of a row per thread.  Rows of up to 768 chunks stay with 128 threads (several rows in flight per SM keep
+// more loads outstanding than one wide CTA per row does); only wider rows take 512 threads.
+template <typename T, int G, int MC = kNormFwdChunks>
 __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_fwd_kernel(const ssm_norm_args a) {
   using Cfg = NormCfg<T, G>;
   constexpr int V = Cfg::V;
+  constexpr int kNormFwdChunks = MC;
   __shared__ float scratch[32];
   const int gt = threadIdx.x % G;
   const int64_t row = (int64_t)blockIdx.x * Cfg::RPC + threadIdx.x / G;
@@ -480,11 +483,11 @@ static int norm_bwd_ctas(const ssm_norm_args& a, int rpc) {
   return (int)(npass < kNormBwdMaxCtas ? npass : kNormBwdMaxCtas);
 }
 
-template <typename T, int G>
+template <typename T, int G, int MC = kNormFwdChunks>
 static int norm_fwd_launch(const ssm_norm_args& a, cudaStream_t st) {
   using Cfg = NormCfg<T, G>;
   const unsigned grid = (unsigned)((a.rows + Cfg::RPC - 1) / Cfg::RPC);
-  norm_fwd_kernel<T, G><<<grid, Cfg::BLOCK, 0, st>>>(a);
+  norm_fwd_kernel<T, G, MC><<<grid, Cfg::BLOCK, 0, st>>>(a);
   return launch_status("norm_fwd_kernel");
 }
 template <typename T, int G, int MC>
@@ -529,10 +532,11 @@ static int norm_fwd_t(const ssm_norm_args& a, cudaStream_t st) {
     norm_scalar_kernel<T, false><<<(unsigned)a.rows, 128, 0, st>>>(g);
     return launch_status("norm_scalar_kernel");
   }
+  const int nchunk = a.hidden / (16 / (int)sizeof(T));
   switch (norm_group(a, kNormFwdChunks)) {
     case 32: return norm_fwd_launch<T, 32>(a, st);
     case 128: return norm_fwd_launch<T, 128>(a, st);
-    default: return norm_fwd_launch<T, 512>(a, st);
+    default: return nchunk <= 128 * 6 ? norm_fwd_launch<T, 128, 6>(a, st) : norm_fwd_launch<T, 512>(a, st);
   }
 }
 template <typename T>
