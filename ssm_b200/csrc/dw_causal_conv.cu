@@ -300,11 +300,16 @@ __global__ void __launch_bounds__(kConvThreads) conv_cl_fwd_kernel(const ssm_con
   constexpr int V = 16 / sizeof(T);
   constexpr int U = 4;  // steps per batch of loads
   const int C = a.channels, L = a.len, K = a.width;
-  const int c0 = (blockIdx.x * kConvThreads + threadIdx.x) * V;
-  if (c0 >= C) return;
+  // work item = (time tile, channel vector), channel vectors fastest: a narrow tensor packs several time tiles into one CTA
+  const int nvec = (C + V - 1) / V;
+  const int64_t item = (int64_t)blockIdx.x * kConvThreads + threadIdx.x;
+  const int c0 = (int)(item % nvec) * V;
+  const int64_t tile_idx = item / nvec;
+  const int64_t ts64 = tile_idx * tile;
+  if (ts64 >= L) return;
+  const int ts = (int)ts64, te = min(L, ts + tile);
   const int nvalid = min(V, C - c0);
   const int b = blockIdx.z;
-  const int ts = blockIdx.y * tile, te = min(L, ts + tile);
   const T* __restrict__ x = reinterpret_cast<const T*>(a.x) + (int64_t)b * L * C + c0;
   T* __restrict__ y = reinterpret_cast<T*>(a.y) + (int64_t)b * L * C + c0;
   float wr[KM][V], bias[V];
@@ -499,17 +504,20 @@ static int conv_validate(const ssm_conv_args* a) {
   return SSM_OK;
 }
 
-static dim3 conv_cl_grid(const ssm_conv_args& a, int V, int tile = kConvTimeTile) {
-  return dim3(((a.channels + V - 1) / V + kConvThreads - 1) / kConvThreads, (a.len + tile - 1) / tile, a.batch);
+static dim3 conv_cl_grid(const ssm_conv_args& a, int V) {
+  return dim3(((a.channels + V - 1) / V + kConvThreads - 1) / kConvThreads, (a.len + kConvTimeTile - 1) / kConvTimeTile, a.batch);
 }
 
-// Steps per thread of the channels-last forward: the full tile when the tensor is wide enough to occupy the GPU, shorter
-// walks (down to 8 steps: every walk re-reads K - 1 earlier inputs) when channels x batch alone would leave it idle.
+// Steps per thread of the channels-last forward: the full tile when that still gives the GPU eight or more waves of CTAs
+// (a ragged last wave then costs little), shorter walks otherwise, down to 8 steps (every walk re-reads K - 1 earlier inputs).
+static int64_t conv_cl_fwd_ctas(const ssm_conv_args& a, int V, int tile) {
+  const int64_t items = (int64_t)((a.channels + V - 1) / V) * ((a.len + tile - 1) / tile);
+  return (items + kConvThreads - 1) / kConvThreads;
+}
 static int conv_cl_fwd_tile(const ssm_conv_args& a, int V) {
-  const int64_t lanes = (int64_t)((a.channels + V - 1) / V) * a.batch;  // threads per time tile
   int tile = kConvTimeTile;
-  while (tile > 8 && lanes * ((a.len + tile - 1) / tile) < 148 * 1024) tile >>= 1;
-  while ((a.len + tile - 1) / tile > 65535) tile <<= 1;  // grid.y
+  while (tile > 8 && conv_cl_fwd_ctas(a, V, tile) * a.batch < 8 * 4 * 148) tile >>= 1;
+  while (conv_cl_fwd_ctas(a, V, tile) >= (1ll << 31)) tile <<= 1;
   return tile;
 }
 
@@ -522,7 +530,7 @@ static int conv_fwd_launch(const ssm_conv_args& a, cudaStream_t st) {
   } else {
     const int vec = (a.channels % V == 0) && aligned_to(a.x, 16) && aligned_to(a.y, 16);
     const int tile = conv_cl_fwd_tile(a, V);
-    conv_cl_fwd_kernel<T, KM><<<conv_cl_grid(a, V, tile), kConvThreads, 0, st>>>(a, vec, tile);
+    conv_cl_fwd_kernel<T, KM><<<dim3((unsigned)conv_cl_fwd_ctas(a, V, tile), 1, a.batch), kConvThreads, 0, st>>>(a, vec, tile);
   }
   return launch_status("dw_causal_conv_fwd");
 }

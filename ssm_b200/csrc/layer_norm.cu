@@ -110,7 +110,7 @@ struct NormCfg {
 };
 
 // Loads the row into registers as s = x (+ residual when prenorm); returns through refs.
-template <typename T, int G, int MC>
+template <typename T, int G, int MC, bool RES = true>
 __device__ __forceinline__ void norm_load_row(const ssm_norm_args& a, int64_t row, int gt, int nchunk, float (&s)[MC][16 / sizeof(T)],
                                               float (&r)[MC][16 / sizeof(T)]) {
   constexpr int V = 16 / sizeof(T);
@@ -122,7 +122,7 @@ __device__ __forceinline__ void norm_load_row(const ssm_norm_args& a, int64_t ro
       Vec16<T> v;
       v.load_stream(reinterpret_cast<const T*>(a.x) + off);
       v.unpack(s[c]);
-      if (a.residual) {
+      if (RES && a.residual) {
         load_dyn_vec<V>(a.residual, off, a.res_dtype, r[c]);
         if (a.prenorm) {
 #pragma unroll
@@ -166,7 +166,8 @@ __device__ __forceinline__ void norm_stats(const ssm_norm_args& a, int gt, int n
 
 // MC = 16-byte chunks of a row per thread.  Rows of up to 768 chunks stay with 128 threads (several rows in flight per SM keep
 // more loads outstanding than one wide CTA per row does); only wider rows take 512 threads.
-template <typename T, int G, int MC = kNormFwdChunks>
+// RES = false: the call has no residual (its registers are then free, which raises the number of rows in flight).
+template <typename T, int G, int MC = kNormFwdChunks, bool RES = true>
 __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_fwd_kernel(const ssm_norm_args a) {
   using Cfg = NormCfg<T, G>;
   constexpr int V = Cfg::V;
@@ -177,7 +178,7 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_fwd_kernel(const ss
   if (row >= a.rows) return;  // whole groups leave together (G >= 32; G > 32 has one row per CTA)
   const int nchunk = a.hidden / V;
   float s[kNormFwdChunks][V], r[kNormFwdChunks][V];
-  norm_load_row<T, G, kNormFwdChunks>(a, row, gt, nchunk, s, r);
+  norm_load_row<T, G, kNormFwdChunks, RES>(a, row, gt, nchunk, s, r);
   if (a.residual_out) {
 #pragma unroll
     for (int c = 0; c < kNormFwdChunks; ++c) {
@@ -185,7 +186,7 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_fwd_kernel(const ss
       if (ch < nchunk) {
         float o[V];
 #pragma unroll
-        for (int i = 0; i < V; ++i) o[i] = (a.residual && !a.prenorm) ? s[c][i] + r[c][i] : s[c][i];
+        for (int i = 0; i < V; ++i) o[i] = (RES && a.residual && !a.prenorm) ? s[c][i] + r[c][i] : s[c][i];
         store_dyn_vec<V>(a.residual_out, row * a.hidden + (int64_t)ch * V, a.resout_dtype, o);
       }
     }
@@ -207,7 +208,7 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_fwd_kernel(const ss
 #pragma unroll
       for (int i = 0; i < V; ++i) {
         float y = fmaf((s[c][i] - mean) * rstd, wv[i], bv[i]);
-        if (a.residual && !a.prenorm) y += r[c][i];
+        if (RES && a.residual && !a.prenorm) y += r[c][i];
         o[i] = y;
       }
       Vec16<T> v;
@@ -487,7 +488,8 @@ template <typename T, int G, int MC = kNormFwdChunks>
 static int norm_fwd_launch(const ssm_norm_args& a, cudaStream_t st) {
   using Cfg = NormCfg<T, G>;
   const unsigned grid = (unsigned)((a.rows + Cfg::RPC - 1) / Cfg::RPC);
-  norm_fwd_kernel<T, G, MC><<<grid, Cfg::BLOCK, 0, st>>>(a);
+  if (a.residual) norm_fwd_kernel<T, G, MC, true><<<grid, Cfg::BLOCK, 0, st>>>(a);
+  else norm_fwd_kernel<T, G, MC, false><<<grid, Cfg::BLOCK, 0, st>>>(a);
   return launch_status("norm_fwd_kernel");
 }
 template <typename T, int G, int MC>
