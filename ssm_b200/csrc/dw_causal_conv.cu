@@ -292,13 +292,13 @@ __device__ __forceinline__ void load_x_cl(const ssm_conv_args& a, const T* __res
 }
 
 // Channels-last forward: thread = V channels, walking `tile` consecutive steps with the K - 1 previous inputs in registers.
-// Four steps' loads are issued before their results are formed, so every thread keeps four 16-byte loads in flight; the
+// Eight steps' loads are issued before their results are formed, so every thread keeps eight 16-byte loads in flight; the
 // host picks `tile` so that narrow tensors (the 128-channel B / C inputs of a Mamba-2 layer) still fill the machine.
 template <typename T, int KM>
-__global__ void __launch_bounds__(kConvThreads) conv_cl_fwd_kernel(const ssm_conv_args a, int vec, int tile) {
+__global__ void __launch_bounds__(kConvThreads, 4) conv_cl_fwd_kernel(const ssm_conv_args a, int vec, int tile) {
   constexpr int KH = KM - 1;
   constexpr int V = 16 / sizeof(T);
-  constexpr int U = 4;  // steps per batch of loads
+  constexpr int U = 8;  // steps per batch of loads
   const int C = a.channels, L = a.len, K = a.width;
   // work item = (time tile, channel vector), channel vectors fastest: a narrow tensor packs several time tiles into one CTA
   const int nvec = (C + V - 1) / V;
@@ -312,53 +312,82 @@ __global__ void __launch_bounds__(kConvThreads) conv_cl_fwd_kernel(const ssm_con
   const int b = blockIdx.z;
   const T* __restrict__ x = reinterpret_cast<const T*>(a.x) + (int64_t)b * L * C + c0;
   T* __restrict__ y = reinterpret_cast<T*>(a.y) + (int64_t)b * L * C + c0;
-  float wr[KM][V], bias[V];
+  // channel pairs as float2 for the packed-fp32 multiply-adds
+  float2 wr[KM][V / 2], bias[V / 2];
 #pragma unroll
-  for (int i = 0; i < V; ++i) {
-    const int cc = min(c0 + i, C - 1);
-    bias[i] = a.bias ? __ldg(a.bias + cc) : 0.f;
+  for (int i = 0; i < V; i += 2) {
+    const int c1 = min(c0 + i, C - 1), c2 = min(c0 + i + 1, C - 1);
+    bias[i / 2] = a.bias ? make_float2(__ldg(a.bias + c1), __ldg(a.bias + c2)) : make_float2(0.f, 0.f);
 #pragma unroll
-    for (int m = 0; m < KM; ++m) wr[m][i] = m < K ? __ldg(a.weight + (int64_t)cc * K + (K - 1 - m)) : 0.f;
+    for (int m = 0; m < KM; ++m)
+      wr[m][i / 2] = m < K ? make_float2(__ldg(a.weight + (int64_t)c1 * K + (K - 1 - m)), __ldg(a.weight + (int64_t)c2 * K + (K - 1 - m))) : make_float2(0.f, 0.f);
   }
-  float hist[KH > 0 ? KH : 1][V];  // hist[m] = x[t - 1 - m]
+  float2 hist[KH > 0 ? KH : 1][V / 2];  // hist[m] = x[t - 1 - m]
 #pragma unroll
   for (int m = 0; m < KH; ++m) {
-    if (m < K - 1) load_x_cl<T, V>(a, x, b, c0, ts - 1 - m, vec, nvalid, hist[m]);
-    else {
+    float f[V];
+    if (m < K - 1) {
+      load_x_cl<T, V>(a, x, b, c0, ts - 1 - m, vec, nvalid, f);
+    } else {
 #pragma unroll
-      for (int i = 0; i < V; ++i) hist[m][i] = 0.f;
+      for (int i = 0; i < V; ++i) f[i] = 0.f;
     }
+#pragma unroll
+    for (int i = 0; i < V; i += 2) hist[m][i / 2] = make_float2(f[i], f[i + 1]);
   }
-  for (int t = ts; t < te; t += U) {
-    float cur[U][V];
+  // one step: inputs f of step tt -> output row, then the window moves on
+  auto step = [&](int tt, const float (&f)[V]) {
+    float out[V];
+    float2 c2[V / 2];
 #pragma unroll
-    for (int j = 0; j < U; ++j) {
-      if (t + j < te) load_group<T, V>(x + (int64_t)(t + j) * C, vec, nvalid, cur[j]);
+    for (int i = 0; i < V; i += 2) {
+      c2[i / 2] = make_float2(f[i], f[i + 1]);
+      float2 acc = __ffma2_rn(wr[0][i / 2], c2[i / 2], bias[i / 2]);
+#pragma unroll
+      for (int m = 1; m < KM; ++m)
+        if (m < K) acc = __ffma2_rn(wr[m][i / 2], hist[m - 1][i / 2], acc);
+      if (a.silu) {
+        out[i] = sizeof(T) == 2 ? silu_half_io(acc.x) : silu_fast(acc.x);
+        out[i + 1] = sizeof(T) == 2 ? silu_half_io(acc.y) : silu_fast(acc.y);
+      } else {
+        out[i] = acc.x, out[i + 1] = acc.y;
+      }
     }
+    store_group<T, V>(y + (int64_t)tt * C, vec, nvalid, out);
 #pragma unroll
-    for (int j = 0; j < U; ++j) {
-      if (t + j < te) {
-        float out[V];
+    for (int m = KH - 1; m >= 1; --m)
+      if (m < K - 1) {
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-          float acc = fmaf(wr[0][i], cur[j][i], bias[i]);
+        for (int i = 0; i < V / 2; ++i) hist[m][i] = hist[m - 1][i];
+      }
+    if (KH > 0) {
 #pragma unroll
-          for (int m = 1; m < KM; ++m)
-            if (m < K) acc = fmaf(wr[m][i], hist[m - 1][i], acc);
-          out[i] = a.silu ? silu_fast(acc) : acc;
-        }
-        store_group<T, V>(y + (int64_t)(t + j) * C, vec, nvalid, out);
+      for (int i = 0; i < V / 2; ++i) hist[0][i] = c2[i];
+    }
+  };
+  if (vec) {
+    // the loads of U steps are issued first and stay packed (16 bytes each) until their step is formed
+    for (int t = ts; t < te; t += U) {
+      uint4 raw[U];
 #pragma unroll
-        for (int m = KH - 1; m >= 1; --m)
-          if (m < K - 1) {
+      for (int j = 0; j < U; ++j)
+        if (t + j < te) raw[j] = __ldcs(reinterpret_cast<const uint4*>(x + (int64_t)(t + j) * C));
 #pragma unroll
-            for (int i = 0; i < V; ++i) hist[m][i] = hist[m - 1][i];
-          }
-        if (KH > 0) {
+      for (int j = 0; j < U; ++j) {
+        if (t + j < te) {
+          float f[V];
+          const T* e = reinterpret_cast<const T*>(&raw[j]);
 #pragma unroll
-          for (int i = 0; i < V; ++i) hist[0][i] = cur[j][i];
+          for (int i = 0; i < V; ++i) f[i] = to_f<T>(e[i]);
+          step(t + j, f);
         }
       }
+    }
+  } else {
+    for (int t = ts; t < te; ++t) {
+      float f[V];
+      load_group<T, V>(x + (int64_t)t * C, false, nvalid, f);
+      step(t, f);
     }
   }
 }
