@@ -13,7 +13,7 @@
 //   ssd_fold_shards_kernel / ssd_fold_init_kernel   (sequence shards only) fold the other ranks' summaries into this
 //                       shard's incoming state, and add that late-arriving state to the per-chunk states by linearity
 //   ssd_scan_kernel     per (batch, chunk, 128-row block, part of a head group):  G = C B^T once (TMEM -> registers), then per
-//                       head the decay mask exp2(c_i - c_j) delta_j [j <= i] re-packed as the A operand of
+//                       head the decay mask exp2(c_i - c_j) delta_j [j <= i] written back to TMEM (tcgen05.st) as the A operand of
 //                       Y_intra = (G o L) X, plus  Y_inter = C S_in;  y = Y_intra + exp2(c_i) Y_inter + D x, gated, stored.
 //
 // Exponent differences are always formed before exp2 (never exp2(c_i) / exp2(c_j)), so long
@@ -622,11 +622,13 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     for (int k = 0; k < NCH; ++k) {
       const int cc = wg + kScanWG * k;  // chunk of 32 steps: fully causal (cc < rc), diagonal (cc == rc) or empty (cc > rc) for this warp's rows
       const int jb = cc * 32;
-      unsigned char* dst = sBA + ((size_t)(jb / 8) * kBlk + i_loc) * 16;
+      // the masked row goes to tensor memory as the A operand: 32 steps = 16 columns of two 16-bit values
+      const uint32_t dst = tmem + lane_base + cc * 16;
+      uint32_t packed[16];
       if (cc > rc) {
-        const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + (size_t)q * kBlk * 16) = zero;
+        for (int q = 0; q < 16; ++q) packed[q] = 0u;
+        tc::tmem_st16(dst, packed);
         continue;
       }
       const bool diag = cc == rc;
@@ -647,7 +649,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
           }
           Vec16<T> o;
           o.pack(f);
-          *reinterpret_cast<uint4*>(dst + (size_t)(q / 8) * kBlk * 16) = o.raw;
+          packed[q / 2] = o.raw.x, packed[q / 2 + 1] = o.raw.y, packed[q / 2 + 2] = o.raw.z, packed[q / 2 + 3] = o.raw.w;
         }
       } else {
 #pragma unroll
@@ -664,10 +666,12 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
           }
           Vec16<T> o;
           o.pack(f);
-          *reinterpret_cast<uint4*>(dst + (size_t)(q / 8) * kBlk * 16) = o.raw;
+          packed[q / 2] = o.raw.x, packed[q / 2 + 1] = o.raw.y, packed[q / 2 + 2] = o.raw.z, packed[q / 2 + 3] = o.raw.w;
         }
       }
+      tc::tmem_st16(dst, packed);
     }
+    tc::tmem_wait_st();
     // this row of x (for D x in the epilogue one iteration later)
     uint4 xr[kEU];
 #pragma unroll
@@ -681,7 +685,6 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     // ---- Y_intra = (G o L) X,  Y_inter = C_m S_in  for this head ------------------------------------------
     if (tid == 0) {
       // descriptors differ from instruction to instruction only in the start address (16-byte units, low bits)
-      const uint64_t da0 = tc::smem_desc(tc::smem_u32(sBA), kBlk * 16, 128);
       const uint64_t dx0 = tc::smem_desc_sw128(tc::smem_u32(sX + buf * M::X_BYTES), 16, 1024);
       const uint64_t dc0 = tc::smem_desc_sw128(tc::smem_u32(sC), 16, 1024);
       const uint64_t ds0 = tc::smem_desc(tc::smem_u32(sS + buf * M::S_BYTES), 128, kN * 16);
@@ -690,7 +693,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
       const uint32_t dY = tmem + 256 + buf * 128, dS = dY + 64;
 #pragma unroll
       for (int kk = 0; kk < KJ / 16; ++kk)  // 16 steps = 16 rows of 128 bytes of the x tile
-        tc::mma_ss(dY, da0 + (uint64_t)(kk * ((2 * kBlk * 16) >> 4)), dx0 + (uint64_t)(kk * (2048 >> 4)), idY, kk > 0);
+        tc::mma_ts(dY, tmem + kk * 8, dx0 + (uint64_t)(kk * (2048 >> 4)), idY, kk > 0);  // A: 16 steps = 8 columns of the masked rows
 #pragma unroll
       for (int kk = 0; kk < kN / 16; ++kk)
         tc::mma_ss(dS, dc0 + (uint64_t)(((kk >> 2) * (kBlk * 128) + (kk & 3) * 32) >> 4), ds0 + (uint64_t)(kk * (256 >> 4)), idS, kk > 0);
