@@ -25,8 +25,15 @@ extern "C" {
 
 #define SSM_B200_ABI_VERSION 3
 
-/* element types of activation tensors */
-enum { SSM_F32 = 0, SSM_BF16 = 1, SSM_F16 = 2 };
+/* element types of activation tensors.  SSM_F64 selects the double-precision variants of the five operators (forward and
+ * backward; written for gradient checking as in upstream's tests/ops/test_backend_gradients.py:1172-1612, not for speed): with
+ * io_dtype == SSM_F64 EVERY floating-point tensor of the call -- activations, A, B, C, D, biases, weights, states, gradients --
+ * is double, whatever C type the argument struct gives its pointer; bc_dtype, par_dtype, res_dtype, resout_dtype and last_dtype
+ * are ignored; d_state <= 256; the scan backward takes batch * dim * len * nstate doubles of scratch through fwd.checkpoints (no
+ * forward checkpoints are needed); the chunk-scan history is double; the norm backward ACCUMULATES into dweight / dbias (the
+ * caller zero-fills them) and needs no `partial`.  The decode-time conv update, the SSD entry points and the allocation-free norm
+ * backward have no fp64 variant. */
+enum { SSM_F32 = 0, SSM_BF16 = 1, SSM_F16 = 2, SSM_F64 = 3 };
 
 enum {
   SSM_OK = 0,

@@ -51,7 +51,8 @@ def load_extension():
 class Backend:
     """The ten entry points of upstream's ``ssm_cuda_ops`` module, served by ``ssm_b200_ext``.
 
-    Nine are the extension's functions as they are.  ``selective_scan`` adapts the return arity to
+    Nine are the extension's functions as they are for fp32 / bf16 / fp16 tensors; float64 tensors (upstream's
+    ``gradcheck`` matrix) go to the double-precision kernels through ``ops_f64.backend_*``.  ``selective_scan`` adapts the return arity to
     upstream's two call sites: its autograd wrapper unpacks ``(out, last_state, cache)``
     (src/ssm/ops/__init__.py:317), its inference path -- taken when no input requires a gradient
     -- unpacks ``(out, last_state)`` (src/ssm/ops/__init__.py:1304) and would fail on the
@@ -63,13 +64,43 @@ class Backend:
         self.ext = ext
         for name in NAMES:
             if name != "selective_scan":
-                setattr(self, name, getattr(ext, name))
+                setattr(self, name, self._route(name, getattr(ext, name)))
+
+    @staticmethod
+    def _is_f64(args) -> bool:
+        """float64 calls (upstream's gradient checks) go to the double-precision kernels: ``ops_f64.backend_*``."""
+        import torch
+
+        for a in args[:3]:  # the activation tensor is the first argument, or follows one or two gradients
+            if isinstance(a, torch.Tensor) and a.is_floating_point():
+                return a.dtype == torch.float64
+        return False
+
+    def _route(self, name, fn):
+        def call(*args, **kw):
+            if self._is_f64(args):
+                from . import ops_f64
+
+                return getattr(ops_f64, "backend_" + name)(*args, **kw)
+            return fn(*args, **kw)
+
+        call.__name__ = name
+        call.__doc__ = fn.__doc__
+        return call
 
     def selective_scan(self, u, delta, A, B, C, D=None, z=None, dt_bias=None, softplus=False, return_last_state=False):
-        out, last, cache = self.ext.selective_scan(u, delta, A, B, C, D, z, dt_bias, softplus, return_last_state)
+        if self._is_f64((u,)):
+            from . import ops_f64
+
+            out, last, cache = ops_f64.backend_selective_scan(u, delta, A, B, C, D, z, dt_bias, softplus, return_last_state)
+        else:
+            out, last, cache = self._scan(u, delta, A, B, C, D, z, dt_bias, softplus, return_last_state)
         if any(t is not None and t.requires_grad for t in (u, delta, A, B, C, D, z, dt_bias)):
             return out, last, cache
         return out, last
+
+    def _scan(self, u, delta, A, B, C, D, z, dt_bias, softplus, return_last_state):
+        return self.ext.selective_scan(u, delta, A, B, C, D, z, dt_bias, softplus, return_last_state)
 
 
 def install(ssm_ops_module=None) -> Backend:

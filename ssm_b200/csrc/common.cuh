@@ -25,6 +25,14 @@ inline int fail(int code, const char* what) {
     if (!(cond)) return ::ssmb::fail((code), (what)); \
   } while (0)
 
+// double-precision variants (fp64_ops.cu), reached from the ordinary entry points when io_dtype == SSM_F64
+int f64_scan_fwd(const ssm_scan_fwd_args& a, cudaStream_t st);
+int f64_scan_bwd(const ssm_scan_bwd_args& g, cudaStream_t st);
+int f64_step(const ssm_step_bwd_args& g, bool backward, cudaStream_t st);
+int f64_chunk(const ssm_chunk_bwd_args& g, bool backward, cudaStream_t st);
+int f64_conv(const ssm_conv_bwd_args& g, bool backward, cudaStream_t st);
+int f64_norm(const ssm_norm_bwd_args& g, bool backward, cudaStream_t st);
+
 inline int launch_status(const char* kernel) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

@@ -595,6 +595,11 @@ static int conv_bwd_k(const ssm_conv_bwd_args& g, cudaStream_t st) {
 using namespace ssmb;
 
 extern "C" int ssm_dw_causal_conv_fwd(const ssm_conv_args* a, ssm_stream_t stream) {
+  if (a && a->io_dtype == SSM_F64) {
+    ssm_conv_bwd_args g{};
+    g.fwd = *a;
+    return f64_conv(g, false, reinterpret_cast<cudaStream_t>(stream));
+  }
   if (int rc = conv_validate(a)) return rc;
   if (a->batch == 0 || a->channels == 0 || a->len == 0) return SSM_OK;
   SSM_REQUIRE(a->x && a->y && a->weight, SSM_ERR_NULL, "dw_causal_conv: x, weight and y are required");
@@ -609,6 +614,7 @@ extern "C" int ssm_dw_causal_conv_fwd(const ssm_conv_args* a, ssm_stream_t strea
 extern "C" int ssm_dw_causal_conv_bwd(const ssm_conv_bwd_args* g, ssm_stream_t stream) {
   SSM_REQUIRE(g != nullptr, SSM_ERR_NULL, "dw_causal_conv_backward: args is NULL");
   const ssm_conv_args* a = &g->fwd;
+  if (a->io_dtype == SSM_F64) return f64_conv(*g, true, reinterpret_cast<cudaStream_t>(stream));
   if (int rc = conv_validate(a)) return rc;
   if (a->batch == 0 || a->channels == 0 || a->len == 0) return SSM_OK;
   SSM_REQUIRE(a->x && a->weight && g->dy && g->dx && g->dweight, SSM_ERR_NULL, "dw_causal_conv_backward: missing pointer");

@@ -616,6 +616,11 @@ static int norm_bwd_noalloc_t(const ssm_norm_bwd_args& g, float* scratch, cudaSt
 using namespace ssmb;
 
 extern "C" int ssm_fused_add_norm_fwd(const ssm_norm_args* a, ssm_stream_t stream) {
+  if (a && a->io_dtype == SSM_F64) {
+    ssm_norm_bwd_args g{};
+    g.fwd = *a;
+    return f64_norm(g, false, reinterpret_cast<cudaStream_t>(stream));
+  }
   if (int rc = norm_validate(a)) return rc;
   if (a->rows == 0) return SSM_OK;
   SSM_REQUIRE(a->x && a->y && a->weight, SSM_ERR_NULL, "fused_layer_norm: x, weight and y are required");
@@ -635,6 +640,7 @@ extern "C" int64_t ssm_norm_bwd_scratch_floats(int64_t rows, int32_t hidden) {
 extern "C" int ssm_fused_add_norm_bwd(const ssm_norm_bwd_args* g, ssm_stream_t stream) {
   SSM_REQUIRE(g != nullptr, SSM_ERR_NULL, "fused_layer_norm_backward: args is NULL");
   const ssm_norm_args* a = &g->fwd;
+  if (a->io_dtype == SSM_F64) return f64_norm(*g, true, reinterpret_cast<cudaStream_t>(stream));
   if (int rc = norm_validate(a)) return rc;
   SSM_REQUIRE(g->dweight, SSM_ERR_NULL, "fused_layer_norm_backward: dweight is required");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

@@ -16,6 +16,7 @@ using namespace ssmb;
 extern "C" int ssm_selective_scan_bwd(const ssm_scan_bwd_args* g, ssm_stream_t stream) {
   SSM_REQUIRE(g != nullptr, SSM_ERR_NULL, "selective_scan_backward: args is NULL");
   const ssm_scan_fwd_args* a = &g->fwd;
+  if (a->io_dtype == SSM_F64) return f64_scan_bwd(*g, reinterpret_cast<cudaStream_t>(stream));
   ScanFlags fl{};
   if (int rc = scan_validate(a, &fl, 1)) return rc;
   if (a->batch == 0 || a->dim == 0 || a->len == 0) return SSM_OK;

@@ -48,6 +48,7 @@ extern "C" int ssm_scan_split_segments(int32_t batch, int32_t dim, int32_t len, 
 }
 
 extern "C" int ssm_selective_scan_fwd(const ssm_scan_fwd_args* a, ssm_stream_t stream) {
+  if (a && a->io_dtype == SSM_F64) return f64_scan_fwd(*a, reinterpret_cast<cudaStream_t>(stream));
   ScanFlags fl{};
   if (int rc = scan_validate(a, &fl, 1)) return rc;
   SSM_REQUIRE(valid_dtype(a->last_dtype) || !a->last_state, SSM_ERR_DTYPE, "selective_scan: unknown last_state dtype");

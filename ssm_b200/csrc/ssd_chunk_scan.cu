@@ -419,6 +419,11 @@ extern "C" int64_t ssm_chunk_scan_bwd_scratch_floats(int32_t batch, int32_t len,
 }
 
 extern "C" int ssm_chunk_scan_fwd(const ssm_chunk_args* a, ssm_stream_t stream) {
+  if (a && a->io_dtype == SSM_F64) {
+    ssm_chunk_bwd_args g{};
+    g.fwd = *a;
+    return f64_chunk(g, false, reinterpret_cast<cudaStream_t>(stream));
+  }
   if (int rc = chunk_validate(a)) return rc;
   if (a->batch == 0 || a->heads == 0 || a->proj == 0) return SSM_OK;
   SSM_REQUIRE(a->A.ptr && a->Bm.ptr && a->Cm.ptr, SSM_ERR_NULL, "ssd_chunk_scan: A, B and C are required");
@@ -437,6 +442,7 @@ extern "C" int ssm_chunk_scan_fwd(const ssm_chunk_args* a, ssm_stream_t stream) 
 extern "C" int ssm_chunk_scan_bwd(const ssm_chunk_bwd_args* g, ssm_stream_t stream) {
   SSM_REQUIRE(g != nullptr, SSM_ERR_NULL, "ssd_chunk_scan_backward: args is NULL");
   const ssm_chunk_args* a = &g->fwd;
+  if (a->io_dtype == SSM_F64) return f64_chunk(*g, true, reinterpret_cast<cudaStream_t>(stream));
   if (int rc = chunk_validate(a)) return rc;
   if (a->batch == 0 || a->heads == 0 || a->proj == 0 || a->len == 0) return SSM_OK;
   SSM_REQUIRE(a->A.ptr && a->Bm.ptr && a->Cm.ptr && a->X && a->dt, SSM_ERR_NULL, "ssd_chunk_scan_backward: missing input");

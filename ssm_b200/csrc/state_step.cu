@@ -379,6 +379,11 @@ static int step_bwd_t(const ssm_step_bwd_args& g, cudaStream_t st) {
 using namespace ssmb;
 
 extern "C" int ssm_selective_state_step(const ssm_step_args* a, ssm_stream_t stream) {
+  if (a && a->io_dtype == SSM_F64) {
+    ssm_step_bwd_args g{};
+    g.fwd = *a;
+    return f64_step(g, false, reinterpret_cast<cudaStream_t>(stream));
+  }
   if (int rc = step_validate(a)) return rc;
   if (a->batch == 0 || a->dim == 0) return SSM_OK;
   SSM_REQUIRE(a->out, SSM_ERR_NULL, "selective_state_step: out is required");
@@ -393,6 +398,7 @@ extern "C" int ssm_selective_state_step(const ssm_step_args* a, ssm_stream_t str
 extern "C" int ssm_selective_state_step_bwd(const ssm_step_bwd_args* g, ssm_stream_t stream) {
   SSM_REQUIRE(g != nullptr, SSM_ERR_NULL, "selective_state_step_backward: args is NULL");
   const ssm_step_args* a = &g->fwd;
+  if (a->io_dtype == SSM_F64) return f64_step(*g, true, reinterpret_cast<cudaStream_t>(stream));
   if (int rc = step_validate(a)) return rc;
   SSM_REQUIRE(a->param_heads == 0, SSM_ERR_UNSUPPORTED, "selective_state_step_backward: per-head parameters have no backward");
   if (a->batch == 0 || a->dim == 0) return SSM_OK;

@@ -394,6 +394,9 @@ def selective_scan(
     receives a gradient like any other input); ``keep_state_fp32`` returns the last state in
     fp32 instead of ``u.dtype``.
     """
+    if u.dtype == torch.float64:  # double-precision kernels, meant for gradient checks (ops_f64.py)
+        from . import ops_f64
+        return ops_f64.selective_scan(u, delta, A, B, C, D, z, dt_bias, softplus, return_last_state, initial_state)
     res = _SelectiveScanFn.apply(u, delta, A, B, C, D, z, dt_bias, softplus, return_last_state, initial_state, keep_state_fp32)
     return res
 
@@ -553,6 +556,9 @@ def selective_state_step(
 ) -> Tensor:
     """One decode token; ``state`` ``(B, D, N)`` is overwritten in place (upstream
     ``ssm.ops.selective_state_step``, reference.py:197-309)."""
+    if x.dtype == torch.float64:
+        from . import ops_f64
+        return ops_f64.selective_state_step(state, x, dt, A, B, C, D, z, dt_bias, softplus)
     if any(t is not None and t.requires_grad for t in (state, x, dt, A, B, C, D, z, dt_bias)) and torch.is_grad_enabled():
         y, new = _StateStepFn.apply(state, x, dt, A, B, C, D, z, dt_bias, softplus)
         with torch.no_grad():
@@ -801,6 +807,9 @@ def ssd_chunk_scan(
 ) -> Tensor:
     """Element-wise chunked recurrence over ``(B, L, H, P)`` (upstream ``ssm.ops.ssd_chunk_scan``,
     reference.py:312-463)."""
+    if X.dtype == torch.float64:
+        from . import ops_f64
+        return ops_f64.ssd_chunk_scan(X, dt, A, B, C, chunk_size, D, z, seq_meta, initial_states)
     return _ChunkScanFn.apply(X, dt, A, B, C, chunk_size, D, z, seq_meta, initial_states)
 
 
@@ -892,6 +901,11 @@ def dw_causal_conv(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, act
     """Depthwise causal conv1d with optional SiLU (upstream ``ssm.ops.dw_causal_conv``,
     reference.py:466-537).  Extension: ``halo`` ``(B, C, K-1)`` supplies the inputs that precede
     ``t = 0`` (sequence-sharded prefill) instead of zeros; no gradient flows into it."""
+    if x.dtype == torch.float64:
+        if halo is not None:
+            raise ValueError("dw_causal_conv in float64 takes no halo.")
+        from . import ops_f64
+        return ops_f64.dw_causal_conv(x, weight, bias, activation)
     return _ConvFn.apply(x, weight, bias, activation, halo)
 
 
@@ -1019,6 +1033,9 @@ def fused_layer_norm(
     and fp16 inputs whatever ``residual_in_fp32`` says.  Extension: ``return_residual`` also
     returns ``x + residual`` (fp32 when ``residual_in_fp32``, else ``x.dtype``), the residual
     stream a stack of blocks passes on; gradients flow back through both outputs."""
+    if x.dtype == torch.float64:
+        from . import ops_f64
+        return ops_f64.fused_layer_norm(x, weight, bias, residual, is_rms, eps, prenorm, residual_in_fp32, return_residual)
     rd = torch.float32 if residual_in_fp32 else x.dtype
     return _NormFn.apply(x, weight, bias, residual, is_rms, eps, prenorm, return_residual, rd)
 
