@@ -554,6 +554,47 @@ def bench_conv_norm():
             "norm_bwd_bytes": el_n * (2 + 4 + 2 + 4 + 2 + 4)}    # x, residual, dy, d(residual stream) in; dx, dresidual out
 
 
+def bench_mamba2_layer_ops():
+    """The bandwidth kernels of one Mamba-2 layer on the shard one of eight ranks holds (32768 tokens, d_model 2560, d_inner 5120):
+    channels-last conv + SiLU over 5120 and over 128 channels, RMSNorm over 5120 columns, fused add + RMSNorm over 2560 columns with the
+    fp32 residual stream in and out; forward, CUDA-graph replays over two alternating input sets."""
+    from ssm_b200 import ops
+
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(6)
+    kw = dict(generator=g, device=dev)
+    bf = torch.bfloat16
+    B, Lq, dm, di, n = 2, 16384, 2560, 5120, 128
+    cx = [torch.randn(B, Lq, di, **kw).to(bf) for _ in range(2)]
+    cb = [torch.randn(B, Lq, n, **kw).to(bf) for _ in range(2)]
+    wx, wb = torch.rand(di, 4, **kw) - 0.5, torch.rand(n, 4, **kw) - 0.5
+    nx = [torch.randn(B, Lq, dm, **kw).to(bf) for _ in range(2)]
+    nr = [torch.randn(B, Lq, dm, **kw) for _ in range(2)]
+    w_dm, w_di = torch.ones(dm, device=dev, dtype=bf), torch.ones(di, device=dev, dtype=bf)
+
+    @torch.no_grad()
+    def conv_x(i):
+        return ops.dw_causal_conv(cx[i % 2], wx, None, "silu")
+
+    @torch.no_grad()
+    def conv_b(i):
+        return ops.dw_causal_conv(cb[i % 2], wb, None, "silu")
+
+    @torch.no_grad()
+    def norm_wide(i):
+        return ops.fused_layer_norm(cx[i % 2], w_di, None, is_rms=True)
+
+    @torch.no_grad()
+    def add_norm(i):
+        return ops.fused_layer_norm(nx[i % 2], w_dm, None, residual=nr[i % 2], is_rms=True, prenorm=True, return_residual=True)
+
+    rows = B * Lq
+    return {"conv_cl_5120_ms": graph_time(conv_x), "conv_cl_5120_bytes": 2 * rows * di * 2,
+            "conv_cl_128_ms": graph_time(conv_b), "conv_cl_128_bytes": 2 * rows * n * 2,
+            "norm_5120_ms": graph_time(norm_wide), "norm_5120_bytes": 2 * rows * di * 2,
+            "add_norm_2560_ms": graph_time(add_norm), "add_norm_2560_bytes": rows * dm * (2 + 4 + 2 + 4)}
+
+
 def bench_ssd(batch=8, steps=20):
     """State-space-dual scan forward: seqlen 8192, 48 heads x 64, d_state 128, one group, chunk 256, bf16."""
     from ssm_b200 import ops
@@ -734,6 +775,9 @@ def operator_table(args):
     t["c3_ssd_ms"], t["c3_ssd_frac"], t["c3_ssd_tflops"] = c3["ms"], frac(c3["bytes"], c3["ms"]), c3["flops"] / (c3["ms"] * 1e-3) / 1e12
     t["c3_ssd_tokens_per_s"] = c3["tokens"] / (c3["ms"] * 1e-3)
     t["c3_ssd_bwd_ms"] = c3["bwd_ms"]
+    c5 = bench_mamba2_layer_ops()  # the bandwidth kernels of one layer of the default workload at the 8-rank shard size
+    for tag in ("conv_cl_5120", "conv_cl_128", "norm_5120", "add_norm_2560"):
+        t[f"c5_{tag}_us"], t[f"c5_{tag}_frac"] = c5[tag + "_ms"] * 1e3, frac(c5[tag + "_bytes"], c5[tag + "_ms"])
     c4 = bench_decode()
     t["c4a_step_us"], t["c4a_step_frac"] = c4["state_kernels_us"], frac(c4["state_kernels_bytes"], c4["state_kernels_us"] * 1e-3)
     t["c4b_step_us"], t["c4b_step_frac"] = c4["mamba2_step_us"], frac(c4["mamba2_step_bytes"], c4["mamba2_step_us"] * 1e-3)
