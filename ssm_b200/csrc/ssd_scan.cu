@@ -572,7 +572,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     // MMAs of the previous head: the masked tile, the other buffer and its accumulators are free / ready
     if (hi > 0) ok = tc::mbar_wait(mb_mma(buf ^ 1), ((hi - 1) >> 1) & 1) && ok;
     tc::fence_after_sync();
-    ok = __syncthreads_and(ok);  // the staged y of the head before last is complete; the verdict on the waits is CTA-wide
+    ok = __syncthreads_and(ok);  // the staged y of the head before last is complete; the outcome of the waits is CTA-wide
     if (!ok) {
       fail = 1;
       break;
