@@ -419,13 +419,18 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   unsigned char* sZ = reinterpret_cast<unsigned char*>(sVec) + 2 * M::VEC_BYTES;
   // mbar: 0 G done; 1 + b MMAs of a head into accumulator pair b done; 3 + b operands of buffer b landed; 5 z tile landed;
   // 6 C and B tiles landed
-  const uint32_t mb_g = tc::smem_u32(&mbar[0]), mb_z = tc::smem_u32(&mbar[5]);
+  const uint32_t mb_g = tc::smem_u32(&mbar[0]);
+  auto mb_z = [&](int bf) { return tc::smem_u32(&mbar[bf ? 7 : 5]); };  // gate tile of buffer bf landed
   auto mb_mma = [&](int bf) { return tc::smem_u32(&mbar[1 + bf]); };
   auto mb_full = [&](int bf) { return tc::smem_u32(&mbar[3 + bf]); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wg = tid >> 7;                     // column chunks wg, wg + kScanWG, ... in the mask stage; column slice in the epilogue
   float* sW = reinterpret_cast<float*>(sZ + M::Z_BYTES) + warp * (NCH * 32);  // this warp's column factors
+  // The gate rows of a head get buffers of their own, over the B tile (dead once G is formed: the masked operand lives in
+  // tensor memory): head h's tile is requested at the top of its own iteration and read by its epilogue one iteration later,
+  // instead of waiting, in the shared staging tile, for the previous head's y to be stored first.
+  auto sZin = [&](int bf) { return sBA + bf * M::Z_BYTES; };
   const int half_grid = gridDim.x >> 1;
   const int rem = (int)blockIdx.x % half_grid;
   const int part = rem % nparts, bc = rem / nparts;
@@ -533,7 +538,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
       if (has_z) {
         float zv[8];
         Vec16<T> zz;
-        zz.raw = *reinterpret_cast<const uint4*>(slot);
+        zz.raw = *reinterpret_cast<const uint4*>(swz(sZin(buf), i_loc, wg * kEU + q));
         zz.unpack(zv);
         if (dots) {
 #pragma unroll
@@ -564,7 +569,6 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
 #pragma unroll
   for (int q = 0; q < kEU; ++q) xr_prev[q] = make_uint4(0, 0, 0, 0);
   int fail = 0;
-  int nz = 0;  // z tiles requested so far (parity of the z barrier)
 #pragma unroll 1
   for (int hi = 0; hi < nh; ++hi) {
     const int h = h0 + hi, buf = hi & 1;
@@ -583,9 +587,9 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
         tc::bulk_commit();
         tc::bulk_wait_read();  // the tile may be overwritten
       }
-      if (hi >= 1 && has_z) {
-        tc::mbar_expect_tx(mb_z, M::Z_BYTES);
-        tc::tma_load_4d(tc::smem_u32(sZ), &maps.z, mb_z, 0, h - 1, t_blk, b);
+      if (has_z) {  // its buffer was last read by the epilogue of head h - 2, one iteration ago
+        tc::mbar_expect_tx(mb_z(buf), M::Z_BYTES);
+        tc::tma_load_4d(tc::smem_u32(sZin(buf)), &maps.z, mb_z(buf), 0, h, t_blk, b);
       }
       if (hi + 1 < nh) prefetch(h + 1, buf ^ 1);
     }
@@ -701,10 +705,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     }
     // ---- the previous head's result, while the tensor cores work on this one ---------------------------------
     if (hi > 0) {
-      if (has_z) {
-        ok = tc::mbar_wait(mb_z, nz & 1);
-        ++nz;
-      }
+      if (has_z) ok = tc::mbar_wait(mb_z(buf ^ 1), ((hi - 1) >> 1) & 1);
       if (ok) epilogue(h - 1, buf ^ 1, ct_prev, xr_prev);
       else fail = 1;  // becomes CTA-wide at the next iteration's barrier (or right after the loop)
     }
@@ -726,12 +727,8 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
           tc::bulk_commit();
           tc::bulk_wait_read();
         }
-        if (has_z) {
-          tc::mbar_expect_tx(mb_z, M::Z_BYTES);
-          tc::tma_load_4d(tc::smem_u32(sZ), &maps.z, mb_z, 0, h0 + last, t_blk, b);
-        }
       }
-      if (has_z) ok = tc::mbar_wait(mb_z, nz & 1);
+      if (has_z) ok = tc::mbar_wait(mb_z(buf), (last >> 1) & 1);
       ok = __syncthreads_and(ok);  // also orders thread 0's wait on the store's reads before everyone's writes
       if (ok) {
         epilogue(h0 + last, buf, ct_prev, xr_prev);
@@ -756,12 +753,12 @@ __global__ void __launch_bounds__(kScanThreads, 1)
     ssd_scan_kernel(const ssm_ssd_args a, const __grid_constant__ ScanMaps maps, int nchunks, int hpc, int nparts) {
   extern __shared__ unsigned char smdyn[];
   unsigned char* smraw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smdyn) + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t mbar[7];
+  __shared__ __align__(8) uint64_t mbar[8];
   __shared__ uint32_t tmem_slot;
   const int warp = threadIdx.x >> 5;
   if (warp == 0) tc::tmem_alloc(tc::smem_u32(&tmem_slot), 512);
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 7; ++i) tc::mbar_init(tc::smem_u32(&mbar[i]), 1);
+    for (int i = 0; i < 8; ++i) tc::mbar_init(tc::smem_u32(&mbar[i]), 1);
   }
   __syncthreads();  // barriers and the TMEM address are set up before anyone arms or polls them
   // the heavier blocks (rows 128..255) are scheduled first
