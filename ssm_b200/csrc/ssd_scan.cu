@@ -397,6 +397,8 @@ constexpr int kEU = kEC / 8;                  // ... in 16-byte units
 // Thread that issues the bulk copies (TMA): lane 0 of the warp with the least mask work (rows 0..31 of the block, odd
 // chunks), so that its issue time hides behind the other warps' mask stage; thread 0 issues the MMAs.
 constexpr int kCopyThread = 128;
+// Issues the per-head MMAs: lane 0 of the warp with the least mask work (rows 0..31 of the block, last column slice).
+constexpr int kMmaWarp = 12;
 
 // tensor maps of one call: x (box of 128 or 256 steps), z and y (boxes of 128 rows); rank 4 (p, head, step, batch)
 struct ScanMaps {
@@ -417,7 +419,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   unsigned char* sS = sX + 2 * M::X_BYTES;     // two buffers
   float* sVec = reinterpret_cast<float*>(sS + 2 * M::S_BYTES);  // two buffers of [c | c - log2 delta]
   unsigned char* sZ = reinterpret_cast<unsigned char*>(sVec) + 2 * M::VEC_BYTES;
-  // mbar: 0 G done; 1 + b MMAs of a head into accumulator pair b done; 3 + b operands of buffer b landed; 5 z tile landed;
+  // mbar: 0 G done; 1 + b MMAs of a head into accumulator pair b done; 3 + b operands of buffer b landed; 5, 7 gate tiles landed;
   // 6 C and B tiles landed
   const uint32_t mb_g = tc::smem_u32(&mbar[0]);
   auto mb_z = [&](int bf) { return tc::smem_u32(&mbar[bf ? 7 : 5]); };  // gate tile of buffer bf landed
@@ -482,8 +484,9 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  const bool mma_warp = __shfl_sync(0xffffffffu, warp, 0) == kMmaWarp;  // the same in every lane, and visibly so
 
   // ---- G = C_m B^T ------------------------------------------------------------------------------------
   // K-major operands in 128-byte-swizzled rows: 16 states = 32 bytes further along the row, 64 states = the next block
@@ -545,7 +548,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
           for (int e = 0; e < 8; ++e) dot = fmaf(f[e], zv[e], dot), f[e] = fmaf(dv[e], xv[e], f[e]);
         } else {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = fmaf(dv[e], xv[e], f[e]) * silu_fast(zv[e]);
+          for (int e = 0; e < 8; ++e) f[e] = fmaf(dv[e], xv[e], f[e]) * silu_half_io(zv[e]);
         }
       } else {
 #pragma unroll
@@ -576,10 +579,22 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     // MMAs of the previous head: the masked tile, the other buffer and its accumulators are free / ready
     if (hi > 0) ok = tc::mbar_wait(mb_mma(buf ^ 1), ((hi - 1) >> 1) & 1) && ok;
     tc::fence_after_sync();
+    tc::fence_before_sync();     // the accumulator reads of the previous epilogue precede the MMAs issued below
     ok = __syncthreads_and(ok);  // the staged y of the head before last is complete; the outcome of the waits is CTA-wide
     if (!ok) {
       fail = 1;
       break;
+    }
+    if (mma_warp && tc::elect_one()) {
+      // Y_inter = C_m S_in needs nothing of the mask: issued first, it runs on the tensor cores while the mask is formed
+      tc::fence_after_sync();
+      const uint64_t dc0 = tc::smem_desc_sw128(tc::smem_u32(sC), 16, 1024);
+      const uint64_t ds0 = tc::smem_desc(tc::smem_u32(sS + buf * M::S_BYTES), 128, kN * 16);
+      constexpr uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 1);
+      const uint32_t dS = tmem + 256 + buf * 128 + 64;
+#pragma unroll
+      for (int kk = 0; kk < kN / 16; ++kk)
+        tc::mma_ss(dS, dc0 + (uint64_t)(((kk >> 2) * (kBlk * 128) + (kk & 3) * 32) >> 4), ds0 + (uint64_t)(kk * (256 >> 4)), idS, kk > 0);
     }
     if (tid == kCopyThread) {
       if (hi >= 2) {  // staged by the epilogue of the previous iteration
@@ -636,7 +651,24 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
         continue;
       }
       const bool diag = cc == rc;
-      if (fast[k]) {
+      if (fast[k] && !diag) {  // the common case: every step of the chunk precedes every row of this warp, nothing to cut
+        const float2 a2 = make_float2(arow[k], arow[k]);
+#pragma unroll
+        for (int q = 0; q < 32; q += 8) {
+          const float4 b0 = *reinterpret_cast<const float4*>(sW + k * 32 + q);
+          const float4 b1 = *reinterpret_cast<const float4*>(sW + k * 32 + q + 4);
+          const float2 bp[4] = {make_float2(b0.x, b0.y), make_float2(b0.z, b0.w), make_float2(b1.x, b1.y), make_float2(b1.z, b1.w)};
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            const float2 w = __fmul2_rn(__fmul2_rn(make_float2(vG[k][q + e], vG[k][q + e + 1]), bp[e / 2]), a2);
+            f[e] = w.x, f[e + 1] = w.y;
+          }
+          Vec16<T> o;
+          o.pack(f);
+          packed[q / 2] = o.raw.x, packed[q / 2 + 1] = o.raw.y, packed[q / 2 + 2] = o.raw.z, packed[q / 2 + 3] = o.raw.w;
+        }
+      } else if (fast[k]) {  // the chunk of this warp's own rows: steps after the row are cut
         const float2 a2 = make_float2(arow[k], arow[k]);
 #pragma unroll
         for (int q = 0; q < 32; q += 8) {
@@ -647,8 +679,8 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
 #pragma unroll
           for (int e = 0; e < 8; e += 2) {
             float2 w = __fmul2_rn(__fmul2_rn(make_float2(vG[k][q + e], vG[k][q + e + 1]), bp[e / 2]), a2);
-            if (diag && q + e > lane) w.x = 0.f;
-            if (diag && q + e + 1 > lane) w.y = 0.f;
+            if (q + e > lane) w.x = 0.f;
+            if (q + e + 1 > lane) w.y = 0.f;
             f[e] = w.x, f[e + 1] = w.y;
           }
           Vec16<T> o;
@@ -681,26 +713,20 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
 #pragma unroll
     for (int q = 0; q < kEU; ++q) xr[q] = *reinterpret_cast<const uint4*>(swz(sX + buf * M::X_BYTES, i_chunk, wg * kEU + q));
 
-    tc::fence_async_smem();
+
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
 
-    // ---- Y_intra = (G o L) X,  Y_inter = C_m S_in  for this head ------------------------------------------
-    if (tid == 0) {
+    // ---- Y_intra = (G o L) X  for this head; the commit also covers the Y_inter MMAs issued above --------------
+    if (mma_warp && tc::elect_one()) {
       // descriptors differ from instruction to instruction only in the start address (16-byte units, low bits)
       const uint64_t dx0 = tc::smem_desc_sw128(tc::smem_u32(sX + buf * M::X_BYTES), 16, 1024);
-      const uint64_t dc0 = tc::smem_desc_sw128(tc::smem_u32(sC), 16, 1024);
-      const uint64_t ds0 = tc::smem_desc(tc::smem_u32(sS + buf * M::S_BYTES), 128, kN * 16);
       constexpr uint32_t idY = tc::instr_desc(kBlk, kP, fmt, 0, 1);
-      constexpr uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 1);
-      const uint32_t dY = tmem + 256 + buf * 128, dS = dY + 64;
+      const uint32_t dY = tmem + 256 + buf * 128;
 #pragma unroll
       for (int kk = 0; kk < KJ / 16; ++kk)  // 16 steps = 16 rows of 128 bytes of the x tile
         tc::mma_ts(dY, tmem + kk * 8, dx0 + (uint64_t)(kk * (2048 >> 4)), idY, kk > 0);  // A: 16 steps = 8 columns of the masked rows
-#pragma unroll
-      for (int kk = 0; kk < kN / 16; ++kk)
-        tc::mma_ss(dS, dc0 + (uint64_t)(((kk >> 2) * (kBlk * 128) + (kk & 3) * 32) >> 4), ds0 + (uint64_t)(kk * (256 >> 4)), idS, kk > 0);
       tc::commit(mb_mma(buf));
     }
     // ---- the previous head's result, while the tensor cores work on this one ---------------------------------

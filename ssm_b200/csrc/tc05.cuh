@@ -112,6 +112,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity, int li
   return false;
 }
 
+// True in exactly one lane of a converged warp.  Inside a branch the whole warp takes, the compiler keeps operands that are the
+// same in every lane (descriptors, tensor-memory addresses) in uniform registers for the single-thread instructions that follow.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// One arrival (release) on an mbarrier of this CTA.
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(mbar) : "memory"); }
+
 // ---- bulk asynchronous copies (TMA); completion is counted in bytes on an mbarrier -----------------------------
 __device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbar), "r"(bytes) : "memory");
