@@ -406,8 +406,10 @@ struct ScanMaps {
   CUtensorMap c, bm;  // C and B rows: rank 4 (state, group, step, batch), boxes of 64 states x 128 steps
 };
 
-// Body for row block MB (0: rows 0..127, steps 0..127; 1: rows 128..255, steps 0..255).
-template <typename T, int MB>
+// Body for row block MB (0: rows 0..127, steps 0..127; 1: rows 128..255, steps 0..255).  XSKIP: the skip term D x is added
+// in the epilogue (a weight per channel, or the row sums of the backward pass are wanted), which carries each thread's x row
+// from one iteration to the next; without it a weight per head rides on the diagonal of the masked operand.
+template <typename T, int MB, bool XSKIP>
 __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanMaps& maps, int nchunks, int hpc, int nparts, unsigned char* smraw,
                                               uint64_t* mbar, uint32_t* tmem_slot) {
   using M = ScanSmem<T>;
@@ -516,51 +518,71 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     }
   }
 
-  // epilogue of head h from accumulator pair `buf`: y = Y_intra + exp2(c_i) Y_inter + D x, gated by the z row in
-  // the staging tile, written back to the same slots.  Thread = row i_loc, this warpgroup's 32 columns.
-  auto epilogue = [&](int h, int buf, float ct, const uint4 (&xr)[kEU]) {
+  // A skip weight per head (not per channel) rides on the diagonal of the masked operand: (G o L + D I) X = Y_intra + D x.
+  // The row sums for the backward pass want y without the skip term, so that mode keeps the explicit form.
+  const bool fold_d = !XSKIP && a.D;
+  constexpr bool skip_explicit = XSKIP;
+
+  // epilogue of head h from accumulator pair `buf`: y = Y_intra + exp2(c_i) Y_inter (+ D x where it is not folded), gated by
+  // the z row, staged for the bulk store.  Thread = row i_loc, this warpgroup's 16 columns; the arithmetic runs on pairs.
+  constexpr int kXR = XSKIP ? kEU : 1;  // x row registers exist only where the explicit skip term needs them
+  auto epilogue = [&](int h, int buf, float ct, const uint4 (&xr)[kXR]) {
     const float escale = ex2_approx(ct);
+    const float2 es2 = make_float2(escale, escale);
     float yi[kEC], ys[kEC];
     tc::tmem_ld16(tmem + lane_base + 256 + buf * 128 + wg * kEC, yi);
     tc::tmem_ld16(tmem + lane_base + 320 + buf * 128 + wg * kEC, ys);
-    const float Dh = (a.D && !a.d_has_p) ? __ldg(a.D + h) : 0.f;
+    const float Dh = (skip_explicit && !a.d_has_p) ? __ldg(a.D + h) : 0.f;
     const bool dots = a.row_dots != nullptr;
-    float dot = 0.f;  // row_dots: this thread's 32 columns of  sum_p y[p] z[p]  (y before the skip term and unrounded)
+    float dot = 0.f;  // row_dots: this thread's 16 columns of  sum_p y[p] z[p]  (y before the skip term and unrounded)
 #pragma unroll
     for (int q = 0; q < kEU; ++q) {
-      float f[8], xv[8], dv[8];
-      Vec16<T> xx;
-      xx.raw = xr[q];
-      xx.unpack(xv);
+      float2 f2[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        dv[e] = (a.D && a.d_has_p) ? __ldg(a.D + h * kP + wg * kEC + q * 8 + e) : Dh;
-        f[e] = fmaf(escale, ys[q * 8 + e], yi[q * 8 + e]);
-      }
-      unsigned char* slot = swz(sZ, i_loc, wg * kEU + q);
+      for (int e = 0; e < 4; ++e)
+        f2[e] = __ffma2_rn(es2, make_float2(ys[q * 8 + 2 * e], ys[q * 8 + 2 * e + 1]), make_float2(yi[q * 8 + 2 * e], yi[q * 8 + 2 * e + 1]));
+      float zv[8];
       if (has_z) {
-        float zv[8];
         Vec16<T> zz;
         zz.raw = *reinterpret_cast<const uint4*>(swz(sZin(buf), i_loc, wg * kEU + q));
         zz.unpack(zv);
         if (dots) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(f[e], zv[e], dot), f[e] = fmaf(dv[e], xv[e], f[e]);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = fmaf(dv[e], xv[e], f[e]) * silu_half_io(zv[e]);
+          for (int e = 0; e < 4; ++e) dot = fmaf(f2[e].x, zv[2 * e], dot), dot = fmaf(f2[e].y, zv[2 * e + 1], dot);
         }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = fmaf(dv[e], xv[e], f[e]);
       }
+      if (skip_explicit) {
+        float xv[8];
+        Vec16<T> xx;
+        xx.raw = xr[XSKIP ? q : 0];
+        xx.unpack(xv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 d2 = a.d_has_p ? make_float2(__ldg(a.D + h * kP + wg * kEC + q * 8 + 2 * e), __ldg(a.D + h * kP + wg * kEC + q * 8 + 2 * e + 1))
+                                      : make_float2(Dh, Dh);
+          f2[e] = __ffma2_rn(d2, make_float2(xv[2 * e], xv[2 * e + 1]), f2[e]);
+        }
+      }
+      if (has_z && !dots) {  // y silu(z), silu(z) = h + h tanh(h) with h = z / 2
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 h2 = __fmul2_rn(make_float2(zv[2 * e], zv[2 * e + 1]), make_float2(0.5f, 0.5f));
+          float2 t2;
+          asm("tanh.approx.f32 %0, %1;" : "=f"(t2.x) : "f"(h2.x));
+          asm("tanh.approx.f32 %0, %1;" : "=f"(t2.y) : "f"(h2.y));
+          f2[e] = __fmul2_rn(f2[e], __ffma2_rn(h2, t2, h2));
+        }
+      }
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) f[2 * e] = f2[e].x, f[2 * e + 1] = f2[e].y;
       Vec16<T> o;
       o.pack(f);
-      *reinterpret_cast<uint4*>(slot) = o.raw;
+      *reinterpret_cast<uint4*>(swz(sZ, i_loc, wg * kEU + q)) = o.raw;
     }
     if (dots && has_z) {
       const int t = t0 + MB * kBlk + i_loc;
-      // two threads (column halves) add to one zero-initialised word: the sum does not depend on their order
+      // the threads of a row (column slices) add to one zero-initialised word: the sum does not depend on their order
       if (t < a.len) atomicAdd(a.row_dots + ((int64_t)b * a.len + t) * a.heads + h, dot);
     }
     tc::fence_async_smem();  // the staged rows leave through a bulk store
@@ -568,9 +590,9 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   const int t_blk = t0 + MB * kBlk;  // first step of this block's rows
 
   float ct_prev = 0.f;   // the previous head's row exponent and x row, carried into its (deferred) epilogue
-  uint4 xr_prev[kEU];
+  uint4 xr_prev[kXR];
 #pragma unroll
-  for (int q = 0; q < kEU; ++q) xr_prev[q] = make_uint4(0, 0, 0, 0);
+  for (int q = 0; q < kXR; ++q) xr_prev[q] = make_uint4(0, 0, 0, 0);
   int fail = 0;
 #pragma unroll 1
   for (int hi = 0; hi < nh; ++hi) {
@@ -612,6 +634,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     // ---- decay mask: G (registers) -> masked tile, K-major over j: unit (i, j/8) at (j/8) * 2048 + i * 16
     const float* vc = sVec + buf * (2 * kQ);
     const float* vcp = vc + kQ;
+    const float Dfold = fold_d ? __ldg(a.D + h) : 0.f;
     float ct = vc[i_chunk];
     if (a.row_scale) {
       // optional weight of this thread's row, folded into the row exponent: it scales the mask before rounding and the
@@ -681,6 +704,8 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
             float2 w = __fmul2_rn(__fmul2_rn(make_float2(vG[k][q + e], vG[k][q + e + 1]), bp[e / 2]), a2);
             if (q + e > lane) w.x = 0.f;
             if (q + e + 1 > lane) w.y = 0.f;
+            if (q + e == lane) w.x += Dfold;
+            if (q + e + 1 == lane) w.y += Dfold;
             f[e] = w.x, f[e + 1] = w.y;
           }
           Vec16<T> o;
@@ -699,6 +724,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
             float w = ex2_approx(ct - cj[e]);
             if (diag && q + e > lane) w = 0.f;
             f[e] = vG[k][q + e] * w;
+            if (diag && q + e == lane) f[e] += Dfold;
           }
           Vec16<T> o;
           o.pack(f);
@@ -709,9 +735,10 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     }
     tc::tmem_wait_st();
     // this row of x (for D x in the epilogue one iteration later)
-    uint4 xr[kEU];
+    uint4 xr[kXR];
 #pragma unroll
-    for (int q = 0; q < kEU; ++q) xr[q] = *reinterpret_cast<const uint4*>(swz(sX + buf * M::X_BYTES, i_chunk, wg * kEU + q));
+    for (int q = 0; q < kXR; ++q)
+      xr[q] = XSKIP ? *reinterpret_cast<const uint4*>(swz(sX + buf * M::X_BYTES, i_chunk, wg * kEU + q)) : make_uint4(0, 0, 0, 0);
 
 
     tc::fence_before_sync();
@@ -737,7 +764,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     }
     ct_prev = ct;
 #pragma unroll
-    for (int q = 0; q < kEU; ++q) xr_prev[q] = xr[q];
+    for (int q = 0; q < kXR; ++q) xr_prev[q] = xr[q];
   }
   // leave the loop together: a thread that saw a wait run out above still reaches the same barriers
   fail = __syncthreads_or(fail);
@@ -774,7 +801,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   if (fail && tid == 0 && a.status) atomicExch(a.status, 2);
 }
 
-template <typename T>
+template <typename T, bool XSKIP>
 __global__ void __launch_bounds__(kScanThreads, 1)
     ssd_scan_kernel(const ssm_ssd_args a, const __grid_constant__ ScanMaps maps, int nchunks, int hpc, int nparts) {
   extern __shared__ unsigned char smdyn[];
@@ -788,8 +815,8 @@ __global__ void __launch_bounds__(kScanThreads, 1)
   }
   __syncthreads();  // barriers and the TMEM address are set up before anyone arms or polls them
   // the heavier blocks (rows 128..255) are scheduled first
-  if ((int)blockIdx.x < (int)(gridDim.x >> 1)) ssd_scan_body<T, 1>(a, maps, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
-  else ssd_scan_body<T, 0>(a, maps, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
+  if ((int)blockIdx.x < (int)(gridDim.x >> 1)) ssd_scan_body<T, 1, XSKIP>(a, maps, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
+  else ssd_scan_body<T, 0, XSKIP>(a, maps, nchunks, hpc, nparts, smraw, mbar, &tmem_slot);
   tc::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem_slot, 512);
@@ -927,8 +954,14 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
     if (int rc = encode_rows_map(&maps.c, a.Cm, a, kBlk, bcw, a.groups)) return rc;
     if (int rc = encode_rows_map(&maps.bm, a.Bm, a, kBlk, bcw, a.groups)) return rc;
     const size_t smem = ScanSmem<T>::ALLOC;
-    cudaFuncSetAttribute(ssd_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ssd_scan_kernel<T><<<2 * nparts * a.batch * nchunks, kScanThreads, smem, st>>>(a, maps, nchunks, hpc, nparts);
+    const unsigned ctas = 2u * nparts * a.batch * nchunks;
+    if (a.D && (a.d_has_p || a.row_dots)) {
+      cudaFuncSetAttribute(ssd_scan_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      ssd_scan_kernel<T, true><<<ctas, kScanThreads, smem, st>>>(a, maps, nchunks, hpc, nparts);
+    } else {
+      cudaFuncSetAttribute(ssd_scan_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      ssd_scan_kernel<T, false><<<ctas, kScanThreads, smem, st>>>(a, maps, nchunks, hpc, nparts);
+    }
     if (int rc = launch_status("ssd_scan_kernel")) return rc;
   }
   return SSM_OK;
