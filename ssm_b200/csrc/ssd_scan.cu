@@ -91,17 +91,17 @@ __global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, i
 }
 
 // ---------------------------------------------------------------------------------------------
-// chunk states, local and carried, in one pass:  one CTA (256 threads) per (batch, head) walks the
-// chunks in order.  Per chunk the tensor cores form  S_c[n][p] = sum_j B[j][n] * (w_j x[j][p]),
-// w_j = exp2(c_last - (c_j - log2 delta_j)), in two half-chunk stages of a four-stage ring
-//   A operand = B^T, MN-major, stored [j/8][n/8][j%8][8];  B operand = w x of the CTA's heads side by side, MN-major
-//   [j/8][head][p/8][j%8][8];  M = 128 (n), N = 64 per head (p), K = 64 per stage.  (Units that are neighbours along M / N are 128 bytes apart, so the tensor core's reads of one
-//   K slice fall on different banks; with the [n/8][j][8] order they were 2 KB apart and the MMAs ran 4-5x slower.)
-// while the threads keep the running state in registers (thread = state n, 32 of the 64 columns p):
-//   state <- exp2(c_last) * state + S_c ;  the state BEFORE each chunk goes out in the operand dtype,
-// in the operand order of the scan kernel (MN-major units [p/8][n][8]).  The per-chunk local states
-// never touch global memory.  Copies (cp.async, whole rows) run two stages ahead; a stage's buffer
-// is refilled once the MMAs that read it have completed (tcgen05.commit -> mbarrier).
+// chunk states, local and carried, in one pass:  one CTA per (batch, a few heads) walks the chunks in order.
+// Per chunk the tensor cores form  S_c[n][p] = sum_j B[j][n] * (w_j x[j][p]),  w_j = exp2(c_last - (c_j - log2 delta_j)),
+// in four stages of 64 steps from a ring of TMA-filled buffers:
+//   A operand = B^T, MN-major;  B operand = w x of the CTA's heads side by side, MN-major;  M = 128 (n), N = 64 per head (p),
+//   K = 64 per stage.  (Units that are neighbours along M / N are 128 bytes apart, so the tensor core's reads of one K slice
+//   fall on different banks; with units 2 KB apart the MMAs ran 4-5x slower.)
+// Eight compute warps scale the x rows of a landed stage in place and keep the running state in registers (thread = state n,
+// 32 of the 64 columns p):  state <- exp2(c_last) * state + S_c ;  the state BEFORE each chunk goes out in the operand dtype,
+// in the operand order of the scan kernel (MN-major units [p/8][n][8]).  The per-chunk local states never touch global memory.
+// A ninth warp issues the copies (a buffer is refilled once the MMAs that read it have completed: tcgen05.commit -> mbarrier),
+// a tenth the MMAs (once the eight compute warps have arrived on the stage's barrier).
 // ---------------------------------------------------------------------------------------------
 // HPC heads of one B / C group per CTA share the B^T tile of every stage (the grid is sized to about one CTA per SM).
 // Tiles are rows of 128 bytes (64 elements along M / N) written by TMA with the 128-byte swizzle, 64 steps each:
@@ -113,9 +113,11 @@ struct StateSmem {
   static constexpr int A_BYTES = 2 * BLK_BYTES;               // 16 KB
   static constexpr int STAGE = A_BYTES + HPC * BLK_BYTES;
   static constexpr int NSTAGE = HPC <= 2 ? 6 : (HPC == 3 ? 5 : 4);
-  static constexpr int AHEAD = NSTAGE - 2;                    // stages copied ahead of the one being multiplied
-  static constexpr int VEC_BYTES = HPC * kQ * 4;              // c - log2(delta) of a chunk, per head (x2)
-  static constexpr int TOTAL = NSTAGE * STAGE + 2 * VEC_BYTES;
+  static constexpr int VEC_BYTES = HPC * kQ * 4;              // c - log2(delta) of a chunk, per head
+  // The copies run up to NSTAGE stages ahead of the MMAs, so a chunk's vectors may arrive while the chunk before last is still
+  // being scaled: three buffers (NSTAGE <= 6 stages = one and a half chunks).
+  static constexpr int NVEC = 3;
+  static constexpr int TOTAL = NSTAGE * STAGE + NVEC * VEC_BYTES;
   static constexpr int ALLOC = TOTAL + 1024;
 };
 
@@ -124,15 +126,23 @@ struct StateMaps {
   CUtensorMap b, x;
 };
 
+// Threads: eight warps scale the x rows and keep the running states; one warp issues the copies, one the MMAs.  The stages pass
+// from role to role through mbarriers only (landed -> scaled -> multiplied -> free), so no warp waits for another role's
+// instruction issue.
+constexpr int kStateComputeThreads = 256;
+constexpr int kStateThreads = kStateComputeThreads + 64;
+constexpr int kStateCopyWarp = 8, kStateMmaWarp = 9;
+
 template <typename T, int HPC>
-__global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a, const __grid_constant__ StateMaps maps, int nchunks) {
+__global__ void __launch_bounds__(kStateThreads, 1) ssd_state_kernel(const ssm_ssd_args a, const __grid_constant__ StateMaps maps, int nchunks) {
   using M = StateSmem<HPC>;
-  constexpr int kStep = M::kStep, NS = M::NSTAGE, AHEAD = M::AHEAD;
+  constexpr int kStep = M::kStep, NS = M::NSTAGE;
   constexpr int SPC = kQ / kStep;  // stages per chunk
   extern __shared__ unsigned char smdyn[];
   unsigned char* smraw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smdyn) + 1023) & ~(uintptr_t)1023);
-  float* sVec = reinterpret_cast<float*>(smraw + NS * M::STAGE);  // [2][HPC][kQ]
+  float* sVec = reinterpret_cast<float*>(smraw + NS * M::STAGE);  // [NVEC][HPC][kQ]
   __shared__ __align__(8) uint64_t mbar_full[NS];   // a stage's copies have landed
+  __shared__ __align__(8) uint64_t mbar_scaled[NS]; // every compute warp has scaled its part of a stage's x rows
   __shared__ __align__(8) uint64_t mbar_free[NS];   // the MMAs that read a stage's buffer have completed
   __shared__ __align__(8) uint64_t mbar_acc[2];     // a chunk's accumulators are complete
   __shared__ uint32_t tmem_slot;
@@ -148,14 +158,16 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
       tc::mbar_init(tc::smem_u32(&mbar_full[i]), 1);
+      tc::mbar_init(tc::smem_u32(&mbar_scaled[i]), kStateComputeThreads / 32);
       tc::mbar_init(tc::smem_u32(&mbar_free[i]), 1);
     }
     tc::mbar_init(tc::smem_u32(&mbar_acc[0]), 1);
     tc::mbar_init(tc::smem_u32(&mbar_acc[1]), 1);
   }
   __syncthreads();  // TMEM address and barriers are set up
-  const uint32_t tmem = tmem_slot;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  const int role = __shfl_sync(0xffffffffu, warp, 0);  // the same in every lane, and visibly so
 
   const int64_t vrow0 = ((int64_t)b * a.heads + h0) * nchunks * kQ;  // exponent vectors of head h0 (next head: + nchunks * kQ)
   const int nst = SPC * nchunks;
@@ -174,13 +186,50 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
       const int c = s / SPC;
 #pragma unroll
       for (int hh = 0; hh < HPC; ++hh)
-        tc::bulk_load(tc::smem_u32(sVec + ((c & 1) * HPC + hh) * kQ), a.ws_dt + vrow0 + ((int64_t)hh * nchunks + c) * kQ, kQ * 4, full);
+        tc::bulk_load(tc::smem_u32(sVec + ((c % M::NVEC) * HPC + hh) * kQ), a.ws_dt + vrow0 + ((int64_t)hh * nchunks + c) * kQ, kQ * 4, full);
     }
   };
-  if (tid == 0) {
-    for (int s = 0; s < AHEAD && s < nst; ++s) copy_stage(s);
-  }
-
+  int fail = 0;
+  if (role == kStateCopyWarp) {
+    // ---- copies: a buffer is refilled once the MMAs of the stage that used it before have completed ------------
+#pragma unroll 1
+    for (int s = 0; s < nst; ++s) {
+      bool okf = true;
+      if (s >= NS) okf = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_free[s % NS]), ((s - NS) / NS) & 1));
+      if (!okf) {  // the stage never lands and the waits of the other warps report it too
+        fail = 1;
+        break;
+      }
+      if (tc::elect_one()) copy_stage(s);
+      __syncwarp();
+    }
+  } else if (role == kStateMmaWarp) {
+    // ---- MMAs: S_c (+)= B^T (w x) over the 64 steps of a stage, as soon as the eight compute warps have scaled it ----
+#pragma unroll 1
+    for (int s = 0; s < nst; ++s) {
+      const int c = s / SPC, part = s % SPC;
+      const bool okm = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_scaled[s % NS]), (s / NS) & 1));
+      if (!okm) {
+        fail = 1;
+        break;
+      }
+      tc::fence_after_sync();
+      if (tc::elect_one()) {
+        // M = 128 states = two 64-element blocks, N = 64 HPC = one block per head; blocks 8 KB apart, 8 steps 1 KB apart
+        unsigned char* base = smraw + (s % NS) * M::STAGE;
+        constexpr uint32_t idesc = tc::instr_desc(kN, HPC * kP, fmt, 1, 1);
+        const uint64_t da0 = tc::smem_desc_sw128(tc::smem_u32(base), M::BLK_BYTES, 1024);
+        const uint64_t db0 = tc::smem_desc_sw128(tc::smem_u32(base + M::A_BYTES), M::BLK_BYTES, 1024);
+#pragma unroll
+        for (int kk = 0; kk < kStep / 16; ++kk)  // 16 steps = 16 rows of 128 bytes
+          tc::mma_ss(tmem + (c & 1) * HPC * 64, da0 + (uint64_t)(kk * (2048 >> 4)), db0 + (uint64_t)(kk * (2048 >> 4)), idesc, part > 0 || kk > 0);
+        tc::commit(tc::smem_u32(&mbar_free[s % NS]));
+        if (part == SPC - 1) tc::commit(tc::smem_u32(&mbar_acc[c & 1]));
+      }
+      __syncwarp();
+    }
+  } else {
+  // ======== compute warps ========================================================================================
   // running states: st[hh][i] = S_{h0 + hh}[n][wg * 32 + i]
   float st[HPC][32];
 #pragma unroll
@@ -213,9 +262,12 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
     }
   };
   // last exponent of the current / previous chunk per head (the decay across the chunk is exp2 of it)
-  float clast[HPC], clast_prev[HPC], ctot[HPC];
+  float clast[HPC], clast_prev[HPC], clast_next[HPC], ctot[HPC];
 #pragma unroll
-  for (int hh = 0; hh < HPC; ++hh) clast[hh] = 0.f, clast_prev[hh] = 0.f, ctot[hh] = 0.f;
+  for (int hh = 0; hh < HPC; ++hh) {
+    clast[hh] = 0.f, clast_prev[hh] = 0.f, ctot[hh] = 0.f;
+    clast_next[hh] = nchunks > 0 ? __ldg(a.ws_cum + vrow0 + (int64_t)hh * nchunks * kQ + kQ - 1) : 0.f;  // chunk 0
+  }
   // fold chunk c's finished accumulators into the running states
   auto fold_chunk = [&](int c, const float (&cl)[HPC]) -> bool {
     const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_acc[c & 1]), (c >> 1) & 1));
@@ -233,22 +285,15 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
     return ok;
   };
 
-  int fail = 0;
 #pragma unroll 1
   for (int s = 0; s < nst; ++s) {
     const int c = s / SPC, part = s % SPC;
-    // ---- refill the buffer AHEAD stages ahead; it was last read by the MMAs of stage s + AHEAD - NS ----------
-    if (tid == 0 && s + AHEAD < nst) {
-      const int sp = s + AHEAD - NS;  // previous user of that buffer
-      bool okf = true;
-      if (sp >= 0) okf = tc::mbar_wait(tc::smem_u32(&mbar_free[(s + AHEAD) % NS]), (sp / NS) & 1);
-      if (okf) copy_stage(s + AHEAD);  // if that wait ran out the stage never lands and the waits below report it
-    }
-    if (part == 0) {  // a new chunk begins: its last exponents (loaded early, used by the scaling below)
+    if (part == 0) {  // a new chunk begins: its last exponents (read one chunk ahead, used by the scaling below)
 #pragma unroll
       for (int hh = 0; hh < HPC; ++hh) {
         clast_prev[hh] = clast[hh];
-        clast[hh] = __ldg(a.ws_cum + vrow0 + ((int64_t)hh * nchunks + c) * kQ + kQ - 1);
+        clast[hh] = clast_next[hh];
+        if (c + 1 < nchunks) clast_next[hh] = __ldg(a.ws_cum + vrow0 + ((int64_t)hh * nchunks + c + 1) * kQ + kQ - 1);
         // exponent (base 2) of the decay from the start of the sequence to the start of this chunk: what a state
         // that arrives later (phase 2 of a sequence shard) is multiplied by before it joins this chunk's state
         if (tid == 0) a.ws_state[ssd_summary_floats_padded(a.batch, a.heads) + ((int64_t)b * a.heads + h0 + hh) * nchunks + c] = ctot[hh];
@@ -268,7 +313,7 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
     unsigned char* base = smraw + (s % NS) * M::STAGE;
 #pragma unroll
     for (int hh = 0; hh < HPC; ++hh) {
-      const float* vcp = sVec + ((c & 1) * HPC + hh) * kQ + part * kStep;
+      const float* vcp = sVec + ((c % M::NVEC) * HPC + hh) * kQ + part * kStep;
       const float c_last = clast[hh];
 #pragma unroll
       for (int k = 0; k < M::BLK_BYTES / 16 / 256; ++k) {
@@ -285,22 +330,12 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
         *reinterpret_cast<uint4*>(px) = v.raw;
       }
     }
+    // the scaled rows become visible to the tensor cores' reads; the accumulator reads of an earlier fold precede the MMAs
+    // that will overwrite that pair.  A warp whose wait ran out still arrives, so that the others do not wait for it.
     tc::fence_async_smem();
     tc::fence_before_sync();
-    __syncthreads();
-    tc::fence_after_sync();
-
-    if (tid == 0) {
-      // M = 128 states = two 64-element blocks, N = 64 HPC = one block per head; blocks 8 KB apart, 8 steps 1 KB apart
-      constexpr uint32_t idesc = tc::instr_desc(kN, HPC * kP, fmt, 1, 1);
-      const uint64_t da0 = tc::smem_desc_sw128(tc::smem_u32(base), M::BLK_BYTES, 1024);
-      const uint64_t db0 = tc::smem_desc_sw128(tc::smem_u32(base + M::A_BYTES), M::BLK_BYTES, 1024);
-#pragma unroll
-      for (int kk = 0; kk < kStep / 16; ++kk)  // 16 steps = 16 rows of 128 bytes
-        tc::mma_ss(tmem + (c & 1) * HPC * 64, da0 + (uint64_t)(kk * (2048 >> 4)), db0 + (uint64_t)(kk * (2048 >> 4)), idesc, part > 0 || kk > 0);
-      tc::commit(tc::smem_u32(&mbar_free[s % NS]));
-      if (part == SPC - 1) tc::commit(tc::smem_u32(&mbar_acc[c & 1]));
-    }
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(tc::smem_u32(&mbar_scaled[s % NS]));
   }
   if (nchunks > 0 && !fail) fail = !fold_chunk(nchunks - 1, clast);
   // final states in fp32, (p, n) order: to the caller, and kept in scratch for a later phase 2
@@ -318,6 +353,7 @@ __global__ void __launch_bounds__(256, 1) ssd_state_kernel(const ssm_ssd_args a,
       if (tid == 0) a.ws_state[(int64_t)a.batch * a.heads * kP * kN + (int64_t)b * a.heads + h0 + hh] = ctot[hh] * kLn2;
     }
   }
+  }  // compute warps
   if (fail && lane == 0 && a.status) atomicExch(a.status, 1);
   tc::fence_before_sync();
   __syncthreads();
@@ -598,40 +634,9 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   for (int hi = 0; hi < nh; ++hi) {
     const int h = h0 + hi, buf = hi & 1;
     ok = !fail && tc::mbar_wait(mb_full(buf), (hi >> 1) & 1);  // this head's operands (no more waiting once a wait ran out)
-    // MMAs of the previous head: the masked tile, the other buffer and its accumulators are free / ready
-    if (hi > 0) ok = tc::mbar_wait(mb_mma(buf ^ 1), ((hi - 1) >> 1) & 1) && ok;
-    tc::fence_after_sync();
-    tc::fence_before_sync();     // the accumulator reads of the previous epilogue precede the MMAs issued below
-    ok = __syncthreads_and(ok);  // the staged y of the head before last is complete; the outcome of the waits is CTA-wide
-    if (!ok) {
-      fail = 1;
-      break;
-    }
-    if (mma_warp && tc::elect_one()) {
-      // Y_inter = C_m S_in needs nothing of the mask: issued first, it runs on the tensor cores while the mask is formed
-      tc::fence_after_sync();
-      const uint64_t dc0 = tc::smem_desc_sw128(tc::smem_u32(sC), 16, 1024);
-      const uint64_t ds0 = tc::smem_desc(tc::smem_u32(sS + buf * M::S_BYTES), 128, kN * 16);
-      constexpr uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 1);
-      const uint32_t dS = tmem + 256 + buf * 128 + 64;
-#pragma unroll
-      for (int kk = 0; kk < kN / 16; ++kk)
-        tc::mma_ss(dS, dc0 + (uint64_t)(((kk >> 2) * (kBlk * 128) + (kk & 3) * 32) >> 4), ds0 + (uint64_t)(kk * (256 >> 4)), idS, kk > 0);
-    }
-    if (tid == kCopyThread) {
-      if (hi >= 2) {  // staged by the epilogue of the previous iteration
-        tc::tma_store_4d(&maps.y, tc::smem_u32(sZ), 0, h - 2, t_blk, b);
-        tc::bulk_commit();
-        tc::bulk_wait_read();  // the tile may be overwritten
-      }
-      if (has_z) {  // its buffer was last read by the epilogue of head h - 2, one iteration ago
-        tc::mbar_expect_tx(mb_z(buf), M::Z_BYTES);
-        tc::tma_load_4d(tc::smem_u32(sZin(buf)), &maps.z, mb_z(buf), 0, h, t_blk, b);
-      }
-      if (hi + 1 < nh) prefetch(h + 1, buf ^ 1);
-    }
-
-    // ---- decay mask: G (registers) -> masked tile, K-major over j: unit (i, j/8) at (j/8) * 2048 + i * 16
+    // ---- factors of the decay mask, formed before the CTA-wide barrier below so that their latency (shared-memory reads, ex2,
+    // the exchange of the column factors through sW) overlaps the wait for the slowest warp; the barrier also orders the
+    // writes to sW before the reads of the other lanes
     const float* vc = sVec + buf * (2 * kQ);
     const float* vcp = vc + kQ;
     const float Dfold = fold_d ? __ldg(a.D + h) : 0.f;
@@ -659,7 +664,44 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
         sW[k * 32 + lane] = ex2_approx(r - vcp[cc * 32 + lane]);
       }
     }
-    __syncwarp();
+    // MMAs of the previous head: the masked tile, the other buffer and its accumulators are free / ready
+    if (hi > 0) ok = tc::mbar_wait(mb_mma(buf ^ 1), ((hi - 1) >> 1) & 1) && ok;
+    tc::fence_after_sync();
+    tc::fence_before_sync();     // the accumulator reads of the previous epilogue precede the MMAs issued below
+    ok = __syncthreads_and(ok);  // the staged y of the head before last is complete; the outcome of the waits is CTA-wide
+    if (!ok) {
+      fail = 1;
+      break;
+    }
+    if (mma_warp && tc::elect_one()) {
+      // Y_inter = C_m S_in needs nothing of the mask: issued first, it runs on the tensor cores while the mask is formed
+      tc::fence_after_sync();
+      const uint64_t dc0 = tc::smem_desc_sw128(tc::smem_u32(sC), 16, 1024);
+      const uint64_t ds0 = tc::smem_desc(tc::smem_u32(sS + buf * M::S_BYTES), 128, kN * 16);
+      constexpr uint32_t idS = tc::instr_desc(kBlk, kP, fmt, 0, 1);
+      const uint32_t dS = tmem + 256 + buf * 128 + 64;
+#pragma unroll
+      for (int kk = 0; kk < kN / 16; ++kk)
+        tc::mma_ss(dS, dc0 + (uint64_t)(((kk >> 2) * (kBlk * 128) + (kk & 3) * 32) >> 4), ds0 + (uint64_t)(kk * (256 >> 4)), idS, kk > 0);
+    }
+    if (tid == kCopyThread) {
+      if (hi + 1 < nh) prefetch(h + 1, buf ^ 1);
+      if (has_z) {  // its buffer was last read by the epilogue of head h - 2, one iteration ago
+        tc::mbar_expect_tx(mb_z(buf), M::Z_BYTES);
+        tc::tma_load_4d(tc::smem_u32(sZin(buf)), &maps.z, mb_z(buf), 0, h, t_blk, b);
+      }
+      if (hi >= 2) {  // staged by the epilogue of the previous iteration; its reads are awaited after the mask, below
+        tc::tma_store_4d(&maps.y, tc::smem_u32(sZ), 0, h - 2, t_blk, b);
+        tc::bulk_commit();
+      }
+      if (hi + 2 < nh) {  // the tiles of the head after next on their way into the L2: one iteration alone does not cover the latency
+        tc::tma_prefetch_4d(mapx, 0, h + 2, t0, b);
+        if (has_z) tc::tma_prefetch_4d(&maps.z, 0, h + 2, t_blk, b);
+        tc::bulk_prefetch(reinterpret_cast<const T*>(a.ws_state_in) + (((int64_t)b * nchunks + c) * a.heads + h + 2) * (int64_t)(kP * kN), M::S_BYTES);
+      }
+    }
+
+    // ---- decay mask: G (registers) x the factors formed above -> the A operand in tensor memory
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       const int cc = wg + kScanWG * k;  // chunk of 32 steps: fully causal (cc < rc), diagonal (cc == rc) or empty (cc > rc) for this warp's rows
@@ -741,6 +783,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
       xr[q] = XSKIP ? *reinterpret_cast<const uint4*>(swz(sX + buf * M::X_BYTES, i_chunk, wg * kEU + q)) : make_uint4(0, 0, 0, 0);
 
 
+    if (tid == kCopyThread && hi >= 2) tc::bulk_wait_read();  // the staging tile may be overwritten by the epilogue below
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
@@ -858,7 +901,7 @@ static int ssd_state_launch(const ssm_ssd_args& a, int nchunks, cudaStream_t st)
   if (int rc = encode_rows_map(&maps.x, a.X, a, StateSmem<HPC>::kStep)) return rc;
   const size_t smem = StateSmem<HPC>::ALLOC;
   cudaFuncSetAttribute(ssd_state_kernel<T, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  ssd_state_kernel<T, HPC><<<dim3(a.heads / HPC, a.batch), 256, smem, st>>>(a, maps, nchunks);
+  ssd_state_kernel<T, HPC><<<dim3(a.heads / HPC, a.batch), kStateThreads, smem, st>>>(a, maps, nchunks);
   return launch_status("ssd_state_kernel");
 }
 

@@ -144,6 +144,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint
                "l"(tmap), "r"(mbar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                : "memory");
 }
+// hints: bring one box / one contiguous piece into the L2 ahead of the copy that will fetch it (nothing to wait for)
+__device__ __forceinline__ void tma_prefetch_4d(const void* tmap, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];\n" ::"l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(src), "r"(bytes) : "memory");
+}
 // one box, shared -> global; elements outside the tensor are not written
 __device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src, int c0, int c1, int c2, int c3) {
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n" ::"l"(tmap), "r"(src), "r"(c0), "r"(c1),
