@@ -13,8 +13,10 @@
 //   ssd_fold_shards_kernel / ssd_fold_init_kernel   (sequence shards only) fold the other ranks' summaries into this
 //                       shard's incoming state, and add that late-arriving state to the per-chunk states by linearity
 //   ssd_scan_kernel     per (batch, chunk, 128-row block, part of a head group):  G = C B^T once (TMEM -> registers), then per
-//                       head the decay mask exp2(c_i - c_j) delta_j [j <= i] written back to TMEM (tcgen05.st) as the A operand of
-//                       Y_intra = (G o L) X, plus  Y_inter = C S_in;  y = Y_intra + exp2(c_i) Y_inter + D x, gated, stored.
+//                       head the decay mask exp2(c_i - c_j) delta_j [j <= i] (+ D on the diagonal) written back to TMEM
+//                       (tcgen05.st) as the A operand of Y_intra = (G o L) X, plus  Y_inter = C S_in;
+//                       y = Y_intra + exp2(c_i) Y_inter, gated, stored by TMA.  Sixteen warps form masks and epilogues; an
+//                       elected lane of the warp with the least mask work issues the MMAs, one thread the copies.
 //
 // Exponent differences are always formed before exp2 (never exp2(c_i) / exp2(c_j)), so long
 // sequences stay finite.  Every wait on an mbarrier is bounded and reports through the status word.
@@ -38,55 +40,90 @@ __host__ __device__ inline int64_t ssd_summary_floats_padded(int batch, int head
 }
 
 // ---------------------------------------------------------------------------------------------
-// delta and within-chunk cumulative log-decay; one warp per (batch, head, chunk)
+// delta and within-chunk cumulative log-decay.  One CTA per (batch, chunk, 32 heads): the step sizes are read the way they
+// lie in memory (heads innermost: each thread the 32 heads of one step), activated, transposed through shared memory, and
+// each warp then scans whole heads, a lane owning 8 consecutive steps and writing them as 16-byte pieces.
 // ---------------------------------------------------------------------------------------------
+constexpr int kCumHeads = 32;
+constexpr int kCumLd = kQ + 8;  // row pitch of the transposed tile (floats): rows stay 16-byte aligned, lanes 32 bytes apart
+
 template <typename T>
-__global__ void __launch_bounds__(128) ssd_cumsum_kernel(const ssm_ssd_args a, int nchunks) {
-  const int warp = (blockIdx.x * 128 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  const int total = a.batch * a.heads * nchunks;
-  if (warp >= total) return;
-  const int c = warp % nchunks, h = (warp / nchunks) % a.heads, b = warp / (nchunks * a.heads);
-  const float Ah = __ldg(a.A + h);
-  const float bias = a.dt_bias ? __ldg(a.dt_bias + h) : 0.f;
-  const T* dt = reinterpret_cast<const T*>(a.dt);
-  const float* dt_ready = reinterpret_cast<const float*>(a.dt);  // dt_mode & 1: fp32 step sizes, already activated
-  float* odt = a.ws_dt + ((int64_t)b * a.heads + h) * nchunks * kQ + (int64_t)c * kQ;
-  float* ocum = a.ws_cum + ((int64_t)b * a.heads + h) * nchunks * kQ + (int64_t)c * kQ;
-  float d[kQ / 32], run = 0.f;
-#pragma unroll
-  for (int k = 0; k < kQ / 32; ++k) {
-    const int i = lane * (kQ / 32) + k;  // each lane owns 8 consecutive steps
-    const int t = c * kQ + i;
-    float v = 0.f;
+__global__ void __launch_bounds__(kQ) ssd_cumsum_kernel(const ssm_ssd_args a, int nchunks) {
+  __shared__ __align__(16) float sD[kCumHeads * kCumLd];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h0 = blockIdx.x * kCumHeads, c = blockIdx.y, b = blockIdx.z;
+  const int nh = min(kCumHeads, a.heads - h0);
+  {
+    const int t = c * kQ + tid;
     if (t < a.len) {
-      const int64_t at = ((int64_t)b * a.len + t) * a.heads + h;
-      if (a.dt_mode & 1) {
-        v = __ldg(dt_ready + at);
+      const int64_t at = ((int64_t)b * a.len + t) * a.heads + h0;
+      if (a.dt_mode & 1) {  // fp32 step sizes, already activated
+        const float* p = reinterpret_cast<const float*>(a.dt) + at;
+        for (int hh = 0; hh < nh; ++hh) sD[hh * kCumLd + tid] = __ldg(p + hh);
       } else {
-        v = to_f<T>(dt[at]) + bias;
-        if (a.dt_softplus) v = softplus_f(v);
+        const T* p = reinterpret_cast<const T*>(a.dt) + at;
+        if (nh == kCumHeads && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+          for (int q = 0; q < kCumHeads / 8; ++q) {
+            Vec16<T> v;
+            v.load(p + q * 8);
+            float f[8];
+            v.unpack(f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float x = f[e] + (a.dt_bias ? __ldg(a.dt_bias + h0 + q * 8 + e) : 0.f);
+              if (a.dt_softplus) x = softplus_f(x);
+              sD[(q * 8 + e) * kCumLd + tid] = x;
+            }
+          }
+        } else {
+          for (int hh = 0; hh < nh; ++hh) {
+            float x = to_f<T>(p[hh]) + (a.dt_bias ? __ldg(a.dt_bias + h0 + hh) : 0.f);
+            if (a.dt_softplus) x = softplus_f(x);
+            sD[hh * kCumLd + tid] = x;
+          }
+        }
       }
+    } else {
+      for (int hh = 0; hh < nh; ++hh) sD[hh * kCumLd + tid] = 0.f;  // steps beyond the sequence: no decay, no input
     }
-    d[k] = v;
-    run += v * Ah;
   }
-  // exclusive prefix of the lane sums
-  float pre = run;
+  __syncthreads();
+  for (int hh = warp; hh < nh; hh += kQ / 32) {
+    const int h = h0 + hh;
+    const float Ah = __ldg(a.A + h);
+    float* odt = a.ws_dt + (((int64_t)b * a.heads + h) * nchunks + c) * kQ + lane * 8;
+    float* ocum = a.ws_cum + (((int64_t)b * a.heads + h) * nchunks + c) * kQ + lane * 8;
+    float d[8], run = 0.f;  // each lane owns 8 consecutive steps
+    {
+      const float4 d0 = *reinterpret_cast<const float4*>(sD + hh * kCumLd + lane * 8);
+      const float4 d1 = *reinterpret_cast<const float4*>(sD + hh * kCumLd + lane * 8 + 4);
+      d[0] = d0.x, d[1] = d0.y, d[2] = d0.z, d[3] = d0.w, d[4] = d1.x, d[5] = d1.y, d[6] = d1.z, d[7] = d1.w;
+    }
 #pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    const float o = __shfl_up_sync(0xffffffffu, pre, off);
-    if (lane >= off) pre += o;
-  }
-  float acc = pre - run;
+    for (int k = 0; k < 8; ++k) run += d[k] * Ah;
+    // exclusive prefix of the lane sums
+    float pre = run;
 #pragma unroll
-  for (int k = 0; k < kQ / 32; ++k) {
-    const int i = lane * (kQ / 32) + k;
-    acc += d[k] * Ah;
-    const float c2 = acc * kLog2e;
-    ocum[i] = c2;                      // running decay exponent, base 2
-    // the same with delta folded in: exp2(x - odt[j]) = exp2(x - c2_j) * delta_j  (delta 0 -> +inf -> weight 0);
-    // dt_mode & 2: the inputs enter with unit weight, only the decay uses delta
-    odt[i] = (a.dt_mode & 2) ? c2 : c2 - lg2_approx(d[k]);
+    for (int off = 1; off < 32; off <<= 1) {
+      const float o = __shfl_up_sync(0xffffffffu, pre, off);
+      if (lane >= off) pre += o;
+    }
+    float acc = pre - run;
+    float oc[8], od[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      acc += d[k] * Ah;
+      const float c2 = acc * kLog2e;
+      oc[k] = c2;                      // running decay exponent, base 2
+      // the same with delta folded in: exp2(x - odt[j]) = exp2(x - c2_j) * delta_j  (delta 0 -> +inf -> weight 0);
+      // dt_mode & 2: the inputs enter with unit weight, only the decay uses delta
+      od[k] = (a.dt_mode & 2) ? c2 : c2 - lg2_approx(d[k]);
+    }
+    reinterpret_cast<float4*>(ocum)[0] = make_float4(oc[0], oc[1], oc[2], oc[3]);
+    reinterpret_cast<float4*>(ocum)[1] = make_float4(oc[4], oc[5], oc[6], oc[7]);
+    reinterpret_cast<float4*>(odt)[0] = make_float4(od[0], od[1], od[2], od[3]);
+    reinterpret_cast<float4*>(odt)[1] = make_float4(od[4], od[5], od[6], od[7]);
   }
 }
 
@@ -117,7 +154,8 @@ struct StateSmem {
   // The copies run up to NSTAGE stages ahead of the MMAs, so a chunk's vectors may arrive while the chunk before last is still
   // being scaled: three buffers (NSTAGE <= 6 stages = one and a half chunks).
   static constexpr int NVEC = 3;
-  static constexpr int TOTAL = NSTAGE * STAGE + NVEC * VEC_BYTES;
+  static constexpr int LAST_BYTES = HPC * 16;                 // the last four running exponents of a chunk, per head
+  static constexpr int TOTAL = NSTAGE * STAGE + NVEC * (VEC_BYTES + LAST_BYTES);
   static constexpr int ALLOC = TOTAL + 1024;
 };
 
@@ -141,6 +179,7 @@ __global__ void __launch_bounds__(kStateThreads, 1) ssd_state_kernel(const ssm_s
   extern __shared__ unsigned char smdyn[];
   unsigned char* smraw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smdyn) + 1023) & ~(uintptr_t)1023);
   float* sVec = reinterpret_cast<float*>(smraw + NS * M::STAGE);  // [NVEC][HPC][kQ]
+  float* sLast = sVec + M::NVEC * HPC * kQ;                       // [NVEC][HPC][4]: c at the chunk's last four steps
   __shared__ __align__(8) uint64_t mbar_full[NS];   // a stage's copies have landed
   __shared__ __align__(8) uint64_t mbar_scaled[NS]; // every compute warp has scaled its part of a stage's x rows
   __shared__ __align__(8) uint64_t mbar_free[NS];   // the MMAs that read a stage's buffer have completed
@@ -177,7 +216,7 @@ __global__ void __launch_bounds__(kStateThreads, 1) ssd_state_kernel(const ssm_s
     const uint32_t base = tc::smem_u32(smraw + (s % NS) * M::STAGE);
     const uint32_t full = tc::smem_u32(&mbar_full[s % NS]);
     const bool first = s % SPC == 0;
-    tc::mbar_expect_tx(full, M::STAGE + (first ? HPC * kQ * 4 : 0));
+    tc::mbar_expect_tx(full, M::STAGE + (first ? HPC * kQ * 4 + M::LAST_BYTES : 0));
     tc::tma_load_4d(base, &maps.b, full, 0, g, s * kStep, b);
     tc::tma_load_4d(base + M::BLK_BYTES, &maps.b, full, 64, g, s * kStep, b);
 #pragma unroll
@@ -185,8 +224,10 @@ __global__ void __launch_bounds__(kStateThreads, 1) ssd_state_kernel(const ssm_s
     if (first) {
       const int c = s / SPC;
 #pragma unroll
-      for (int hh = 0; hh < HPC; ++hh)
+      for (int hh = 0; hh < HPC; ++hh) {
         tc::bulk_load(tc::smem_u32(sVec + ((c % M::NVEC) * HPC + hh) * kQ), a.ws_dt + vrow0 + ((int64_t)hh * nchunks + c) * kQ, kQ * 4, full);
+        tc::bulk_load(tc::smem_u32(sLast + ((c % M::NVEC) * HPC + hh) * 4), a.ws_cum + vrow0 + ((int64_t)hh * nchunks + c) * kQ + kQ - 4, 16, full);
+      }
     }
   };
   int fail = 0;
@@ -262,12 +303,9 @@ __global__ void __launch_bounds__(kStateThreads, 1) ssd_state_kernel(const ssm_s
     }
   };
   // last exponent of the current / previous chunk per head (the decay across the chunk is exp2 of it)
-  float clast[HPC], clast_prev[HPC], clast_next[HPC], ctot[HPC];
+  float clast[HPC], clast_prev[HPC], ctot[HPC];
 #pragma unroll
-  for (int hh = 0; hh < HPC; ++hh) {
-    clast[hh] = 0.f, clast_prev[hh] = 0.f, ctot[hh] = 0.f;
-    clast_next[hh] = nchunks > 0 ? __ldg(a.ws_cum + vrow0 + (int64_t)hh * nchunks * kQ + kQ - 1) : 0.f;  // chunk 0
-  }
+  for (int hh = 0; hh < HPC; ++hh) clast[hh] = 0.f, clast_prev[hh] = 0.f, ctot[hh] = 0.f;
   // fold chunk c's finished accumulators into the running states
   auto fold_chunk = [&](int c, const float (&cl)[HPC]) -> bool {
     const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_acc[c & 1]), (c >> 1) & 1));
@@ -288,19 +326,7 @@ __global__ void __launch_bounds__(kStateThreads, 1) ssd_state_kernel(const ssm_s
 #pragma unroll 1
   for (int s = 0; s < nst; ++s) {
     const int c = s / SPC, part = s % SPC;
-    if (part == 0) {  // a new chunk begins: its last exponents (read one chunk ahead, used by the scaling below)
-#pragma unroll
-      for (int hh = 0; hh < HPC; ++hh) {
-        clast_prev[hh] = clast[hh];
-        clast[hh] = clast_next[hh];
-        if (c + 1 < nchunks) clast_next[hh] = __ldg(a.ws_cum + vrow0 + ((int64_t)hh * nchunks + c + 1) * kQ + kQ - 1);
-        // exponent (base 2) of the decay from the start of the sequence to the start of this chunk: what a state
-        // that arrives later (phase 2 of a sequence shard) is multiplied by before it joins this chunk's state
-        if (tid == 0) a.ws_state[ssd_summary_floats_padded(a.batch, a.heads) + ((int64_t)b * a.heads + h0 + hh) * nchunks + c] = ctot[hh];
-        ctot[hh] += clast[hh];
-      }
-      if (c == 0) emit_state_in(0);
-    }
+    if (part == 0 && c == 0) emit_state_in(0);
     // ---- one stage into a chunk its predecessor's MMAs have surely finished: fold them, hand out the states
     // ---- before this chunk (its accumulators are the other pair, so the stage already issued is not disturbed)
     if (part == 1 && c >= 1) {
@@ -308,6 +334,17 @@ __global__ void __launch_bounds__(kStateThreads, 1) ssd_state_kernel(const ssm_s
       emit_state_in(c);
     }
     if (!fail) fail = !__all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&mbar_full[s % NS]), (s / NS) & 1));  // this stage's copies
+    if (part == 0) {  // a new chunk begins: its last exponent arrived with the stage
+#pragma unroll
+      for (int hh = 0; hh < HPC; ++hh) {
+        clast_prev[hh] = clast[hh];
+        clast[hh] = sLast[((c % M::NVEC) * HPC + hh) * 4 + 3];
+        // exponent (base 2) of the decay from the start of the sequence to the start of this chunk: what a state
+        // that arrives later (phase 2 of a sequence shard) is multiplied by before it joins this chunk's state
+        if (tid == 0) a.ws_state[ssd_summary_floats_padded(a.batch, a.heads) + ((int64_t)b * a.heads + h0 + hh) * nchunks + c] = ctot[hh];
+        ctot[hh] += clast[hh];
+      }
+    }
 
     // ---- scale the x rows in place: w_j x_j (a row is one step, whatever the swizzle does inside it) ------------
     unsigned char* base = smraw + (s % NS) * M::STAGE;
@@ -959,8 +996,7 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
   }
   const int nparts = a.heads / hpc;
   if (a.phase != 2) {
-    const int warps = a.batch * a.heads * nchunks;
-    ssd_cumsum_kernel<T><<<(warps * 32 + 127) / 128, 128, 0, st>>>(a, nchunks);
+    ssd_cumsum_kernel<T><<<dim3((a.heads + kCumHeads - 1) / kCumHeads, nchunks, a.batch), kQ, 0, st>>>(a, nchunks);
     if (int rc = launch_status("ssd_cumsum_kernel")) return rc;
   }
   if (a.phase != 2) {
