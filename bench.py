@@ -353,7 +353,7 @@ def run_prefill(args):
 
 
 # DRAM bytes per (token, head) of the three state-space-dual kernels, from the ncu capture named in `roofline.traffic`
-TRAFFIC_PER_TOKEN_HEAD = 578.0e6 / (2 * 8192 * 48)
+TRAFFIC_PER_TOKEN_HEAD = 572.3e6 / (2 * 8192 * 48)
 
 
 def bench_ssd_sharded(rank, world, local, dev, total_len=131072, steps=0):
