@@ -109,21 +109,85 @@ struct NormCfg {
   static constexpr int RPC = BLOCK / G;  // rows per CTA pass
 };
 
-// Loads the row into registers as s = x (+ residual when prenorm); returns through refs.
-template <typename T, int G, int MC, bool RES = true>
-__device__ __forceinline__ void norm_load_row(const ssm_norm_args& a, int64_t row, int gt, int nchunk, float (&s)[MC][16 / sizeof(T)],
-                                              float (&r)[MC][16 / sizeof(T)]) {
+// A row's pieces of a tensor of run-time element type, in two steps: every load of the row is issued first (the type switch
+// sits outside the loop over chunks, so each arm is a straight run of independent loads), the conversions come afterwards.
+// With the load, the conversion and the next load of a chunk in one loop body the loads of a row went out one memory
+// latency after the other.  Threads beyond the end of the row read its last chunk (a valid address) and drop the value.
+template <int V, int G, int MC>
+__device__ __forceinline__ void dyn_issue_row(const void* base, int64_t row_off, int gt, int nchunk, int dtype, uint4 (&a)[MC], uint4 (&b)[MC]) {
+  if (dtype == SSM_F32) {
+#pragma unroll
+    for (int c = 0; c < MC; ++c) {
+      const int ch = min(c * G + gt, nchunk - 1);
+      const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(base) + row_off + (int64_t)ch * V);
+      a[c] = __ldcs(p);
+      if constexpr (V == 8) b[c] = __ldcs(p + 1);
+    }
+  } else if constexpr (V == 8) {
+#pragma unroll
+    for (int c = 0; c < MC; ++c) {
+      const int ch = min(c * G + gt, nchunk - 1);
+      a[c] = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + row_off + (int64_t)ch * V));
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < MC; ++c) {
+      const int ch = min(c * G + gt, nchunk - 1);
+      const uint2 t = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + row_off + (int64_t)ch * V));
+      a[c] = make_uint4(t.x, t.y, 0u, 0u);
+    }
+  }
+}
+template <int V>
+__device__ __forceinline__ void dyn_convert(int dtype, const uint4& a, const uint4& b, float (&f)[V]) {
+  if (dtype == SSM_F32) {
+    f[0] = __uint_as_float(a.x), f[1] = __uint_as_float(a.y), f[2] = __uint_as_float(a.z), f[3] = __uint_as_float(a.w);
+    if constexpr (V == 8) f[4] = __uint_as_float(b.x), f[5] = __uint_as_float(b.y), f[6] = __uint_as_float(b.z), f[7] = __uint_as_float(b.w);
+  } else if (dtype == SSM_BF16) {
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&a);
+#pragma unroll
+    for (int k = 0; k < V; ++k) f[k] = __bfloat162float(e[k]);
+  } else {
+    const __half* e = reinterpret_cast<const __half*>(&a);
+#pragma unroll
+    for (int k = 0; k < V; ++k) f[k] = __half2float(e[k]);
+  }
+}
+// the row's pieces of a tensor of the io type
+template <typename T, int G, int MC>
+__device__ __forceinline__ void io_issue_row(const void* base, int64_t row_off, int gt, int nchunk, uint4 (&a)[MC]) {
   constexpr int V = 16 / sizeof(T);
 #pragma unroll
   for (int c = 0; c < MC; ++c) {
-    const int ch = c * G + gt;
-    if (ch < nchunk) {
-      const int64_t off = row * a.hidden + (int64_t)ch * V;
+    const int ch = min(c * G + gt, nchunk - 1);
+    a[c] = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(base) + row_off + (int64_t)ch * V));
+  }
+}
+
+// Raw pieces of a row of x and of the residual, in flight.
+template <int MC>
+struct NormRowRaw {
+  uint4 x[MC], ra[MC], rb[MC];
+};
+template <typename T, int G, int MC, bool RES = true>
+__device__ __forceinline__ void norm_issue_row(const ssm_norm_args& a, int64_t row, int gt, int nchunk, NormRowRaw<MC>& raw) {
+  constexpr int V = 16 / sizeof(T);
+  io_issue_row<T, G, MC>(a.x, row * a.hidden, gt, nchunk, raw.x);
+  if (RES && a.residual) dyn_issue_row<V, G, MC>(a.residual, row * a.hidden, gt, nchunk, a.res_dtype, raw.ra, raw.rb);
+}
+// s = x (+ residual when prenorm), r = residual; zero beyond the end of the row.
+template <typename T, int G, int MC, bool RES = true>
+__device__ __forceinline__ void norm_convert_row(const ssm_norm_args& a, int gt, int nchunk, const NormRowRaw<MC>& raw, float (&s)[MC][16 / sizeof(T)],
+                                                 float (&r)[MC][16 / sizeof(T)]) {
+  constexpr int V = 16 / sizeof(T);
+#pragma unroll
+  for (int c = 0; c < MC; ++c) {
+    if (c * G + gt < nchunk) {
       Vec16<T> v;
-      v.load_stream(reinterpret_cast<const T*>(a.x) + off);
+      v.raw = raw.x[c];
       v.unpack(s[c]);
       if (RES && a.residual) {
-        load_dyn_vec<V>(a.residual, off, a.res_dtype, r[c]);
+        dyn_convert<V>(a.res_dtype, raw.ra[c], raw.rb[c], r[c]);
         if (a.prenorm) {
 #pragma unroll
           for (int i = 0; i < V; ++i) s[c][i] += r[c][i];
@@ -134,6 +198,14 @@ __device__ __forceinline__ void norm_load_row(const ssm_norm_args& a, int64_t ro
       for (int i = 0; i < V; ++i) s[c][i] = 0.f, r[c][i] = 0.f;
     }
   }
+}
+// Loads the row into registers as s = x (+ residual when prenorm); returns through refs.
+template <typename T, int G, int MC, bool RES = true>
+__device__ __forceinline__ void norm_load_row(const ssm_norm_args& a, int64_t row, int gt, int nchunk, float (&s)[MC][16 / sizeof(T)],
+                                              float (&r)[MC][16 / sizeof(T)]) {
+  NormRowRaw<MC> raw;
+  norm_issue_row<T, G, MC, RES>(a, row, gt, nchunk, raw);
+  norm_convert_row<T, G, MC, RES>(a, gt, nchunk, raw, s, r);
 }
 
 template <typename T, int G, int MC>
@@ -220,21 +292,37 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK) norm_fwd_kernel(const ss
 
 // MC = 16-byte chunks of a row per thread.  A row of up to 32 * MC chunks is owned by ONE warp (G = 32): every reduction is
 // a shuffle tree and four rows are in flight per CTA; wider rows take 128 or 512 threads with block-wide reductions.
+// The time of a row is a chain of latencies (loads, two reductions, stores), so what counts is how many loads an SM has in
+// flight: all loads of a row are issued before the first use, and with 128-thread CTAs the running weight / bias gradients
+// of a thread's columns live in shared-memory slots of its own (same additions in the same order) instead of 16 MC registers,
+// which leaves the registers to the loads in flight and lets more CTAs fit.
+template <int G, int MC>
+constexpr int norm_bwd_min_ctas() {
+  return G <= 128 ? (MC <= 2 ? 5 : (MC == 3 ? 3 : 2)) : 1;
+}
 template <typename T, int G, int MC>
-__global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 128 ? (MC <= 2 ? 4 : (MC == 3 ? 3 : 2)) : 1) norm_bwd_kernel(const ssm_norm_bwd_args g) {
+__global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, norm_bwd_min_ctas<G, MC>()) norm_bwd_kernel(const ssm_norm_bwd_args g) {
   using Cfg = NormCfg<T, G>;
   constexpr int V = Cfg::V;
   constexpr int kNormBwdChunks = MC;
+  constexpr bool kSmemAcc = G <= 128;
+  constexpr int kAccRegs = kSmemAcc ? 1 : MC;
+  constexpr int kAccRow = MC * V * G + 1;
   const ssm_norm_args& a = g.fwd;
   __shared__ float scratch[32];
+  __shared__ float acc_all[kSmemAcc ? Cfg::RPC * 2 * kAccRow : 1];  // [row slot][weight | bias][chunk][element][thread]
   const int gt = threadIdx.x % G, slot = threadIdx.x / G;
+  float* acc = acc_all + (kSmemAcc ? slot * 2 * kAccRow : 0);
   const int nchunk = a.hidden / V;
   const float inv = 1.f / (float)a.hidden;
-  float dw[kNormBwdChunks][V], db[kNormBwdChunks][V];
+  float dw[kAccRegs][V], db[kAccRegs][V];
 #pragma unroll
   for (int c = 0; c < kNormBwdChunks; ++c)
 #pragma unroll
-    for (int i = 0; i < V; ++i) dw[c][i] = 0.f, db[c][i] = 0.f;
+    for (int i = 0; i < V; ++i) {
+      if constexpr (kSmemAcc) acc[(c * V + i) * G + gt] = 0.f, acc[kAccRow + (c * V + i) * G + gt] = 0.f;
+      else dw[c][i] = 0.f, db[c][i] = 0.f;
+    }
   // the weights of this thread's columns are re-read from L1 for every row (16-byte loads) instead of occupying registers
   auto load_w = [&](int c, float (&wv)[V]) {
     const int ch = c * G + gt;
@@ -249,27 +337,32 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 
     const int64_t row = pass * Cfg::RPC + slot;
     const bool live = row < a.rows;  // G == 32: a dead warp still joins nothing but its own shuffles
     float s[kNormBwdChunks][V], r[kNormBwdChunks][V], dy[kNormBwdChunks][V];
-    if (live) norm_load_row<T, G, kNormBwdChunks>(a, row, gt, nchunk, s, r);
-    else {
+    if (live) {
+      // every load of the row goes out before the first value is used: x, the residual, dy and the gradient arriving through
+      // the x + residual output (which takes the place of the residual values, dead once the row sum is formed)
+      NormRowRaw<kNormBwdChunks> raw;
+      uint4 dyr[kNormBwdChunks], ga[kNormBwdChunks], gb[kNormBwdChunks];
+      norm_issue_row<T, G, kNormBwdChunks>(a, row, gt, nchunk, raw);
+      io_issue_row<T, G, kNormBwdChunks>(g.dy, row * a.hidden, gt, nchunk, dyr);
+      if (g.dresidual_out) dyn_issue_row<V, G, kNormBwdChunks>(g.dresidual_out, row * a.hidden, gt, nchunk, a.resout_dtype, ga, gb);
+      norm_convert_row<T, G, kNormBwdChunks>(a, gt, nchunk, raw, s, r);
+#pragma unroll
+      for (int c = 0; c < kNormBwdChunks; ++c) {
+        if (c * G + gt < nchunk) {
+          Vec16<T> v;
+          v.raw = dyr[c];
+          v.unpack(dy[c]);
+          if (g.dresidual_out) dyn_convert<V>(a.resout_dtype, ga[c], gb[c], r[c]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) dy[c][i] = 0.f;
+        }
+      }
+    } else {
 #pragma unroll
       for (int c = 0; c < kNormBwdChunks; ++c)
 #pragma unroll
-        for (int i = 0; i < V; ++i) s[c][i] = 0.f, r[c][i] = 0.f;
-    }
-#pragma unroll
-    for (int c = 0; c < kNormBwdChunks; ++c) {
-      const int ch = c * G + gt;
-      if (live && ch < nchunk) {
-        Vec16<T> v;
-        v.load_stream(reinterpret_cast<const T*>(g.dy) + row * a.hidden + (int64_t)ch * V);
-        v.unpack(dy[c]);
-        // the gradient arriving through the x + residual output travels with the other loads of the row (the residual values in
-        // r[] are dead once the row sum is formed)
-        if (g.dresidual_out) load_dyn_vec<V>(g.dresidual_out, row * a.hidden + (int64_t)ch * V, a.resout_dtype, r[c]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < V; ++i) dy[c][i] = 0.f;
-      }
+        for (int i = 0; i < V; ++i) s[c][i] = 0.f, r[c][i] = 0.f, dy[c][i] = 0.f;
     }
     float mean, rstd;
     norm_stats<T, G, kNormBwdChunks>(a, gt, nchunk, s, scratch, mean, rstd);
@@ -286,8 +379,15 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 
         c1 = fmaf(wdy, xh, c1);
         c2 += wdy;
         if (live && (c * G + gt) < nchunk) {
-          dw[c][i] = fmaf(dy[c][i], xh, dw[c][i]);
-          db[c][i] += dy[c][i];
+          if constexpr (kSmemAcc) {
+            float* pw = acc + (c * V + i) * G + gt;
+            float* pb = acc + kAccRow + (c * V + i) * G + gt;
+            *pw = fmaf(dy[c][i], xh, *pw);
+            *pb += dy[c][i];
+          } else {
+            dw[c][i] = fmaf(dy[c][i], xh, dw[c][i]);
+            db[c][i] += dy[c][i];
+          }
         }
       }
     }
@@ -319,28 +419,7 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 
     }
   }
   // fold the RPC row slots of this CTA, then write the CTA's partial rows
-  if constexpr (Cfg::RPC > 1) {
-    __shared__ float fold[Cfg::RPC][2][kNormBwdChunks * V * G + 1];
-#pragma unroll
-    for (int c = 0; c < kNormBwdChunks; ++c)
-#pragma unroll
-      for (int i = 0; i < V; ++i) {
-        fold[slot][0][(c * V + i) * G + gt] = dw[c][i];
-        fold[slot][1][(c * V + i) * G + gt] = db[c][i];
-      }
-    __syncthreads();
-    if (slot == 0) {
-#pragma unroll
-      for (int c = 0; c < kNormBwdChunks; ++c)
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-          float tw = 0.f, tb = 0.f;
-#pragma unroll
-          for (int q = 0; q < Cfg::RPC; ++q) tw += fold[q][0][(c * V + i) * G + gt], tb += fold[q][1][(c * V + i) * G + gt];
-          dw[c][i] = tw, db[c][i] = tb;
-        }
-    }
-  }
+  if constexpr (Cfg::RPC > 1) __syncthreads();
   if (slot == 0) {
     float* pw = g.partial + (int64_t)blockIdx.x * 2 * a.hidden;
     float* pb = pw + a.hidden;
@@ -349,7 +428,19 @@ __global__ void __launch_bounds__(NormCfg<T, G>::BLOCK, NormCfg<T, G>::BLOCK == 
       const int ch = c * G + gt;
       if (ch < nchunk) {
 #pragma unroll
-        for (int i = 0; i < V; ++i) pw[ch * V + i] = dw[c][i], pb[ch * V + i] = db[c][i];
+        for (int i = 0; i < V; ++i) {
+          if constexpr (kSmemAcc) {
+            float tw = 0.f, tb = 0.f;
+#pragma unroll
+            for (int q = 0; q < Cfg::RPC; ++q) {
+              tw += acc_all[q * 2 * kAccRow + (c * V + i) * G + gt];
+              tb += acc_all[q * 2 * kAccRow + kAccRow + (c * V + i) * G + gt];
+            }
+            pw[ch * V + i] = tw, pb[ch * V + i] = tb;
+          } else {
+            pw[ch * V + i] = dw[c][i], pb[ch * V + i] = db[c][i];
+          }
+        }
       }
     }
   }
@@ -522,6 +613,7 @@ static int norm_bwd_dispatch(const ssm_norm_bwd_args& g, cudaStream_t st, int ma
   if (nchunk <= 96) return norm_bwd_launch<T, 32, 3>(g, st, max_ctas);
   if (nchunk <= 128) return norm_bwd_launch<T, 32, 4>(g, st, max_ctas);
   if (nchunk <= 256) return norm_bwd_launch<T, 128, 2>(g, st, max_ctas);
+  if (nchunk <= 384) return norm_bwd_launch<T, 128, 3>(g, st, max_ctas);  // e.g. 2560 columns of 16 bits: three CTAs per SM, not two
   if (nchunk <= 512) return norm_bwd_launch<T, 128, 4>(g, st, max_ctas);
   return norm_bwd_launch<T, 512, 2>(g, st, max_ctas);
 }
