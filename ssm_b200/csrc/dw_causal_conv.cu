@@ -295,7 +295,7 @@ __device__ __forceinline__ void load_x_cl(const ssm_conv_args& a, const T* __res
 // Eight steps' loads are issued before their results are formed, so every thread keeps eight 16-byte loads in flight; the
 // host picks `tile` so that narrow tensors (the 128-channel B / C inputs of a Mamba-2 layer) still fill the machine.
 template <typename T, int KM>
-__global__ void __launch_bounds__(kConvThreads, 4) conv_cl_fwd_kernel(const ssm_conv_args a, int vec, int tile) {
+__global__ void __launch_bounds__(kConvThreads, 3) conv_cl_fwd_kernel(const ssm_conv_args a, int vec, int tile) {
   constexpr int KH = KM - 1;
   constexpr int V = 16 / sizeof(T);
   constexpr int U = 8;  // steps per batch of loads
@@ -314,19 +314,47 @@ __global__ void __launch_bounds__(kConvThreads, 4) conv_cl_fwd_kernel(const ssm_
   T* __restrict__ y = reinterpret_cast<T*>(a.y) + (int64_t)b * L * C + c0;
   // channel pairs as float2 for the packed-fp32 multiply-adds
   float2 wr[KM][V / 2], bias[V / 2];
+  if (K == KM && nvalid == V && (reinterpret_cast<uintptr_t>(a.weight) & 15) == 0 && (!a.bias || (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0)) {
+    // the thread's V x K weights are one contiguous run: 16-byte loads (a scalar load per weight costs a sector request per lane,
+    // more of them than the whole tile of x)
+    float wf[V * KM];
+    const float4* wp = reinterpret_cast<const float4*>(a.weight + (int64_t)c0 * KM);
 #pragma unroll
-  for (int i = 0; i < V; i += 2) {
-    const int c1 = min(c0 + i, C - 1), c2 = min(c0 + i + 1, C - 1);
-    bias[i / 2] = a.bias ? make_float2(__ldg(a.bias + c1), __ldg(a.bias + c2)) : make_float2(0.f, 0.f);
+    for (int q = 0; q < V * KM / 4; ++q) {
+      const float4 w4 = __ldg(wp + q);
+      wf[4 * q] = w4.x, wf[4 * q + 1] = w4.y, wf[4 * q + 2] = w4.z, wf[4 * q + 3] = w4.w;
+    }
+    float bf[V];
 #pragma unroll
-    for (int m = 0; m < KM; ++m)
-      wr[m][i / 2] = m < K ? make_float2(__ldg(a.weight + (int64_t)c1 * K + (K - 1 - m)), __ldg(a.weight + (int64_t)c2 * K + (K - 1 - m))) : make_float2(0.f, 0.f);
+    for (int q = 0; q < V / 4; ++q) {
+      const float4 b4 = a.bias ? __ldg(reinterpret_cast<const float4*>(a.bias + c0) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+      bf[4 * q] = b4.x, bf[4 * q + 1] = b4.y, bf[4 * q + 2] = b4.z, bf[4 * q + 3] = b4.w;
+    }
+#pragma unroll
+    for (int i = 0; i < V; i += 2) {
+      bias[i / 2] = make_float2(bf[i], bf[i + 1]);
+#pragma unroll
+      for (int m = 0; m < KM; ++m) wr[m][i / 2] = make_float2(wf[i * KM + (KM - 1 - m)], wf[(i + 1) * KM + (KM - 1 - m)]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; i += 2) {
+      const int c1 = min(c0 + i, C - 1), c2 = min(c0 + i + 1, C - 1);
+      bias[i / 2] = a.bias ? make_float2(__ldg(a.bias + c1), __ldg(a.bias + c2)) : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int m = 0; m < KM; ++m)
+        wr[m][i / 2] = m < K ? make_float2(__ldg(a.weight + (int64_t)c1 * K + (K - 1 - m)), __ldg(a.weight + (int64_t)c2 * K + (K - 1 - m))) : make_float2(0.f, 0.f);
+    }
   }
   float2 hist[KH > 0 ? KH : 1][V / 2];  // hist[m] = x[t - 1 - m]
+  // Where the K - 1 steps before the tile lie inside the tensor (every tile but the first of a sequence) and the rows can be
+  // read as 16-byte pieces, they are not fetched here, one dependent load after the other, but run through the pipelined loop
+  // below as steps without output.
+  const bool warm = vec && ts >= K - 1;
 #pragma unroll
   for (int m = 0; m < KH; ++m) {
     float f[V];
-    if (m < K - 1) {
+    if (m < K - 1 && !warm) {
       load_x_cl<T, V>(a, x, b, c0, ts - 1 - m, vec, nvalid, f);
     } else {
 #pragma unroll
@@ -337,6 +365,19 @@ __global__ void __launch_bounds__(kConvThreads, 4) conv_cl_fwd_kernel(const ssm_
   }
   // one step: inputs f of step tt -> output row, then the window moves on
   auto step = [&](int tt, const float (&f)[V]) {
+    if (tt < ts) {  // a step before the tile: it only enters the window
+#pragma unroll
+      for (int m = KH - 1; m >= 1; --m)
+        if (m < K - 1) {
+#pragma unroll
+          for (int i = 0; i < V / 2; ++i) hist[m][i] = hist[m - 1][i];
+        }
+      if (KH > 0) {
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) hist[0][i] = make_float2(f[2 * i], f[2 * i + 1]);
+      }
+      return;
+    }
     float out[V];
     float2 c2[V / 2];
 #pragma unroll
@@ -366,12 +407,19 @@ __global__ void __launch_bounds__(kConvThreads, 4) conv_cl_fwd_kernel(const ssm_
     }
   };
   if (vec) {
-    // the loads of U steps are issued first and stay packed (16 bytes each) until their step is formed
-    for (int t = ts; t < te; t += U) {
-      uint4 raw[U];
+    // The loads of U steps are issued together and stay packed (16 bytes each) until their step is formed; the loads of the
+    // next U steps go out before the current ones are used, so a thread always has loads in flight.
+    uint4 raw[U], nxt[U];
+    const int tb = warm ? ts - (K - 1) : ts;
+#pragma unroll
+    for (int j = 0; j < U; ++j)
+      if (tb + j < te) nxt[j] = __ldcs(reinterpret_cast<const uint4*>(x + (int64_t)(tb + j) * C));
+    for (int t = tb; t < te; t += U) {
+#pragma unroll
+      for (int j = 0; j < U; ++j) raw[j] = nxt[j];
 #pragma unroll
       for (int j = 0; j < U; ++j)
-        if (t + j < te) raw[j] = __ldcs(reinterpret_cast<const uint4*>(x + (int64_t)(t + j) * C));
+        if (t + U + j < te) nxt[j] = __ldcs(reinterpret_cast<const uint4*>(x + (int64_t)(t + U + j) * C));
 #pragma unroll
       for (int j = 0; j < U; ++j) {
         if (t + j < te) {
@@ -545,7 +593,7 @@ static int64_t conv_cl_fwd_ctas(const ssm_conv_args& a, int V, int tile) {
 }
 static int conv_cl_fwd_tile(const ssm_conv_args& a, int V) {
   int tile = kConvTimeTile;
-  while (tile > 8 && conv_cl_fwd_ctas(a, V, tile) * a.batch < 8 * 4 * 148) tile >>= 1;
+  while (tile > 8 && conv_cl_fwd_ctas(a, V, tile) * a.batch < 4 * 3 * 148) tile >>= 1;  // four waves of three CTAs per SM
   while (conv_cl_fwd_ctas(a, V, tile) >= (1ll << 31)) tile <<= 1;
   return tile;
 }
