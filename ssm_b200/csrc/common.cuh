@@ -163,6 +163,14 @@ __device__ __forceinline__ float silu_half_io(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
   return fmaf(h, t, h);
 }
+// d/dx silu for gradients that are rounded to 16 bits: sigmoid(x) = 0.5 + 0.5 tanh(x / 2) on the hardware tanh (one
+// special-function instruction instead of two)
+__device__ __forceinline__ float silu_grad_half_io(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  const float s = fmaf(0.5f, t, 0.5f);
+  return fmaf(x * s, 1.f - s, s);
+}
 __device__ __forceinline__ float silu_grad_fast(float x) {
   const float s = sigmoid_fast(x);
   return s * (1.f + x * (1.f - s));

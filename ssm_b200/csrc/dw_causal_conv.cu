@@ -45,27 +45,49 @@ __global__ void __launch_bounds__(kConvThreads) conv_cf_fwd_kernel(const ssm_con
   const float bias = a.bias ? __ldg(a.bias + c) : 0.f;
 
   if (vec) {
+    // A thread takes UB vectors of 16 bytes per pass and issues their loads, and those of the vectors before them (the K - 1
+    // earlier inputs: the neighbouring thread's vector, served by the L1), before the first value is used.  Vectors beyond the
+    // end of the row are read at the last valid address and dropped.
+    constexpr int UB = 4;
     const int nch = L / V;
-    for (int ch = threadIdx.x; ch < nch; ch += kConvThreads) {
-      const int t0 = ch * V;
-      Vec16<T> v;
-      v.load_stream(x + t0);
-      float cur[V], hist[KH];  // hist[m] = x[t0 - 1 - m]
-      v.unpack(cur);
+    for (int base = threadIdx.x; base < nch; base += kConvThreads * UB) {
+      uint4 curr[UB], prvr[UB];
 #pragma unroll
-      for (int m = 0; m < KH; ++m) hist[m] = m < K - 1 ? conv_x_at<T>(x, halo, K, t0 - 1 - m, L) : 0.f;
-      float out[V];
-#pragma unroll
-      for (int i = 0; i < V; ++i) {
-        float acc = bias;
-#pragma unroll
-        for (int m = 0; m < KM; ++m) {
-          if (m < K) acc = fmaf(wr[m], (i - m >= 0) ? cur[(i - m >= 0) ? i - m : 0] : hist[(m - i - 1 >= 0) ? m - i - 1 : 0], acc);
-        }
-        out[i] = a.silu ? silu_fast(acc) : acc;
+      for (int j = 0; j < UB; ++j) {
+        const int ch = min(base + j * kConvThreads, nch - 1);
+        curr[j] = __ldcs(reinterpret_cast<const uint4*>(x + (int64_t)ch * V));
+        prvr[j] = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)max(ch - 1, 0) * V));
       }
-      v.pack(out);
-      v.store_stream(y + t0);
+#pragma unroll
+      for (int j = 0; j < UB; ++j) {
+        const int ch = base + j * kConvThreads;
+        if (ch >= nch) break;
+        const int t0 = ch * V;
+        Vec16<T> v;
+        float cur[V], prv[V], hist[KH > 0 ? KH : 1];  // hist[m] = x[t0 - 1 - m]
+        v.raw = curr[j];
+        v.unpack(cur);
+        v.raw = prvr[j];
+        v.unpack(prv);
+#pragma unroll
+        for (int m = 0; m < KH; ++m) {
+          float hv = 0.f;
+          if (m < K - 1) hv = (ch > 0 && m < V) ? prv[m < V ? V - 1 - m : 0] : conv_x_at<T>(x, halo, K, t0 - 1 - m, L);
+          hist[m] = hv;
+        }
+        float out[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          float acc = bias;
+#pragma unroll
+          for (int m = 0; m < KM; ++m) {
+            if (m < K) acc = fmaf(wr[m], (i - m >= 0) ? cur[(i - m >= 0) ? i - m : 0] : hist[(m - i - 1 >= 0) ? m - i - 1 : 0], acc);
+          }
+          out[i] = a.silu ? (sizeof(T) == 2 ? silu_half_io(acc) : silu_fast(acc)) : acc;
+        }
+        v.pack(out);
+        v.store_stream(y + t0);
+      }
     }
   } else {
     for (int t = threadIdx.x; t < L; t += kConvThreads) {
@@ -105,14 +127,21 @@ __global__ void __launch_bounds__(kConvThreads) conv_cf_bwd_kernel(const ssm_con
     // vectors of x (both sides) and dy (later side) through L1.
     constexpr int V = 16 / sizeof(T);
     constexpr int NB = (KH + V - 1) / V;  // neighbour vectors per side
+    const int last = L - V;  // start of the row's last vector: what out-of-range neighbours read (and drop)
     for (int t0 = threadIdx.x * V; t0 < L; t0 += kConvThreads * V) {
+      // every load of the pass is issued before the first value is used
+      uint4 xr[2 * NB + 1], dyr[NB + 1];
+#pragma unroll
+      for (int j = 0; j <= 2 * NB; ++j) xr[j] = __ldg(reinterpret_cast<const uint4*>(x + min(max(t0 + (j - NB) * V, 0), last)));
+#pragma unroll
+      for (int j = 0; j <= NB; ++j) dyr[j] = __ldg(reinterpret_cast<const uint4*>(dy + min(t0 + j * V, last)));
       float xa[(2 * NB + 1) * V];  // xa[q] = x[t0 - NB * V + q]
 #pragma unroll
       for (int j = 0; j <= 2 * NB; ++j) {
         const int tv = t0 + (j - NB) * V;
         if (tv >= 0 && tv < L) {
           Vec16<T> v;
-          v.load(x + tv);
+          v.raw = xr[j];
           float f[V];
           v.unpack(f);
 #pragma unroll
@@ -129,7 +158,7 @@ __global__ void __launch_bounds__(kConvThreads) conv_cf_bwd_kernel(const ssm_con
         float f[V];
         if (tv < L) {
           Vec16<T> v;
-          v.load(dy + tv);
+          v.raw = dyr[j];
           v.unpack(f);
         } else {
 #pragma unroll
@@ -146,7 +175,7 @@ __global__ void __launch_bounds__(kConvThreads) conv_cf_bwd_kernel(const ssm_con
         for (int m = 0; m < KM; ++m)
           if (m < K) pre = fmaf(wr[m], xa[NB * V + i - m], pre);
         float v = dya[i];
-        if (a.silu) v *= silu_grad_fast(pre);
+        if (a.silu) v *= sizeof(T) == 2 ? silu_grad_half_io(pre) : silu_grad_fast(pre);
         dp[i] = (i < V + K - 1) ? v : 0.f;
       }
       float out[V];
@@ -501,7 +530,7 @@ __global__ void __launch_bounds__(kConvThreads) conv_cl_bwd_kernel(const ssm_con
 #pragma unroll
       for (int m = 1; m < KM; ++m)
         if (m < K) pre = fmaf(wr[m][i], xh[m - 1][i], pre);
-      dp[i] = s < L ? (a.silu ? dyv[i] * silu_grad_fast(pre) : dyv[i]) : 0.f;
+      dp[i] = s < L ? (a.silu ? dyv[i] * (sizeof(T) == 2 ? silu_grad_half_io(pre) : silu_grad_fast(pre)) : dyv[i]) : 0.f;
       if (s < te) {  // each position's parameter gradient is counted by the tile that owns it
         db[i] += dp[i];
         dwr[0][i] = fmaf(dp[i], cur[i], dwr[0][i]);
