@@ -401,6 +401,9 @@ int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* args, ssm_stream_t s
  * bc_width: stored width of the rows of Bm and Cm.  0 or nstate: (batch, len, groups, nstate).  64: (batch, len, groups, 64),
  * read as nstate-wide rows whose upper part is zero (the tensor-map copies fill what lies outside the tensor with
  * zeros) -- how the backward pass feeds x and dy in the places of B and C.
+ * x_heads: 0, or the number of distinct input heads: X is then (batch, len, x_heads, headdim) and head h reads input head
+ * h % x_heads (heads % x_heads == 0) -- how the backward pass feeds the two halves of a single group's B (or C) row to every
+ * head without writing them out per head.  dt, z, Y and the states keep `heads` heads.
  * ------------------------------------------------------------------------------------- */
 typedef struct {
   int32_t batch, len, heads, headdim;
@@ -425,7 +428,7 @@ typedef struct {
   float* row_dots; /* nullable */
   const float* row_scale; /* nullable */
   int32_t bc_width;       /* 0 (= nstate) or 64 */
-  int32_t reserved2;
+  int32_t x_heads;        /* 0 (= heads) or a divisor of heads */
   float* ws_state_in_f32; /* nullable */
 } ssm_ssd_args;
 

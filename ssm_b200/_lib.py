@@ -129,7 +129,7 @@ class SsdArgs(C.Structure):
         ("X", vp), ("dt", vp), ("A", fp), ("Bm", vp), ("Cm", vp), ("D", fp), ("z", vp), ("dt_bias", fp),
         ("initial_states", fp), ("Y", vp), ("final_states", fp),
         ("ws_dt", fp), ("ws_cum", fp), ("ws_state", fp), ("ws_state_in", vp), ("status", vp),
-        ("row_dots", fp), ("row_scale", fp), ("bc_width", i32), ("reserved2", i32),
+        ("row_dots", fp), ("row_scale", fp), ("bc_width", i32), ("x_heads", i32),
         ("ws_state_in_f32", fp),
     ]
 

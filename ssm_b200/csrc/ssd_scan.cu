@@ -220,7 +220,8 @@ __global__ void __launch_bounds__(kStateThreads, 1) ssd_state_kernel(const ssm_s
     tc::tma_load_4d(base, &maps.b, full, 0, g, s * kStep, b);
     tc::tma_load_4d(base + M::BLK_BYTES, &maps.b, full, 64, g, s * kStep, b);
 #pragma unroll
-    for (int hh = 0; hh < HPC; ++hh) tc::tma_load_4d(base + M::A_BYTES + hh * M::BLK_BYTES, &maps.x, full, 0, h0 + hh, s * kStep, b);
+    for (int hh = 0; hh < HPC; ++hh)
+      tc::tma_load_4d(base + M::A_BYTES + hh * M::BLK_BYTES, &maps.x, full, 0, a.x_heads ? (h0 + hh) % a.x_heads : h0 + hh, s * kStep, b);
     if (first) {
       const int c = s / SPC;
 #pragma unroll
@@ -542,7 +543,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   auto prefetch = [&](int h, int buf) {
     const uint32_t full = mb_full(buf);
     tc::mbar_expect_tx(full, kOperandBytes);
-    tc::tma_load_4d(tc::smem_u32(sX + buf * M::X_BYTES), mapx, full, 0, h, t0, b);
+    tc::tma_load_4d(tc::smem_u32(sX + buf * M::X_BYTES), mapx, full, 0, a.x_heads ? h % a.x_heads : h, t0, b);
     const T* ss = reinterpret_cast<const T*>(a.ws_state_in) + (((int64_t)b * nchunks + c) * a.heads + h) * (int64_t)(kP * kN);
     tc::bulk_load(tc::smem_u32(sS + buf * M::S_BYTES), ss, M::S_BYTES, full);
     const int64_t voff = (((int64_t)b * a.heads + h) * nchunks + c) * kQ;
@@ -732,7 +733,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
         tc::bulk_commit();
       }
       if (hi + 2 < nh) {  // the tiles of the head after next on their way into the L2: one iteration alone does not cover the latency
-        tc::tma_prefetch_4d(mapx, 0, h + 2, t0, b);
+        tc::tma_prefetch_4d(mapx, 0, a.x_heads ? (h + 2) % a.x_heads : h + 2, t0, b);
         if (has_z) tc::tma_prefetch_4d(&maps.z, 0, h + 2, t_blk, b);
         tc::bulk_prefetch(reinterpret_cast<const T*>(a.ws_state_in) + (((int64_t)b * nchunks + c) * a.heads + h + 2) * (int64_t)(kP * kN), M::S_BYTES);
       }
@@ -935,7 +936,7 @@ template <typename T, int HPC>
 static int ssd_state_launch(const ssm_ssd_args& a, int nchunks, cudaStream_t st) {
   StateMaps maps;
   if (int rc = encode_rows_map(&maps.b, a.Bm, a, StateSmem<HPC>::kStep, a.bc_width ? a.bc_width : kN, a.groups)) return rc;
-  if (int rc = encode_rows_map(&maps.x, a.X, a, StateSmem<HPC>::kStep)) return rc;
+  if (int rc = encode_rows_map(&maps.x, a.X, a, StateSmem<HPC>::kStep, kP, a.x_heads ? a.x_heads : a.heads)) return rc;
   const size_t smem = StateSmem<HPC>::ALLOC;
   cudaFuncSetAttribute(ssd_state_kernel<T, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   ssd_state_kernel<T, HPC><<<dim3(a.heads / HPC, a.batch), kStateThreads, smem, st>>>(a, maps, nchunks);
@@ -1024,9 +1025,10 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
   }
   if (a.phase != 1) {
     ScanMaps maps;
-    if (int rc = encode_rows_map(&maps.x0, a.X, a, kBlk)) return rc;
-    if (int rc = encode_rows_map(&maps.x1, a.X, a, kQ)) return rc;
-    if (int rc = encode_rows_map(&maps.z, a.z ? a.z : a.X, a, kBlk)) return rc;
+    const int xh = a.x_heads ? a.x_heads : a.heads;  // input heads stored
+    if (int rc = encode_rows_map(&maps.x0, a.X, a, kBlk, kP, xh)) return rc;
+    if (int rc = encode_rows_map(&maps.x1, a.X, a, kQ, kP, xh)) return rc;
+    if (int rc = encode_rows_map(&maps.z, a.z ? a.z : a.Y, a, kBlk)) return rc;
     if (int rc = encode_rows_map(&maps.y, a.Y, a, kBlk)) return rc;
     // narrower stored rows (bc_width 64): the copies of the upper 64 states start outside the tensor and bring zeros
     const int bcw = a.bc_width ? a.bc_width : kN;
@@ -1097,6 +1099,7 @@ extern "C" int ssm_ssd_fwd(const ssm_ssd_args* a, ssm_stream_t stream) {
   SSM_REQUIRE(a->phase >= 0 && a->phase <= 2, SSM_ERR_SHAPE, "ssd_scan: phase must be 0, 1 or 2");
   SSM_REQUIRE(a->dt_mode >= 0 && a->dt_mode <= 3 && a->dt_mode != 2, SSM_ERR_SHAPE, "ssd_scan: dt_mode must be 0, 1 or 3");
   SSM_REQUIRE(a->bc_width == 0 || a->bc_width == kN || a->bc_width == 64, SSM_ERR_SHAPE, "ssd_scan: bc_width must be 0, 64 or nstate");
+  SSM_REQUIRE(a->x_heads >= 0 && (a->x_heads == 0 || a->heads % a->x_heads == 0), SSM_ERR_SHAPE, "ssd_scan: x_heads must be 0 or divide heads");
   SSM_REQUIRE(a->X && a->dt && a->A && a->Bm && a->Cm && (a->Y || a->phase == 1), SSM_ERR_NULL, "ssd_scan: missing tensor");
   SSM_REQUIRE(a->ws_dt && a->ws_cum && a->ws_state && a->ws_state_in, SSM_ERR_NULL, "ssd_scan: missing scratch");
   SSM_REQUIRE(aligned_to(a->X, 16) && aligned_to(a->Bm, 16) && aligned_to(a->Cm, 16) && (!a->Y || aligned_to(a->Y, 16)) && aligned_to(a->ws_state_in, 16) &&

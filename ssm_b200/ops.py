@@ -1092,8 +1092,12 @@ class _SsdWorkspace:
     """Scratch and bookkeeping of one tensor-core SSD call, kept so that a sequence shard can run
     the state phase, exchange states, and then finish from the same scratch."""
 
-    def __init__(self, X, dt, A, B, C_, D, z, dt_bias, dt_softplus, chunk_size, dt_mode: int = 0, bc_width: int = 0):
+    def __init__(self, X, dt, A, B, C_, D, z, dt_bias, dt_softplus, chunk_size, dt_mode: int = 0, bc_width: int = 0, x_heads: int = 0):
         nb, nl, nh, npj = X.shape
+        # x_heads: X holds only x_heads distinct input heads (head h reads input head h % x_heads); dt has one entry per head
+        self.x_heads = int(x_heads)
+        if x_heads:
+            nh = dt.shape[2]
         # bc_width: B and C are stored bc_width (< d_state) wide and read as d_state-wide rows with zeros above
         self.bc_width = int(bc_width)
         self.shape = (nb, nl, nh, npj, B.shape[2], 2 * B.shape[3] if bc_width else B.shape[3])
@@ -1118,7 +1122,7 @@ class _SsdWorkspace:
         nb, nl, nh, npj, ng, nn = self.shape
         dev = self.X.device
         init32 = _f32(initial_states)
-        Y = torch.empty_like(self.X) if want_y else None
+        Y = torch.empty(nb, nl, nh, npj, dtype=self.io, device=dev) if want_y else None
         final = torch.empty(nb, nh, npj, nn, dtype=torch.float32, device=dev)
         vec = nb * nh * self.nchunks * self.chunk * 4
         fin = int(L.load().ssm_ssd_state_scratch_bytes(nb, nl, nh))
@@ -1135,6 +1139,7 @@ class _SsdWorkspace:
         a.row_dots = _p(row_dots)  # (B, L, H) fp32 zeros: z is then a dot-product partner, not a gate
         a.row_scale = _p(row_scale)  # (B, L, H) fp32 weights of the output rows
         a.bc_width = self.bc_width
+        a.x_heads = self.x_heads
         self.states_f32 = None
         if keep_states_f32:  # (B, nchunks, H, P * N): the state before every chunk, unrounded
             self.states_f32 = torch.empty(nb, self.nchunks, nh, npj * nn, dtype=torch.float32, device=dev)
@@ -1179,11 +1184,11 @@ def ssd_tensor_core_supported(X: Tensor, B: Tensor, chunk_size: int) -> bool:
 
 
 
-def _ssd_dual_run(X, delta, A, B, C_, init, chunk, dt_mode, partner=None, row_scale=None, bc_width=0, keep_states_f32=False):
+def _ssd_dual_run(X, delta, A, B, C_, init, chunk, dt_mode, partner=None, row_scale=None, bc_width=0, keep_states_f32=False, x_heads=0):
     """One pass of the tensor-core kernels on ready-made fp32 step sizes; returns (Y, final_states, workspace, dots).
     With ``partner (B, L, H, P)`` the pass also returns ``dots[b, t, h] = sum_p y[p] partner[p]`` from the fp32 accumulators."""
-    w = _SsdWorkspace(X, delta, A, B, C_, None, partner, None, False, chunk, dt_mode=dt_mode, bc_width=bc_width)
-    dots = None if partner is None else torch.zeros(X.shape[:3], dtype=torch.float32, device=X.device)
+    w = _SsdWorkspace(X, delta, A, B, C_, None, partner, None, False, chunk, dt_mode=dt_mode, bc_width=bc_width, x_heads=x_heads)
+    dots = None if partner is None else torch.zeros(delta.shape[:3], dtype=torch.float32, device=X.device)
     Y, final = w.run(0, init, True, row_dots=dots, row_scale=None if row_scale is None else _c(row_scale.float()),
                      keep_states_f32=keep_states_f32)
     return Y, final, w, dots
@@ -1265,9 +1270,12 @@ def _ssd_backward_dual(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, init, chunk,
     del y_plain, dx_r
 
     # (3) dC and dB: head and state axes exchanged, one group per head, the halves of B (C) as the inputs of two heads
+    # With a single group the halves are not written out per head: the kernels read input head h % 2 (x_heads = 2).
+    xh2 = 2 if (ng == 1 and rep > 1) else 0
+
     def halves(t):  # (B, L, G, N) -> (B, L, 2 H, N / 2): every head gets its group's row, the two halves as two heads
-        if rep == 1:
-            return t.reshape(nb, lp, 2 * nh, nn // 2)
+        if rep == 1 or xh2:
+            return t.reshape(nb, lp, 2 * ng, nn // 2)
         out = torch.empty(nb, lp, 2 * nh, nn // 2, dtype=io, device=dev)
         L.check(lib.ssm_ssd_bwd_spread(_p(t), _p(out), nb * lp, nh, ng, nn * t.element_size(), _stream()))
         return out
@@ -1282,10 +1290,10 @@ def _ssd_backward_dual(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, init, chunk,
         return out
 
     A2 = A32.repeat_interleave(2)
-    yc = _ssd_dual_run(halves(Bp), delta.repeat_interleave(2, 2), A2, Xp, dy, state_t(init), chunk, 1, bc_width=npj)[0]
+    yc = _ssd_dual_run(halves(Bp), delta.repeat_interleave(2, 2), A2, Xp, dy, state_t(init), chunk, 1, bc_width=npj, x_heads=xh2)[0]
     dC = group_sum(yc, None, False, C_)
     del yc
-    yb = _ssd_dual_run(halves(C_r), delta_r.repeat_interleave(2, 2), A2, dy_r, X_r, state_t(g_init), chunk, 3, bc_width=npj)[0]
+    yb = _ssd_dual_run(halves(C_r), delta_r.repeat_interleave(2, 2), A2, dy_r, X_r, state_t(g_init), chunk, 3, bc_width=npj, x_heads=xh2)[0]
     dB = group_sum(yb, delta, True, B)
     del yb
     # (4) decay exponent: chunk-local running sums started from <adjoint state, state> at the chunk boundaries
