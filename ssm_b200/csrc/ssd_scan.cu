@@ -403,9 +403,11 @@ __global__ void __launch_bounds__(kStateThreads, 1) ssd_state_kernel(const ssm_s
 // formed from a zero state.  By linearity  state_before_chunk_c += exp2(sum_{c' < c} c_last[c']) * S0
 // and  final += exp2(sum_c c_last[c]) * S0.  One thread per element, operand order of the scan kernel.
 // ---------------------------------------------------------------------------------------------
+constexpr int kFoldChunks = 8;  // chunks per thread: the eight values of S0 are read once for them, their loads go out together
 template <typename T>
 __global__ void __launch_bounds__(256) ssd_fold_init_kernel(const ssm_ssd_args a, int nchunks) {
-  // thread = one 16-byte unit (p / 8, n) of the state before one chunk; blockIdx.y = 0 .. nchunks (the last row: final states)
+  // thread = one 16-byte unit (p / 8, n) of the states before kFoldChunks chunks; blockIdx.y = group of chunks (the row after
+  // the last chunk: final states)
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;  // unit of one (batch, head): 1024 units each
   const int64_t units = (int64_t)a.batch * a.heads * (kP * kN / 8);
   if (i >= units) return;
@@ -413,26 +415,42 @@ __global__ void __launch_bounds__(256) ssd_fold_init_kernel(const ssm_ssd_args a
   const int u = (int)(i % (kP * kN / 8));
   const int n = u % kN, pc = u / kN;
   const int b = (int)(bh / a.heads), h = (int)(bh % a.heads);
-  const int c = blockIdx.y;
-  const float* s0 = a.initial_states + bh * (int64_t)(kP * kN) + (int64_t)(pc * 8) * kN + n;  // 8 values p = 8 pc .. 8 pc + 7 of state n
+  const int c0 = blockIdx.y * kFoldChunks;
+  const float* s0p = a.initial_states + bh * (int64_t)(kP * kN) + (int64_t)(pc * 8) * kN + n;  // 8 values p = 8 pc .. 8 pc + 7 of state n
   const float* pre = a.ws_state + ssd_summary_floats_padded(a.batch, a.heads);
-  if (c < nchunks) {
-    const float w = ex2_approx(__ldg(pre + bh * nchunks + c));
-    T* blk = reinterpret_cast<T*>(a.ws_state_in) + (((int64_t)b * nchunks + c) * a.heads + h) * (int64_t)(kP * kN) + (int64_t)u * 8;
-    Vec16<T> v;
-    v.raw = *reinterpret_cast<const uint4*>(blk);
-    float f[8];
-    v.unpack(f);
+  float s0[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = fmaf(w, __ldg(s0 + (int64_t)e * kN), f[e]);
-    v.pack(f);
-    *reinterpret_cast<uint4*>(blk) = v.raw;
-  } else if (a.final_states) {
-    const float w = __expf(__ldg(a.ws_state + (int64_t)a.batch * a.heads * kP * kN + bh));  // total log-decay of the call
+  for (int e = 0; e < 8; ++e) s0[e] = __ldg(s0p + (int64_t)e * kN);
+  T* blk0 = reinterpret_cast<T*>(a.ws_state_in) + (((int64_t)b * nchunks) * a.heads + h) * (int64_t)(kP * kN) + (int64_t)u * 8;
+  const int64_t cstride = (int64_t)a.heads * (kP * kN);
+  uint4 raw[kFoldChunks];
+  float wl[kFoldChunks];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int64_t off = bh * (int64_t)(kP * kN) + (int64_t)(pc * 8 + e) * kN + n;
-      a.final_states[off] = fmaf(w, __ldg(s0 + (int64_t)e * kN), a.ws_state[off]);
+  for (int k = 0; k < kFoldChunks; ++k) {
+    const int c = min(c0 + k, nchunks - 1);  // beyond the last chunk: a valid address, dropped below
+    raw[k] = *reinterpret_cast<const uint4*>(blk0 + c * cstride);
+    wl[k] = __ldg(pre + bh * nchunks + c);
+  }
+#pragma unroll
+  for (int k = 0; k < kFoldChunks; ++k) {
+    const int c = c0 + k;
+    if (c < nchunks) {
+      const float w = ex2_approx(wl[k]);
+      Vec16<T> v;
+      v.raw = raw[k];
+      float f[8];
+      v.unpack(f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = fmaf(w, s0[e], f[e]);
+      v.pack(f);
+      *reinterpret_cast<uint4*>(blk0 + c * cstride) = v.raw;
+    } else if (c == nchunks && a.final_states) {
+      const float w = __expf(__ldg(a.ws_state + (int64_t)a.batch * a.heads * kP * kN + bh));  // total log-decay of the call
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int64_t off = bh * (int64_t)(kP * kN) + (int64_t)(pc * 8 + e) * kN + n;
+        a.final_states[off] = fmaf(w, s0[e], a.ws_state[off]);
+      }
     }
   }
 }
@@ -1017,7 +1035,7 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
     if (rc) return rc;
   } else if (a.initial_states) {
     const int64_t units = (int64_t)a.batch * a.heads * (kP * kN / 8);
-    ssd_fold_init_kernel<T><<<dim3((unsigned)((units + 255) / 256), nchunks + 1), 256, 0, st>>>(a, nchunks);
+    ssd_fold_init_kernel<T><<<dim3((unsigned)((units + 255) / 256), (nchunks + 1 + kFoldChunks - 1) / kFoldChunks), 256, 0, st>>>(a, nchunks);
     if (int rc = launch_status("ssd_fold_init_kernel")) return rc;
   } else if (a.final_states) {  // nothing arrives: the final state is the one phase 1 left in the scratch
     const cudaError_t e = cudaMemcpyAsync(a.final_states, a.ws_state, sizeof(float) * (size_t)a.batch * a.heads * kP * kN, cudaMemcpyDeviceToDevice, st);
