@@ -17,6 +17,8 @@
 // Every thread keeps raw pointers that advance by one time stride per step, and the loads of
 // eight steps are issued before the first of them is used, so that enough bytes are in flight.
 // Without scratch memory a single serial pass is used instead.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace ssmb {
@@ -84,12 +86,12 @@ struct Lane {
 // ---------------------------------------------------------------------------------------------
 // mode 0: serial over the whole sequence (no scratch).  mode 1: phase 1 (local state + decay).  mode 3: phase 3.
 template <typename T, typename PT, int MODE>
-__global__ void __launch_bounds__(kChunkThreads) chunk_fwd_kernel(const ssm_chunk_args a, int nchunks) {
+__global__ void __launch_bounds__(kChunkThreads) chunk_fwd_kernel(const ssm_chunk_args a, int nchunks, int chunk_len) {
   Lane<T> ln;
   if (!ln.init(a)) return;
   const int c = MODE == 0 ? 0 : blockIdx.y;
-  const int t0 = MODE == 0 ? 0 : c * a.chunk_size;
-  const int t1 = MODE == 0 ? a.len : min(a.len, t0 + a.chunk_size);
+  const int t0 = MODE == 0 ? 0 : c * chunk_len;
+  const int t1 = MODE == 0 ? a.len : min(a.len, t0 + chunk_len);
   const int te = max(t0, min(t1, ln.valid));
   float* P = a.scratch;                                                             // [batch][nchunks][HP] decay products
   float* S = a.scratch ? a.scratch + (int64_t)a.batch * nchunks * ln.HP : nullptr;  // local end state, then incoming state
@@ -148,6 +150,118 @@ __global__ void __launch_bounds__(kChunkThreads) chunk_fwd_kernel(const ssm_chun
   if (MODE == 0 && a.final_state) a.final_state[(int64_t)ln.b * ln.HP + ln.hp] = s;
 }
 
+// 16-bit rows with the projection axis contiguous and a multiple of 8: a thread takes 8 neighbouring lanes of one head, so every
+// load and store is 16 bytes (a scalar lane moves 2 bytes per instruction and the kernels above are bound by instruction issue,
+// not by bytes), and the loads of kVecUnroll steps go out before the first is used.  MODE 1: local state and decay product of a
+// chunk.  MODE 3: the chunk replayed from its incoming state, Y written.
+constexpr int kVecUnroll = 4;
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kChunkThreads) chunk_fwd_vec_kernel(const ssm_chunk_args a, int nchunks, int chunk_len) {
+  constexpr int V = 8;
+  const int HP = a.heads * a.proj;
+  const int hp = (blockIdx.x * kChunkThreads + threadIdx.x) * V;
+  if (hp >= HP) return;
+  const int h = hp / a.proj, q = hp % a.proj;
+  const int b = blockIdx.z, c = blockIdx.y;
+  const int valid = chunk_valid_len(a, b);
+  const int t0 = c * chunk_len, t1 = min(a.len, t0 + chunk_len);
+  const int n = max(t0, min(t1, valid)) - t0;
+  float Av[V], Dv[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) {
+    Av[e] = bc4_load_f32(a.A, 0, 0, h, q + e) * kLog2e;
+    Dv[e] = (MODE == 3 && a.D.ptr) ? bc4_load_f32(a.D, 0, 0, h, q + e) : 0.f;
+  }
+  float* P = a.scratch;                                            // [batch][nchunks][HP] decay products
+  float* S = a.scratch + (int64_t)a.batch * nchunks * HP;          // local end state, then incoming state
+  const int64_t slot = ((int64_t)b * nchunks + c) * HP + hp;
+  const T* px = reinterpret_cast<const T*>(a.X) + ((int64_t)b * a.len + t0) * HP + hp;
+  const T* pdt = reinterpret_cast<const T*>(a.dt) + ((int64_t)b * a.len + t0) * a.heads + h;
+  const T* pB = reinterpret_cast<const T*>(a.Bm.ptr) + bc4_off(a.Bm, b, t0, h, q);
+  auto unpack8 = [](const uint4& r, float (&f)[V]) {
+    Vec16<T> v;
+    v.raw = r;
+    v.unpack(f);
+  };
+  float s[V];
+  if (MODE == 1) {
+#pragma unroll
+    for (int e = 0; e < V; ++e) s[e] = 0.f;
+    float sumdt = 0.f;
+    for (int k = 0; k < n; k += kVecUnroll) {
+      uint4 xr[kVecUnroll], br[kVecUnroll];
+      float d[kVecUnroll];
+#pragma unroll
+      for (int i = 0; i < kVecUnroll; ++i) {
+        const int kk = min(k + i, n - 1);  // beyond the chunk: a valid address, dropped below
+        xr[i] = __ldg(reinterpret_cast<const uint4*>(px + (int64_t)kk * HP));
+        br[i] = __ldg(reinterpret_cast<const uint4*>(pB + (int64_t)kk * a.Bm.st));
+        d[i] = to_f<T>(__ldg(pdt + (int64_t)kk * a.heads));
+      }
+#pragma unroll
+      for (int i = 0; i < kVecUnroll; ++i) {
+        if (k + i < n) {
+          float x[V], bv[V];
+          unpack8(xr[i], x);
+          unpack8(br[i], bv);
+#pragma unroll
+          for (int e = 0; e < V; ++e) s[e] = fmaf(ex2_approx(d[i] * Av[e]), s[e], d[i] * bv[e] * x[e]);
+          sumdt += d[i];
+        }
+      }
+    }
+    float pr[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) pr[e] = ex2_approx(sumdt * Av[e]);
+    reinterpret_cast<float4*>(P + slot)[0] = make_float4(pr[0], pr[1], pr[2], pr[3]);
+    reinterpret_cast<float4*>(P + slot)[1] = make_float4(pr[4], pr[5], pr[6], pr[7]);
+    reinterpret_cast<float4*>(S + slot)[0] = make_float4(s[0], s[1], s[2], s[3]);
+    reinterpret_cast<float4*>(S + slot)[1] = make_float4(s[4], s[5], s[6], s[7]);
+    return;
+  }
+  const T* pC = reinterpret_cast<const T*>(a.Cm.ptr) + bc4_off(a.Cm, b, t0, h, q);
+  const bool has_z = a.z.ptr != nullptr;
+  const T* pz = has_z ? reinterpret_cast<const T*>(a.z.ptr) + bc4_off(a.z, b, t0, h, q) : nullptr;
+  T* Y = reinterpret_cast<T*>(a.Y) + ((int64_t)b * a.len + t0) * HP + hp;
+  {
+    const float4 s0 = reinterpret_cast<const float4*>(S + slot)[0], s1 = reinterpret_cast<const float4*>(S + slot)[1];
+    s[0] = s0.x, s[1] = s0.y, s[2] = s0.z, s[3] = s0.w, s[4] = s1.x, s[5] = s1.y, s[6] = s1.z, s[7] = s1.w;
+  }
+  for (int k = 0; k < n; k += kVecUnroll) {
+    uint4 xr[kVecUnroll], br[kVecUnroll], cr[kVecUnroll], zr[kVecUnroll];
+    float d[kVecUnroll];
+#pragma unroll
+    for (int i = 0; i < kVecUnroll; ++i) {
+      const int kk = min(k + i, n - 1);
+      xr[i] = __ldg(reinterpret_cast<const uint4*>(px + (int64_t)kk * HP));
+      br[i] = __ldg(reinterpret_cast<const uint4*>(pB + (int64_t)kk * a.Bm.st));
+      cr[i] = __ldg(reinterpret_cast<const uint4*>(pC + (int64_t)kk * a.Cm.st));
+      zr[i] = has_z ? __ldg(reinterpret_cast<const uint4*>(pz + (int64_t)kk * a.z.st)) : make_uint4(0, 0, 0, 0);
+      d[i] = to_f<T>(__ldg(pdt + (int64_t)kk * a.heads));
+    }
+#pragma unroll
+    for (int i = 0; i < kVecUnroll; ++i) {
+      if (k + i < n) {
+        float x[V], bv[V], cv[V], zv[V], y[V];
+        unpack8(xr[i], x);
+        unpack8(br[i], bv);
+        unpack8(cr[i], cv);
+        unpack8(zr[i], zv);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          s[e] = fmaf(ex2_approx(d[i] * Av[e]), s[e], d[i] * bv[e] * x[e]);
+          y[e] = fmaf(Dv[e], x[e], s[e] * cv[e]);
+          if (has_z) y[e] *= silu_fast(zv[e]);
+        }
+        Vec16<T> o;
+        o.pack(y);
+        *reinterpret_cast<uint4*>(Y + (int64_t)(k + i) * HP) = o.raw;
+      }
+    }
+  }
+  for (int t = t0 + n; t < t1; ++t) *reinterpret_cast<uint4*>(Y + (int64_t)(t - t0) * HP) = make_uint4(0, 0, 0, 0);
+}
+
 // phase 2: serial over chunks; S[c] <- state entering chunk c
 __global__ void __launch_bounds__(kChunkThreads) chunk_carry_kernel(const ssm_chunk_args a, int nchunks) {
   const int HP = a.heads * a.proj;
@@ -158,11 +272,22 @@ __global__ void __launch_bounds__(kChunkThreads) chunk_carry_kernel(const ssm_ch
   float* P = a.scratch;
   float* S = a.scratch + (int64_t)a.batch * nchunks * HP;
   float s = a.initial.ptr ? bc4_load_f32(a.initial, b, 0, h, q) : 0.f;
-  for (int c = 0; c < nchunks; ++c) {
-    const int64_t slot = ((int64_t)b * nchunks + c) * HP + hp;
-    const float local = S[slot];
-    S[slot] = s;
-    s = fmaf(P[slot], s, local);
+  // the loads do not depend on the running state: eight chunks' worth go out together, only the multiply-adds are serial
+  constexpr int U = 8;
+  for (int c0 = 0; c0 < nchunks; c0 += U) {
+    float local[U], pr[U];
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      const int64_t slot = ((int64_t)b * nchunks + min(c0 + i, nchunks - 1)) * HP + hp;
+      local[i] = S[slot], pr[i] = P[slot];
+    }
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      if (c0 + i < nchunks) {
+        S[((int64_t)b * nchunks + c0 + i) * HP + hp] = s;
+        s = fmaf(pr[i], s, local[i]);
+      }
+    }
   }
   if (a.final_state) a.final_state[(int64_t)b * HP + hp] = s;
 }
@@ -221,11 +346,21 @@ __global__ void __launch_bounds__(kChunkThreads) chunk_bwd_carry_kernel(const ss
   const float* P = g.scratch;
   float* R = g.scratch + 2 * (int64_t)a.batch * nchunks * HP;
   float carry = 0.f;
-  for (int c = nchunks - 1; c >= 0; --c) {
-    const int64_t slot = ((int64_t)b * nchunks + c) * HP + hp;
-    const float local = R[slot];
-    R[slot] = carry;
-    carry = fmaf(P[slot], carry, local);
+  constexpr int U = 8;  // loads of eight chunks together; only the multiply-adds are serial
+  for (int c0 = nchunks - 1; c0 >= 0; c0 -= U) {
+    float local[U], pr[U];
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      const int64_t slot = ((int64_t)b * nchunks + max(c0 - i, 0)) * HP + hp;
+      local[i] = R[slot], pr[i] = P[slot];
+    }
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      if (c0 - i >= 0) {
+        R[((int64_t)b * nchunks + c0 - i) * HP + hp] = carry;
+        carry = fmaf(pr[i], carry, local[i]);
+      }
+    }
   }
   if (g.dinitial.ptr) {
     const int h = hp / a.proj, q = hp % a.proj;
@@ -361,22 +496,46 @@ static int chunk_validate(const ssm_chunk_args* a) {
   return SSM_OK;
 }
 
+// The recurrence does not depend on where the sequence is cut, so the forward cuts it where it suits the machine: pieces of
+// at most kFwdChunkMax steps (more pieces in flight than the caller's chunk size gives at short sequences).  The scratch size
+// function uses the same length.
+constexpr int kFwdChunkMax = 64;
+static int chunk_fwd_len(int chunk_size) { return chunk_size < kFwdChunkMax ? chunk_size : kFwdChunkMax; }
+
+// 16-byte rows for the vector kernels: the projection axis contiguous and a multiple of 8, every other stride a multiple of 8
+template <typename T>
+static bool chunk_vec_ok(const ssm_chunk_args& a) {
+  if (sizeof(T) != 2 || a.proj % 8 != 0 || a.scratch == nullptr) return false;
+  auto dense8 = [](const ssm_bcast4& p) { return p.sq == 1 && p.sb % 8 == 0 && p.st % 8 == 0 && p.sh % 8 == 0 && aligned_to(p.ptr, 16); };
+  if (!dense8(a.Bm) || !dense8(a.Cm) || (a.z.ptr && !dense8(a.z))) return false;
+  return aligned_to(a.X, 16) && aligned_to(a.Y, 16) && aligned_to(a.scratch, 16);
+}
+
+// chunk_len: steps per piece (the backward passes the caller's chunk size, which its own scratch and history are sized by)
 template <typename T, typename PT>
-static int chunk_fwd_t(const ssm_chunk_args& a, cudaStream_t st, bool through_phase2_only = false) {
+static int chunk_fwd_t(const ssm_chunk_args& a, cudaStream_t st, int chunk_len, bool through_phase2_only = false) {
   const int HP = a.heads * a.proj;
   const unsigned gx = (HP + kChunkThreads - 1) / kChunkThreads;
-  const int nchunks = (a.len + a.chunk_size - 1) / a.chunk_size;
+  const int nchunks = (a.len + chunk_len - 1) / chunk_len;
   if (!a.scratch || nchunks <= 1) {
-    chunk_fwd_kernel<T, PT, 0><<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(a, 1);
+    chunk_fwd_kernel<T, PT, 0><<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(a, 1, chunk_len);
     return launch_status("chunk_fwd_kernel<serial>");
   }
   SSM_REQUIRE(nchunks <= 65535, SSM_ERR_TOO_LARGE, "ssd_chunk_scan: more than 65535 chunks");
-  chunk_fwd_kernel<T, PT, 1><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(a, nchunks);
+  const bool vec = std::is_same<T, PT>::value && chunk_vec_ok<T>(a);
+  const unsigned gv = (HP / 8 + kChunkThreads - 1) / kChunkThreads;
+  if constexpr (sizeof(T) == 2) {
+    if (vec) chunk_fwd_vec_kernel<T, 1><<<dim3(gv, nchunks, a.batch), kChunkThreads, 0, st>>>(a, nchunks, chunk_len);
+  }
+  if (!vec) chunk_fwd_kernel<T, PT, 1><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(a, nchunks, chunk_len);
   if (int rc = launch_status("chunk_fwd_kernel<local>")) return rc;
   chunk_carry_kernel<<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(a, nchunks);
   if (int rc = launch_status("chunk_carry_kernel")) return rc;
   if (through_phase2_only) return SSM_OK;
-  chunk_fwd_kernel<T, PT, 3><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(a, nchunks);
+  if constexpr (sizeof(T) == 2) {
+    if (vec) chunk_fwd_vec_kernel<T, 3><<<dim3(gv, nchunks, a.batch), kChunkThreads, 0, st>>>(a, nchunks, chunk_len);
+  }
+  if (!vec) chunk_fwd_kernel<T, PT, 3><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(a, nchunks, chunk_len);
   return launch_status("chunk_fwd_kernel<apply>");
 }
 
@@ -393,7 +552,7 @@ static int chunk_bwd_t(const ssm_chunk_bwd_args& g, cudaStream_t st) {
   // states entering every chunk (forward phases 1 and 2 on the backward call's scratch; no final state, no Y)
   ssm_chunk_args f = a;
   f.scratch = g.scratch, f.final_state = nullptr;
-  if (int rc = chunk_fwd_t<T, PT>(f, st, true)) return rc;
+  if (int rc = chunk_fwd_t<T, PT>(f, st, a.chunk_size, true)) return rc;
   chunk_bwd_local_kernel<T, PT><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
   if (int rc = launch_status("chunk_bwd_local_kernel")) return rc;
   chunk_bwd_carry_kernel<<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
@@ -408,7 +567,8 @@ using namespace ssmb;
 
 extern "C" int64_t ssm_chunk_scan_scratch_floats(int32_t batch, int32_t len, int32_t heads, int32_t proj, int32_t chunk_size) {
   if (chunk_size < 1) return 0;
-  const int64_t nchunks = (len + (int64_t)chunk_size - 1) / chunk_size;
+  const int64_t piece = chunk_fwd_len(chunk_size);
+  const int64_t nchunks = (len + piece - 1) / piece;
   return 2 * (int64_t)batch * nchunks * heads * proj;
 }
 
@@ -432,10 +592,11 @@ extern "C" int ssm_chunk_scan_fwd(const ssm_chunk_args* a, ssm_stream_t stream) 
               "ssd_chunk_scan: B, C and z must have the element type of X, or float32");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool same = a->par_dtype == a->io_dtype;
+  const int cl = chunk_fwd_len(a->chunk_size);
   switch (a->io_dtype) {
-    case SSM_F32: return chunk_fwd_t<float, float>(*a, st);
-    case SSM_BF16: return same ? chunk_fwd_t<__nv_bfloat16, __nv_bfloat16>(*a, st) : chunk_fwd_t<__nv_bfloat16, float>(*a, st);
-    default: return same ? chunk_fwd_t<__half, __half>(*a, st) : chunk_fwd_t<__half, float>(*a, st);
+    case SSM_F32: return chunk_fwd_t<float, float>(*a, st, cl);
+    case SSM_BF16: return same ? chunk_fwd_t<__nv_bfloat16, __nv_bfloat16>(*a, st, cl) : chunk_fwd_t<__nv_bfloat16, float>(*a, st, cl);
+    default: return same ? chunk_fwd_t<__half, __half>(*a, st, cl) : chunk_fwd_t<__half, float>(*a, st, cl);
   }
 }
 
