@@ -208,7 +208,7 @@ typedef struct {
 
 typedef struct {
   int32_t batch, len, heads, proj;
-  int32_t io_dtype, par_dtype, reserved0, reserved1;
+  int32_t io_dtype, par_dtype, reserved0, typed_grads; /* typed_grads: backward only, see ssm_chunk_bwd_args */
   const void* X;
   const void* dt;
   ssm_bcast4 A, Bm, Cm, D, z, initial; /* D, z, initial: ptr may be NULL */
@@ -225,7 +225,10 @@ int ssm_chunk_scan_fwd(const ssm_chunk_args* args, ssm_stream_t stream);
 /* Backward.  Replaces ssd_chunk_scan_backward_cuda (src/ssm/ops/cuda/ssd_chunk_scan.cu:341-635).
  * dY io_dtype.  dX (io_dtype), ddt fp32 (batch, len, heads), and fp32 gradient buffers
  * dA/dB/dC/dD/dz/dinitial addressed with the strides given here (broadcast axes = stride 0),
- * accumulated into (caller zero-fills).  history: scratch (batch, len, heads, proj) fp32. */
+ * accumulated into (caller zero-fills).  history: scratch (batch, len, heads, proj) fp32.
+ * fwd.typed_grads, bits 0 / 1 / 2: dB / dC / dz is instead a buffer of par_dtype elements with no broadcast axis (every
+ * (b, t, h, q) a distinct element) that the call WRITES, every element of it, zeros beyond a row's length included: no zero-fill
+ * by the caller, no fp32 copy to convert afterwards. */
 typedef struct {
   ssm_chunk_args fwd;
   const void* dY;

@@ -69,7 +69,7 @@ class Bcast4(C.Structure):
 class ChunkArgs(C.Structure):
     _fields_ = [
         ("batch", i32), ("len", i32), ("heads", i32), ("proj", i32),
-        ("io_dtype", i32), ("par_dtype", i32), ("reserved0", i32), ("reserved1", i32),
+        ("io_dtype", i32), ("par_dtype", i32), ("reserved0", i32), ("typed_grads", i32),
         ("X", vp), ("dt", vp),
         ("A", Bcast4), ("Bm", Bcast4), ("Cm", Bcast4), ("D", Bcast4), ("z", Bcast4), ("initial", Bcast4),
         ("seq_lens", vp), ("Y", vp), ("final_state", fp), ("scratch", fp),

@@ -428,7 +428,19 @@ __global__ void __launch_bounds__(kChunkThreads) chunk_bwd_kernel(const ssm_chun
       hist[(int64_t)k * ln.HP] = s;
     }
   }
-  for (int t = te; t < t1; ++t) dX[(int64_t)(t - t0) * ln.HP] = from_f<T>(0.f);
+  // typed gradient buffers (a.typed_grads) are written in full, the rows beyond the sequence as zeros
+  const bool typed_b = a.typed_grads & 1, typed_c = a.typed_grads & 2, typed_z = has_z && (a.typed_grads & 4);
+  auto put = [&](const ssm_bcast4& p, bool typed, int t, float v) {
+    const int64_t off = bc4_off(p, ln.b, t, ln.h, ln.q);
+    if (typed) const_cast<PT*>(reinterpret_cast<const PT*>(p.ptr))[off] = from_f<PT>(v);
+    else const_cast<float*>(reinterpret_cast<const float*>(p.ptr))[off] = v;
+  };
+  for (int t = te; t < t1; ++t) {
+    dX[(int64_t)(t - t0) * ln.HP] = from_f<T>(0.f);
+    if (typed_b) put(g.dB, true, t, 0.f);
+    if (typed_c) put(g.dC, true, t, 0.f);
+    if (typed_z) put(g.dz, true, t, 0.f);
+  }
 
   // ---- reverse recurrence  g_t = C_t dy_t + exp(dt_{t+1} A) g_{t+1} -------------------------------------------
   const bool dense_b = bc4_dense(g.dB), dense_c = bc4_dense(g.dC), dense_z = has_z && bc4_dense(g.dz);
@@ -442,16 +454,16 @@ __global__ void __launch_bounds__(kChunkThreads) chunk_bwd_kernel(const ssm_chun
       const float sg = sigmoid_fast(zv);
       const float yfull = fmaf(ln.Dv, x, st * cv);
       const float dzv = dout * yfull * sg * (1.f + zv * (1.f - sg));
-      if (dense_z) *bc4_ptr(g.dz, ln.b, t, ln.h, ln.q) = dzv;
+      if (dense_z) put(g.dz, typed_z, t, dzv);
       else if (a.z.sq == 0) add_reduced(bc4_ptr(g.dz, ln.b, t, ln.h, 0), dzv, warp_heads);
       else atomicAdd(bc4_ptr(g.dz, ln.b, t, ln.h, ln.q), dzv);
       dyv = dout * zv * sg;
     }
     const float da = ex2_approx(d * ln.Av);
     const float G = fmaf(cv, dyv, carry);
-    if (dense_c) *bc4_ptr(g.dC, ln.b, t, ln.h, ln.q) = dyv * st;
+    if (dense_c) put(g.dC, typed_c, t, dyv * st);
     else atomicAdd(bc4_ptr(g.dC, ln.b, t, ln.h, ln.q), dyv * st);
-    if (dense_b) *bc4_ptr(g.dB, ln.b, t, ln.h, ln.q) = G * d * x;
+    if (dense_b) put(g.dB, typed_b, t, G * d * x);
     else atomicAdd(bc4_ptr(g.dB, ln.b, t, ln.h, ln.q), G * d * x);
     dX[(int64_t)k * ln.HP] = from_f<T>(fmaf(dyv, ln.Dv, G * d * bv));
     const float gsa = G * sp * da;
@@ -486,6 +498,200 @@ __global__ void __launch_bounds__(kChunkThreads) chunk_bwd_kernel(const ssm_chun
   }
   if (MODE == 0 && g.dinitial.ptr) atomicAdd(bc4_ptr(g.dinitial, ln.b, 0, ln.h, ln.q), carry);
 }
+
+
+// Final backward pass on 16-byte lanes: a thread takes 8 neighbouring projections of one head and one chunk (states and
+// adjoints entering the chunk from the scratch).  Same arithmetic as chunk_bwd_kernel<.., 1>; every stream is read and
+// written as 16-byte pieces, the per-(b, t, h) sum for ddt is formed over the thread's 8 lanes and, where the threads of a
+// head are neighbouring lanes of one warp, over those by shuffles before one atomic add.
+template <typename T>
+__global__ void __launch_bounds__(kChunkThreads) chunk_bwd_vec_kernel(const ssm_chunk_bwd_args g, int nchunks) {
+  constexpr int V = 8, U = 2;
+  const ssm_chunk_args& a = g.fwd;
+  const int HP = a.heads * a.proj;
+  const int hp_raw = (blockIdx.x * kChunkThreads + threadIdx.x) * V;
+  const bool active = hp_raw < HP;
+  const int hp = active ? hp_raw : HP - V;  // idle threads of the last CTA shadow a valid lane group and write nothing
+  const int h = hp / a.proj, q = hp % a.proj;
+  const int b = blockIdx.z, c = blockIdx.y;
+  const int valid = chunk_valid_len(a, b);
+  const int t0 = c * a.chunk_size, t1 = min(a.len, t0 + a.chunk_size);
+  const int n = max(t0, min(t1, valid)) - t0;
+  const int64_t slot = ((int64_t)b * nchunks + c) * HP + hp;
+  float Av[V], Dv[V], s0[V], carry[V];
+  {
+    const float* ps = g.scratch + (int64_t)a.batch * nchunks * HP + slot;
+    const float* pr = g.scratch + 2 * (int64_t)a.batch * nchunks * HP + slot;
+    const float4 a0 = reinterpret_cast<const float4*>(ps)[0], a1 = reinterpret_cast<const float4*>(ps)[1];
+    const float4 r0 = reinterpret_cast<const float4*>(pr)[0], r1 = reinterpret_cast<const float4*>(pr)[1];
+    s0[0] = a0.x, s0[1] = a0.y, s0[2] = a0.z, s0[3] = a0.w, s0[4] = a1.x, s0[5] = a1.y, s0[6] = a1.z, s0[7] = a1.w;
+    carry[0] = r0.x, carry[1] = r0.y, carry[2] = r0.z, carry[3] = r0.w, carry[4] = r1.x, carry[5] = r1.y, carry[6] = r1.z, carry[7] = r1.w;
+  }
+#pragma unroll
+  for (int e = 0; e < V; ++e) {
+    Av[e] = bc4_load_f32(a.A, 0, 0, h, q + e) * kLog2e;
+    Dv[e] = a.D.ptr ? bc4_load_f32(a.D, 0, 0, h, q + e) : 0.f;
+  }
+  const int64_t row0 = ((int64_t)b * a.len + t0) * HP + hp;
+  const T* px = reinterpret_cast<const T*>(a.X) + row0;
+  const T* pdy = reinterpret_cast<const T*>(g.dY) + row0;
+  const T* pdt = reinterpret_cast<const T*>(a.dt) + ((int64_t)b * a.len + t0) * a.heads + h;
+  const T* pB = reinterpret_cast<const T*>(a.Bm.ptr) + bc4_off(a.Bm, b, t0, h, q);
+  const T* pC = reinterpret_cast<const T*>(a.Cm.ptr) + bc4_off(a.Cm, b, t0, h, q);
+  const bool has_z = a.z.ptr != nullptr;
+  const T* pz = has_z ? reinterpret_cast<const T*>(a.z.ptr) + bc4_off(a.z, b, t0, h, q) : nullptr;
+  float* hist = g.history + row0;
+  T* dX = reinterpret_cast<T*>(g.dX) + row0;
+  // element offsets of this thread's first step in the gradient buffers of B, C, z (fp32, or the io type: a.typed_grads)
+  const int64_t oB = bc4_off(g.dB, b, t0, h, q), oC = bc4_off(g.dC, b, t0, h, q), oZ = has_z ? bc4_off(g.dz, b, t0, h, q) : 0;
+  const bool typed_b = a.typed_grads & 1, typed_c = a.typed_grads & 2, typed_z = a.typed_grads & 4;
+  auto unpack8 = [](const uint4& r, float (&f)[V]) {
+    Vec16<T> v;
+    v.raw = r;
+    v.unpack(f);
+  };
+  auto ld8 = [](const float* p, float (&f)[V]) {
+    const float4 u0 = reinterpret_cast<const float4*>(p)[0], u1 = reinterpret_cast<const float4*>(p)[1];
+    f[0] = u0.x, f[1] = u0.y, f[2] = u0.z, f[3] = u0.w, f[4] = u1.x, f[5] = u1.y, f[6] = u1.z, f[7] = u1.w;
+  };
+  auto st8 = [](float* p, const float (&f)[V]) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+  };
+  auto put8 = [&](const ssm_bcast4& p, bool typed, int64_t off, const float (&f)[V]) {
+    if (typed) {
+      Vec16<T> o;
+      o.pack(f);
+      *reinterpret_cast<uint4*>(const_cast<T*>(reinterpret_cast<const T*>(p.ptr)) + off) = o.raw;
+    } else {
+      st8(const_cast<float*>(reinterpret_cast<const float*>(p.ptr)) + off, f);
+    }
+  };
+
+  // ---- states of the chunk, into the history ---------------------------------------------------------------
+  {
+    constexpr int UF = 4;
+    float s[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) s[e] = s0[e];
+    for (int k = 0; k < n; k += UF) {
+      uint4 xr[UF], br[UF];
+      float d[UF];
+#pragma unroll
+      for (int i = 0; i < UF; ++i) {
+        const int kk = min(k + i, n - 1);
+        xr[i] = __ldg(reinterpret_cast<const uint4*>(px + (int64_t)kk * HP));
+        br[i] = __ldg(reinterpret_cast<const uint4*>(pB + (int64_t)kk * a.Bm.st));
+        d[i] = to_f<T>(__ldg(pdt + (int64_t)kk * a.heads));
+      }
+#pragma unroll
+      for (int i = 0; i < UF; ++i) {
+        if (k + i < n) {
+          float x[V], bv[V];
+          unpack8(xr[i], x);
+          unpack8(br[i], bv);
+#pragma unroll
+          for (int e = 0; e < V; ++e) s[e] = fmaf(ex2_approx(d[i] * Av[e]), s[e], d[i] * bv[e] * x[e]);
+          if (active) st8(hist + (int64_t)(k + i) * HP, s);
+        }
+      }
+    }
+  }
+  if (active) {
+    const float zero8[V] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int t = t0 + n; t < t1; ++t) {  // beyond the sequence: zeros in what this call writes in full
+      *reinterpret_cast<uint4*>(dX + (int64_t)(t - t0) * HP) = make_uint4(0, 0, 0, 0);
+      if (typed_b) put8(g.dB, true, oB + (int64_t)(t - t0) * g.dB.st, zero8);
+      if (typed_c) put8(g.dC, true, oC + (int64_t)(t - t0) * g.dC.st, zero8);
+      if (has_z && typed_z) put8(g.dz, true, oZ + (int64_t)(t - t0) * g.dz.st, zero8);
+    }
+  }
+
+  // ---- reverse recurrence  g_t = C_t dy_t + exp(dt_{t+1} A) g_{t+1} -------------------------------------------
+  // threads of one head: proj / 8 neighbouring threads; reduced by shuffles when that is a power of two within a warp
+  const int group = a.proj / V;
+  const bool shuffle_heads = (group & (group - 1)) == 0 && group <= 32;
+  float dA_acc[V], dD_acc = 0.f;
+#pragma unroll
+  for (int e = 0; e < V; ++e) dA_acc[e] = 0.f;
+  for (int k = n; k > 0; k -= U) {
+    uint4 xr[U], br[U], cr[U], zr[U], gr[U];
+    float d[U], st[U + 1][V];
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      const int kk = max(k - 1 - i, 0);
+      xr[i] = __ldg(reinterpret_cast<const uint4*>(px + (int64_t)kk * HP));
+      br[i] = __ldg(reinterpret_cast<const uint4*>(pB + (int64_t)kk * a.Bm.st));
+      cr[i] = __ldg(reinterpret_cast<const uint4*>(pC + (int64_t)kk * a.Cm.st));
+      zr[i] = has_z ? __ldg(reinterpret_cast<const uint4*>(pz + (int64_t)kk * a.z.st)) : make_uint4(0, 0, 0, 0);
+      gr[i] = __ldg(reinterpret_cast<const uint4*>(pdy + (int64_t)kk * HP));
+      d[i] = to_f<T>(__ldg(pdt + (int64_t)kk * a.heads));
+    }
+#pragma unroll
+    for (int i = 0; i <= U; ++i) {
+      const int kk = k - 1 - i;  // the state after step kk; before the chunk's first step: the incoming state
+      if (kk >= 0) {
+        ld8(hist + (int64_t)kk * HP, st[i]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) st[i][e] = s0[e];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      const int kk = k - 1 - i;
+      if (kk < 0) break;
+      float x[V], bv[V], cv[V], zv[V], dout[V], dxo[V], dbo[V], dco[V], dzo[V];
+      unpack8(xr[i], x);
+      unpack8(br[i], bv);
+      unpack8(cr[i], cv);
+      unpack8(zr[i], zv);
+      unpack8(gr[i], dout);
+      float ddt_sum = 0.f;
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        float dyv = dout[e];
+        if (has_z) {
+          const float sg = sigmoid_fast(zv[e]);
+          const float yfull = fmaf(Dv[e], x[e], st[i][e] * cv[e]);
+          dzo[e] = dout[e] * yfull * sg * (1.f + zv[e] * (1.f - sg));
+          dyv = dout[e] * zv[e] * sg;
+        }
+        const float da = ex2_approx(d[i] * Av[e]);
+        const float G = fmaf(cv[e], dyv, carry[e]);
+        dco[e] = dyv * st[i][e];
+        dbo[e] = G * d[i] * x[e];
+        dxo[e] = fmaf(dyv, Dv[e], G * d[i] * bv[e]);
+        const float gsa = G * st[i + 1][e] * da;
+        ddt_sum += fmaf(G, bv[e] * x[e], gsa * (Av[e] * kLn2));
+        dA_acc[e] = fmaf(gsa, d[i], dA_acc[e]);
+        dD_acc = fmaf(dyv, x[e], dD_acc);
+        carry[e] = G * da;
+      }
+      if (!active) ddt_sum = 0.f;
+      if (shuffle_heads) {
+        for (int m = 1; m < group; m <<= 1) ddt_sum += __shfl_xor_sync(0xffffffffu, ddt_sum, m);
+        if (active && (threadIdx.x & (group - 1)) == 0) atomicAdd(g.ddt + ((int64_t)b * a.len + t0 + kk) * a.heads + h, ddt_sum);
+      } else if (active) {
+        atomicAdd(g.ddt + ((int64_t)b * a.len + t0 + kk) * a.heads + h, ddt_sum);
+      }
+      if (active) {
+        put8(g.dC, typed_c, oC + (int64_t)kk * g.dC.st, dco);
+        put8(g.dB, typed_b, oB + (int64_t)kk * g.dB.st, dbo);
+        if (has_z) put8(g.dz, typed_z, oZ + (int64_t)kk * g.dz.st, dzo);
+        Vec16<T> o;
+        o.pack(dxo);
+        *reinterpret_cast<uint4*>(dX + (int64_t)kk * HP) = o.raw;
+      }
+    }
+  }
+  if (!active) return;
+#pragma unroll
+  for (int e = 0; e < V; ++e) atomicAdd(bc4_ptr(g.dA, 0, 0, h, q + e), dA_acc[e]);
+  if (g.dD.ptr) atomicAdd(bc4_ptr(g.dD, 0, 0, h, 0), dD_acc);  // one skip weight per head (the launcher checks)
+}
+
+static bool bc4_dense_host(const ssm_bcast4& p) { return p.ptr && p.sb != 0 && p.st != 0 && p.sh != 0 && p.sq != 0; }
 
 static int chunk_validate(const ssm_chunk_args* a) {
   SSM_REQUIRE(a != nullptr, SSM_ERR_NULL, "ssd_chunk_scan: args is NULL");
@@ -557,6 +763,24 @@ static int chunk_bwd_t(const ssm_chunk_bwd_args& g, cudaStream_t st) {
   if (int rc = launch_status("chunk_bwd_local_kernel")) return rc;
   chunk_bwd_carry_kernel<<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
   if (int rc = launch_status("chunk_bwd_carry_kernel")) return rc;
+  if constexpr (sizeof(T) == 2 && std::is_same<T, PT>::value) {
+    // 16-byte lanes: dense 16-bit B, C, z (see chunk_vec_ok), dense fp32 gradient buffers for them with 16-byte rows, and a
+    // skip weight per head (or none), whose gradient is then one sum per thread
+    // (a broadcast axis, stride 0, would make several steps write one element: those buffers keep the atomic path)
+    auto dense4 = [](const ssm_bcast4& p) {  // multiples of 8 elements: 16-byte rows whether the buffer is fp32 or 16-bit
+      return p.ptr && p.sq == 1 && p.sb != 0 && p.st != 0 && p.sh != 0 && p.sb % 8 == 0 && p.st % 8 == 0 && p.sh % 8 == 0 && aligned_to(p.ptr, 16);
+    };
+    ssm_chunk_args f2 = a;
+    f2.scratch = g.scratch;
+    f2.Y = g.dX;  // only its alignment is looked at
+    const bool vec = chunk_vec_ok<T>(f2) && dense4(g.dB) && dense4(g.dC) && (!a.z.ptr || dense4(g.dz)) && (!a.D.ptr || !g.dD.ptr || a.D.sq == 0) &&
+                     aligned_to(g.dY, 16) && aligned_to(g.history, 16) && (a.heads * a.proj) % 8 == 0;
+    if (vec) {
+      const unsigned gv = (a.heads * a.proj / 8 + kChunkThreads - 1) / kChunkThreads;
+      chunk_bwd_vec_kernel<T><<<dim3(gv, nchunks, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
+      return launch_status("chunk_bwd_vec_kernel");
+    }
+  }
   chunk_bwd_kernel<T, PT, 1><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
   return launch_status("chunk_bwd_kernel");
 }
@@ -610,6 +834,9 @@ extern "C" int ssm_chunk_scan_bwd(const ssm_chunk_bwd_args* g, ssm_stream_t stre
   SSM_REQUIRE(g->dY && g->dX && g->ddt && g->dA.ptr && g->dB.ptr && g->dC.ptr && g->history, SSM_ERR_NULL,
               "ssd_chunk_scan_backward: missing gradient buffer");
   SSM_REQUIRE(!a->z.ptr || g->dz.ptr, SSM_ERR_NULL, "ssd_chunk_scan_backward: dz is required when z is given");
+  SSM_REQUIRE((a->typed_grads & ~7) == 0 && (!(a->typed_grads & 1) || bc4_dense_host(g->dB)) && (!(a->typed_grads & 2) || bc4_dense_host(g->dC)) &&
+                  (!(a->typed_grads & 4) || (a->z.ptr && bc4_dense_host(g->dz))),
+              SSM_ERR_SHAPE, "ssd_chunk_scan_backward: a typed gradient buffer must have no broadcast axis");
   SSM_REQUIRE(a->par_dtype == a->io_dtype || a->par_dtype == SSM_F32, SSM_ERR_UNSUPPORTED,
               "ssd_chunk_scan_backward: B, C and z must have the element type of X, or float32");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

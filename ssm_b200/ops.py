@@ -770,10 +770,14 @@ class _ChunkScanFn(torch.autograd.Function):
         zeros = lambda t: None if t is None else torch.zeros(t.shape, dtype=torch.float32, device=dev)  # noqa: E731
         dX = torch.empty_like(cc.X)
         ddt = torch.zeros(nb, nl, nh, dtype=torch.float32, device=dev)
-        dA, dB, dC, dD, dz, dI = zeros(cc.A), zeros(cc.B), zeros(cc.C), zeros(cc.D), zeros(cc.z), zeros(cc.init)
+        # per-token B / C / z: their gradients are written by the kernel in the tensor's own type (no zero-fill, no fp32 copy)
+        typed = [t is not None and k == "blhp" for t, k in ((cc.B, cc.kB), (cc.C, cc.kC), (cc.z, cc.kz))]
+        own = lambda t, ty: torch.empty_like(t) if ty else zeros(t)  # noqa: E731
+        dA, dB, dC, dD, dz, dI = zeros(cc.A), own(cc.B, typed[0]), own(cc.C, typed[1]), zeros(cc.D), own(cc.z, typed[2]), zeros(cc.init)
         hist = torch.empty(nb, max(nl, 1), nh, npj, dtype=torch.float32, device=dev)
         g = L.ChunkBwdArgs()
         cc.fill(g.fwd)
+        g.fwd.typed_grads = sum(1 << i for i, ty in enumerate(typed) if ty)
         gy = _c(gY.to(cc.X.dtype))
         scratch = torch.empty(max(1, int(lib.ssm_chunk_scan_bwd_scratch_floats(nb, nl, nh, npj, cc.chunk))), dtype=torch.float32, device=dev)
         g.dY, g.dX, g.ddt, g.history, g.scratch = _p(gy), _p(dX), _p(ddt), _p(hist), _p(scratch)

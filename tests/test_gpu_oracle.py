@@ -196,6 +196,10 @@ def test_conv_update_matches_full_conv():
 CHUNK_CASES = [
     (2, 100, 3, 16, 32, "blhp", torch.float32, None), (2, 64, 2, 8, 16, "hp", torch.float32, [64, 20]),
     (1, 130, 4, 32, 64, "bhp", torch.float32, None), (2, 96, 2, 64, 32, "blhp", torch.bfloat16, [50, 96]),
+    # 16-bit per-token B / C / z: the 16-byte-lane kernels.  Three threads per head (no shuffle reduction) and ragged lengths;
+    # one piece in the backward but several in the forward; sixteen threads per head and a chunk that ends inside a load batch
+    (2, 150, 5, 24, 48, "blhp", torch.float16, [150, 7]), (1, 77, 3, 8, 200, "blhp", torch.bfloat16, None),
+    (2, 131, 2, 128, 33, "blhp", torch.bfloat16, [131, 65]),
 ]
 
 
