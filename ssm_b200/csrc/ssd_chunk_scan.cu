@@ -336,6 +336,54 @@ __global__ void __launch_bounds__(kChunkThreads) chunk_bwd_local_kernel(const ss
   R[slot] = carry;
 }
 
+// the same on 16-byte lanes (8 neighbouring projections of one head per thread; 16-bit per-token C / z, see chunk_vec_ok)
+template <typename T>
+__global__ void __launch_bounds__(kChunkThreads) chunk_bwd_local_vec_kernel(const ssm_chunk_bwd_args g, int nchunks) {
+  constexpr int V = 8, U = 4;
+  const ssm_chunk_args& a = g.fwd;
+  const int HP = a.heads * a.proj;
+  const int hp = (blockIdx.x * kChunkThreads + threadIdx.x) * V;
+  if (hp >= HP) return;
+  const int h = hp / a.proj, q = hp % a.proj;
+  const int b = blockIdx.z, c = blockIdx.y;
+  const int t0 = c * a.chunk_size, t1 = min(a.len, t0 + a.chunk_size);
+  const int n = max(t0, min(t1, chunk_valid_len(a, b))) - t0;
+  float* R = g.scratch + 2 * (int64_t)a.batch * nchunks * HP + ((int64_t)b * nchunks + c) * HP + hp;
+  float Av[V], carry[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) Av[e] = bc4_load_f32(a.A, 0, 0, h, q + e) * kLog2e, carry[e] = 0.f;
+  const T* pdy = reinterpret_cast<const T*>(g.dY) + ((int64_t)b * a.len + t0) * HP + hp;
+  const T* pdt = reinterpret_cast<const T*>(a.dt) + ((int64_t)b * a.len + t0) * a.heads + h;
+  const T* pC = reinterpret_cast<const T*>(a.Cm.ptr) + bc4_off(a.Cm, b, t0, h, q);
+  const bool has_z = a.z.ptr != nullptr;
+  const T* pz = has_z ? reinterpret_cast<const T*>(a.z.ptr) + bc4_off(a.z, b, t0, h, q) : nullptr;
+  for (int k = n; k > 0; k -= U) {
+    uint4 gr[U], cr[U], zr[U];
+    float d[U];
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      const int kk = max(k - 1 - i, 0);
+      gr[i] = __ldg(reinterpret_cast<const uint4*>(pdy + (int64_t)kk * HP));
+      cr[i] = __ldg(reinterpret_cast<const uint4*>(pC + (int64_t)kk * a.Cm.st));
+      zr[i] = has_z ? __ldg(reinterpret_cast<const uint4*>(pz + (int64_t)kk * a.z.st)) : make_uint4(0, 0, 0, 0);
+      d[i] = to_f<T>(__ldg(pdt + (int64_t)kk * a.heads));
+    }
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      if (k - 1 - i < 0) break;
+      float dout[V], cv[V], zv[V];
+      Vec16<T> v;
+      v.raw = gr[i], v.unpack(dout);
+      v.raw = cr[i], v.unpack(cv);
+      v.raw = zr[i], v.unpack(zv);
+#pragma unroll
+      for (int e = 0; e < V; ++e) carry[e] = ex2_approx(d[i] * Av[e]) * fmaf(cv[e], gated_dy(dout[e], has_z, zv[e]), carry[e]);
+    }
+  }
+  reinterpret_cast<float4*>(R)[0] = make_float4(carry[0], carry[1], carry[2], carry[3]);
+  reinterpret_cast<float4*>(R)[1] = make_float4(carry[4], carry[5], carry[6], carry[7]);
+}
+
 // reverse phase 2: serial over chunks from the right; R[c] <- adjoint entering chunk c from chunk c + 1
 __global__ void __launch_bounds__(kChunkThreads) chunk_bwd_carry_kernel(const ssm_chunk_bwd_args g, int nchunks) {
   const ssm_chunk_args& a = g.fwd;
@@ -706,7 +754,11 @@ static int chunk_validate(const ssm_chunk_args* a) {
 // at most kFwdChunkMax steps (more pieces in flight than the caller's chunk size gives at short sequences).  The scratch size
 // function uses the same length.
 constexpr int kFwdChunkMax = 64;
-static int chunk_fwd_len(int chunk_size) { return chunk_size < kFwdChunkMax ? chunk_size : kFwdChunkMax; }
+static int chunk_fwd_len(int chunk_size, int len) {
+  int piece = chunk_size < kFwdChunkMax ? chunk_size : kFwdChunkMax;
+  while (piece < chunk_size && ((int64_t)len + piece - 1) / piece > 65535) piece *= 2;  // the pieces are a grid axis
+  return piece < chunk_size ? piece : chunk_size;
+}
 
 // 16-byte rows for the vector kernels: the projection axis contiguous and a multiple of 8, every other stride a multiple of 8
 template <typename T>
@@ -745,8 +797,19 @@ static int chunk_fwd_t(const ssm_chunk_args& a, cudaStream_t st, int chunk_len, 
   return launch_status("chunk_fwd_kernel<apply>");
 }
 
+// The backward cuts the sequence into pieces of at most kBwdChunkMax steps, whatever the caller's chunk size: each piece is one
+// serial walk per thread (replay, then the walk back), and short pieces are what puts enough of them in flight.
+constexpr int kBwdChunkMax = 32;
+static int chunk_bwd_len(int chunk_size, int len) {
+  int piece = chunk_size < kBwdChunkMax ? chunk_size : kBwdChunkMax;
+  while (piece < chunk_size && ((int64_t)len + piece - 1) / piece > 65535) piece *= 2;  // the pieces are a grid axis
+  return piece < chunk_size ? piece : chunk_size;
+}
+
 template <typename T, typename PT>
-static int chunk_bwd_t(const ssm_chunk_bwd_args& g, cudaStream_t st) {
+static int chunk_bwd_t(const ssm_chunk_bwd_args& g_in, cudaStream_t st) {
+  ssm_chunk_bwd_args g = g_in;
+  g.fwd.chunk_size = chunk_bwd_len(g_in.fwd.chunk_size, g_in.fwd.len);  // the kernels cut the sequence by this field
   const ssm_chunk_args& a = g.fwd;
   const int HP = a.heads * a.proj;
   const unsigned gx = (HP + kChunkThreads - 1) / kChunkThreads;
@@ -759,7 +822,18 @@ static int chunk_bwd_t(const ssm_chunk_bwd_args& g, cudaStream_t st) {
   ssm_chunk_args f = a;
   f.scratch = g.scratch, f.final_state = nullptr;
   if (int rc = chunk_fwd_t<T, PT>(f, st, a.chunk_size, true)) return rc;
-  chunk_bwd_local_kernel<T, PT><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
+  bool local_vec = false;
+  if constexpr (sizeof(T) == 2 && std::is_same<T, PT>::value) {
+    ssm_chunk_args f2 = a;
+    f2.scratch = g.scratch;
+    f2.Y = g.dX;  // only its alignment is looked at
+    local_vec = chunk_vec_ok<T>(f2) && aligned_to(g.dY, 16);
+    if (local_vec) {
+      const unsigned gv = (HP / 8 + kChunkThreads - 1) / kChunkThreads;
+      chunk_bwd_local_vec_kernel<T><<<dim3(gv, nchunks, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
+    }
+  }
+  if (!local_vec) chunk_bwd_local_kernel<T, PT><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
   if (int rc = launch_status("chunk_bwd_local_kernel")) return rc;
   chunk_bwd_carry_kernel<<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
   if (int rc = launch_status("chunk_bwd_carry_kernel")) return rc;
@@ -791,14 +865,15 @@ using namespace ssmb;
 
 extern "C" int64_t ssm_chunk_scan_scratch_floats(int32_t batch, int32_t len, int32_t heads, int32_t proj, int32_t chunk_size) {
   if (chunk_size < 1) return 0;
-  const int64_t piece = chunk_fwd_len(chunk_size);
+  const int64_t piece = chunk_fwd_len(chunk_size, len);
   const int64_t nchunks = (len + piece - 1) / piece;
   return 2 * (int64_t)batch * nchunks * heads * proj;
 }
 
 extern "C" int64_t ssm_chunk_scan_bwd_scratch_floats(int32_t batch, int32_t len, int32_t heads, int32_t proj, int32_t chunk_size) {
   if (chunk_size < 1) return 0;
-  const int64_t nchunks = (len + (int64_t)chunk_size - 1) / chunk_size;
+  const int64_t piece = chunk_bwd_len(chunk_size, len);
+  const int64_t nchunks = (len + piece - 1) / piece;
   return 3 * (int64_t)batch * nchunks * heads * proj;  // decay products, states entering, adjoints entering every chunk
 }
 
@@ -816,7 +891,7 @@ extern "C" int ssm_chunk_scan_fwd(const ssm_chunk_args* a, ssm_stream_t stream) 
               "ssd_chunk_scan: B, C and z must have the element type of X, or float32");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool same = a->par_dtype == a->io_dtype;
-  const int cl = chunk_fwd_len(a->chunk_size);
+  const int cl = chunk_fwd_len(a->chunk_size, a->len);
   switch (a->io_dtype) {
     case SSM_F32: return chunk_fwd_t<float, float>(*a, st, cl);
     case SSM_BF16: return same ? chunk_fwd_t<__nv_bfloat16, __nv_bfloat16>(*a, st, cl) : chunk_fwd_t<__nv_bfloat16, float>(*a, st, cl);
