@@ -753,7 +753,7 @@ static int chunk_validate(const ssm_chunk_args* a) {
 // The recurrence does not depend on where the sequence is cut, so the forward cuts it where it suits the machine: pieces of
 // at most kFwdChunkMax steps (more pieces in flight than the caller's chunk size gives at short sequences).  The scratch size
 // function uses the same length.
-constexpr int kFwdChunkMax = 64;
+constexpr int kFwdChunkMax = 32;
 static int chunk_fwd_len(int chunk_size, int len) {
   int piece = chunk_size < kFwdChunkMax ? chunk_size : kFwdChunkMax;
   while (piece < chunk_size && ((int64_t)len + piece - 1) / piece > 65535) piece *= 2;  // the pieces are a grid axis
