@@ -588,8 +588,19 @@ def bench_mamba2_layer_ops():
     def add_norm(i):
         return ops.fused_layer_norm(nx[i % 2], w_dm, None, residual=nr[i % 2], is_rms=True, prenorm=True, return_residual=True)
 
+    # backward of the wide conv (what training a Mamba-2 layer adds): forward + backward minus forward
+    cxg = [t.clone().requires_grad_(True) for t in cx]
+    wxg = wx.clone().requires_grad_(True)
+    gyc = [torch.randn(B, Lq, di, **kw).to(bf) for _ in range(2)]
+
+    def conv_x_both(i):
+        y = ops.dw_causal_conv(cxg[i % 2], wxg, None, "silu")
+        return torch.autograd.grad(y, (cxg[i % 2], wxg), gyc[i % 2])
+
     rows = B * Lq
-    return {"conv_cl_5120_ms": graph_time(conv_x), "conv_cl_5120_bytes": 2 * rows * di * 2,
+    t_conv = graph_time(conv_x)
+    return {"conv_cl_5120_ms": t_conv, "conv_cl_5120_bytes": 2 * rows * di * 2,
+            "conv_cl_5120_bwd_ms": graph_time(conv_x_both) - t_conv, "conv_cl_5120_bwd_bytes": 3 * rows * di * 2,
             "conv_cl_128_ms": graph_time(conv_b), "conv_cl_128_bytes": 2 * rows * n * 2,
             "norm_5120_ms": graph_time(norm_wide), "norm_5120_bytes": 2 * rows * di * 2,
             "add_norm_2560_ms": graph_time(add_norm), "add_norm_2560_bytes": rows * dm * (2 + 4 + 2 + 4)}
@@ -776,7 +787,7 @@ def operator_table(args):
     t["c3_ssd_tokens_per_s"] = c3["tokens"] / (c3["ms"] * 1e-3)
     t["c3_ssd_bwd_ms"] = c3["bwd_ms"]
     c5 = bench_mamba2_layer_ops()  # the bandwidth kernels of one layer of the default workload at the 8-rank shard size
-    for tag in ("conv_cl_5120", "conv_cl_128", "norm_5120", "add_norm_2560"):
+    for tag in ("conv_cl_5120", "conv_cl_5120_bwd", "conv_cl_128", "norm_5120", "add_norm_2560"):
         t[f"c5_{tag}_us"], t[f"c5_{tag}_frac"] = c5[tag + "_ms"] * 1e3, frac(c5[tag + "_bytes"], c5[tag + "_ms"])
     c4 = bench_decode()
     t["c4a_step_us"], t["c4a_step_frac"] = c4["state_kernels_us"], frac(c4["state_kernels_bytes"], c4["state_kernels_us"] * 1e-3)

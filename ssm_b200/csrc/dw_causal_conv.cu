@@ -8,6 +8,8 @@
 //
 // Taps are held newest-first: wr[m] = weight[K-1-m] multiplies x[t-m], so that every
 // register-array index below is a compile-time constant for any run-time width K <= 8.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace ssmb {
@@ -488,14 +490,31 @@ __global__ void __launch_bounds__(kConvThreads) conv_cl_bwd_kernel(const ssm_con
   const T* __restrict__ dy = reinterpret_cast<const T*>(g.dy) + (int64_t)b * L * C + c0;
   T* __restrict__ dx = reinterpret_cast<T*>(g.dx) + (int64_t)b * L * C + c0;
   float w[KM][V], wr[KM][V], bias[V];  // w[q] = weight[c][q];  wr[m] = weight[c][K-1-m]
+  if (K == KM && nvalid == V && (reinterpret_cast<uintptr_t>(a.weight) & 15) == 0 && (!a.bias || (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0)) {
+    // the thread's V x K weights are one contiguous run: 16-byte loads instead of a sector request per lane and weight
+    float wf[V * KM];
+    const float4* wp = reinterpret_cast<const float4*>(a.weight + (int64_t)c0 * KM);
 #pragma unroll
-  for (int i = 0; i < V; ++i) {
-    const int cc = min(c0 + i, C - 1);
-    bias[i] = a.bias ? __ldg(a.bias + cc) : 0.f;
+    for (int q = 0; q < V * KM / 4; ++q) {
+      const float4 w4 = __ldg(wp + q);
+      wf[4 * q] = w4.x, wf[4 * q + 1] = w4.y, wf[4 * q + 2] = w4.z, wf[4 * q + 3] = w4.w;
+    }
+    const float4 b4 = a.bias ? __ldg(reinterpret_cast<const float4*>(a.bias + c0)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    bias[0] = b4.x, bias[1] = b4.y, bias[2] = b4.z, bias[3] = b4.w;
 #pragma unroll
-    for (int q = 0; q < KM; ++q) {
-      w[q][i] = q < K ? __ldg(a.weight + (int64_t)cc * K + q) : 0.f;
-      wr[q][i] = q < K ? __ldg(a.weight + (int64_t)cc * K + (K - 1 - q)) : 0.f;
+    for (int i = 0; i < V; ++i)
+#pragma unroll
+      for (int q = 0; q < KM; ++q) w[q][i] = wf[i * KM + q], wr[q][i] = wf[i * KM + (KM - 1 - q)];
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int cc = min(c0 + i, C - 1);
+      bias[i] = a.bias ? __ldg(a.bias + cc) : 0.f;
+#pragma unroll
+      for (int q = 0; q < KM; ++q) {
+        w[q][i] = q < K ? __ldg(a.weight + (int64_t)cc * K + q) : 0.f;
+        wr[q][i] = q < K ? __ldg(a.weight + (int64_t)cc * K + (K - 1 - q)) : 0.f;
+      }
     }
   }
   float dwr[KM][V], db[V];
@@ -506,23 +525,50 @@ __global__ void __launch_bounds__(kConvThreads) conv_cl_bwd_kernel(const ssm_con
     for (int m = 0; m < KM; ++m) dwr[m][i] = 0.f;
   }
   float xh[KH > 0 ? KH : 1][V], dph[KH > 0 ? KH : 1][V];  // xh[m] = x[s-1-m], dph[m] = dpre[s-1-m]
+  // Where the K - 1 steps before the tile lie inside the tensor and the rows can be read as whole pieces, they run through the
+  // batched loop below as steps that only enter the window, instead of being fetched here one dependent load after the other.
+  const bool warm = vec && ts >= K - 1;
 #pragma unroll
   for (int m = 0; m < KH; ++m) {
 #pragma unroll
     for (int i = 0; i < V; ++i) dph[m][i] = 0.f;  // dx[ts..] never needs dpre before ts
-    if (m < K - 1) load_x_cl<T, V>(a, x, b, c0, ts - 1 - m, vec, nvalid, xh[m]);
+    if (m < K - 1 && !warm) load_x_cl<T, V>(a, x, b, c0, ts - 1 - m, vec, nvalid, xh[m]);
     else {
 #pragma unroll
       for (int i = 0; i < V; ++i) xh[m][i] = 0.f;
     }
   }
-  for (int s = ts; s < te + K - 1; ++s) {
-    float cur[V], dyv[V], dp[V];
-    load_x_cl<T, V>(a, x, b, c0, s, vec, nvalid, cur);
-    if (s < L) load_group<T, V>(dy + (int64_t)s * C, vec, nvalid, dyv);
-    else {
+  // the loads of U steps (x and dy, as packed pieces) go out together; steps beyond the sequence read its last row and drop it
+  constexpr int U = 8;
+  using Raw = typename std::conditional<sizeof(T) == 2, uint2, uint4>::type;
+  const int sb = warm ? ts - (K - 1) : ts, se = te + K - 1;
+  for (int s0 = sb; s0 < se; s0 += U) {
+    Raw xr[U], gr[U];
+    if (vec) {
 #pragma unroll
-      for (int i = 0; i < V; ++i) dyv[i] = 0.f;
+      for (int j = 0; j < U; ++j) {
+        const int sc = min(s0 + j, L - 1);
+        xr[j] = __ldcs(reinterpret_cast<const Raw*>(x + (int64_t)sc * C));
+        gr[j] = __ldcs(reinterpret_cast<const Raw*>(dy + (int64_t)sc * C));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+    const int s = s0 + j;
+    if (s >= se) break;
+    float cur[V], dyv[V], dp[V];
+    if (vec) {
+      const T* ex = reinterpret_cast<const T*>(&xr[j]);
+      const T* eg = reinterpret_cast<const T*>(&gr[j]);
+#pragma unroll
+      for (int i = 0; i < V; ++i) cur[i] = s < L ? to_f<T>(ex[i]) : 0.f, dyv[i] = (s < L && s >= ts) ? to_f<T>(eg[i]) : 0.f;
+    } else {
+      load_x_cl<T, V>(a, x, b, c0, s, vec, nvalid, cur);
+      if (s < L) load_group<T, V>(dy + (int64_t)s * C, vec, nvalid, dyv);
+      else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) dyv[i] = 0.f;
+      }
     }
 #pragma unroll
     for (int i = 0; i < V; ++i) {
@@ -531,7 +577,7 @@ __global__ void __launch_bounds__(kConvThreads) conv_cl_bwd_kernel(const ssm_con
       for (int m = 1; m < KM; ++m)
         if (m < K) pre = fmaf(wr[m][i], xh[m - 1][i], pre);
       dp[i] = s < L ? (a.silu ? dyv[i] * (sizeof(T) == 2 ? silu_grad_half_io(pre) : silu_grad_fast(pre)) : dyv[i]) : 0.f;
-      if (s < te) {  // each position's parameter gradient is counted by the tile that owns it
+      if (s >= ts && s < te) {  // each position's parameter gradient is counted by the tile that owns it
         db[i] += dp[i];
         dwr[0][i] = fmaf(dp[i], cur[i], dwr[0][i]);
 #pragma unroll
@@ -561,6 +607,7 @@ __global__ void __launch_bounds__(kConvThreads) conv_cl_bwd_kernel(const ssm_con
     if (KH > 0) {
 #pragma unroll
       for (int i = 0; i < V; ++i) xh[0][i] = cur[i], dph[0][i] = dp[i];
+    }
     }
   }
 #pragma unroll
