@@ -262,34 +262,65 @@ __global__ void __launch_bounds__(kChunkThreads) chunk_fwd_vec_kernel(const ssm_
   for (int t = t0 + n; t < t1; ++t) *reinterpret_cast<uint4*>(Y + (int64_t)(t - t0) * HP) = make_uint4(0, 0, 0, 0);
 }
 
-// phase 2: serial over chunks; S[c] <- state entering chunk c
-__global__ void __launch_bounds__(kChunkThreads) chunk_carry_kernel(const ssm_chunk_args a, int nchunks) {
-  const int HP = a.heads * a.proj;
-  const int hp = blockIdx.x * kChunkThreads + threadIdx.x;
-  if (hp >= HP) return;
-  const int b = blockIdx.z;
-  const int h = hp / a.proj, q = hp % a.proj;
-  float* P = a.scratch;
-  float* S = a.scratch + (int64_t)a.batch * nchunks * HP;
-  float s = a.initial.ptr ? bc4_load_f32(a.initial, b, 0, h, q) : 0.f;
-  // the loads do not depend on the running state: eight chunks' worth go out together, only the multiply-adds are serial
-  constexpr int U = 8;
-  for (int c0 = 0; c0 < nchunks; c0 += U) {
-    float local[U], pr[U];
+// The carry over the pieces: v_{c+1} = P[c] v_c + L[c], and L[c] is replaced by v_c (what enters piece c).  One lane per hp,
+// kCarryGroups threads per lane: each composes kCarryPer consecutive pieces (all their loads in flight at once), the
+// composites of the groups meet in shared memory, and each group then replays its pieces from what enters it; a serial
+// chain of 16 + 4 + 16 multiply-adds per 64 pieces instead of 64 dependent on 64 loads.  REVERSE walks the pieces from the
+// right (the adjoint).  Returns the value that leaves the last piece.
+constexpr int kCarryLanes = 128, kCarryGroups = 4, kCarryPer = 16;
+template <bool REVERSE>
+__device__ __forceinline__ float carry_pieces(const float* __restrict__ P, float* __restrict__ Lc, int nchunks, int64_t stride, float v_in, bool live) {
+  __shared__ float sP[kCarryGroups][kCarryLanes], sS[kCarryGroups][kCarryLanes];
+  const int lane = threadIdx.x % kCarryLanes, grp = threadIdx.x / kCarryLanes;
+  for (int base = 0; base < nchunks; base += kCarryGroups * kCarryPer) {
+    const int r0 = base + grp * kCarryPer;  // position in walking order
+    float local[kCarryPer], pr[kCarryPer];
 #pragma unroll
-    for (int i = 0; i < U; ++i) {
-      const int64_t slot = ((int64_t)b * nchunks + min(c0 + i, nchunks - 1)) * HP + hp;
-      local[i] = S[slot], pr[i] = P[slot];
+    for (int i = 0; i < kCarryPer; ++i) {
+      const int r = min(r0 + i, nchunks - 1);
+      const int64_t at = (int64_t)(REVERSE ? nchunks - 1 - r : r) * stride;
+      local[i] = Lc[at], pr[i] = P[at];
+    }
+    float Pg = 1.f, Sg = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCarryPer; ++i) {
+      if (r0 + i < nchunks) Sg = fmaf(pr[i], Sg, local[i]), Pg *= pr[i];
+    }
+    sP[grp][lane] = Pg, sS[grp][lane] = Sg;
+    __syncthreads();
+    float v = v_in, v_next = v_in;
+#pragma unroll
+    for (int g2 = 0; g2 < kCarryGroups; ++g2) {
+      if (g2 < grp) v = fmaf(sP[g2][lane], v, sS[g2][lane]);
+      v_next = fmaf(sP[g2][lane], v_next, sS[g2][lane]);
     }
 #pragma unroll
-    for (int i = 0; i < U; ++i) {
-      if (c0 + i < nchunks) {
-        S[((int64_t)b * nchunks + c0 + i) * HP + hp] = s;
-        s = fmaf(pr[i], s, local[i]);
+    for (int i = 0; i < kCarryPer; ++i) {
+      const int r = r0 + i;
+      if (r < nchunks) {
+        if (live) Lc[(int64_t)(REVERSE ? nchunks - 1 - r : r) * stride] = v;
+        v = fmaf(pr[i], v, local[i]);
       }
     }
+    v_in = v_next;
+    __syncthreads();
   }
-  if (a.final_state) a.final_state[(int64_t)b * HP + hp] = s;
+  return v_in;
+}
+
+// phase 2: S[c] <- state entering piece c
+__global__ void __launch_bounds__(kCarryLanes * kCarryGroups) chunk_carry_kernel(const ssm_chunk_args a, int nchunks) {
+  const int HP = a.heads * a.proj;
+  const int hp_raw = blockIdx.x * kCarryLanes + threadIdx.x % kCarryLanes;
+  const bool live = hp_raw < HP;
+  const int hp = live ? hp_raw : HP - 1;  // idle lanes of the last CTA shadow a valid lane: they meet the barriers and write nothing
+  const int b = blockIdx.z;
+  const int h = hp / a.proj, q = hp % a.proj;
+  const float* P = a.scratch + (int64_t)b * nchunks * HP + hp;
+  float* S = a.scratch + (int64_t)a.batch * nchunks * HP + (int64_t)b * nchunks * HP + hp;
+  const float s0 = a.initial.ptr ? bc4_load_f32(a.initial, b, 0, h, q) : 0.f;
+  const float s = carry_pieces<false>(P, S, nchunks, HP, s0, live);
+  if (live && threadIdx.x < kCarryLanes && a.final_state) a.final_state[(int64_t)b * HP + hp] = s;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -384,33 +415,18 @@ __global__ void __launch_bounds__(kChunkThreads) chunk_bwd_local_vec_kernel(cons
   reinterpret_cast<float4*>(R)[1] = make_float4(carry[4], carry[5], carry[6], carry[7]);
 }
 
-// reverse phase 2: serial over chunks from the right; R[c] <- adjoint entering chunk c from chunk c + 1
-__global__ void __launch_bounds__(kChunkThreads) chunk_bwd_carry_kernel(const ssm_chunk_bwd_args g, int nchunks) {
+// reverse phase 2: over the pieces from the right; R[c] <- adjoint entering piece c from piece c + 1
+__global__ void __launch_bounds__(kCarryLanes * kCarryGroups) chunk_bwd_carry_kernel(const ssm_chunk_bwd_args g, int nchunks) {
   const ssm_chunk_args& a = g.fwd;
   const int HP = a.heads * a.proj;
-  const int hp = blockIdx.x * kChunkThreads + threadIdx.x;
-  if (hp >= HP) return;
+  const int hp_raw = blockIdx.x * kCarryLanes + threadIdx.x % kCarryLanes;
+  const bool live = hp_raw < HP;
+  const int hp = live ? hp_raw : HP - 1;
   const int b = blockIdx.z;
-  const float* P = g.scratch;
-  float* R = g.scratch + 2 * (int64_t)a.batch * nchunks * HP;
-  float carry = 0.f;
-  constexpr int U = 8;  // loads of eight chunks together; only the multiply-adds are serial
-  for (int c0 = nchunks - 1; c0 >= 0; c0 -= U) {
-    float local[U], pr[U];
-#pragma unroll
-    for (int i = 0; i < U; ++i) {
-      const int64_t slot = ((int64_t)b * nchunks + max(c0 - i, 0)) * HP + hp;
-      local[i] = R[slot], pr[i] = P[slot];
-    }
-#pragma unroll
-    for (int i = 0; i < U; ++i) {
-      if (c0 - i >= 0) {
-        R[((int64_t)b * nchunks + c0 - i) * HP + hp] = carry;
-        carry = fmaf(pr[i], carry, local[i]);
-      }
-    }
-  }
-  if (g.dinitial.ptr) {
+  const float* P = g.scratch + (int64_t)b * nchunks * HP + hp;
+  float* R = g.scratch + 2 * (int64_t)a.batch * nchunks * HP + (int64_t)b * nchunks * HP + hp;
+  const float carry = carry_pieces<true>(P, R, nchunks, HP, 0.f, live);
+  if (live && threadIdx.x < kCarryLanes && g.dinitial.ptr) {
     const int h = hp / a.proj, q = hp % a.proj;
     atomicAdd(bc4_ptr(g.dinitial, b, 0, h, q), carry);
   }
@@ -787,7 +803,7 @@ static int chunk_fwd_t(const ssm_chunk_args& a, cudaStream_t st, int chunk_len, 
   }
   if (!vec) chunk_fwd_kernel<T, PT, 1><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(a, nchunks, chunk_len);
   if (int rc = launch_status("chunk_fwd_kernel<local>")) return rc;
-  chunk_carry_kernel<<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(a, nchunks);
+  chunk_carry_kernel<<<dim3((HP + kCarryLanes - 1) / kCarryLanes, 1, a.batch), kCarryLanes * kCarryGroups, 0, st>>>(a, nchunks);
   if (int rc = launch_status("chunk_carry_kernel")) return rc;
   if (through_phase2_only) return SSM_OK;
   if constexpr (sizeof(T) == 2) {
@@ -835,7 +851,7 @@ static int chunk_bwd_t(const ssm_chunk_bwd_args& g_in, cudaStream_t st) {
   }
   if (!local_vec) chunk_bwd_local_kernel<T, PT><<<dim3(gx, nchunks, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
   if (int rc = launch_status("chunk_bwd_local_kernel")) return rc;
-  chunk_bwd_carry_kernel<<<dim3(gx, 1, a.batch), kChunkThreads, 0, st>>>(g, nchunks);
+  chunk_bwd_carry_kernel<<<dim3((HP + kCarryLanes - 1) / kCarryLanes, 1, a.batch), kCarryLanes * kCarryGroups, 0, st>>>(g, nchunks);
   if (int rc = launch_status("chunk_bwd_carry_kernel")) return rc;
   if constexpr (sizeof(T) == 2 && std::is_same<T, PT>::value) {
     // 16-byte lanes: dense 16-bit B, C, z (see chunk_vec_ok), dense fp32 gradient buffers for them with 16-byte rows, and a

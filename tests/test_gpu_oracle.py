@@ -200,6 +200,8 @@ CHUNK_CASES = [
     # one piece in the backward but several in the forward; sixteen threads per head and a chunk that ends inside a load batch
     (2, 150, 5, 24, 48, "blhp", torch.float16, [150, 7]), (1, 77, 3, 8, 200, "blhp", torch.bfloat16, None),
     (2, 131, 2, 128, 33, "blhp", torch.bfloat16, [131, 65]),
+    # more than 64 pieces: the carry over the pieces runs several passes of its four groups
+    (1, 1100, 2, 8, 7, "hp", torch.float32, None),
 ]
 
 
