@@ -393,7 +393,8 @@ int ssm_fused_add_norm_bwd_noalloc(const ssm_norm_bwd_args* args, ssm_stream_t s
  * dt_mode: 0 = dt is (batch, len, heads) in io_dtype and goes through dt_bias / dt_softplus.  1 = dt is fp32 and holds
  * the step sizes as they are used (dt_bias and dt_softplus are ignored).  3 = as 1, and the step size enters the
  * decay exp(dt A) only: the inputs are added with unit weight, S_t = exp(dt_t A) S_{t-1} + x_t B_t^T.  Modes 1 and 3
- * are what the backward pass uses to run the adjoint recurrence through the same kernels.
+ * are what the backward pass uses to run the adjoint recurrence through the same kernels.  + 4 (to any mode): the caller
+ * promises that heads 2 i and 2 i + 1 have equal step sizes and decay; the decay mask is then formed once per pair.
  * row_dots: (batch, len, heads) fp32, zero-filled by the caller.  When given, z is not a gate: Y is written ungated and
  * row_dots[b, t, h] receives sum_p y[p] z[p], with y taken before the D x term and before rounding to io_dtype (the
  * backward pass forms dy . y and d(dt x) . x this way).

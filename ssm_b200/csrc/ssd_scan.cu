@@ -613,6 +613,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
   // A skip weight per head (not per channel) rides on the diagonal of the masked operand: (G o L + D I) X = Y_intra + D x.
   // The row sums for the backward pass want y without the skip term, so that mode keeps the explicit form.
   const bool fold_d = !XSKIP && a.D;
+  const bool pair_reuse = (a.dt_mode & 4) && !a.D && !a.row_scale;  // nothing per head may ride on the mask
   constexpr bool skip_explicit = XSKIP;
 
   // epilogue of head h from accumulator pair `buf`: y = Y_intra + exp2(c_i) Y_inter (+ D x where it is not folded), gated by
@@ -707,13 +708,16 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     // chunk's first step (row factor <= 1 for causal rows, column factor bounded by the decay inside the chunk).
     // Each lane forms one column factor per chunk, each thread one row factor per chunk: 2 ex2 per 32 elements
     // instead of 32.  Chunks whose internal decay exceeds 2^60 keep the exact per-element form.
+    // dt_mode & 4: heads 2 i and 2 i + 1 have the same step sizes and decay, so the masked operand the even head left in
+    // tensor memory serves the odd head as it is (its MMAs have completed and only read it)
+    const bool reuse = pair_reuse && (h & 1) && hi > 0;
     float arow[NCH];
     bool fast[NCH];
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       const int cc = wg + kScanWG * k;
       arow[k] = 0.f, fast[k] = false;
-      if (cc <= rc) {
+      if (cc <= rc && !reuse) {
         const float r = vc[cc * 32];
         fast[k] = r - vc[cc * 32 + 31] < 60.f;  // same for every lane
         arow[k] = ex2_approx(ct - r);
@@ -758,6 +762,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
     }
 
     // ---- decay mask: G (registers) x the factors formed above -> the A operand in tensor memory
+    if (!reuse) {
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       const int cc = wg + kScanWG * k;  // chunk of 32 steps: fully causal (cc < rc), diagonal (cc == rc) or empty (cc > rc) for this warp's rows
@@ -832,6 +837,7 @@ __device__ __forceinline__ void ssd_scan_body(const ssm_ssd_args& a, const ScanM
       tc::tmem_st16(dst, packed);
     }
     tc::tmem_wait_st();
+    }
     // this row of x (for D x in the epilogue one iteration later)
     uint4 xr[kXR];
 #pragma unroll
@@ -1115,7 +1121,7 @@ extern "C" int ssm_ssd_fwd(const ssm_ssd_args* a, ssm_stream_t stream) {
               "ssd_scan: the tensor-core path is built for headdim 64, d_state 128, chunk 256, bf16 / fp16");
   if (a->batch == 0 || a->len == 0) return SSM_OK;
   SSM_REQUIRE(a->phase >= 0 && a->phase <= 2, SSM_ERR_SHAPE, "ssd_scan: phase must be 0, 1 or 2");
-  SSM_REQUIRE(a->dt_mode >= 0 && a->dt_mode <= 3 && a->dt_mode != 2, SSM_ERR_SHAPE, "ssd_scan: dt_mode must be 0, 1 or 3");
+  SSM_REQUIRE(a->dt_mode >= 0 && a->dt_mode <= 7 && (a->dt_mode & 3) != 2, SSM_ERR_SHAPE, "ssd_scan: dt_mode must be 0, 1 or 3, optionally + 4");
   SSM_REQUIRE(a->bc_width == 0 || a->bc_width == kN || a->bc_width == 64, SSM_ERR_SHAPE, "ssd_scan: bc_width must be 0, 64 or nstate");
   SSM_REQUIRE(a->x_heads >= 0 && (a->x_heads == 0 || a->heads % a->x_heads == 0), SSM_ERR_SHAPE, "ssd_scan: x_heads must be 0 or divide heads");
   SSM_REQUIRE(a->X && a->dt && a->A && a->Bm && a->Cm && (a->Y || a->phase == 1), SSM_ERR_NULL, "ssd_scan: missing tensor");

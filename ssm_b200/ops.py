@@ -1294,10 +1294,10 @@ def _ssd_backward_dual(X, dt, A, B, C_, D, z, dt_bias, dt_softplus, init, chunk,
         return out
 
     A2 = A32.repeat_interleave(2)
-    yc = _ssd_dual_run(halves(Bp), delta.repeat_interleave(2, 2), A2, Xp, dy, state_t(init), chunk, 1, bc_width=npj, x_heads=xh2)[0]
+    yc = _ssd_dual_run(halves(Bp), delta.repeat_interleave(2, 2), A2, Xp, dy, state_t(init), chunk, 1 | 4, bc_width=npj, x_heads=xh2)[0]
     dC = group_sum(yc, None, False, C_)
     del yc
-    yb = _ssd_dual_run(halves(C_r), delta_r.repeat_interleave(2, 2), A2, dy_r, X_r, state_t(g_init), chunk, 3, bc_width=npj, x_heads=xh2)[0]
+    yb = _ssd_dual_run(halves(C_r), delta_r.repeat_interleave(2, 2), A2, dy_r, X_r, state_t(g_init), chunk, 3 | 4, bc_width=npj, x_heads=xh2)[0]
     dB = group_sum(yb, delta, True, B)
     del yb
     # (4) decay exponent: chunk-local running sums started from <adjoint state, state> at the chunk boundaries
