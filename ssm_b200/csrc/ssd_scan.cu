@@ -149,7 +149,8 @@ struct StateSmem {
   static constexpr int BLK_BYTES = kStep * 128;               // 8 KB: 64 steps x 64 elements
   static constexpr int A_BYTES = 2 * BLK_BYTES;               // 16 KB
   static constexpr int STAGE = A_BYTES + HPC * BLK_BYTES;
-  static constexpr int NSTAGE = HPC <= 2 ? 6 : (HPC == 3 ? 5 : 4);
+  // one head per CTA: four stages (100 KB), so that two CTAs share an SM when there are more heads than SMs
+  static constexpr int NSTAGE = HPC == 1 ? 4 : (HPC == 2 ? 6 : (HPC == 3 ? 5 : 4));
   static constexpr int VEC_BYTES = HPC * kQ * 4;              // c - log2(delta) of a chunk, per head
   // The copies run up to NSTAGE stages ahead of the MMAs, so a chunk's vectors may arrive while the chunk before last is still
   // being scaled: three buffers (NSTAGE <= 6 stages = one and a half chunks).
@@ -172,7 +173,7 @@ constexpr int kStateThreads = kStateComputeThreads + 64;
 constexpr int kStateCopyWarp = 8, kStateMmaWarp = 9;
 
 template <typename T, int HPC>
-__global__ void __launch_bounds__(kStateThreads, 1) ssd_state_kernel(const ssm_ssd_args a, const __grid_constant__ StateMaps maps, int nchunks) {
+__global__ void __launch_bounds__(kStateThreads, HPC == 1 ? 2 : 1) ssd_state_kernel(const ssm_ssd_args a, const __grid_constant__ StateMaps maps, int nchunks) {
   using M = StateSmem<HPC>;
   constexpr int kStep = M::kStep, NS = M::NSTAGE;
   constexpr int SPC = kQ / kStep;  // stages per chunk
@@ -1031,6 +1032,9 @@ static int ssd_launch(const ssm_ssd_args& a, cudaStream_t st) {
     int shpc = (int)(((int64_t)a.batch * a.heads + sm_count - 1) / sm_count);
     shpc = shpc < 1 ? 1 : (shpc > 4 ? 4 : shpc);
     while (hpg % shpc != 0) --shpc;
+    // between one and two (batch, head) pairs per SM: two heads per CTA would leave almost half of the SMs idle; one head per
+    // CTA, two CTAs per SM (they fit) keeps every SM busy and halves what the longest SM has to walk
+    if ((int64_t)a.batch * a.heads > sm_count && (int64_t)a.batch * a.heads <= 2 * (int64_t)sm_count) shpc = 1;
     int rc;
     switch (shpc) {
       case 1: rc = ssd_state_launch<T, 1>(a, nchunks, st); break;
