@@ -460,11 +460,19 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, OptTensor, OptTensor, OptTens
   const auto f32 = c.X.options().dtype(at::kFloat);
   auto zeros_like = [&](const OptTensor& t) { return t.has_value() ? OptTensor(at::zeros(t->sizes(), f32)) : OptTensor(); };
   Tensor dX = at::empty_like(c.X), ddt = at::zeros({c.nb, c.nl, c.nh}, f32);
-  OptTensor dA = zeros_like(c.A), dB = zeros_like(c.B), dC = zeros_like(c.C), dD = zeros_like(c.D), dz = zeros_like(c.z), dI = zeros_like(c.init);
+  // per-token B / C / z: the kernel writes their gradients in the tensor's own type (no zero-fill, no fp32 copy to convert)
+  int typed = 0;
+  auto own = [&](const OptTensor& t, Kind k, int bit) {
+    if (!t.has_value() || k != Kind::BLHP) return zeros_like(t);
+    typed |= bit;
+    return OptTensor(at::empty_like(*t));
+  };
+  OptTensor dA = zeros_like(c.A), dB = own(c.B, c.kB, 1), dC = own(c.C, c.kC, 2), dD = zeros_like(c.D), dz = own(c.z, c.kz, 4), dI = zeros_like(c.init);
   Tensor hist = at::empty({c.nb, std::max<int64_t>(c.nl, 1), c.nh, c.np}, f32);
   Tensor gy = like(grad_output, c.X);
   ssm_chunk_bwd_args g{};
   c.fill(g.fwd);
+  g.fwd.typed_grads = typed;
   Tensor scratch = at::empty({std::max<int64_t>(1, ssm_chunk_scan_bwd_scratch_floats((int)c.nb, (int)c.nl, (int)c.nh, (int)c.np, c.chunk))}, f32);
   g.dY = gy.data_ptr(), g.dX = dX.data_ptr(), g.ddt = ddt.data_ptr<float>(), g.history = hist.data_ptr<float>();
   g.scratch = scratch.data_ptr<float>();

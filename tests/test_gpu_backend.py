@@ -168,7 +168,8 @@ def test_ssd_chunk_scan_and_backward(case, dtype, shape):
     nb, nl, nh, npj, chunk = shape
     zshape = (nb, nl, nh, npj) if case["name"] == "ragged" else (nb, nl, nh)
     ins = dict(X=_mk(gen, nb, nl, nh, npj, dtype=dtype), dt=(torch.rand(nb, nl, nh, generator=gen) * 0.5).to(dtype), A=-torch.exp(_mk(gen, nh, npj, scale=0.5)),
-               B=_mk(gen, nh, npj, dtype=dtype), C=_mk(gen, nh, npj, dtype=dtype), D=_mk(gen, nh, dtype=dtype) if case["with_D"] else None,
+               B=_mk(gen, *(zshape if len(zshape) == 4 else (nh, npj)), dtype=dtype), C=_mk(gen, *(zshape if len(zshape) == 4 else (nh, npj)), dtype=dtype),
+               D=_mk(gen, nh, dtype=dtype) if case["with_D"] else None,
                z=_mk(gen, *zshape, dtype=dtype) if case["with_z"] else None,
                initial_states=_mk(gen, nb, nh, npj, dtype=dtype) if case["with_initial_state"] else None)
     lens = torch.tensor([nl, nl - 1], dtype=torch.int64) if case["with_seq_meta"] else None
