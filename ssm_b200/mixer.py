@@ -193,25 +193,30 @@ def mamba2_mixer_forward(ops: Any, w: dict, cfg: dict, u: Tensor, group=None, sh
     if sharded:
         from . import seqpar
 
-        halos = seqpar.exchange_conv_halos([px, pB, pC], w["conv_x"].shape[1], group)  # one message for the three inputs
+        # one message for the three inputs; the step-size projection is enqueued while it travels
+        posted = seqpar.post_conv_halos([px, pB, pC], w["conv_x"].shape[1], group)
+        dt = proj("in_dt")
+        halos = posted.wait()
 
     def conv(t, name, halo):
         if halo is None:
             return ops.dw_causal_conv(t, w[name], w[name + "_b"], "silu")
         return ops.dw_causal_conv(t, w[name], w[name + "_b"], "silu", halo=halo)
 
-    z = proj("in_z").view(nb, nl, nh, hp)
     x = conv(px, "conv_x", halos[0]).view(nb, nl, nh, hp)
     Bm = conv(pB, "conv_B", halos[1]).view(nb, nl, g, n)
     Cm = conv(pC, "conv_C", halos[2]).view(nb, nl, g, n)
-    dt = proj("in_dt")
     A = -torch.exp(w["A_log"])
     if sharded:
         from . import seqpar
 
-        y, _ = seqpar.ssd_scan_sharded(x, dt, A, Bm, Cm, cfg.get("chunk_size", 256), D=w["D"], z=z, dt_bias=w["dt_bias"], dt_softplus=True,
-                                       group=group)
+        # the gate's projection is the largest piece of work that does not depend on the other shards: it is enqueued after
+        # this shard's state phase, while the states are gathered and the ranks wait for the slowest of them
+        y, _ = seqpar.ssd_scan_sharded(x, dt, A, Bm, Cm, cfg.get("chunk_size", 256), D=w["D"], z=lambda: proj("in_z").view(nb, nl, nh, hp),
+                                       dt_bias=w["dt_bias"], dt_softplus=True, group=group)
     else:
+        z = proj("in_z").view(nb, nl, nh, hp)
+        dt = proj("in_dt")
         y = ops.ssd_scan(x, dt, A, Bm, Cm, cfg.get("chunk_size", 256), D=w["D"], z=z, dt_bias=w["dt_bias"], dt_softplus=True)
     y = ops.fused_layer_norm(y.reshape(nb, nl, nh * hp), w["norm_w"], None, is_rms=True, eps=eps)
     return torch.matmul(y.reshape(nb * nl, nh * hp), w["out_proj"].t()).view(nb, nl, dm)

@@ -75,8 +75,14 @@ def ssd_scan_sequence_parallel(
 
 def ssd_scan_sharded(X, dt, A, B, C, chunk_size=256, D=None, z=None, dt_bias=None, dt_softplus=False,
                      initial_states=None, group=None):
-    """Sequence-parallel :func:`ssm_b200.ops.ssd_scan` on this rank's shard (tensor-core path)."""
+    """Sequence-parallel :func:`ssm_b200.ops.ssd_scan` on this rank's shard (tensor-core path).
+
+    ``z`` may be a zero-argument callable that returns the gate: it is called once the exchange of the shard states has
+    been posted, so the work that produces the gate (a projection GEMM) runs while the ranks wait for one another."""
     from . import ops
+    z_fn = z if callable(z) else None
+    if z_fn is not None:
+        z = None
 
     if not ops.ssd_tensor_core_supported(X, B, chunk_size):
         raise ValueError("ssd_scan_sharded needs the tensor-core shape (headdim 64, d_state 128, chunk 256, bf16/fp16)")
@@ -84,6 +90,15 @@ def ssd_scan_sharded(X, dt, A, B, C, chunk_size=256, D=None, z=None, dt_bias=Non
         raise RuntimeError("ssd_scan_sharded is forward-only: call it under torch.no_grad() (its outputs carry no autograd history)")
     ops._ssd_check(X, dt, A, B, C, D, z, dt_bias, None)
     w = ops._SsdWorkspace(X, dt, A, B, C, D, z, dt_bias, dt_softplus, chunk_size)
+
+    def resolve_gate():
+        if z_fn is None:
+            return
+        gate = z_fn()
+        if gate is not None:
+            if tuple(gate.shape) != tuple(X.shape):
+                raise ValueError("z must have the shape of X.")
+            w.z = gate.to(w.io).contiguous()
 
     def state_phase():
         _, s_loc = w.run(1, None, False)
@@ -102,7 +117,9 @@ def ssd_scan_sharded(X, dt, A, B, C, chunk_size=256, D=None, z=None, dt_bias=Non
         w.run(1, None, False)
         mine = w.shard_summary()
         gathered = torch.empty(world * mine.numel(), dtype=torch.float32, device=mine.device)
-        dist.all_gather_into_tensor(gathered, mine, group=group)
+        work = dist.all_gather_into_tensor(gathered, mine, group=group, async_op=True)
+        resolve_gate()  # enqueued behind phase 1 on this stream, beside the gather on the communicator's
+        work.wait()
         if rank == 0 and initial_states is None:
             return finish_phase(None)
         nb, _, nh, npj, _, nn = w.shape
@@ -111,10 +128,11 @@ def ssd_scan_sharded(X, dt, A, B, C, chunk_size=256, D=None, z=None, dt_bias=Non
         L.check(L.load().ssm_ssd_fold_shards(gathered.data_ptr(), world, rank, nb, nh, None if init is None else init.data_ptr(), s_in.data_ptr(),
                                              torch.cuda.current_stream().cuda_stream))
         return finish_phase(s_in)
+    resolve_gate()
     return ssd_scan_sequence_parallel(state_phase, finish_phase, group, initial_states)
 
 
-def exchange_conv_halo(x_shard: Tensor, width: int, group=None, channels_first: bool = True) -> Optional[Tensor]:
+def exchange_conv_halo(x_shard: Tensor, width: int, group=None, channels_first: bool = True, _defer: Optional[list] = None) -> Optional[Tensor]:
     """Send this shard's last ``width-1`` inputs to the next rank; returns the halo ``(B, C, width-1)``
     fp32 received from the previous rank (``None`` on rank 0), for ``dw_causal_conv(..., halo=)``."""
     alone = not (dist.is_available() and dist.is_initialized())
@@ -129,25 +147,52 @@ def exchange_conv_halo(x_shard: Tensor, width: int, group=None, channels_first: 
         ops_.append(dist.P2POp(dist.isend, tail, dist.get_global_rank(group, rank + 1) if group else rank + 1, group))
     if rank > 0:
         ops_.append(dist.P2POp(dist.irecv, recv, dist.get_global_rank(group, rank - 1) if group else rank - 1, group))
-    for req in dist.batch_isend_irecv(ops_):
+    reqs = dist.batch_isend_irecv(ops_)
+    if _defer is not None:  # the caller waits later (post_conv_halos)
+        _defer.extend(reqs)
+        _defer.append(tail)  # the message stays alive until then
+        return recv if rank > 0 else None
+    for req in reqs:
         req.wait()
     return recv if rank > 0 else None
+
+
+class PostedHalos:
+    """The conv halos of a shard on their way (see :func:`post_conv_halos`); ``wait()`` returns them."""
+
+    def __init__(self, widths, halo, pending):
+        self._widths, self._halo, self._pending = widths, halo, pending
+
+    def wait(self):
+        for req in self._pending:
+            if hasattr(req, "wait"):
+                req.wait()
+        self._pending = []
+        if self._halo is None:
+            return [None for _ in self._widths]
+        out, c0 = [], 0
+        for c in self._widths:
+            out.append(self._halo[:, c0:c0 + c, :].contiguous())
+            c0 += c
+        return out
+
+
+def post_conv_halos(parts, width: int, group=None) -> PostedHalos:
+    """Posts the exchange of :func:`exchange_conv_halos` and returns without waiting for it: what the caller enqueues
+    before ``wait()`` (projections that do not need the halo) runs while the message travels."""
+    alone = not (dist.is_available() and dist.is_initialized())
+    world = 1 if alone else dist.get_world_size(group)
+    widths = [p.shape[-1] for p in parts]
+    if width <= 1 or world == 1:
+        return PostedHalos(widths, None, [])
+    joined = torch.cat([p[:, -(width - 1):, :] for p in parts], dim=-1)  # (B, K-1, sum C_i)
+    pending: list = []
+    halo = exchange_conv_halo(joined, width, group, channels_first=False, _defer=pending)
+    return PostedHalos(widths, halo, pending)
 
 
 def exchange_conv_halos(parts, width: int, group=None):
     """One exchange for several channels-last conv inputs ``(B, L, C_i)`` of the same shard: their last
     ``width-1`` tokens travel to the next rank as one message.  Returns one halo ``(B, C_i, width-1)`` per
     part (fp32), or ``None`` for each on rank 0 / without a process group."""
-    alone = not (dist.is_available() and dist.is_initialized())
-    world = 1 if alone else dist.get_world_size(group)
-    if width <= 1 or world == 1:
-        return [None for _ in parts]
-    joined = torch.cat([p[:, -(width - 1):, :] for p in parts], dim=-1)  # (B, K-1, sum C_i)
-    halo = exchange_conv_halo(joined, width, group, channels_first=False)
-    if halo is None:
-        return [None for _ in parts]
-    out, c0 = [], 0
-    for p in parts:
-        out.append(halo[:, c0:c0 + p.shape[-1], :].contiguous())
-        c0 += p.shape[-1]
-    return out
+    return post_conv_halos(parts, width, group).wait()
