@@ -66,6 +66,19 @@ def _worker(rank, world, port, out):
         xs_ext = xs if halo is None else torch.cat([halo, xs], dim=-1)
         got = orc.dw_causal_conv(xs_ext, w, None, "silu")[:, :, -xs.shape[-1]:]
         torch.testing.assert_close(got, full[:, :, rank * (24 // world):(rank + 1) * (24 // world)], rtol=1e-5, atol=1e-6)
+        # several channels-last inputs in one message, posted first and awaited after other work was enqueued
+        parts = [xs.transpose(1, 2).contiguous(), (2.0 * xs[:, :2]).transpose(1, 2).contiguous()]  # (B, L, 5) and (B, L, 2)
+        posted = seqpar.post_conv_halos(parts, 4)
+        busy = (parts[0] @ torch.ones(5, 3)).sum()  # stands for the projection that runs while the message travels
+        halos = posted.wait()
+        assert torch.isfinite(busy)
+        if rank == 0:
+            assert halos == [None, None]
+        else:
+            torch.testing.assert_close(halos[0], halo)
+            torch.testing.assert_close(halos[1], 2.0 * halo[:, :2])
+        assert [None if h is None else tuple(h.shape) for h in seqpar.exchange_conv_halos(parts, 4)] == \
+            [None if h is None else tuple(h.shape) for h in halos]
         out.put((rank, "ok"))
     except Exception as exc:  # noqa: BLE001
         out.put((rank, repr(exc)))
